@@ -1,0 +1,106 @@
+// C launch API of the sm_100a kernel library.
+//
+// Every kernel is reachable through a plain C function taking raw device pointers and a stream, so the
+// library can be driven from the PyTorch bindings, from ctypes, or from another C++ runtime. All
+// functions return 0 on success or a negative b2::StatusCode for rejected arguments; device-side
+// problems are reported through the `b2::Status*` word passed in (may be null).
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+#include "b2/status.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- elementwise / normalisation ---------------------------------------------------------------
+// out = rmsnorm(x (+ residual)) * weight. If `residual` is non-null it is updated in place to x + residual.
+// If `q_out`/`q_scale` are non-null the normalised row is also emitted as e4m3 with one f32 scale per
+// 128 columns (dynamic activation quantisation for the fp8 GEMM).
+int b2_rmsnorm_bf16(const void* x, void* residual, const void* weight, void* out, void* q_out, float* q_scale,
+                    int rows, int hidden, float eps, cudaStream_t stream);
+// Per-row 1x128 e4m3 quantisation of a bf16 matrix: q[r, c] = x[r, c] / s[r, c/128], s = amax/448.
+int b2_quant_e4m3_1x128(const void* x, void* q_out, float* scale_out, int rows, int cols, cudaStream_t stream);
+// Rotary embedding on q and k (in place) + scatter of k, v into the paged cache.
+// q: [T, n_q, D] with row stride q_stride (elements); k, v likewise. cos_sin: f32 [max_pos, rot_dim]
+// (cos in the first half of a row, sin in the second). slot < 0 skips the cache write.
+// cache layout: [num_pages, n_kv, page_size, D].
+int b2_rope_kvwrite_bf16(void* q, void* k, const void* v, const float* cos_sin, const int32_t* positions,
+                         const int64_t* slots, void* k_cache, void* v_cache, int tokens, int n_q, int n_kv,
+                         int head_dim, int rot_dim, int interleaved, int64_t q_stride, int64_t k_stride,
+                         int64_t v_stride, int page_size, int64_t num_slots, int max_pos, b2::Status* status,
+                         cudaStream_t stream);
+// out[t, j] = silu(gate_up[t, j]) * gate_up[t, F + j]
+int b2_swiglu_bf16(const void* gate_up, void* out, int rows, int ffn, cudaStream_t stream);
+// out[t, :] = table[ids[t] - vocab_start, :] for ids inside [vocab_start, vocab_start + vocab_rows), else 0.
+int b2_embedding_bf16(const int64_t* ids, const void* table, void* out, int tokens, int hidden, int64_t vocab_start,
+                      int64_t vocab_rows, cudaStream_t stream);
+// out[i, :] = src[index[i], :] (row gather, 16-byte vectorised; used for last-token selection).
+int b2_gather_rows_bf16(const void* src, const int64_t* index, void* out, int rows_out, int cols, int64_t rows_src,
+                        b2::Status* status, cudaStream_t stream);
+// Copy whole KV pages inside a cache tensor: dst_page[i] <- src_page[i] (preemption swap / prefix share).
+int b2_copy_pages(void* cache, const int64_t* src_pages, const int64_t* dst_pages, int n, int64_t page_bytes,
+                  int64_t num_pages, b2::Status* status, cudaStream_t stream);
+
+// ---- sampling ----------------------------------------------------------------------------------
+// Greedy: ids[r] = argmax_j logits[r, j] (lowest index on ties); also writes the max value.
+int b2_argmax(const void* logits, int is_bf16, int64_t* ids, float* max_out, int rows, int vocab, int64_t row_stride,
+              cudaStream_t stream);
+// Temperature / top-k / top-p sampling. Per-row parameters; top_k <= 0 disables, top_p >= 1 disables,
+// temperature == 0 means greedy. u = Philox4x32-10(seed, row, step) unless `uniforms` is given.
+int b2_sample(const void* logits, int is_bf16, int64_t* ids, const float* temperature, const int32_t* top_k,
+              const float* top_p, const float* uniforms, uint64_t seed, uint64_t step, int rows, int vocab,
+              int64_t row_stride, cudaStream_t stream);
+
+// ---- attention ---------------------------------------------------------------------------------
+// Causal GQA attention over a paged KV cache for a ragged batch of query chunks.
+// q/out: [T, n_q, D]; cache: [num_pages, n_kv, page_size, D]; cu_q: [B+1] query offsets; ctx_lens: [B]
+// total context (cached prefix + this chunk); block_tables: [B, max_blocks]. D == 128 or 64.
+int b2_attn_prefill_bf16(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* cu_q,
+                         const int32_t* ctx_lens, const int32_t* block_tables, int batch, int max_blocks, int n_q,
+                         int n_kv, int head_dim, int page_size, int max_q_len, float scale, int64_t q_stride,
+                         int64_t out_stride, int64_t num_pages, b2::Status* status, cudaStream_t stream);
+// One query token per sequence, split over the KV length. workspace: f32, size from b2_attn_decode_workspace.
+int b2_attn_decode_bf16(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* ctx_lens,
+                        const int32_t* block_tables, float* workspace, int batch, int max_blocks, int n_q, int n_kv,
+                        int head_dim, int page_size, int num_splits, float scale, int64_t q_stride,
+                        int64_t out_stride, int64_t num_pages, b2::Status* status, cudaStream_t stream);
+int64_t b2_attn_decode_workspace(int batch, int n_q, int head_dim, int num_splits);
+// MLA decode with absorbed weights: q_lat [B, H, 512], q_rope [B, H, 64]; cache [num_pages, page, 576]
+// (512 latent + 64 rope); out_lat [B, H, 512].
+int b2_mla_decode_bf16(const void* q_lat, const void* q_rope, const void* kv_cache, void* out_lat,
+                       const int32_t* ctx_lens, const int32_t* block_tables, float* workspace, int batch,
+                       int max_blocks, int n_heads, int page_size, int num_splits, float scale, int64_t num_pages,
+                       b2::Status* status, cudaStream_t stream);
+int64_t b2_mla_decode_workspace(int batch, int n_heads, int num_splits);
+
+// ---- GEMM (tcgen05 / TMEM / TMA) ---------------------------------------------------------------
+// Epilogue selector for the tcgen05 GEMMs.
+enum B2Epilogue { B2_EPI_NONE = 0, B2_EPI_ADD_RESIDUAL = 1, B2_EPI_SWIGLU = 2 };
+// Y[M, N] = X[M, K] * W[N, K]^T (+ residual), bf16 in, f32 accumulate, bf16 out.
+// ldx/ldw/ldy are row strides in elements. `workspace`/`counters` are split-K scratch (may be null when
+// the chosen configuration does not split); sizes from b2_gemm_workspace_bytes.
+int b2_gemm_bf16(const void* x, const void* w, void* y, const void* residual, int M, int N, int K, int64_t ldx,
+                 int64_t ldw, int64_t ldy, int epilogue, int config, void* workspace, int64_t workspace_bytes,
+                 b2::Status* status, cudaStream_t stream);
+int64_t b2_gemm_workspace_bytes(int M, int N, int K);
+// fp8 block-scaled: X e4m3 [M, K] with f32 scales [M, K/128]; W e4m3 [N, K] with f32 scales [N/128, K/128].
+int b2_gemm_fp8_block(const void* xq, const float* xs, const void* wq, const float* ws, void* y, int M, int N, int K,
+                      int64_t ldy, int config, b2::Status* status, cudaStream_t stream);
+// GGUF: W stored as Q4_K (type 12) or Q6_K (type 14) super-blocks, row-major [N, K/256 blocks].
+int b2_gemm_gguf(const void* x, const void* wq, int ggml_type, void* y, int M, int N, int K, b2::Status* status,
+                 cudaStream_t stream);
+int b2_dequant_gguf(const void* wq, int ggml_type, void* out_bf16, int64_t n_elems, cudaStream_t stream);
+
+// ---- device capability probe -------------------------------------------------------------------
+struct B2DeviceCaps {
+  int cc_major, cc_minor, sm_count, smem_per_block_optin, l2_bytes, max_cluster;
+  int64_t total_mem;
+  int can_map_peer, multicast_supported, clock_khz, mem_clock_khz;
+  char name[128];
+};
+int b2_device_caps(int device, struct B2DeviceCaps* out);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,267 @@
+// Warp-specialised persistent tcgen05 GEMM core for sm_100a.
+//
+//   D[p, q] = sum_k P[p, k] * Q[q, k]      P: [rows_p, K] K-major, tile 128 x 64 (UMMA A operand)
+//                                           Q: [rows_q, K] K-major, tile BN  x 64 (UMMA B operand)
+//
+// Roles inside one CTA of 192 threads:
+//   warp 0      one elected lane issues TMA loads into a STAGES-deep shared-memory ring (128-byte swizzle)
+//   warp 1      allocates TMEM; one elected lane issues tcgen05.mma (M=128, N=BN, K=16 per instruction) into one
+//               of two TMEM accumulators and commits to mbarriers
+//   warps 2-5   epilogue: tcgen05.ld the finished accumulator (each warp owns 32 TMEM lanes = 32 rows of D),
+//               hand 32-column chunks to an Epilogue functor, release the accumulator
+// The mainloop of work unit i+1 overlaps the epilogue of work unit i through the double-buffered accumulator.
+//
+// Every wait is bounded (ptx::mbar_wait). On expiry the role records a TIMEOUT in the status word, stops
+// issuing work, waits (bounded) for its own copies / MMAs in flight, and the CTA still releases TMEM and exits.
+//
+// The core is parameterised by three policies so the fused tensor-parallel kernels reuse it unchanged:
+//   Sched  maps a linear work index to a tile (which 128-row P block, which BN-row Q block, which K range)
+//   Gate   is called by the producer before the first load of a work unit (e.g. wait for a peer's shard)
+//   Epi    consumes accumulator chunks
+// There is no counterpart in the reference: its newest tensor-core-capable gate is sm_90a
+// (stdlib/src/sys/info.mojo:423-434) and it contains no MMA code at all.
+#pragma once
+#include <cstdint>
+#include <cuda.h>
+#include "b2/ptx.cuh"
+#include "b2/status.h"
+
+namespace b2 {
+namespace gemm {
+
+constexpr int kBlockP = 128;     // UMMA M
+constexpr int kBlockK = 64;      // elements of a 16-bit type per 128-byte swizzle row
+constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;
+
+struct WorkUnit {
+  int pb;       // P block index (128 rows)
+  int qb;       // Q block index (BN rows)
+  int kb0;      // first 64-wide k-block
+  int kb1;      // one past the last k-block
+  int split;    // split-K index
+  int tile;     // linear output tile id (pb, qb) for split-K bookkeeping
+  int p_coord;  // TMA row coordinate of the P tile (normally pb * 128)
+  int q_coord;  // TMA row coordinate of the Q tile (normally qb * BN)
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int kPBytes = kBlockP * kBlockK * 2;
+  static constexpr int kQBytes = BN * kBlockK * 2;
+  static constexpr int kStageBytes = kPBytes + kQBytes;
+  static constexpr int kRingBytes = STAGES * kStageBytes;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], drain, tmem base holder, epilogue flag
+  static constexpr int kBarrierBytes = (2 * STAGES + 5) * 8 + 16;
+  static constexpr int kTotalBytes = kRingBytes + kBarrierBytes + 1024;  // + alignment slack
+  static_assert(kQBytes % 1024 == 0 || BN == 8, "Q stage must keep 1024-byte alignment of the next stage");
+};
+
+template <int BN>
+constexpr int tmem_cols_for() {
+  int need = 2 * BN;
+  int c = 32;
+  while (c < need) c *= 2;
+  return c;
+}
+
+// elem_bytes: 2 for bf16/f16 (UMMA K = 16), 1 for fp8 (UMMA K = 32); a k-block is always 128 bytes wide.
+template <int BN, int STAGES, int ELEM_BYTES, class Sched, class Gate, class Epi>
+__device__ __forceinline__ void run(const CUtensorMap* tmap_p, const CUtensorMap* tmap_q, uint32_t idesc,
+                                    uint64_t policy_p, uint64_t policy_q, Sched sched, Gate gate, Epi epi,
+                                    Status* status) {
+  using L = SmemLayout<BN, STAGES>;
+  constexpr int kTmemCols = tmem_cols_for<BN>();
+  constexpr int kMmaPerKb = 4;                       // 128 bytes / 32 bytes per instruction
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + L::kRingBytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 4);
+  const uint32_t tmem_holder = bar_base + 8u * (2 * STAGES + 5);
+  uint32_t* tmem_holder_ptr =
+      reinterpret_cast<uint32_t*>(smem_raw + (tmem_holder - ptx::smem_u32(smem_raw)));
+  uint32_t* epi_flag_ptr = tmem_holder_ptr + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    ptx::prefetch_tensormap(tmap_p);
+    ptx::prefetch_tensormap(tmap_q);
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tmem_full_bar(a), 1);
+      ptx::mbar_init(tmem_empty_bar(a), 4);  // one arrival per epilogue warp
+    }
+    ptx::mbar_init(drain_bar, 1);
+    ptx::fence_mbar_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_holder, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder_ptr;
+
+  const int total = sched.total();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (ptx::elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      long issued = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total; w += gridDim.x) {
+        const WorkUnit u = sched.get(w);
+        if (!gate(u, status)) { ok = false; break; }
+        for (int kb = u.kb0; kb < u.kb1; ++kb) {
+          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u)) {
+            status_record(status, kTimeout, kSiteGemmEmpty, w, kb);
+            ok = false;
+            break;
+          }
+          const uint32_t sp = smem_base + stage * L::kStageBytes;
+          ptx::mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
+          const int kx = kb * (128 / ELEM_BYTES);
+          ptx::tma_load_2d(sp, tmap_p, full_bar(stage), kx, u.p_coord, policy_p);
+          ptx::tma_load_2d(sp + L::kPBytes, tmap_q, full_bar(stage), kx, u.q_coord, policy_q);
+          ++issued;
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // Unwind: let every copy this thread started land before the CTA gives up its shared memory.
+        long pending = issued < STAGES ? issued : STAGES;
+        int s = stage;
+        uint32_t ph = phase;
+        for (long i = 0; i < pending; ++i) {
+          if (--s < 0) { s = STAGES - 1; ph ^= 1u; }
+          if (!ptx::mbar_wait(full_bar(s), ph, 200000000ull)) break;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (ptx::elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total; w += gridDim.x) {
+        const WorkUnit u = sched.get(w);
+        if (!ptx::mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u)) {
+          status_record(status, kTimeout, kSiteGemmTmemEmpty, w, acc);
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = u.kb0; kb < u.kb1; ++kb) {
+          if (!ptx::mbar_wait(full_bar(stage), phase)) {
+            status_record(status, kTimeout, kSiteGemmFull, w, kb);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sp = smem_base + stage * L::kStageBytes;
+          const uint64_t da = ptx::make_smem_desc_sw128(sp);
+          const uint64_t db = ptx::make_smem_desc_sw128(sp + L::kPBytes);
+#pragma unroll
+          for (int k = 0; k < kMmaPerKb; ++k) {
+            // +32 bytes along K inside the swizzle atom = +2 in the (address >> 4) field
+            const uint32_t accumulate = (kb > u.kb0 || k > 0) ? 1u : 0u;
+            if (ELEM_BYTES == 2)
+              ptx::tc_mma_f16(d_tmem, da + 2u * k, db + 2u * k, idesc, accumulate);
+            else
+              ptx::tc_mma_f8(d_tmem, da + 2u * k, db + 2u * k, idesc, accumulate);
+          }
+          ptx::tc_commit(empty_bar(stage));  // smem slot is free once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        ptx::tc_commit(tmem_full_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+      if (!ok) {
+        // Unwind: wait for MMAs in flight before TMEM is released.
+        ptx::tc_commit(drain_bar);
+        ptx::mbar_wait(drain_bar, 0, 200000000ull);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may access
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; ok && w < total; w += gridDim.x) {
+      const WorkUnit u = sched.get(w);
+      if (!ptx::mbar_wait(tmem_full_bar(acc), acc_phase)) {
+        if (lane == 0) status_record(status, kTimeout, kSiteGemmTmemFull, w, acc);
+        ok = false;
+        break;
+      }
+      ptx::tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      epi(u, taddr, quarter, lane, epi_flag_ptr, status);
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(tmem_empty_bar(acc));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// Default scheduler: tiles rastered in groups of 8 P-blocks so that one wave of CTAs shares Q tiles in L2;
+// the `splits` K-slices of a tile are adjacent work units.
+struct TileSched {
+  int p_blocks, q_blocks, splits, num_kb, kb_per_split, bn;
+  __device__ __forceinline__ int total() const { return p_blocks * q_blocks * splits; }
+  __device__ __forceinline__ WorkUnit get(int w) const {
+    WorkUnit u;
+    u.split = w % splits;
+    const int t = w / splits;
+    const int group_size = 8 * q_blocks;
+    const int group = t / group_size;
+    const int first_p = group * 8;
+    const int gp = min(p_blocks - first_p, 8);
+    const int r = t - group * group_size;
+    u.pb = first_p + r % gp;
+    u.qb = r / gp;
+    u.tile = u.pb * q_blocks + u.qb;
+    u.kb0 = u.split * kb_per_split;
+    u.kb1 = min(num_kb, u.kb0 + kb_per_split);
+    u.p_coord = u.pb * kBlockP;
+    u.q_coord = u.qb * bn;
+    return u;
+  }
+};
+
+struct NoGate {
+  __device__ __forceinline__ bool operator()(const WorkUnit&, Status*) const { return true; }
+};
+
+}  // namespace gemm
+}  // namespace b2

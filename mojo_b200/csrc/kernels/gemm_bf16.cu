@@ -1,0 +1,341 @@
+// bf16 GEMM on tcgen05/TMEM: Y[M, N] = X[M, K] * W[N, K]^T, f32 accumulate, bf16 out.
+//
+// Two operand assignments of the same core (b2/gemm_tc.cuh):
+//   normal  P = X, Q = W   D[m, n]: each epilogue thread owns one output row and writes 64-byte row segments.
+//                          Used for prefill-sized M.
+//   swapped P = W, Q = X   D[n, m]: the 128-row UMMA M dimension is filled by weight rows, the token count
+//                          becomes the UMMA N (16..256). Every byte staged in shared memory is weight data, so
+//                          decode-sized M streams the weights once at HBM rate; K can be split across CTAs
+//                          (f32 partials in a workspace, last CTA of a tile reduces) to fill all 148 SMs.
+// Epilogues: plain store, + residual, SwiGLU on 16-row-interleaved gate/up weights.
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include "b2/api.h"
+#include "b2/gemm_tc.cuh"
+#include "b2/ptx.cuh"
+#include "b2/tma.h"
+
+namespace b2 {
+namespace {
+
+using gemm::WorkUnit;
+
+struct EpiParams {
+  __nv_bfloat16* y;
+  const __nv_bfloat16* residual;
+  int64_t ldy;
+  int64_t ldr;
+  int M, N;          // logical output shape before any SwiGLU halving
+  int splits;
+  float* workspace;  // [tiles][splits][BN][128] f32 partials
+  uint32_t* counters;  // [tiles], zero on entry and on exit
+  int mode;          // B2Epilogue
+};
+
+// Shared by both layouts: either pull a 32-column chunk out of TMEM or, for the reducing CTA of a split-K
+// tile, sum the f32 partials of all splits.
+template <int BN, int CH>
+struct AccSource {
+  bool from_ws;
+  uint32_t taddr;
+  const float* ws_tile;  // partials of this tile: [splits][BN][128]
+  int splits;
+  int p_local;
+  __device__ __forceinline__ void load(int c, float (&v)[CH]) const {
+    if (!from_ws) {
+      uint32_t r[CH];
+      if constexpr (CH == 32) ptx::tmem_ld_32x32(taddr + c * CH, r);
+      else ptx::tmem_ld_32x16(taddr + c * CH, r);
+      ptx::tc_wait_ld();
+#pragma unroll
+      for (int j = 0; j < CH; ++j) v[j] = __uint_as_float(r[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < CH; ++j) v[j] = 0.0f;
+      for (int s = 0; s < splits; ++s) {
+        const float* base = ws_tile + (static_cast<size_t>(s) * BN + c * CH) * 128 + p_local;
+#pragma unroll
+        for (int j = 0; j < CH; ++j) v[j] += __ldcg(base + j * 128);
+      }
+    }
+  }
+};
+
+template <int BN, bool SWAP>
+struct Epilogue {
+  static constexpr int CH = BN >= 32 ? 32 : 16;
+  EpiParams p;
+
+  __device__ __forceinline__ void store_chunk(const WorkUnit& u, int c, int p_local, int lane, float (&v)[CH]) const {
+    if constexpr (!SWAP) {
+      // thread = output row m; chunk = CH consecutive output columns
+      const int m = u.pb * 128 + p_local;
+      const int n0 = u.qb * BN + c * CH;
+      if (m >= p.M) return;
+      if (p.mode == B2_EPI_SWIGLU) {
+        // columns [0, CH/2) of the chunk are gate, [CH/2, CH) are up for the same CH/2 ffn indices
+        constexpr int HALF = CH / 2;
+        if (n0 >= p.N) return;
+        float o[HALF];
+#pragma unroll
+        for (int j = 0; j < HALF; ++j) o[j] = ptx::silu(v[j]) * v[HALF + j];
+        __nv_bfloat16* dst = p.y + static_cast<int64_t>(m) * p.ldy + n0 / 2;
+#pragma unroll
+        for (int g = 0; g < HALF / 8; ++g) {
+          uint4 pk;
+          pk.x = ptx::pack_bf16x2(o[g * 8 + 0], o[g * 8 + 1]);
+          pk.y = ptx::pack_bf16x2(o[g * 8 + 2], o[g * 8 + 3]);
+          pk.z = ptx::pack_bf16x2(o[g * 8 + 4], o[g * 8 + 5]);
+          pk.w = ptx::pack_bf16x2(o[g * 8 + 6], o[g * 8 + 7]);
+          ptx::st_v4(dst + g * 8, pk);
+        }
+        return;
+      }
+      __nv_bfloat16* dst = p.y + static_cast<int64_t>(m) * p.ldy + n0;
+      const __nv_bfloat16* res = p.mode == B2_EPI_ADD_RESIDUAL ? p.residual + static_cast<int64_t>(m) * p.ldr + n0 : nullptr;
+#pragma unroll
+      for (int g = 0; g < CH / 8; ++g) {
+        if (n0 + g * 8 >= p.N) break;
+        float a[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] = v[g * 8 + j];
+        if (res != nullptr) {
+          const uint4 rv = ptx::ld_v4(res + g * 8);
+          a[0] += ptx::bf16_lo(rv.x); a[1] += ptx::bf16_hi(rv.x);
+          a[2] += ptx::bf16_lo(rv.y); a[3] += ptx::bf16_hi(rv.y);
+          a[4] += ptx::bf16_lo(rv.z); a[5] += ptx::bf16_hi(rv.z);
+          a[6] += ptx::bf16_lo(rv.w); a[7] += ptx::bf16_hi(rv.w);
+        }
+        uint4 pk;
+        pk.x = ptx::pack_bf16x2(a[0], a[1]);
+        pk.y = ptx::pack_bf16x2(a[2], a[3]);
+        pk.z = ptx::pack_bf16x2(a[4], a[5]);
+        pk.w = ptx::pack_bf16x2(a[6], a[7]);
+        ptx::st_v4(dst + g * 8, pk);
+      }
+    } else {
+      // thread = output column n; chunk = CH consecutive output rows (tokens)
+      const int n = u.pb * 128 + p_local;
+      const int m0 = u.qb * BN + c * CH;
+      if (p.mode == B2_EPI_SWIGLU) {
+        // lanes 0-15 hold gate rows, lanes 16-31 the matching up rows (16-row interleave of W)
+        const int out_col = (u.pb * 128 + (p_local & ~31)) / 2 + (lane & 15);
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+          const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+          if (lane < 16 && n < p.N && m0 + j < p.M)
+            p.y[static_cast<int64_t>(m0 + j) * p.ldy + out_col] = __float2bfloat16(ptx::silu(v[j]) * other);
+        }
+        return;
+      }
+      if (n >= p.N) return;
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        if (m0 + j >= p.M) break;
+        float a = v[j];
+        if (p.mode == B2_EPI_ADD_RESIDUAL) a += __bfloat162float(p.residual[static_cast<int64_t>(m0 + j) * p.ldr + n]);
+        p.y[static_cast<int64_t>(m0 + j) * p.ldy + n] = __float2bfloat16(a);
+      }
+    }
+  }
+
+  __device__ __forceinline__ void operator()(const WorkUnit& u, uint32_t taddr, int quarter, int lane,
+                                             uint32_t* flag, Status* status) const {
+    const int p_local = quarter * 32 + lane;
+    AccSource<BN, CH> src{false, taddr, nullptr, p.splits, p_local};
+    if (p.splits > 1) {
+      // 1. publish this CTA's partial
+      float* ws_tile = p.workspace + static_cast<size_t>(u.tile) * p.splits * BN * 128;
+      float* mine = ws_tile + static_cast<size_t>(u.split) * BN * 128 + p_local;
+#pragma unroll 1
+      for (int c = 0; c < BN / CH; ++c) {
+        float v[CH];
+        src.load(c, v);
+#pragma unroll
+        for (int j = 0; j < CH; ++j) __stcg(mine + (c * CH + j) * 128, v[j]);
+      }
+      __threadfence();
+      ptx::named_barrier_sync(1, gemm::kEpiThreads);
+      if (threadIdx.x == 64) {  // first epilogue thread
+        const uint32_t old = atomicAdd(p.counters + u.tile, 1u);
+        const bool last = old == static_cast<uint32_t>(p.splits - 1);
+        if (last) p.counters[u.tile] = 0;  // leave the counter ready for the next launch
+        __threadfence();
+        *flag = last ? 1u : 0u;
+      }
+      ptx::named_barrier_sync(1, gemm::kEpiThreads);
+      const bool last = *flag != 0;
+      ptx::named_barrier_sync(1, gemm::kEpiThreads);  // flag may be rewritten by the next work unit
+      if (!last) return;
+      src.from_ws = true;
+      src.ws_tile = ws_tile;
+    }
+#pragma unroll 1
+    for (int c = 0; c < BN / CH; ++c) {
+      float v[CH];
+      src.load(c, v);
+      store_chunk(u, c, p_local, lane, v);
+    }
+  }
+};
+
+template <int BN, int STAGES, bool SWAP>
+__global__ void __launch_bounds__(gemm::kThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
+                 gemm::TileSched sched, EpiParams ep, uint64_t policy_p, uint64_t policy_q, Status* status) {
+  constexpr uint32_t idesc = ptx::make_idesc(1, 1, 128, BN);
+  Epilogue<BN, SWAP> epi{ep};
+  gemm::run<BN, STAGES, 2>(&tmap_p, &tmap_q, idesc, policy_p, policy_q, sched, gemm::NoGate{}, epi, status);
+}
+
+constexpr int stages_for(int bn) {
+  const int stage = 128 * 64 * 2 + bn * 64 * 2;
+  int s = (200 * 1024) / stage;
+  return s > 10 ? 10 : s;
+}
+
+struct Config {
+  bool swap;
+  int bn;
+  int splits;
+};
+
+Config choose_config(int M, int N, int K, int epilogue) {
+  const int num_kb = (K + 63) / 64;
+  Config c{};
+  if (M <= 256) {
+    c.swap = true;
+    c.bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    const int tiles = ((N + 127) / 128) * ((M + c.bn - 1) / c.bn);
+    int s = 1;
+    // split K until there are about two waves of work units, keeping >= 8 k-blocks per split
+    while (tiles * s < 148 && num_kb / (s * 2) >= 8) s *= 2;
+    c.splits = s;
+  } else {
+    c.swap = false;
+    const int tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
+    c.bn = (N >= 256 && tiles256 >= 148) ? 256 : 128;
+    if (N < 128) c.bn = 64;
+    c.splits = 1;
+  }
+  (void)epilogue;
+  return c;
+}
+
+template <int BN, bool SWAP>
+int launch(const void* x, const void* w, int M, int N, int K, int64_t ldx, int64_t ldw, int splits, EpiParams ep,
+           Status* status, cudaStream_t stream) {
+  constexpr int STAGES = stages_for(BN);
+  using L = gemm::SmemLayout<BN, STAGES>;
+  const void* p_ptr = SWAP ? w : x;
+  const void* q_ptr = SWAP ? x : w;
+  const int rows_p = SWAP ? N : M, rows_q = SWAP ? M : N;
+  const int64_t ldp = SWAP ? ldw : ldx, ldq = SWAP ? ldx : ldw;
+  CUtensorMap tp, tq;
+  if (!make_tmap_2d(&tp, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p_ptr, rows_p, K, ldp * 2, 128, 64,
+                    CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !make_tmap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q_ptr, rows_q, K, ldq * 2, BN, 64,
+                    CU_TENSOR_MAP_SWIZZLE_128B))
+    return -kBadArgument;
+  gemm::TileSched sched;
+  sched.p_blocks = (rows_p + 127) / 128;
+  sched.q_blocks = (rows_q + BN - 1) / BN;
+  sched.splits = splits;
+  sched.num_kb = (K + 63) / 64;
+  sched.kb_per_split = (sched.num_kb + splits - 1) / splits;
+  sched.bn = BN;
+  ep.splits = splits;
+  auto kern = gemm_bf16_kernel<BN, STAGES, SWAP>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes) != cudaSuccess)
+      return -kBadArgument;
+    attr_set = true;
+  }
+  const int total = sched.p_blocks * sched.q_blocks * splits;
+  const int grid = total < kNumSMs ? total : kNumSMs;
+  // Weights are read once per step: stream them; activations are re-read by every weight tile: keep them.
+  const uint64_t pol_w = ptx::kEvictFirst, pol_x = ptx::kEvictLast;
+  const uint64_t pol_p = SWAP ? pol_w : (M <= 1024 ? pol_x : ptx::kEvictNormal);
+  const uint64_t pol_q = SWAP ? pol_x : (M <= 1024 ? pol_w : ptx::kEvictNormal);
+  kern<<<grid, gemm::kThreads, L::kTotalBytes, stream>>>(tp, tq, sched, ep, pol_p, pol_q, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+}
+
+}  // namespace
+}  // namespace b2
+
+using namespace b2;
+
+extern "C" int64_t b2_gemm_workspace_bytes(int M, int N, int K) {
+  // Upper bound over every configuration choose_config can return: counters + partials.
+  const Config c = choose_config(M, N, K, 0);
+  const int64_t counters = 65536 * 4;
+  if (!c.swap) return counters;
+  const int64_t tiles = static_cast<int64_t>((N + 127) / 128) * ((M + c.bn - 1) / c.bn);
+  return counters + tiles * 16 * c.bn * 128 * 4;  // up to 16 splits
+}
+
+extern "C" int b2_gemm_bf16(const void* x, const void* w, void* y, const void* residual, int M, int N, int K,
+                            int64_t ldx, int64_t ldw, int64_t ldy, int epilogue, int config, void* workspace,
+                            int64_t workspace_bytes, Status* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return -kBadArgument;
+  Config c = choose_config(M, N, K, epilogue);
+  if (config != 0) {
+    c.swap = (config >> 30) & 1;
+    c.splits = (config >> 16) & 0xff;
+    c.bn = config & 0xffff;
+    if (c.splits < 1) c.splits = 1;
+  }
+  if (!c.swap) c.splits = 1;
+  const int num_kb = (K + 63) / 64;
+  if (c.splits > num_kb) c.splits = num_kb;
+  if (c.splits > 16) c.splits = 16;
+  // every split must own at least one k-block
+  while (c.splits > 1 && ((num_kb + c.splits - 1) / c.splits) * (c.splits - 1) >= num_kb) --c.splits;
+  if (epilogue == B2_EPI_SWIGLU) {
+    if (N % 32 != 0) return -kBadArgument;
+    if (c.bn < 32 && !c.swap) return -kBadArgument;
+  } else if (!c.swap && (N % 8 != 0 || ldy % 8 != 0)) {
+    return -kBadArgument;
+  }
+  if (epilogue == B2_EPI_ADD_RESIDUAL && residual == nullptr) return -kBadArgument;
+  EpiParams ep{};
+  ep.y = static_cast<__nv_bfloat16*>(y);
+  ep.residual = static_cast<const __nv_bfloat16*>(residual);
+  ep.ldy = ldy;
+  ep.ldr = ldy;
+  ep.M = M;
+  ep.N = N;
+  ep.mode = epilogue;
+  if (c.splits > 1) {
+    const int64_t counters_bytes = 65536 * 4;
+    const int64_t tiles = static_cast<int64_t>((N + 127) / 128) * ((M + c.bn - 1) / c.bn);
+    const int64_t need = counters_bytes + tiles * c.splits * c.bn * 128 * 4;
+    if (workspace == nullptr || workspace_bytes < need || tiles > 65536) return -kTooLarge;
+    ep.counters = static_cast<uint32_t*>(workspace);
+    ep.workspace = reinterpret_cast<float*>(static_cast<char*>(workspace) + counters_bytes);
+  }
+#define B2_LAUNCH(BN_, SWAP_) \
+  return launch<BN_, SWAP_>(x, w, M, N, K, ldx, ldw, c.splits, ep, status, stream)
+  if (c.swap) {
+    switch (c.bn) {
+      case 16: B2_LAUNCH(16, true);
+      case 32: B2_LAUNCH(32, true);
+      case 64: B2_LAUNCH(64, true);
+      case 128: B2_LAUNCH(128, true);
+      case 256: B2_LAUNCH(256, true);
+      default: return -kBadArgument;
+    }
+  } else {
+    switch (c.bn) {
+      case 64: B2_LAUNCH(64, false);
+      case 128: B2_LAUNCH(128, false);
+      case 256: B2_LAUNCH(256, false);
+      default: return -kBadArgument;
+    }
+  }
+#undef B2_LAUNCH
+}
