@@ -1,0 +1,198 @@
+"""The serving engine: request queue -> continuous-batching scheduler (C++) -> model runner -> sampler.
+
+`LLMEngine.step()` is one iteration of the hot loop: the scheduler packs decode tokens and prefill chunks under
+a token budget and hands back flat metadata; the runner stages it in pinned memory, copies it to the device in
+one transfer, runs the model and the sampler, and reads the sampled ids back. Works on CPU (fp32 reference
+ops, the numerics oracle) and on CUDA (sm_100a kernels) with the same code.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from .. import _ext, ops
+from ..models import build_model
+from ..models.config import ModelConfig
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 0.0          # 0 = greedy
+    top_k: int = 0                    # 0 = off
+    top_p: float = 1.0                # 1 = off
+    max_tokens: int = 16
+    stop_token_ids: tuple = ()
+    ignore_eos: bool = False
+    seed: int | None = None
+
+
+@dataclass
+class EngineConfig:
+    model: ModelConfig = None
+    device: str = "cpu"
+    dtype: torch.dtype = torch.float32
+    page_size: int = 16
+    num_pages: int | None = None          # None: size from free device memory
+    gpu_memory_utilization: float = 0.9
+    max_num_seqs: int = 256
+    max_num_batched_tokens: int = 8192
+    max_model_len: int = 4096
+    enable_prefix_cache: bool = False
+    enable_chunked_prefill: bool = True
+    eos_token_id: int | None = None
+    seed: int = 0
+    use_cuda_graphs: bool = True
+    tp_size: int = 1
+    ep_size: int = 1
+
+
+@dataclass
+class RequestState:
+    request_id: int
+    prompt_len: int
+    params: SamplingParams
+    arrival: float
+    output_ids: list = field(default_factory=list)
+    token_times: list = field(default_factory=list)
+    first_token_time: float | None = None
+    finished: bool = False
+    finish_reason: str | None = None
+
+
+@dataclass
+class RequestOutput:
+    request_id: int
+    new_token_ids: list
+    output_ids: list
+    finished: bool
+    finish_reason: str | None
+
+
+class LLMEngine:
+    def __init__(self, cfg: EngineConfig, model=None, comm=None):
+        self.cfg = cfg
+        self.C = _ext.require()
+        self.device = torch.device(cfg.device)
+        self.model = model if model is not None else build_model(cfg.model, self.device, cfg.dtype, comm=comm).init_random(cfg.seed)
+        self.comm = comm
+        num_pages = cfg.num_pages or self._auto_num_pages()
+        self.kv_caches = self.model.allocate_kv_cache(num_pages, cfg.page_size)
+        self.kv = self.C.KVCacheManager(num_pages, cfg.page_size, cfg.enable_prefix_cache)
+        sc = self.C.SchedulerConfig()
+        sc.max_num_seqs = cfg.max_num_seqs
+        sc.max_num_batched_tokens = cfg.max_num_batched_tokens
+        sc.max_model_len = cfg.max_model_len
+        sc.enable_chunked_prefill = cfg.enable_chunked_prefill
+        self.scheduler = self.C.Scheduler(sc, self.kv)
+        self.requests: dict[int, RequestState] = {}
+        self._next_id = 0
+        self.step_count = 0
+        from .model_runner import ModelRunner
+
+        self.runner = ModelRunner(self.model, self.kv_caches, cfg)
+
+    def _auto_num_pages(self) -> int:
+        cfg = self.cfg
+        per_page = self.model.kv_bytes_per_page(cfg.page_size)
+        if self.device.type != "cuda":
+            return max(64, (cfg.max_num_seqs * cfg.max_model_len) // cfg.page_size // 8)
+        free, total = torch.cuda.mem_get_info(self.device)
+        budget = int(total * cfg.gpu_memory_utilization) - (total - free)
+        # activations of one full token budget + logits, with slack
+        budget -= 8 << 30
+        need_max = (cfg.max_num_seqs * cfg.max_model_len + cfg.page_size - 1) // cfg.page_size
+        return int(max(16, min(budget // per_page, need_max)))
+
+    # ------------------------------------------------------------------------------------------------
+    def add_request(self, prompt_ids, params: SamplingParams | None = None, arrival: float | None = None,
+                    request_id: int | None = None) -> int:
+        params = params or SamplingParams()
+        rid = self._next_id if request_id is None else request_id
+        self._next_id = max(self._next_id, rid) + 1
+        prompt = np.asarray(prompt_ids, dtype=np.int32)
+        max_new = max(1, min(params.max_tokens, self.cfg.max_model_len - len(prompt)))
+        now = time.perf_counter() if arrival is None else arrival
+        self.scheduler.add_request(rid, prompt, max_new, now)
+        self.requests[rid] = RequestState(rid, len(prompt), params, now)
+        return rid
+
+    def abort_request(self, rid: int) -> None:
+        if rid in self.requests:
+            self.scheduler.abort(rid)
+            self.requests[rid].finished = True
+            self.requests[rid].finish_reason = "abort"
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished()
+
+    # ------------------------------------------------------------------------------------------------
+    def step(self) -> list[RequestOutput]:
+        """One engine iteration. Returns outputs for every sequence that produced a token."""
+        batch = self.scheduler.step()
+        if batch.num_seqs == 0:
+            return []
+        sample_ids = batch.sample_seq_ids
+        states = [self.requests[int(r)] for r in sample_ids]
+        tokens = self.runner.execute(batch, states, self.step_count)
+        self.step_count += 1
+        now = time.perf_counter()
+        outs = []
+        for rid, tok, st in zip(sample_ids, tokens, states):
+            rid, tok = int(rid), int(tok)
+            hit_max = self.scheduler.append_token(rid, tok)
+            st.output_ids.append(tok)
+            st.token_times.append(now)
+            if st.first_token_time is None:
+                st.first_token_time = now
+            reason = None
+            eos = self.cfg.eos_token_id
+            if not st.params.ignore_eos and eos is not None and tok == eos:
+                reason = "stop"
+            elif tok in st.params.stop_token_ids:
+                reason = "stop"
+            elif hit_max:
+                reason = "length"
+            if reason is not None:
+                st.finished, st.finish_reason = True, reason
+                self.scheduler.finish(rid)
+            outs.append(RequestOutput(rid, [tok], st.output_ids, st.finished, reason))
+        return outs
+
+    def generate(self, prompts, params: SamplingParams | list | None = None) -> list[list[int]]:
+        """Blocking convenience: run a list of token-id prompts to completion, return generated ids in order."""
+        if params is None or isinstance(params, SamplingParams):
+            params = [params] * len(prompts)
+        rids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        while self.has_unfinished():
+            self.step()
+        if self.device.type == "cuda":
+            ops.check_status(self.device)
+        return [list(self.requests[r].output_ids) for r in rids]
+
+    # ------------------------------------------------------------------------------------------------
+    def metrics(self) -> dict:
+        """TTFT / ITL percentiles and throughput over finished requests."""
+        ttft, itl, n_out = [], [], 0
+        t0, t1 = float("inf"), 0.0
+        for st in self.requests.values():
+            if not st.token_times:
+                continue
+            ttft.append(st.first_token_time - st.arrival)
+            tt = st.token_times
+            itl.extend(b - a for a, b in zip(tt[:-1], tt[1:]))
+            n_out += len(tt)
+            t0, t1 = min(t0, st.arrival), max(t1, tt[-1])
+        stats = self.kv.stats()
+        return {
+            "requests": len(ttft), "output_tokens": n_out,
+            "ttft_p50_ms": 1e3 * float(np.median(ttft)) if ttft else None,
+            "ttft_p99_ms": 1e3 * float(np.percentile(ttft, 99)) if ttft else None,
+            "itl_p50_ms": 1e3 * float(np.median(itl)) if itl else None,
+            "itl_p99_ms": 1e3 * float(np.percentile(itl, 99)) if itl else None,
+            "output_tok_per_s": n_out / (t1 - t0) if t1 > t0 else None,
+            "steps": self.step_count, "preemptions": self.scheduler.total_preemptions(),
+            "kv_pages": stats.num_pages, "kv_free_pages": stats.free_pages, "prefix_hits": stats.prefix_hits,
+        }
