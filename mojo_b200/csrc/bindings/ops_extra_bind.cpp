@@ -1,6 +1,103 @@
-// Bindings of the second kernel group (fp8, MLA, GGUF, fused tensor-/expert-parallel ops).
+// Bindings of the second kernel group: fused tensor-parallel ops over symmetric memory (more groups register
+// themselves below as they are added).
 #include <torch/extension.h>
+#include <c10/cuda/CUDAStream.h>
+#include <c10/cuda/CUDAGuard.h>
 #include "b2/api.h"
+#include "b2/tp.h"
 namespace py = pybind11;
 
-void bind_ops_extra(py::module_& m) { (void)m; }
+namespace {
+cudaStream_t cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+void check(int rc, const char* what) {
+  if (rc != 0) throw std::runtime_error(std::string("mojo_b200: ") + what + " rejected its arguments: " + b2::status_code_name(-rc));
+}
+void need(bool cond, const char* msg) {
+  if (!cond) throw std::invalid_argument(std::string("mojo_b200: ") + msg);
+}
+b2::Status* status_ptr(const c10::optional<at::Tensor>& s) {
+  return s.has_value() ? reinterpret_cast<b2::Status*>(s->data_ptr()) : nullptr;
+}
+B2TpRegion make_region(int rank, const std::vector<int64_t>& ptrs) {
+  need(!ptrs.empty() && ptrs.size() <= 8 && rank >= 0 && rank < static_cast<int>(ptrs.size()), "tp region: 1..8 peer pointers and a valid rank");
+  B2TpRegion r{};
+  r.rank = rank;
+  r.tp = static_cast<int>(ptrs.size());
+  for (size_t i = 0; i < ptrs.size(); ++i) r.peer[i] = reinterpret_cast<void*>(ptrs[i]);
+  return r;
+}
+bool is_bf16_2d(const at::Tensor& t) { return t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 2 && t.stride(1) == 1; }
+}  // namespace
+
+void bind_ops_extra(py::module_& m) {
+  py::class_<B2TpLayout>(m, "TpLayout")
+      .def(py::init([]() { return B2TpLayout{}; }))
+      .def_readwrite("off_staging", &B2TpLayout::off_staging)
+      .def_readwrite("staging_half_bytes", &B2TpLayout::staging_half_bytes)
+      .def_readwrite("off_yall", &B2TpLayout::off_yall)
+      .def_readwrite("yall_half_bytes", &B2TpLayout::yall_half_bytes)
+      .def_readwrite("off_xall", &B2TpLayout::off_xall)
+      .def_readwrite("xall_half_bytes", &B2TpLayout::xall_half_bytes)
+      .def_readwrite("off_rs_flags", &B2TpLayout::off_rs_flags)
+      .def_readwrite("rs_flags_bytes", &B2TpLayout::rs_flags_bytes)
+      .def_readwrite("off_ag_flags", &B2TpLayout::off_ag_flags)
+      .def_readwrite("ag_flags_bytes", &B2TpLayout::ag_flags_bytes)
+      .def_readwrite("off_res_flags", &B2TpLayout::off_res_flags)
+      .def_readwrite("off_done", &B2TpLayout::off_done)
+      .def_readwrite("off_barrier", &B2TpLayout::off_barrier)
+      .def_readwrite("off_epoch_rs", &B2TpLayout::off_epoch_rs)
+      .def_readwrite("off_epoch_ag", &B2TpLayout::off_epoch_ag)
+      .def_readwrite("off_epoch_bar", &B2TpLayout::off_epoch_bar)
+      .def_readwrite("total_bytes", &B2TpLayout::total_bytes);
+
+  m.def("tp_gemm_rs",
+        [](const at::Tensor& x, const at::Tensor& w, int rank, const std::vector<int64_t>& peers, const B2TpLayout& lay,
+           c10::optional<at::Tensor> out, c10::optional<at::Tensor> residual, int mode, int slot, uint64_t timeout_ns,
+           int config, c10::optional<at::Tensor> status) {
+          need(is_bf16_2d(x) && is_bf16_2d(w) && x.size(1) == w.size(1), "tp_gemm_rs: x [M, K/tp], w [N, K/tp] bf16");
+          const int M = static_cast<int>(x.size(0)), K = static_cast<int>(x.size(1)), N = static_cast<int>(w.size(0));
+          const B2TpRegion reg = make_region(rank, peers);
+          if (mode == 0) need(out.has_value() && is_bf16_2d(*out) && out->is_contiguous() && out->size(0) * reg.tp == M && out->size(1) == N, "tp_gemm_rs: out must be contiguous [M/tp, N]");
+          if (residual.has_value()) need(is_bf16_2d(*residual) && residual->is_contiguous() && residual->size(1) == N, "tp_gemm_rs: residual must be contiguous [rows, N]");
+          c10::cuda::CUDAGuard g(x.device());
+          check(b2_tp_gemm_rs_bf16(x.data_ptr(), w.data_ptr(), &reg, &lay, out.has_value() ? out->data_ptr() : nullptr,
+                                   residual.has_value() ? residual->data_ptr() : nullptr, M, N, K, x.stride(0), w.stride(0), mode,
+                                   slot, timeout_ns, config, status_ptr(status), cur_stream()),
+                "tp_gemm_rs");
+        },
+        py::arg("x"), py::arg("w"), py::arg("rank"), py::arg("peers"), py::arg("layout"), py::arg("out"), py::arg("residual"),
+        py::arg("mode"), py::arg("slot"), py::arg("timeout_ns"), py::arg("config") = 0, py::arg("status") = py::none());
+
+  m.def("tp_ag_gemm",
+        [](const at::Tensor& w, int rank, const std::vector<int64_t>& peers, const B2TpLayout& lay, at::Tensor& y, int M,
+           int slot, uint64_t timeout_ns, int n_comm, int config, c10::optional<at::Tensor> status) {
+          need(is_bf16_2d(w) && is_bf16_2d(y) && y.size(0) == M && y.size(1) == w.size(0), "tp_ag_gemm: w [N/tp, K], y [M, N/tp] bf16");
+          const B2TpRegion reg = make_region(rank, peers);
+          c10::cuda::CUDAGuard g(w.device());
+          check(b2_tp_ag_gemm_bf16(w.data_ptr(), &reg, &lay, y.data_ptr(), M, static_cast<int>(w.size(0)), static_cast<int>(w.size(1)),
+                                   w.stride(0), y.stride(0), slot, timeout_ns, n_comm, config, status_ptr(status), cur_stream()),
+                "tp_ag_gemm");
+        },
+        py::arg("w"), py::arg("rank"), py::arg("peers"), py::arg("layout"), py::arg("y"), py::arg("M"), py::arg("slot"),
+        py::arg("timeout_ns"), py::arg("n_comm") = 0, py::arg("config") = 0, py::arg("status") = py::none());
+
+  m.def("tp_all_gather",
+        [](int rank, const std::vector<int64_t>& peers, const B2TpLayout& lay, int M, int K, int slot, uint64_t timeout_ns,
+           c10::optional<at::Tensor> status) {
+          const B2TpRegion reg = make_region(rank, peers);
+          check(b2_tp_all_gather(&reg, &lay, M, K, slot, timeout_ns, status_ptr(status), cur_stream()), "tp_all_gather");
+        });
+
+  m.def("symm_barrier",
+        [](int rank, const std::vector<int64_t>& peers, const B2TpLayout& lay, uint64_t timeout_ns,
+           c10::optional<at::Tensor> status) {
+          const B2TpRegion reg = make_region(rank, peers);
+          check(b2_symm_barrier(&reg, &lay, timeout_ns, status_ptr(status), cur_stream()), "symm_barrier");
+        });
+
+  m.def("wait_flag", [](const at::Tensor& flag, uint32_t want, uint64_t timeout_ns, c10::optional<at::Tensor> status) {
+    need(flag.is_cuda() && flag.element_size() == 4, "wait_flag: 32-bit CUDA flag tensor");
+    c10::cuda::CUDAGuard g(flag.device());
+    check(b2_wait_flag(reinterpret_cast<const uint32_t*>(flag.data_ptr()), want, timeout_ns, status_ptr(status), cur_stream()), "wait_flag");
+  });
+}

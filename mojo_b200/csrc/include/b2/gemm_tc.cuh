@@ -69,7 +69,7 @@ constexpr int tmem_cols_for() {
 template <int BN, int STAGES, int ELEM_BYTES, class Sched, class Gate, class Epi>
 __device__ __forceinline__ void run(const CUtensorMap* tmap_p, const CUtensorMap* tmap_q, uint32_t idesc,
                                     uint64_t policy_p, uint64_t policy_q, Sched sched, Gate gate, Epi epi,
-                                    Status* status) {
+                                    Status* status, int cta, int num_ctas) {
   using L = SmemLayout<BN, STAGES>;
   constexpr int kTmemCols = tmem_cols_for<BN>();
   constexpr int kMmaPerKb = 4;                       // 128 bytes / 32 bytes per instruction
@@ -121,7 +121,7 @@ __device__ __forceinline__ void run(const CUtensorMap* tmap_p, const CUtensorMap
       uint32_t phase = 0;
       long issued = 0;
       bool ok = true;
-      for (int w = blockIdx.x; ok && w < total; w += gridDim.x) {
+      for (int w = cta; ok && w < total; w += num_ctas) {
         const WorkUnit u = sched.get(w);
         if (!gate(u, status)) { ok = false; break; }
         for (int kb = u.kb0; kb < u.kb1; ++kb) {
@@ -159,7 +159,7 @@ __device__ __forceinline__ void run(const CUtensorMap* tmap_p, const CUtensorMap
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int w = blockIdx.x; ok && w < total; w += gridDim.x) {
+      for (int w = cta; ok && w < total; w += num_ctas) {
         const WorkUnit u = sched.get(w);
         if (!ptx::mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u)) {
           status_record(status, kTimeout, kSiteGemmTmemEmpty, w, acc);
@@ -208,7 +208,7 @@ __device__ __forceinline__ void run(const CUtensorMap* tmap_p, const CUtensorMap
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int w = blockIdx.x; ok && w < total; w += gridDim.x) {
+    for (int w = cta; ok && w < total; w += num_ctas) {
       const WorkUnit u = sched.get(w);
       if (!ptx::mbar_wait(tmem_full_bar(acc), acc_phase)) {
         if (lane == 0) status_record(status, kTimeout, kSiteGemmTmemFull, w, acc);

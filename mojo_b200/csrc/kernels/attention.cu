@@ -13,6 +13,7 @@
 #include <cuda_bf16.h>
 #include "b2/api.h"
 #include "b2/ptx.cuh"
+#include "b2/tma.h"
 #include "b2/vec.cuh"
 
 namespace b2 {
@@ -45,11 +46,18 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Shared-memory tile [rows][D] of bf16, 16-byte chunks XOR-swizzled by (row & 7).
-template <int D>
+// Shared-memory tile of bf16 in 16-byte chunks. Two layouts:
+//   ROWS == 0  [rows][D], chunk index XOR-swizzled by (row & 7)              (filled by cp.async)
+//   ROWS  > 0  D/64 sub-tiles of [ROWS][64] with 128-byte rows and the 128-byte TMA swizzle: exactly what a
+//              SWIZZLE_128B box of 64 columns x ROWS rows leaves in shared memory (base 1024-byte aligned)
+template <int D, int ROWS = 0>
 __device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk) {
-  constexpr int CPR = D / 8;  // chunks per row
-  return base + static_cast<uint32_t>((row * CPR + (chunk ^ (row & 7))) * 16);
+  if constexpr (ROWS == 0) {
+    constexpr int CPR = D / 8;  // chunks per row
+    return base + static_cast<uint32_t>((row * CPR + (chunk ^ (row & 7))) * 16);
+  } else {
+    return base + static_cast<uint32_t>((chunk >> 3) * (ROWS * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+  }
 }
 
 struct PagedKV {
@@ -88,7 +96,7 @@ __device__ __forceinline__ void load_kv_tile(const PagedKV& kv, int kv0, uint32_
 // One warp: S = Q K^T on a BN-token tile, online softmax, O += P V.
 //   qf      Q fragments of this warp's 16 rows (D/16 k-steps x 4 regs)
 //   max_lo  highest KV position visible to row g, max_hi to row g + 8 (causal + context limit)
-template <int D, int BN>
+template <int D, int BN, int TROWS = 0>
 __device__ __forceinline__ void warp_attend(const uint32_t (&qf)[D / 16][4], uint32_t k_sm, uint32_t v_sm, int kv0,
                                             int max_lo, int max_hi, float scale_log2, float (&o)[D / 8][4],
                                             float (&m)[2], float (&l)[2], int lane) {
@@ -103,7 +111,7 @@ __device__ __forceinline__ void warp_attend(const uint32_t (&qf)[D / 16][4], uin
       uint32_t b0, b1, b2, b3;
       const int row = jp * 16 + (lane & 7) + ((lane >> 4) << 3);
       const int chunk = kk * 2 + ((lane >> 3) & 1);
-      ldmatrix_x4(tile_addr<D>(k_sm, row, chunk), b0, b1, b2, b3);
+      ldmatrix_x4(tile_addr<D, TROWS>(k_sm, row, chunk), b0, b1, b2, b3);
       mma_bf16(s[2 * jp], qf[kk], b0, b1);
       mma_bf16(s[2 * jp + 1], qf[kk], b2, b3);
     }
@@ -157,7 +165,7 @@ __device__ __forceinline__ void warp_attend(const uint32_t (&qf)[D / 16][4], uin
       uint32_t b0, b1, b2, b3;
       const int row = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
       const int chunk = dp * 2 + (lane >> 4);
-      ldmatrix_x4_trans(tile_addr<D>(v_sm, row, chunk), b0, b1, b2, b3);
+      ldmatrix_x4_trans(tile_addr<D, TROWS>(v_sm, row, chunk), b0, b1, b2, b3);
       mma_bf16(o[2 * dp], a, b0, b1);
       mma_bf16(o[2 * dp + 1], a, b2, b3);
     }
@@ -405,6 +413,138 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Decode, TMA path (page_size % 32 == 0): one warp per (split, kv head, sequence). K/V tiles of 32 tokens
+// arrive as SWIZZLE_128B boxes through a STAGES-deep mbarrier ring issued by lane 0, so the address work per
+// 16 KB tile is four instructions instead of a page-table walk per 16-byte chunk, and several small CTAs per
+// SM keep ~200 KB of loads in flight. The cache is addressed as a 2-D matrix [(page, kv head, token), D].
+// ------------------------------------------------------------------------------------------------
+template <int D, int STAGES>
+__global__ void __launch_bounds__(32) attn_decode_tma_kernel(
+    const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+    const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ ctx_lens,
+    const int32_t* __restrict__ block_tables, float* __restrict__ workspace, int max_blocks, int n_q, int n_kv,
+    int page_size, int num_splits, float scale_log2, int64_t q_stride, int64_t out_stride, int64_t num_pages,
+    Status* status) {
+  constexpr int BN = 32;
+  constexpr int HALVES = D / 64;
+  constexpr int SUB_BYTES = BN * 128;              // one [32][64] box
+  constexpr int TILE_BYTES = HALVES * SUB_BYTES;   // K or V tile
+  constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t q_sm = sbase + STAGES * STAGE_BYTES;
+  const uint32_t bar0 = q_sm + 16 * D * 2;
+  const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+  const int lane = threadIdx.x;
+  const int group = n_q / n_kv;
+  const int ctx = ctx_lens[seq];
+  const int32_t* table = block_tables + static_cast<int64_t>(seq) * max_blocks;
+
+  const int tiles_total = (ctx + BN - 1) / BN;
+  const int tiles_per_split = (tiles_total + num_splits - 1) / num_splits;
+  const int tile_begin = split * tiles_per_split;
+  const int tile_end = min(tiles_total, tile_begin + tiles_per_split);
+  const int n_tiles = max(0, tile_end - tile_begin);
+
+  if (lane == 0) {
+    ptx::prefetch_tensormap(&tmap_k);
+    ptx::prefetch_tensormap(&tmap_v);
+    for (int s = 0; s < STAGES; ++s) ptx::mbar_init(bar0 + 8 * s, 1);
+    ptx::fence_mbar_init();
+  }
+  __syncwarp();
+
+  auto issue = [&](int i) {  // lane 0 only: start the loads of this CTA's i-th tile
+    const int t = tile_begin + i;
+    const int pos = t * BN;
+    int64_t page = table[pos / page_size];
+    if (!B2_ASSERT(status, page >= 0 && page < num_pages, kSiteKvIndex, page, num_pages)) page = 0;
+    const int row = static_cast<int>((page * n_kv + kvh) * page_size + pos % page_size);
+    const int s = i % STAGES;
+    const uint32_t dst = sbase + s * STAGE_BYTES;
+    const uint32_t bar = bar0 + 8 * s;
+    ptx::mbar_arrive_expect_tx(bar, STAGE_BYTES);
+#pragma unroll
+    for (int h = 0; h < HALVES; ++h) {
+      ptx::tma_load_2d(dst + h * SUB_BYTES, &tmap_k, bar, h * 64, row, ptx::kEvictFirst);
+      ptx::tma_load_2d(dst + TILE_BYTES + h * SUB_BYTES, &tmap_v, bar, h * 64, row, ptx::kEvictFirst);
+    }
+  };
+  if (lane == 0) {
+    for (int i = 0; i < STAGES - 1 && i < n_tiles; ++i) issue(i);
+  }
+
+  uint32_t qf[D / 16][4];
+  load_q_frags<D>(q, q_stride, seq, 1, group, kvh, 0, q_sm, qf, lane);
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int d = 0; d < D / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+  const int g = lane >> 2;
+  const int max_lo = g < group ? ctx - 1 : -1;
+  const int max_hi = g + 8 < group ? ctx - 1 : -1;
+
+  bool ok = true;
+  for (int i = 0; i < n_tiles; ++i) {
+    const int s = i % STAGES;
+    // the stage being refilled was consumed in iteration i - 1 (program order within the warp)
+    if (lane == 0 && i + STAGES - 1 < n_tiles) issue(i + STAGES - 1);
+    if (!ptx::mbar_wait(bar0 + 8 * s, (i / STAGES) & 1)) {
+      if (lane == 0) status_record(status, kTimeout, kSiteAttn, seq, i);
+      ok = false;
+      break;
+    }
+    const uint32_t kb = sbase + s * STAGE_BYTES;
+    const int kv0 = (tile_begin + i) * BN;
+    if (kv0 + BN > ctx) {
+      // rows past the context hold whatever the page held before: clear V there so 0 * garbage stays 0
+      for (int r = ctx - kv0 + (lane >> 4); r < BN; r += 2)
+#pragma unroll
+        for (int c = (lane & 15); c < D / 8; c += 16) {
+          const uint32_t a = tile_addr<D, BN>(kb + TILE_BYTES, r, c);
+          asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0u) : "memory");
+        }
+      __syncwarp();
+    }
+    warp_attend<D, BN, BN>(qf, kb, kb + TILE_BYTES, kv0, max_lo, max_hi, scale_log2, o, m, l, lane);
+    __syncwarp();
+  }
+  if (!ok) {
+    // let outstanding copies land before the CTA's shared memory is released
+    for (int i = 0; i < STAGES; ++i) ptx::mbar_wait(bar0 + 8 * i, 0, 20000000ull) || ptx::mbar_wait(bar0 + 8 * i, 1, 20000000ull);
+    return;
+  }
+  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1);
+  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
+  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1);
+  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
+  const int t4 = lane & 3;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int row = g + half * 8;
+    if (row >= group) continue;
+    const int head = kvh * group + row;
+    if (num_splits == 1) {
+      const float inv = l[half] > 0.0f ? 1.0f / l[half] : 0.0f;
+      __nv_bfloat16* dst = out + static_cast<int64_t>(seq) * out_stride + static_cast<int64_t>(head) * D;
+#pragma unroll
+      for (int d = 0; d < D / 8; ++d)
+        *reinterpret_cast<uint32_t*>(dst + d * 8 + 2 * t4) = ptx::pack_bf16x2(o[d][half * 2] * inv, o[d][half * 2 + 1] * inv);
+    } else {
+      float* dst = workspace + ((static_cast<int64_t>(seq) * n_q + head) * num_splits + split) * (D + 2);
+#pragma unroll
+      for (int d = 0; d < D / 8; ++d)
+        *reinterpret_cast<float2*>(dst + d * 8 + 2 * t4) = make_float2(o[d][half * 2], o[d][half * 2 + 1]);
+      if (t4 == 0) {
+        dst[D] = m[half];
+        dst[D + 1] = l[half];
+      }
+    }
+  }
+}
+
 // Merge split partials: one warp per (sequence, head).
 template <int D>
 __global__ void attn_decode_reduce_kernel(const float* __restrict__ workspace, __nv_bfloat16* __restrict__ out,
@@ -498,6 +638,41 @@ extern "C" int b2_attn_decode_bf16(const void* q, const void* k_cache, const voi
   auto vp = static_cast<const __nv_bfloat16*>(v_cache);
   auto op = static_cast<__nv_bfloat16*>(out);
   const int total = batch * n_q;
+  if (page_size % 32 == 0) {
+    // TMA path: cache as a 2-D matrix [(page, kv head, token), D], boxes of 32 tokens x 64 columns
+    CUtensorMap tk, tv;
+    const uint64_t rows = static_cast<uint64_t>(num_pages) * n_kv * page_size;
+    if (!make_tmap_2d(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k_cache, rows, head_dim, head_dim * 2, 32, 64, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_tmap_2d(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v_cache, rows, head_dim, head_dim * 2, 32, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+      return -kBadArgument;
+    constexpr int STAGES = 3;
+    if (head_dim == 128) {
+      constexpr int SMEM = STAGES * 2 * 32 * 128 * 2 + 16 * 128 * 2 + 64 + 1024;
+      static bool set = false;
+      if (!set) {
+        cudaFuncSetAttribute(attn_decode_tma_kernel<128, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        set = true;
+      }
+      attn_decode_tma_kernel<128, STAGES><<<grid, 32, SMEM, stream>>>(tk, tv, qp, op, ctx_lens, block_tables, workspace, max_blocks,
+                                                                    n_q, n_kv, page_size, num_splits, scale_log2, q_stride,
+                                                                    out_stride, num_pages, status);
+      if (num_splits > 1)
+        attn_decode_reduce_kernel<128><<<(total + 3) / 4, 128, 0, stream>>>(workspace, op, n_q, num_splits, out_stride, total);
+    } else {
+      constexpr int SMEM = STAGES * 2 * 32 * 64 * 2 + 16 * 64 * 2 + 64 + 1024;
+      static bool set = false;
+      if (!set) {
+        cudaFuncSetAttribute(attn_decode_tma_kernel<64, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        set = true;
+      }
+      attn_decode_tma_kernel<64, STAGES><<<grid, 32, SMEM, stream>>>(tk, tv, qp, op, ctx_lens, block_tables, workspace, max_blocks,
+                                                                   n_q, n_kv, page_size, num_splits, scale_log2, q_stride,
+                                                                   out_stride, num_pages, status);
+      if (num_splits > 1)
+        attn_decode_reduce_kernel<64><<<(total + 3) / 4, 128, 0, stream>>>(workspace, op, n_q, num_splits, out_stride, total);
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  }
   if (head_dim == 128) {
     constexpr int SMEM = 4 * (16 * 128 * 2 + 4 * 32 * 128 * 2);
     static bool set = false;

@@ -186,7 +186,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_consta
                  gemm::TileSched sched, EpiParams ep, uint64_t policy_p, uint64_t policy_q, Status* status) {
   constexpr uint32_t idesc = ptx::make_idesc(1, 1, 128, BN);
   Epilogue<BN, SWAP> epi{ep};
-  gemm::run<BN, STAGES, 2>(&tmap_p, &tmap_q, idesc, policy_p, policy_q, sched, gemm::NoGate{}, epi, status);
+  gemm::run<BN, STAGES, 2>(&tmap_p, &tmap_q, idesc, policy_p, policy_q, sched, gemm::NoGate{}, epi, status,
+                           static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
 }
 
 constexpr int stages_for(int bn) {
@@ -201,26 +202,62 @@ struct Config {
   int splits;
 };
 
+// Cost model behind the automatic configuration (cycles at SM clock; constants fitted to a sweep of the four
+// Llama-8B layer GEMMs at M = 16 ... 1024 on a B200):
+//   one work unit = k-blocks * max(tensor time, shared-memory fill time) + fixed epilogue cost
+//   tensor time of a 128 x bn x 64 block  = 2 * bn / 0.75   (8192 dense bf16 FLOP/clk/SM nominal, ~75 % reachable)
+//   fill time of the same block           = (128 + bn) * 128 B at ~128 B/clk from L2
+//   split-K adds a semaphore round trip and a pass over splits * bn * 128 f32 partials
+//   the kernel is persistent over 148 SMs, so the total is waves * unit + launch/prologue cost,
+//   and never less than streaming every operand once from HBM.
+double model_cycles(int M, int N, int K, bool swap, int bn, int splits) {
+  const int num_kb = (K + 63) / 64;
+  const int rows_p = swap ? N : M, rows_q = swap ? M : N;
+  const long units = static_cast<long>((rows_p + 127) / 128) * ((rows_q + bn - 1) / bn) * splits;
+  const double kb = (num_kb + splits - 1) / splits;
+  const double mma = kb * 2.0 * bn / 0.75;
+  const double fill = kb * (128.0 + bn);
+  double unit = (mma > fill ? mma : fill) + 600.0;
+  if (splits > 1) unit += 2500.0 + splits * bn * 128.0 * 4.0 / 48.0;
+  const double waves = static_cast<double>((units + kNumSMs - 1) / kNumSMs);
+  const double total = waves * unit + 7000.0;
+  const double hbm = (static_cast<double>(N) * K + static_cast<double>(M) * K + static_cast<double>(M) * N) * 2.0 / 3300.0 + 5000.0;
+  return total > hbm ? total : hbm;
+}
+
 Config choose_config(int M, int N, int K, int epilogue) {
   const int num_kb = (K + 63) / 64;
-  Config c{};
-  if (M <= 256) {
-    c.swap = true;
-    c.bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-    const int tiles = ((N + 127) / 128) * ((M + c.bn - 1) / c.bn);
-    int s = 1;
-    // split K until there are about two waves of work units, keeping >= 8 k-blocks per split
-    while (tiles * s < 148 && num_kb / (s * 2) >= 8) s *= 2;
-    c.splits = s;
-  } else {
-    c.swap = false;
-    const int tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
-    c.bn = (N >= 256 && tiles256 >= 148) ? 256 : 128;
-    if (N < 128) c.bn = 64;
-    c.splits = 1;
+  Config best{};
+  double best_t = 1e300;
+  auto consider = [&](bool swap, int bn, int splits) {
+    if (splits > num_kb || (splits > 1 && num_kb / splits < 4)) return;
+    if (epilogue == B2_EPI_SWIGLU && !swap && bn < 32) return;
+    const long rows_p = swap ? N : M, rows_q = swap ? M : N;
+    const long tiles = ((rows_p + 127) / 128) * ((rows_q + bn - 1) / bn);
+    if (splits > 1 && (tiles > 65536 || tiles * splits * bn * 128 * 4 > (64l << 20))) return;
+    const double t = model_cycles(M, N, K, swap, bn, splits);
+    if (t < best_t) {
+      best_t = t;
+      best = Config{swap, bn, splits};
+    }
+  };
+  static const int kSplits[] = {1, 2, 4, 8};
+  if (M <= 128) {
+    static const int kBn[] = {16, 32, 64, 128};
+    for (int bn : kBn) {
+      if (bn * 4 < M || (bn >= 2 * M && bn > 16)) continue;  // neither many token tiles nor mostly padding
+      for (int sp : kSplits) consider(true, bn, sp);
+    }
   }
-  (void)epilogue;
-  return c;
+  if (M > 64) {
+    static const int kBn[] = {64, 128, 256};
+    for (int bn : kBn) {
+      if (N % 8 != 0) continue;
+      for (int sp : kSplits) consider(false, bn, sp);
+    }
+  }
+  if (best_t == 1e300) best = Config{true, 16, 1};
+  return best;
 }
 
 template <int BN, bool SWAP>
@@ -269,12 +306,10 @@ int launch(const void* x, const void* w, int M, int N, int K, int64_t ldx, int64
 using namespace b2;
 
 extern "C" int64_t b2_gemm_workspace_bytes(int M, int N, int K) {
-  // Upper bound over every configuration choose_config can return: counters + partials.
-  const Config c = choose_config(M, N, K, 0);
-  const int64_t counters = 65536 * 4;
-  if (!c.swap) return counters;
-  const int64_t tiles = static_cast<int64_t>((N + 127) / 128) * ((M + c.bn - 1) / c.bn);
-  return counters + tiles * 16 * c.bn * 128 * 4;  // up to 16 splits
+  // counters + the partials bound the automatic configuration respects (explicit configurations are checked
+  // against the caller's actual workspace size at launch)
+  (void)M; (void)N; (void)K;
+  return 65536 * 4 + (64l << 20);
 }
 
 extern "C" int b2_gemm_bf16(const void* x, const void* w, void* y, const void* residual, int M, int N, int K,
@@ -289,7 +324,6 @@ extern "C" int b2_gemm_bf16(const void* x, const void* w, void* y, const void* r
     c.bn = config & 0xffff;
     if (c.splits < 1) c.splits = 1;
   }
-  if (!c.swap) c.splits = 1;
   const int num_kb = (K + 63) / 64;
   if (c.splits > num_kb) c.splits = num_kb;
   if (c.splits > 16) c.splits = 16;
@@ -312,7 +346,9 @@ extern "C" int b2_gemm_bf16(const void* x, const void* w, void* y, const void* r
   ep.mode = epilogue;
   if (c.splits > 1) {
     const int64_t counters_bytes = 65536 * 4;
-    const int64_t tiles = static_cast<int64_t>((N + 127) / 128) * ((M + c.bn - 1) / c.bn);
+    // P is the 128-row operand: W rows when swapped, X rows otherwise
+    const int rows_p = c.swap ? N : M, rows_q = c.swap ? M : N;
+    const int64_t tiles = static_cast<int64_t>((rows_p + 127) / 128) * ((rows_q + c.bn - 1) / c.bn);
     const int64_t need = counters_bytes + tiles * c.splits * c.bn * 128 * 4;
     if (workspace == nullptr || workspace_bytes < need || tiles > 65536) return -kTooLarge;
     ep.counters = static_cast<uint32_t*>(workspace);

@@ -68,13 +68,24 @@ class ModelRunner:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.ids_host = torch.empty(cfg.max_num_seqs, dtype=torch.int64, pin_memory=self.cuda)
-        self.graphs: dict[int, tuple] = {}
+        self.graphs: dict[int, "_DecodeGraph"] = {}
         self.use_graphs = bool(cfg.use_cuda_graphs and self.cuda)
-        self.graph_launches = 0
-        self.launches_per_graph: dict[int, int] = {}
+        self.graph_launches = 0          # graph replays
+        self.graph_kernel_launches = 0   # kernels executed inside replayed graphs
+        self.step_events = None          # optional (start, end) CUDA events recorded around the device work
+        self.last_num_tokens = 0
+        b, self.buckets = 1, []
+        while b < cfg.max_num_seqs:
+            self.buckets.append(b)
+            b = b * 2 if b < 16 else b + max(16, b // 4) // 16 * 16
+        self.buckets.append(cfg.max_num_seqs)
 
     # ------------------------------------------------------------------------------------------------
     def execute(self, batch, states, step: int) -> list[int]:
+        self.last_num_tokens = int(batch.num_tokens)
+        if (self.use_graphs and batch.num_prefill == 0 and batch.num_decode > 0
+                and all(s.params.temperature <= 0.0 for s in states)):
+            return self._execute_decode_graph(batch)
         st = self.staging
         st.begin()
         T, B = int(batch.num_tokens), int(batch.num_seqs)
@@ -101,9 +112,13 @@ class ModelRunner:
         meta = ops.AttnMeta(st.view(seg_cu, torch.int32), st.view(seg_ctx, torch.int32), st.view(seg_bt, torch.int32),
                             batch.num_decode, batch.max_q_len, int(ctx_np.max()) if B else 0)
         rows = st.view(seg_rows, torch.int64)
+        if self.step_events is not None:
+            self.step_events[0].record()
         if S == 0:
             # pure mid-prompt chunks: run the layers for their KV side effect, nothing to sample
             self.model.forward(token_ids, positions, slots, meta, self.kv_caches, rows)
+            if self.step_events is not None:
+                self.step_events[1].record()
             self.d2h_bytes = 0
             return []
         logits = self.model.forward(token_ids, positions, slots, meta, self.kv_caches, rows)
@@ -113,6 +128,8 @@ class ModelRunner:
             seed = self.cfg.seed if states[0].params.seed is None else states[0].params.seed
             ids = ops.sample(logits.float() if not self.cuda else logits, st.view(seg_temp, torch.float32),
                              st.view(seg_topk, torch.int32), st.view(seg_topp, torch.float32), seed, step)
+        if self.step_events is not None:
+            self.step_events[1].record()
         if self.cuda:
             self.ids_host[:S].copy_(ids, non_blocking=True)
             torch.cuda.current_stream(self.device).synchronize()
@@ -121,3 +138,104 @@ class ModelRunner:
             out = ids.tolist()
         self.d2h_bytes = S * 8
         return out
+
+    # ------------------------------------------------------------------------------------------------
+    # decode-only steps: CUDA graph per batch-size bucket
+    # ------------------------------------------------------------------------------------------------
+    def _bucket(self, b: int) -> int:
+        for x in self.buckets:
+            if x >= b:
+                return x
+        return self.buckets[-1]
+
+    def _execute_decode_graph(self, batch) -> list[int]:
+        B = int(batch.num_seqs)
+        bb = self._bucket(B)
+        g = self.graphs.get(bb)
+        if g is None:
+            g = _DecodeGraph(self, bb)
+            self.graphs[bb] = g
+        self.h2d_bytes = g.stage(batch, B)
+        if self.step_events is not None:
+            self.step_events[0].record()
+        g.graph.replay()
+        if self.step_events is not None:
+            self.step_events[1].record()
+        self.graph_launches += 1
+        self.graph_kernel_launches += g.kernel_launches
+        self.ids_host[:B].copy_(g.ids[:B], non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        self.d2h_bytes = B * 8
+        return self.ids_host[:B].tolist()
+
+
+class _DecodeGraph:
+    """Static input buffers + captured forward/argmax for one decode batch-size bucket. Padding rows carry
+    slot -1 (no KV write) and context length 0 (attention produces zeros)."""
+
+    def __init__(self, runner: ModelRunner, bb: int):
+        self.runner, self.bb = runner, bb
+        mb = runner.max_blocks
+        dev = runner.device
+        # host layout: tok i64[bb] | slot i64[bb] | pos i32[bb] | ctx i32[bb] | bt i32[bb * mb]
+        self.o_tok, self.o_slot = 0, 8 * bb
+        self.o_pos, self.o_ctx = 16 * bb, 20 * bb
+        self.o_bt = _align(24 * bb)
+        nbytes = self.o_bt + 4 * bb * mb
+        self.host = torch.zeros(nbytes, dtype=torch.uint8, pin_memory=True)
+        self.np = self.host.numpy()
+        self.dev = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+        d = self.dev
+        self.tok = d[self.o_tok:self.o_tok + 8 * bb].view(torch.int64)
+        self.slot = d[self.o_slot:self.o_slot + 8 * bb].view(torch.int64)
+        self.pos = d[self.o_pos:self.o_pos + 4 * bb].view(torch.int32)
+        self.ctx = d[self.o_ctx:self.o_ctx + 4 * bb].view(torch.int32)
+        self.bt = d[self.o_bt:self.o_bt + 4 * bb * mb].view(torch.int32).view(bb, mb)
+        self.cu = torch.arange(bb + 1, dtype=torch.int32, device=dev)
+        self.h_tok = self.np[self.o_tok:self.o_tok + 8 * bb].view(np.int64)
+        self.h_slot = self.np[self.o_slot:self.o_slot + 8 * bb].view(np.int64)
+        self.h_pos = self.np[self.o_pos:self.o_pos + 4 * bb].view(np.int32)
+        self.h_ctx = self.np[self.o_ctx:self.o_ctx + 4 * bb].view(np.int32)
+        self.h_bt = self.np[self.o_bt:self.o_bt + 4 * bb * mb].view(np.int32).reshape(bb, mb)
+        self.h_slot[:] = -1
+        self.dev.copy_(self.host)
+        self.meta = ops.AttnMeta(self.cu, self.ctx, self.bt, bb, 1, runner.cfg.max_model_len)
+        model, caches = runner.model, runner.kv_caches
+
+        comm = getattr(model, "comm", None)
+
+        def run():
+            if comm is not None and hasattr(comm, "begin_graph"):
+                comm.begin_graph()
+            logits = model.forward(self.tok, self.pos, self.slot, self.meta, caches, None)
+            return ops.argmax(logits)
+
+        # one eager pass on a side stream: one-time kernel attribute set-up must not happen under capture
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            run()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        before = ops.launch_count
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.ids = run()
+        self.kernel_launches = ops.launch_count - before
+        ops.launch_count = before
+
+    def stage(self, batch, B: int) -> int:
+        bb = self.bb
+        self.h_tok[:B] = batch.token_ids
+        self.h_slot[:B] = batch.slots
+        self.h_pos[:B] = batch.positions
+        self.h_ctx[:B] = batch.ctx_lens
+        if B < bb:
+            self.h_tok[B:] = 0
+            self.h_slot[B:] = -1
+            self.h_pos[B:] = 0
+            self.h_ctx[B:] = 0
+        bt = batch.block_tables
+        self.h_bt[:B, :bt.shape[1]] = bt
+        self.dev.copy_(self.host, non_blocking=True)
+        return self.host.numel()

@@ -186,11 +186,13 @@ class AttnMeta:
 
 
 def _decode_splits(batch: int, n_kv: int, max_ctx: int) -> int:
+    """Split the KV range so that small batches still fill the machine: the decode kernel runs one warp per
+    (split, kv head, sequence) with four such CTAs per SM (148 SMs x 4 = 592 per wave)."""
     ctas = batch * n_kv
-    if ctas >= 296 or max_ctx <= 512:
+    if ctas >= 1184 or max_ctx <= 256:
         return 1
-    want = (296 + ctas - 1) // ctas
-    return max(1, min(want, max_ctx // 256, 16))
+    want = (1184 + ctas - 1) // ctas
+    return max(1, min(want, max_ctx // 128, 32))
 
 
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, meta: AttnMeta, scale: float,

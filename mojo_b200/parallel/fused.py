@@ -1,0 +1,145 @@
+"""Tensor-parallel communicator whose collectives run inside the GEMM kernels.
+
+`FusedTPComm` owns one symmetric region per rank and hands the model three fused operations:
+
+  linear_all_reduce(x, w)        row-parallel GEMM + all-reduce          (one kernel, `tp_gemm_rs` mode 1)
+  linear_reduce_scatter(x, w)    row-parallel GEMM + reduce-scatter      (one kernel, mode 0)
+  all_gather_linear(w, M)        all-gather + column-parallel GEMM       (one kernel, `tp_ag_gemm`)
+
+Buffers that peers write into (staging, gathered activations, all-reduce results) are double-buffered; the
+half is chosen by a per-op launch counter kept on the host, while the flag epochs that order the data live
+in device memory so the same launches can be replayed from a CUDA graph. `begin_graph()` must open every
+captured graph: it is a cross-rank barrier, after which no peer can still be reading a half that the graph's
+first launch overwrites.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .. import _ext, ops
+from ..ops import _state
+from .dist import DistInfo
+from .symm import SymmRegion, _align
+
+
+class FusedTPComm:
+    def __init__(self, info: DistInfo, max_tokens: int, hidden: int, max_k: int | None = None, timeout_s: float = 20.0):
+        self.info = info
+        self.world_size, self.rank = info.world_size, info.rank
+        self.group = info.group
+        self.C = _ext.require()
+        tp = self.world_size
+        self.max_tokens = (max_tokens + tp - 1) // tp * tp + tp
+        self.hidden = hidden
+        max_k = max_k or hidden
+        lay = self.C.TpLayout()
+        off = 0
+
+        def take(n):
+            nonlocal off
+            o = off
+            off = _align(off + n)
+            return o
+
+        r_max = self.max_tokens // tp
+        lay.staging_half_bytes = _align(self.max_tokens * hidden * 2)
+        lay.off_staging = take(2 * lay.staging_half_bytes)
+        lay.yall_half_bytes = _align(self.max_tokens * hidden * 2)
+        lay.off_yall = take(2 * lay.yall_half_bytes)
+        lay.xall_half_bytes = _align(self.max_tokens * max_k * 2)
+        lay.off_xall = take(2 * lay.xall_half_bytes)
+        units = ((r_max + 15) // 16 + 2) * ((hidden + 63) // 64)
+        lay.rs_flags_bytes = _align(units * tp * 4)
+        lay.off_rs_flags = take(lay.rs_flags_bytes)
+        lay.ag_flags_bytes = _align(tp * (r_max // 128 + 2) * 4)
+        lay.off_ag_flags = take(lay.ag_flags_bytes)
+        lay.off_res_flags = take(64)
+        lay.off_done = take(64)
+        lay.off_barrier = take(64)
+        lay.off_epoch_rs = take(64)
+        lay.off_epoch_ag = take(64)
+        lay.off_epoch_bar = take(64)
+        lay.total_bytes = off
+        self.layout = lay
+        self.region = SymmRegion(off, info)
+        self.peers = self.region.ptrs
+        self.timeout_ns = int(timeout_s * 1e9)
+        self._rs_calls = 0
+        self._ag_calls = 0
+        self.status = _state.get(info.device).status
+
+    # -- fused ops ---------------------------------------------------------------------------------
+    def linear_all_reduce(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None, config: int = 0) -> torch.Tensor:
+        """y = all_reduce(x @ w.T) (+ residual), replicated on every rank. Returns a view into the symmetric
+        result buffer that stays valid until the second fused reduce launch after this one."""
+        M, N = x.shape[0], w.shape[0]
+        if self.world_size == 1:
+            return ops.linear(x, w, residual)
+        slot = self._rs_calls & 1
+        self._rs_calls += 1
+        self.C.tp_gemm_rs(x, w, self.rank, self.peers, self.layout, None, residual, 1, slot, self.timeout_ns, config, self.status)
+        ops._count()
+        return self.region.view(self.layout.off_yall + slot * self.layout.yall_half_bytes, (M, N), torch.bfloat16)
+
+    def linear_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None, config: int = 0) -> torch.Tensor:
+        """Rows [rank * M/tp, (rank+1) * M/tp) of reduce(x @ w.T) (+ residual rows of the same shard)."""
+        M, N = x.shape[0], w.shape[0]
+        if self.world_size == 1:
+            return ops.linear(x, w, residual)
+        assert M % self.world_size == 0, "reduce-scatter needs a token count divisible by tp"
+        out = torch.empty(M // self.world_size, N, dtype=x.dtype, device=x.device)
+        slot = self._rs_calls & 1
+        self._rs_calls += 1
+        self.C.tp_gemm_rs(x, w, self.rank, self.peers, self.layout, out, residual, 0, slot, self.timeout_ns, config, self.status)
+        ops._count()
+        return out
+
+    def gather_input(self, M: int, K: int) -> torch.Tensor:
+        """The [M/tp, K] slice of the next all-gather's buffer that this rank must fill with its rows."""
+        assert M % self.world_size == 0
+        slot = self._ag_calls & 1
+        r = M // self.world_size
+        full = self.region.view(self.layout.off_xall + slot * self.layout.xall_half_bytes, (M, K), torch.bfloat16)
+        return full[self.rank * r:(self.rank + 1) * r]
+
+    def all_gather_linear(self, w: torch.Tensor, M: int, out: torch.Tensor | None = None, n_comm: int = 0, config: int = 0) -> torch.Tensor:
+        """y = all_gather(x_r) @ w.T where x_r was written into `gather_input(M, K)`."""
+        if out is None:
+            out = torch.empty(M, w.shape[0], dtype=w.dtype, device=w.device)
+        slot = self._ag_calls & 1
+        self._ag_calls += 1
+        self.C.tp_ag_gemm(w, self.rank, self.peers, self.layout, out, M, slot, self.timeout_ns, n_comm, config, self.status)
+        ops._count()
+        return out
+
+    def all_gather_rows(self, M: int, K: int) -> torch.Tensor:
+        """Standalone all-gather of what was written into `gather_input(M, K)`; returns the full [M, K] view."""
+        slot = self._ag_calls & 1
+        self._ag_calls += 1
+        if self.world_size > 1:
+            self.C.tp_all_gather(self.rank, self.peers, self.layout, M, K, slot, self.timeout_ns, self.status)
+            ops._count()
+        return self.region.view(self.layout.off_xall + slot * self.layout.xall_half_bytes, (M, K), torch.bfloat16)
+
+    def barrier(self) -> None:
+        if self.world_size > 1:
+            self.C.symm_barrier(self.rank, self.peers, self.layout, self.timeout_ns, self.status)
+            ops._count()
+
+    def begin_graph(self) -> None:
+        """First node of every captured graph (see module docstring)."""
+        self.barrier()
+
+    # -- plain collectives used off the hot path -----------------------------------------------------
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.world_size > 1:
+            dist.all_reduce(x, group=self.group)
+        return x
+
+    def all_gather_vocab(self, logits: torch.Tensor) -> torch.Tensor:
+        if self.world_size == 1:
+            return logits
+        out = torch.empty(self.world_size, *logits.shape, dtype=logits.dtype, device=logits.device)
+        dist.all_gather_into_tensor(out, logits.contiguous(), group=self.group)
+        return out.permute(1, 0, 2).reshape(logits.shape[0], -1)

@@ -1,0 +1,31 @@
+"""Fused tensor-parallel kernels on 2+ GPUs (spawned with torch.distributed.run); skipped on one GPU."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(script, nproc, port, timeout=600, extra_env=None):
+    env = dict(os.environ)
+    env.update(extra_env or {})
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(ROOT, "tests", script)]
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_tp_kernels_two_gpus():
+    p = _run("mp_tp_fused.py", 2, 29611)
+    assert "TP_FUSED_OK 2" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_fused_tp_kernels_all_gpus():
+    n = 8 if torch.cuda.device_count() >= 8 else 4
+    p = _run("mp_tp_fused.py", n, 29612)
+    assert f"TP_FUSED_OK {n}" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
