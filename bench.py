@@ -229,10 +229,11 @@ def main() -> None:
         if debug_invalid:
             line["invalid"] = "--layers override: not the named model"
         print(json.dumps(line), flush=True)
+    sys.stdout.flush()
     if world > 1:
-        from mojo_b200.parallel.dist import shutdown
-
-        shutdown()
+        # NCCL collectives captured in CUDA graphs make process-group teardown unreliable; leave together instead
+        torch.distributed.barrier()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -1,0 +1,152 @@
+"""Standalone sweep of the fused tensor-parallel ops against the separate matmul + NCCL pattern.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        -m mojo_b200.bench_ops [--sizes 64,256,1024,4096,16384] [--cols 8192] [--inner 28672] [--out result.json]
+
+For every M:
+  gemm_rs   Y = reduce_scatter(X[M, K/tp] W[N, K/tp]^T)       fused kernel  vs  torch.matmul + reduce_scatter_tensor
+  gemm_ar   Y = all_reduce(...)                               fused kernel  vs  torch.matmul + all_reduce
+  ag_gemm   Y = all_gather(X_r[M/tp, K/tp... K_ag]) W^T        fused kernel  vs  all_gather_into_tensor + torch.matmul
+Times are CUDA-event durations on the launching stream after warm-up, max over ranks. The roofline of an op is the
+slower of its FLOPs at the measured GEMM peak and its bytes over NVLink at the measured per-direction bandwidth.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+from . import ops
+from .parallel import init_distributed
+from .parallel.fused import FusedTPComm
+
+NVLINK_GBS = 770.0   # measured peer-copy bandwidth per direction on this pool
+FALLBACK_TFLOPS = 1590.0
+
+
+def _peak_tflops() -> float:
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(p))["bf16_tflops"])
+    except Exception:  # noqa: BLE001
+        return FALLBACK_TFLOPS
+
+
+def timed(fn, iters: int, warm: int, info) -> float:
+    """Median-free simple mean over `iters` back-to-back launches, microseconds, max over ranks."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    if info.world_size > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e) * 1e3 / iters], device=info.device)
+    if info.world_size > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--sizes", default="64,256,1024,4096,16384")
+    ap.add_argument("--cols", type=int, default=8192)
+    ap.add_argument("--inner", type=int, default=28672)
+    ap.add_argument("--inner-ag", type=int, default=8192, help="K of the all-gather GEMM (activation width)")
+    ap.add_argument("--cols-ag", type=int, default=28672, help="N of the all-gather GEMM before sharding")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--out", default=None)
+    a = ap.parse_args()
+    info = init_distributed("cuda")
+    tp, rank, dev = info.world_size, info.rank, info.device
+    ms = [int(x) for x in a.sizes.split(",")]
+    k_local = a.inner // tp
+    n_ag_local = a.cols_ag // tp
+    comm = FusedTPComm(info, max_tokens=max(ms), hidden=a.cols, max_k=a.inner_ag, timeout_s=10.0)
+    peak = _peak_tflops()
+    rows = []
+    for M in ms:
+        Mp = (M + tp - 1) // tp * tp
+        x = torch.randn(Mp, k_local, device=dev).bfloat16()
+        w = (torch.randn(a.cols, k_local, device=dev) * 0.02).bfloat16()
+        y_full = torch.empty(Mp, a.cols, device=dev, dtype=torch.bfloat16)
+        y_shard = torch.empty(Mp // tp, a.cols, device=dev, dtype=torch.bfloat16)
+
+        def base_rs():
+            torch.matmul(x, w.t(), out=y_full)
+            if tp > 1:
+                dist.reduce_scatter_tensor(y_shard, y_full)
+
+        def base_ar():
+            torch.matmul(x, w.t(), out=y_full)
+            if tp > 1:
+                dist.all_reduce(y_full)
+
+        t_base_rs = timed(base_rs, a.iters, 3, info)
+        t_base_ar = timed(base_ar, a.iters, 3, info)
+        t_rs = timed(lambda: comm.linear_reduce_scatter(x, w), a.iters, 3, info)
+        t_ar = timed(lambda: comm.linear_all_reduce(x, w), a.iters, 3, info)
+        t_gemm = timed(lambda: ops.linear(x, w, out=y_full), a.iters, 3, info)
+        flops = 2.0 * Mp * a.cols * k_local
+        t_compute = flops / (peak * 1e6)
+        rs_bytes = (tp - 1) / tp * Mp * a.cols * 2
+        roof_rs = max(t_compute, rs_bytes / (NVLINK_GBS * 1e3))
+        roof_ar = max(t_compute, 2 * rs_bytes / (NVLINK_GBS * 1e3))
+        # all-gather GEMM: X_r [M/tp, k_ag] gathered, W shard [n_ag/tp, k_ag]
+        xs = torch.randn(Mp, a.inner_ag, device=dev).bfloat16()
+        wa = (torch.randn(n_ag_local, a.inner_ag, device=dev) * 0.02).bfloat16()
+        r = Mp // tp
+        x_r = xs[rank * r:(rank + 1) * r].contiguous()
+        x_all = torch.empty(Mp, a.inner_ag, device=dev, dtype=torch.bfloat16)
+        y_ag = torch.empty(Mp, n_ag_local, device=dev, dtype=torch.bfloat16)
+
+        def base_ag():
+            if tp > 1:
+                dist.all_gather_into_tensor(x_all, x_r)
+            else:
+                x_all.copy_(x_r)
+            torch.matmul(x_all, wa.t(), out=y_ag)
+
+        def fused_ag():
+            comm.gather_input(Mp, a.inner_ag).copy_(x_r)
+            comm.all_gather_linear(wa, Mp, out=y_ag)
+
+        t_base_ag = timed(base_ag, a.iters, 3, info)
+        t_ag = timed(fused_ag, a.iters, 3, info)
+        flops_ag = 2.0 * Mp * n_ag_local * a.inner_ag
+        ag_bytes = (tp - 1) / tp * Mp * a.inner_ag * 2
+        roof_ag = max(flops_ag / (peak * 1e6), ag_bytes / (NVLINK_GBS * 1e3))
+        torch.cuda.synchronize()
+        ops.check_status(dev)
+        row = {
+            "M": M, "tp": tp, "N": a.cols, "K_local": k_local,
+            "gemm_only_us": round(t_gemm, 1),
+            "gemm_rs": {"fused_us": round(t_rs, 1), "matmul_nccl_us": round(t_base_rs, 1), "roofline_us": round(roof_rs, 1),
+                        "pct_roofline": round(100 * roof_rs / t_rs, 1)},
+            "gemm_ar": {"fused_us": round(t_ar, 1), "matmul_nccl_us": round(t_base_ar, 1), "roofline_us": round(roof_ar, 1),
+                        "pct_roofline": round(100 * roof_ar / t_ar, 1)},
+            "ag_gemm": {"fused_us": round(t_ag, 1), "all_gather_matmul_us": round(t_base_ag, 1), "roofline_us": round(roof_ag, 1),
+                        "pct_roofline": round(100 * roof_ag / t_ag, 1), "N_local": n_ag_local, "K": a.inner_ag},
+        }
+        rows.append(row)
+        if rank == 0:
+            print(json.dumps(row), flush=True)
+    if rank == 0 and a.out:
+        json.dump({"peak_tflops_measured": peak, "nvlink_gbs": NVLINK_GBS, "rows": rows}, open(a.out, "w"), indent=1)
+    if tp > 1:
+        dist.barrier()
+    sys.stdout.flush()
+    os._exit(0)
+
+
+if __name__ == "__main__":
+    main()

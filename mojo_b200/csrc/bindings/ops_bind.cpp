@@ -108,6 +108,15 @@ void gather_rows(const at::Tensor& src, const at::Tensor& index, at::Tensor& out
         "gather_rows");
 }
 
+void scatter_rows(const at::Tensor& src, const at::Tensor& slots, at::Tensor& dst, c10::optional<at::Tensor> status) {
+  need(src.is_cuda() && is_bf16(src) && src.is_contiguous() && src.dim() == 2 && is_bf16(dst) && dst.is_contiguous() && dst.dim() == 2 && dst.size(1) == src.size(1), "scatter_rows: bf16 contiguous 2-D src/dst with equal width");
+  need(slots.scalar_type() == at::kLong && slots.is_contiguous() && slots.numel() == src.size(0), "scatter_rows: int64 slots [rows]");
+  c10::cuda::CUDAGuard g(src.device());
+  check(b2_scatter_rows_bf16(src.data_ptr(), slots.data_ptr<int64_t>(), dst.data_ptr(), static_cast<int>(src.size(0)),
+                             static_cast<int>(src.size(1)), dst.size(0), status_ptr(status), cur_stream()),
+        "scatter_rows");
+}
+
 void copy_pages(at::Tensor& cache, const at::Tensor& src_pages, const at::Tensor& dst_pages, c10::optional<at::Tensor> status) {
   need(cache.is_cuda() && cache.is_contiguous() && cache.dim() >= 2, "copy_pages: cache must be contiguous CUDA");
   need(src_pages.scalar_type() == at::kLong && dst_pages.scalar_type() == at::kLong && src_pages.numel() == dst_pages.numel(), "copy_pages: int64 page lists of equal length");
@@ -250,6 +259,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swiglu", &swiglu);
   m.def("embedding", &embedding, py::arg("ids"), py::arg("table"), py::arg("out"), py::arg("vocab_start") = 0);
   m.def("gather_rows", &gather_rows, py::arg("src"), py::arg("index"), py::arg("out"), py::arg("status") = py::none());
+  m.def("scatter_rows", &scatter_rows, py::arg("src"), py::arg("slots"), py::arg("dst"), py::arg("status") = py::none());
   m.def("copy_pages", &copy_pages, py::arg("cache"), py::arg("src_pages"), py::arg("dst_pages"), py::arg("status") = py::none());
   m.def("argmax", &argmax, py::arg("logits"), py::arg("ids"), py::arg("max_out") = py::none());
   m.def("sample", &sample, py::arg("logits"), py::arg("ids"), py::arg("temperature") = py::none(), py::arg("top_k") = py::none(),

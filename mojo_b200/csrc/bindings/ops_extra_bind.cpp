@@ -95,6 +95,46 @@ void bind_ops_extra(py::module_& m) {
           check(b2_symm_barrier(&reg, &lay, timeout_ns, status_ptr(status), cur_stream()), "symm_barrier");
         });
 
+  m.def("gemm_fp8",
+        [](const at::Tensor& xq, const at::Tensor& xs, const at::Tensor& wq, const at::Tensor& ws, at::Tensor& y, int config,
+           c10::optional<at::Tensor> status) {
+          need(xq.is_cuda() && xq.element_size() == 1 && wq.element_size() == 1 && xq.dim() == 2 && wq.dim() == 2 && xq.is_contiguous() && wq.is_contiguous(),
+               "gemm_fp8: xq [M, K], wq [N, K] contiguous 8-bit");
+          const int M = static_cast<int>(xq.size(0)), K = static_cast<int>(xq.size(1)), N = static_cast<int>(wq.size(0));
+          need(wq.size(1) == K && K % 128 == 0, "gemm_fp8: K must match and be a multiple of 128");
+          need(xs.scalar_type() == at::kFloat && xs.is_contiguous() && xs.numel() == static_cast<int64_t>(M) * (K / 128), "gemm_fp8: xs f32 [M, K/128]");
+          need(ws.scalar_type() == at::kFloat && ws.is_contiguous() && ws.numel() == static_cast<int64_t>((N + 127) / 128) * (K / 128), "gemm_fp8: ws f32 [ceil(N/128), K/128]");
+          need(is_bf16_2d(y) && y.size(0) == M && y.size(1) == N, "gemm_fp8: y bf16 [M, N]");
+          c10::cuda::CUDAGuard g(xq.device());
+          check(b2_gemm_fp8_block(xq.data_ptr(), xs.data_ptr<float>(), wq.data_ptr(), ws.data_ptr<float>(), y.data_ptr(), M, N, K,
+                                  y.stride(0), config, status_ptr(status), cur_stream()),
+                "gemm_fp8");
+        },
+        py::arg("xq"), py::arg("xs"), py::arg("wq"), py::arg("ws"), py::arg("y"), py::arg("config") = 0, py::arg("status") = py::none());
+
+  m.def("mla_decode",
+        [](const at::Tensor& q_lat, const at::Tensor& q_rope, const at::Tensor& kv_cache, at::Tensor& out_lat, const at::Tensor& ctx_lens,
+           const at::Tensor& block_tables, c10::optional<at::Tensor> workspace, int num_splits, double scale,
+           c10::optional<at::Tensor> status) {
+          need(q_lat.is_cuda() && q_lat.scalar_type() == at::kBFloat16 && q_lat.is_contiguous() && q_lat.dim() == 3 && q_lat.size(2) == 512, "mla_decode: q_lat bf16 [B, H, 512]");
+          need(q_rope.is_contiguous() && q_rope.scalar_type() == at::kBFloat16 && q_rope.dim() == 3 && q_rope.size(2) == 64 && q_rope.size(1) == q_lat.size(1), "mla_decode: q_rope bf16 [B, H, 64]");
+          need(kv_cache.is_contiguous() && kv_cache.scalar_type() == at::kBFloat16 && kv_cache.dim() == 3 && kv_cache.size(2) == 576, "mla_decode: cache bf16 [pages, page, 576]");
+          need(out_lat.is_contiguous() && out_lat.sizes() == q_lat.sizes() && out_lat.scalar_type() == at::kBFloat16, "mla_decode: out bf16 [B, H, 512]");
+          need(ctx_lens.scalar_type() == at::kInt && block_tables.scalar_type() == at::kInt && block_tables.dim() == 2 && block_tables.is_contiguous(), "mla_decode: int32 metadata");
+          const int B = static_cast<int>(q_lat.size(0)), H = static_cast<int>(q_lat.size(1));
+          float* ws = nullptr;
+          if (num_splits > 1) {
+            need(workspace.has_value() && workspace->numel() * 4 >= b2_mla_decode_workspace(B, H, num_splits), "mla_decode: workspace too small");
+            ws = workspace->data_ptr<float>();
+          }
+          c10::cuda::CUDAGuard g(q_lat.device());
+          check(b2_mla_decode_bf16(q_lat.data_ptr(), q_rope.data_ptr(), kv_cache.data_ptr(), out_lat.data_ptr(), ctx_lens.data_ptr<int32_t>(),
+                                   block_tables.data_ptr<int32_t>(), ws, B, static_cast<int>(block_tables.size(1)), H,
+                                   static_cast<int>(kv_cache.size(1)), num_splits, static_cast<float>(scale), kv_cache.size(0),
+                                   status_ptr(status), cur_stream()),
+                "mla_decode");
+        });
+
   m.def("wait_flag", [](const at::Tensor& flag, uint32_t want, uint64_t timeout_ns, c10::optional<at::Tensor> status) {
     need(flag.is_cuda() && flag.element_size() == 4, "wait_flag: 32-bit CUDA flag tensor");
     c10::cuda::CUDAGuard g(flag.device());

@@ -38,6 +38,9 @@ int b2_embedding_bf16(const int64_t* ids, const void* table, void* out, int toke
 // out[i, :] = src[index[i], :] (row gather, 16-byte vectorised; used for last-token selection).
 int b2_gather_rows_bf16(const void* src, const int64_t* index, void* out, int rows_out, int cols, int64_t rows_src,
                         b2::Status* status, cudaStream_t stream);
+// dst[slots[i], :] = src[i, :] for slots[i] >= 0 (negative slots are padding and skipped).
+int b2_scatter_rows_bf16(const void* src, const int64_t* slots, void* dst, int rows, int cols, int64_t rows_dst,
+                         b2::Status* status, cudaStream_t stream);
 // Copy whole KV pages inside a cache tensor: dst_page[i] <- src_page[i] (preemption swap / prefix share).
 int b2_copy_pages(void* cache, const int64_t* src_pages, const int64_t* dst_pages, int n, int64_t page_bytes,
                   int64_t num_pages, b2::Status* status, cudaStream_t stream);

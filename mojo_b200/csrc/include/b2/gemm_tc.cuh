@@ -210,8 +210,11 @@ __device__ __forceinline__ void run(const CUtensorMap* tmap_p, const CUtensorMap
     bool ok = true;
     for (int w = cta; ok && w < total; w += num_ctas) {
       const WorkUnit u = sched.get(w);
-      if (!ptx::mbar_wait(tmem_full_bar(acc), acc_phase)) {
-        if (lane == 0) status_record(status, kTimeout, kSiteGemmTmemFull, w, acc);
+      // The four epilogue warps must take the same decision: epilogues synchronise among themselves with
+      // barriers that have no deadline, so a lone warp giving up would strand the other three.
+      const bool arrived = ptx::mbar_wait(tmem_full_bar(acc), acc_phase);
+      if (!ptx::named_barrier_and(3, kEpiThreads, arrived)) {
+        if (!arrived && lane == 0) status_record(status, kTimeout, kSiteGemmTmemFull, w, acc);
         ok = false;
         break;
       }

@@ -491,7 +491,7 @@ __global__ void __launch_bounds__(32) attn_decode_tma_kernel(
     const int s = i % STAGES;
     // the stage being refilled was consumed in iteration i - 1 (program order within the warp)
     if (lane == 0 && i + STAGES - 1 < n_tiles) issue(i + STAGES - 1);
-    if (!ptx::mbar_wait(bar0 + 8 * s, (i / STAGES) & 1)) {
+    if (!__all_sync(0xffffffffu, ptx::mbar_wait(bar0 + 8 * s, (i / STAGES) & 1))) {
       if (lane == 0) status_record(status, kTimeout, kSiteAttn, seq, i);
       ok = false;
       break;

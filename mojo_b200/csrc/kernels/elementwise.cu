@@ -249,6 +249,15 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ src, const int64_t*
     out[static_cast<size_t>(r) * col_vecs + c] = src[s * col_vecs + c];
 }
 
+__global__ void scatter_rows_kernel(const uint4* __restrict__ src, const int64_t* __restrict__ slots, uint4* __restrict__ dst,
+                                    int col_vecs, int64_t rows_dst, Status* status) {
+  const int r = blockIdx.x;
+  const int64_t d = slots[r];
+  if (d < 0) return;  // padding row
+  if (!B2_ASSERT(status, d < rows_dst, kSiteKvIndex, d, rows_dst)) return;
+  for (int c = threadIdx.x; c < col_vecs; c += blockDim.x) dst[d * col_vecs + c] = src[static_cast<size_t>(r) * col_vecs + c];
+}
+
 __global__ void copy_pages_kernel(uint4* __restrict__ cache, const int64_t* __restrict__ src_pages,
                                   const int64_t* __restrict__ dst_pages, int64_t page_vecs, int64_t num_pages,
                                   Status* status) {
@@ -365,5 +374,14 @@ extern "C" int b2_copy_pages(void* cache, const int64_t* src_pages, const int64_
   if (bx > 64) bx = 64;
   copy_pages_kernel<<<dim3(bx, n), threads, 0, stream>>>(static_cast<uint4*>(cache), src_pages, dst_pages, vecs,
                                                          num_pages, status);
+  return 0;
+}
+
+extern "C" int b2_scatter_rows_bf16(const void* src, const int64_t* slots, void* dst, int rows, int cols, int64_t rows_dst,
+                                    Status* status, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (cols % 8 != 0) return -kBadArgument;
+  scatter_rows_kernel<<<rows, 128, 0, stream>>>(static_cast<const uint4*>(src), slots, static_cast<uint4*>(dst), cols / 8,
+                                                rows_dst, status);
   return 0;
 }

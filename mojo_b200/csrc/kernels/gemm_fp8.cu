@@ -1,0 +1,313 @@
+// Block-scaled fp8 GEMM on tcgen05 (kind::f8f6f4):
+//   Y[M, N] = sum over 128-wide K blocks kb of  sx[m, kb] * sw[n / 128, kb] * (Xq[m, kb-block] . Wq[n, kb-block])
+// Xq: e4m3 [M, K] with one f32 scale per row per 128 columns (dynamic activation quantisation);
+// Wq: e4m3 [N, K] with one f32 scale per 128 x 128 block (checkpoint format). bf16 out.
+//
+// A 128-byte shared-memory row holds exactly one scale block of K, so every pipeline stage is one scale block:
+// the MMA warp issues its four K=32 instructions into a fresh TMEM slab (no accumulation across stages) and
+// commits; the four promotion warps pull the slab out of TMEM, multiply by the two scales and accumulate in f32
+// registers - the fp8 types accumulate in f32 (stdlib/src/utils/numerics.mojo:1031-1054). Slabs are
+// multi-buffered so the promotion of block kb overlaps the MMA of block kb + 1. The reference rejects fp8 on this
+// architecture outright (stdlib/src/builtin/simd.mojo:186-189), so there is no reference kernel to compare to.
+//
+// Operand assignment as in the bf16 GEMM: normal (tokens on the UMMA M side) or swapped (weight rows on the M
+// side, tokens as UMMA N) for decode-sized M.
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include "b2/api.h"
+#include "b2/gemm_tc.cuh"
+#include "b2/ptx.cuh"
+#include "b2/tma.h"
+
+namespace b2 {
+namespace {
+
+constexpr int kThreads = 192;
+
+struct Fp8Params {
+  __nv_bfloat16* y;
+  int64_t ldy;
+  const float* sx;  // [M, KB]
+  const float* sw;  // [ceil(N / 128), KB]
+  int M, N, KB;
+  int p_blocks, q_blocks;
+};
+
+template <int BN, int STAGES, int SLABS, bool SWAP>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q, Fp8Params prm,
+                Status* status) {
+  constexpr int kPBytes = 128 * 128, kQBytes = BN * 128, kStageBytes = kPBytes + kQBytes;
+  constexpr int kTmemCols = (SLABS * BN <= 32) ? 32 : (SLABS * BN <= 64) ? 64 : (SLABS * BN <= 128) ? 128 : (SLABS * BN <= 256) ? 256 : 512;
+  constexpr int CH = BN >= 32 ? 32 : 16;
+  constexpr uint32_t idesc = ptx::make_idesc(0, 0, 128, BN);  // e4m3 x e4m3 -> f32
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + STAGES * kStageBytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto slab_full = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+  auto slab_empty = [&](int s) { return bar_base + 8u * (2 * STAGES + SLABS + s); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 2 * SLABS);
+  const uint32_t holder = bar_base + 8u * (2 * STAGES + 2 * SLABS + 1);
+  uint32_t* holder_ptr = reinterpret_cast<uint32_t*>(smem_raw + (holder - ptx::smem_u32(smem_raw)));
+  float* col_scale = reinterpret_cast<float*>(smem_raw + (holder + 16 - ptx::smem_u32(smem_raw)));  // [4 warps][BN], swapped layout
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    ptx::prefetch_tensormap(&tmap_p);
+    ptx::prefetch_tensormap(&tmap_q);
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < SLABS; ++s) {
+      ptx::mbar_init(slab_full(s), 1);
+      ptx::mbar_init(slab_empty(s), 4);
+    }
+    ptx::mbar_init(drain_bar, 1);
+    ptx::fence_mbar_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(holder, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *holder_ptr;
+  const int total = prm.p_blocks * prm.q_blocks;
+  const int KB = prm.KB;
+
+  if (warp == 0) {
+    if (ptx::elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      long issued = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total; w += gridDim.x) {
+        const int pb = w / prm.q_blocks, qb = w % prm.q_blocks;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u)) {
+            status_record(status, kTimeout, kSiteGemmEmpty, w, kb);
+            ok = false;
+            break;
+          }
+          const uint32_t sp = smem_base + stage * kStageBytes;
+          ptx::mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
+          ptx::tma_load_2d(sp, &tmap_p, full_bar(stage), kb * 128, pb * 128, SWAP ? ptx::kEvictFirst : ptx::kEvictNormal);
+          ptx::tma_load_2d(sp + kPBytes, &tmap_q, full_bar(stage), kb * 128, qb * BN, SWAP ? ptx::kEvictLast : ptx::kEvictNormal);
+          ++issued;
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        long pending = issued < STAGES ? issued : STAGES;
+        int s = stage;
+        uint32_t ph = phase;
+        for (long i = 0; i < pending; ++i) {
+          if (--s < 0) { s = STAGES - 1; ph ^= 1u; }
+          if (!ptx::mbar_wait(full_bar(s), ph, 200000000ull)) break;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (ptx::elect_one()) {
+      int stage = 0, slab = 0;
+      uint32_t phase = 0, slab_phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total; w += gridDim.x) {
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!ptx::mbar_wait(slab_empty(slab), slab_phase ^ 1u)) {
+            status_record(status, kTimeout, kSiteGemmTmemEmpty, w, kb);
+            ok = false;
+            break;
+          }
+          if (!ptx::mbar_wait(full_bar(stage), phase)) {
+            status_record(status, kTimeout, kSiteGemmFull, w, kb);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sp = smem_base + stage * kStageBytes;
+          const uint64_t da = ptx::make_smem_desc_sw128(sp);
+          const uint64_t db = ptx::make_smem_desc_sw128(sp + kPBytes);
+          const uint32_t d_tmem = tmem_base + slab * BN;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) ptx::tc_mma_f8(d_tmem, da + 2u * k, db + 2u * k, idesc, k > 0 ? 1u : 0u);
+          ptx::tc_commit(empty_bar(stage));
+          ptx::tc_commit(slab_full(slab));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (++slab == SLABS) { slab = 0; slab_phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        ptx::tc_commit(drain_bar);
+        ptx::mbar_wait(drain_bar, 0, 200000000ull);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---- promotion + epilogue warps ----
+    const int quarter = warp & 3;
+    const int p_local = quarter * 32 + lane;
+    int slab = 0;
+    uint32_t slab_phase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; ok && w < total; w += gridDim.x) {
+      const int pb = w / prm.q_blocks, qb = w % prm.q_blocks;
+      float acc[BN];
+#pragma unroll
+      for (int j = 0; j < BN; ++j) acc[j] = 0.0f;
+      const int row = pb * 128 + p_local;  // m (normal) or n (swapped)
+      for (int kb = 0; kb < KB; ++kb) {
+        // scale(s) for this k-block
+        float s_row = 0.0f, s_blk0 = 0.0f, s_blk1 = 0.0f;
+        if constexpr (!SWAP) {
+          s_row = row < prm.M ? prm.sx[static_cast<int64_t>(row) * KB + kb] : 0.0f;
+          const int nb = (qb * BN) >> 7;
+          s_blk0 = prm.sw[static_cast<int64_t>(nb) * KB + kb];
+          if (BN > 128) s_blk1 = ((qb * BN + 128) < prm.N) ? prm.sw[static_cast<int64_t>(nb + 1) * KB + kb] : 0.0f;
+        } else {
+          s_row = prm.sw[static_cast<int64_t>(pb) * KB + kb];  // 128 weight rows = one scale block
+          // each warp stages the token scales it needs itself: no barrier that a failed warp could strand
+          float* cs = col_scale + quarter * BN;
+          __syncwarp();
+          for (int j = lane; j < BN; j += 32) {
+            const int m = qb * BN + j;
+            cs[j] = m < prm.M ? prm.sx[static_cast<int64_t>(m) * KB + kb] : 0.0f;
+          }
+          __syncwarp();
+        }
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(slab_full(slab), slab_phase))) {
+          if (lane == 0) status_record(status, kTimeout, kSiteGemmTmemFull, w, kb);
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t taddr = tmem_base + slab * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll
+        for (int c = 0; c < BN / CH; ++c) {
+          uint32_t r[CH];
+          if constexpr (CH == 32) ptx::tmem_ld_32x32(taddr + c * CH, r);
+          else ptx::tmem_ld_32x16(taddr + c * CH, r);
+          ptx::tc_wait_ld();
+          if constexpr (!SWAP) {
+            const float s = s_row * ((c * CH) < 128 ? s_blk0 : s_blk1);
+#pragma unroll
+            for (int j = 0; j < CH; ++j) acc[c * CH + j] = fmaf(__uint_as_float(r[j]), s, acc[c * CH + j]);
+          } else {
+            const float* cs = col_scale + quarter * BN + c * CH;
+#pragma unroll
+            for (int j = 0; j < CH; ++j) acc[c * CH + j] = fmaf(__uint_as_float(r[j]), s_row * cs[j], acc[c * CH + j]);
+          }
+        }
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(slab_empty(slab));
+        if (++slab == SLABS) { slab = 0; slab_phase ^= 1u; }
+      }
+      if (!ok) break;
+      // ---- store ----
+      if constexpr (!SWAP) {
+        if (row < prm.M) {
+          __nv_bfloat16* dst = prm.y + static_cast<int64_t>(row) * prm.ldy + qb * BN;
+#pragma unroll
+          for (int g = 0; g < BN / 8; ++g) {
+            if (qb * BN + g * 8 >= prm.N) break;
+            uint4 pk;
+            pk.x = ptx::pack_bf16x2(acc[g * 8 + 0], acc[g * 8 + 1]);
+            pk.y = ptx::pack_bf16x2(acc[g * 8 + 2], acc[g * 8 + 3]);
+            pk.z = ptx::pack_bf16x2(acc[g * 8 + 4], acc[g * 8 + 5]);
+            pk.w = ptx::pack_bf16x2(acc[g * 8 + 6], acc[g * 8 + 7]);
+            ptx::st_v4(dst + g * 8, pk);
+          }
+        }
+      } else {
+        if (row < prm.N) {
+#pragma unroll
+          for (int j = 0; j < BN; ++j) {
+            const int m = qb * BN + j;
+            if (m >= prm.M) break;
+            prm.y[static_cast<int64_t>(m) * prm.ldy + row] = __float2bfloat16(acc[j]);
+          }
+        }
+      }
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int BN, bool SWAP>
+int launch_fp8(const void* xq, const float* xs, const void* wq, const float* ws, void* y, int M, int N, int K, int64_t ldy,
+               Status* status, cudaStream_t stream) {
+  constexpr int kStageBytes = 128 * 128 + BN * 128;
+  constexpr int STAGES = (190 * 1024 / kStageBytes) > 8 ? 8 : (190 * 1024 / kStageBytes);
+  constexpr int SLABS = BN <= 128 ? 4 : 2;
+  constexpr int SMEM = STAGES * kStageBytes + (2 * STAGES + 2 * SLABS + 1) * 8 + 16 + 4 * BN * 4 + 1024 + 64;
+  const void* p_ptr = SWAP ? wq : xq;
+  const void* q_ptr = SWAP ? xq : wq;
+  const int rows_p = SWAP ? N : M, rows_q = SWAP ? M : N;
+  CUtensorMap tp, tq;
+  if (!make_tmap_2d(&tp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p_ptr, rows_p, K, K, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !make_tmap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q_ptr, rows_q, K, K, BN, 128, CU_TENSOR_MAP_SWIZZLE_128B))
+    return -kBadArgument;
+  Fp8Params prm{};
+  prm.y = static_cast<__nv_bfloat16*>(y);
+  prm.ldy = ldy;
+  prm.sx = xs;
+  prm.sw = ws;
+  prm.M = M;
+  prm.N = N;
+  prm.KB = K / 128;
+  prm.p_blocks = (rows_p + 127) / 128;
+  prm.q_blocks = (rows_q + BN - 1) / BN;
+  auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
+    attr_set = true;
+  }
+  const int total = prm.p_blocks * prm.q_blocks;
+  kern<<<total < kNumSMs ? total : kNumSMs, kThreads, SMEM, stream>>>(tp, tq, prm, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+}
+
+}  // namespace
+}  // namespace b2
+
+using namespace b2;
+
+extern "C" int b2_gemm_fp8_block(const void* xq, const float* xs, const void* wq, const float* ws, void* y, int M, int N,
+                                 int K, int64_t ldy, int config, Status* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 128 != 0 || N % 8 != 0) return -kBadArgument;
+  bool swap = M <= 64;
+  int bn = swap ? (M <= 16 ? 16 : M <= 32 ? 32 : 64) : 128;
+  if (config != 0) {
+    swap = (config >> 30) & 1;
+    bn = config & 0xffff;
+  }
+  if (!swap && ldy % 8 != 0) return -kBadArgument;
+  if (swap) {
+    switch (bn) {
+      case 16: return launch_fp8<16, true>(xq, xs, wq, ws, y, M, N, K, ldy, status, stream);
+      case 32: return launch_fp8<32, true>(xq, xs, wq, ws, y, M, N, K, ldy, status, stream);
+      case 64: return launch_fp8<64, true>(xq, xs, wq, ws, y, M, N, K, ldy, status, stream);
+      case 128: return launch_fp8<128, true>(xq, xs, wq, ws, y, M, N, K, ldy, status, stream);
+      default: return -kBadArgument;
+    }
+  }
+  switch (bn) {
+    case 64: return launch_fp8<64, false>(xq, xs, wq, ws, y, M, N, K, ldy, status, stream);
+    case 128: return launch_fp8<128, false>(xq, xs, wq, ws, y, M, N, K, ldy, status, stream);
+    default: return -kBadArgument;
+  }
+}

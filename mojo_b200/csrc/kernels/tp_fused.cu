@@ -82,54 +82,87 @@ __device__ __forceinline__ int unit_index(const RsParams& p, int owner, int pb, 
   return (qb - (owner * p.R) / BN) * p.p_blocks + pb;
 }
 
+// Bytes of shared memory the reduce-scatter epilogue needs behind the GEMM core's own layout.
+constexpr int kRsRowPad = 16;
+template <int BN, bool SWAP>
+constexpr int rs_epi_bytes() {
+  // normal: two buffers of [128 rows][64 cols] bf16; swapped: two buffers of [32 tokens][128 cols] bf16
+  return SWAP ? 2 * 32 * (256 + kRsRowPad) : 2 * 128 * (128 + kRsRowPad);
+}
+
+// Epilogue of the reduce-scatter GEMM. NVLink moves small scattered writes badly, so the accumulator is first
+// transposed through shared memory and then leaves the SM as 128-byte (normal) or 256-byte (swapped) row
+// segments of consecutive 16-byte stores, straight into the owner rank's staging buffer.
 template <int BN, bool SWAP>
 struct RsEpilogue {
   static constexpr int CH = BN >= 32 ? 32 : 16;
   RsParams p;
+  uint8_t* epi_smem;
+
+  __device__ __forceinline__ __nv_bfloat16* staging_row(int m) const {
+    const int owner = m / p.R;
+    return reinterpret_cast<__nv_bfloat16*>(p.peer[owner] + p.off_staging) +
+           (static_cast<int64_t>(p.rank) * p.R + (m - owner * p.R)) * p.N;
+  }
 
   __device__ __forceinline__ void operator()(const WorkUnit& u, uint32_t taddr, int quarter, int lane, uint32_t* flag,
                                              Status* status) const {
     (void)flag; (void)status;
     const int p_local = quarter * 32 + lane;
+    const int t = static_cast<int>(threadIdx.x) - 64;  // 0..127 among the epilogue threads
+    if constexpr (!SWAP) {
+      constexpr int ROW = 128 + kRsRowPad;               // bytes per staged row (64 bf16 + pad)
+      static_assert(BN % 64 == 0, "normal layout stages 64 columns at a time");
 #pragma unroll 1
-    for (int c = 0; c < BN / CH; ++c) {
-      uint32_t r[CH];
-      if constexpr (CH == 32) ptx::tmem_ld_32x32(taddr + c * CH, r);
-      else ptx::tmem_ld_32x16(taddr + c * CH, r);
-      ptx::tc_wait_ld();
-      if constexpr (!SWAP) {
-        const int m = u.pb * 128 + p_local;
-        const int n0 = u.qb * BN + c * CH;
-        if (m < p.M) {
-          const int owner = m / p.R;
-          const int row_local = m - owner * p.R;
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.peer[owner] + p.off_staging) +
-                               (static_cast<int64_t>(p.rank) * p.R + row_local) * p.N + n0;
+      for (int cg = 0; cg < BN / 64; ++cg) {
+        uint8_t* buf = epi_smem + (cg & 1) * 128 * ROW;
 #pragma unroll
-          for (int g = 0; g < CH / 8; ++g) {
-            if (n0 + g * 8 >= p.N) break;
+        for (int c2 = 0; c2 < 2; ++c2) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(taddr + cg * 64 + c2 * 32, r);
+          ptx::tc_wait_ld();
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
             uint4 pk;
             pk.x = ptx::pack_bf16x2(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
             pk.y = ptx::pack_bf16x2(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
             pk.z = ptx::pack_bf16x2(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
             pk.w = ptx::pack_bf16x2(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
-            ptx::st_v4(dst + g * 8, pk);
+            *reinterpret_cast<uint4*>(buf + p_local * ROW + c2 * 64 + g * 16) = pk;
           }
         }
-      } else {
-        const int n = u.pb * 128 + p_local;
-        const int m0 = u.qb * BN + c * CH;
-        if (n < p.N) {
+        ptx::named_barrier_sync(1, gemm::kEpiThreads);
+        const int n0 = u.qb * BN + cg * 64;
 #pragma unroll
-          for (int j = 0; j < CH; ++j) {
-            const int m = m0 + j;
-            if (m >= p.M) break;
-            const int owner = m / p.R;
-            const int row_local = m - owner * p.R;
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.peer[owner] + p.off_staging) +
-                                 (static_cast<int64_t>(p.rank) * p.R + row_local) * p.N + n;
-            *dst = __float2bfloat16(__uint_as_float(r[j]));
-          }
+        for (int i = 0; i < 8; ++i) {
+          const int v = t + 128 * i;
+          const int row = v >> 3, cv = v & 7;
+          const int m = u.pb * 128 + row;
+          if (m < p.M && n0 + cv * 8 < p.N)
+            ptx::st_v4(staging_row(m) + n0 + cv * 8, *reinterpret_cast<const uint4*>(buf + row * ROW + cv * 16));
+        }
+      }
+    } else {
+      constexpr int ROW = 256 + kRsRowPad;               // bytes per staged token row (128 bf16 + pad)
+#pragma unroll 1
+      for (int c = 0; c < BN / CH; ++c) {
+        uint8_t* buf = epi_smem + (c & 1) * 32 * ROW;
+        uint32_t r[CH];
+        if constexpr (CH == 32) ptx::tmem_ld_32x32(taddr + c * CH, r);
+        else ptx::tmem_ld_32x16(taddr + c * CH, r);
+        ptx::tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < CH; ++j)
+          *reinterpret_cast<__nv_bfloat16*>(buf + j * ROW + p_local * 2) = __float2bfloat16(__uint_as_float(r[j]));
+        ptx::named_barrier_sync(1, gemm::kEpiThreads);
+        const int m0 = u.qb * BN + c * CH;
+#pragma unroll
+        for (int i = 0; i < CH / 8; ++i) {
+          const int v = t + 128 * i;
+          const int j = v >> 4, cv = v & 15;
+          const int m = m0 + j, n = u.pb * 128 + cv * 8;
+          if (m < p.M && n < p.N)
+            ptx::st_v4(staging_row(m) + n, *reinterpret_cast<const uint4*>(buf + j * ROW + cv * 16));
         }
       }
     }
@@ -139,7 +172,6 @@ struct RsEpilogue {
     const int m_lo = SWAP ? u.qb * BN : u.pb * 128;
     const int m_hi = min(p.M, m_lo + (SWAP ? BN : 128)) - 1;
     const int o_lo = m_lo / p.R, o_hi = m_hi / p.R;
-    const int t = static_cast<int>(threadIdx.x) - 64;
     if (t <= o_hi - o_lo) {
       const int owner = o_lo + t;
       const int unit = unit_index<SWAP, BN>(p, owner, u.pb, u.qb);
@@ -280,7 +312,10 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant
   constexpr uint32_t idesc = ptx::make_idesc(1, 1, 128, BN);
   RsParams prm = prm_in;
   prm.epoch = epoch_begin(ectl);
-  RsEpilogue<BN, SWAP> epi{prm};
+  extern __shared__ uint8_t smem_dyn[];
+  uint8_t* epi_buf = smem_dyn + gemm::SmemLayout<BN, STAGES>::kTotalBytes;
+  epi_buf += (16 - (reinterpret_cast<uintptr_t>(epi_buf) & 15)) & 15;  // 16-byte vector accesses
+  RsEpilogue<BN, SWAP> epi{prm, epi_buf};
   gemm::run<BN, STAGES, 2>(&tmap_p, &tmap_q, idesc, ptx::kEvictNormal, ptx::kEvictNormal, sched, gemm::NoGate{}, epi, status,
                            static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
   reduce_phase<BN, SWAP>(prm, status, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
@@ -292,11 +327,18 @@ constexpr int stages_for(int bn) {
   int s = (200 * 1024) / stage;
   return s > 10 ? 10 : s;
 }
+// the reduce-scatter kernel gives part of its shared memory to the staged epilogue
+constexpr int rs_stages_for(int bn) {
+  const int stage = 128 * 64 * 2 + bn * 64 * 2;
+  int s = (176 * 1024) / stage;
+  return s > 10 ? 10 : s;
+}
 
 template <int BN, bool SWAP>
 int launch_rs(const void* x, const void* w, int M, int N, int K, int64_t ldx, int64_t ldw, RsParams prm, EpochCtl ectl,
               Status* status, cudaStream_t stream) {
-  constexpr int STAGES = stages_for(BN);
+  constexpr int STAGES = rs_stages_for(BN);
+  constexpr int SMEM = gemm::SmemLayout<BN, STAGES>::kTotalBytes + rs_epi_bytes<BN, SWAP>() + 16;
   using L = gemm::SmemLayout<BN, STAGES>;
   const void* p_ptr = SWAP ? w : x;
   const void* q_ptr = SWAP ? x : w;
@@ -321,11 +363,11 @@ int launch_rs(const void* x, const void* w, int M, int N, int K, int64_t ldx, in
   auto kern = gemm_rs_kernel<BN, STAGES, SWAP>;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes) != cudaSuccess) return -kBadArgument;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
     attr_set = true;
   }
   // Always a full persistent grid: CTAs without GEMM tiles still take part in the reduce phase.
-  kern<<<kNumSMs, gemm::kThreads, L::kTotalBytes, stream>>>(tp, tq, sched, prm, ectl, status);
+  kern<<<kNumSMs, gemm::kThreads, SMEM, stream>>>(tp, tq, sched, prm, ectl, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
 }
 

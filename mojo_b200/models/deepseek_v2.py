@@ -1,0 +1,201 @@
+"""DeepSeek-V2(-Lite) decoder: multi-head latent attention (MLA) + mixture of experts with shared experts.
+
+Cache: one row per token per layer, [c_kv (kv_lora_rank) | k_rope (qk_rope_head_dim)], shared by all heads.
+Decode uses the absorbed form (W_UK folded into the query, W_UV applied to the latent-space output) and the MLA
+decode kernel; prefill expands the latents of the sequence into per-head K/V and runs the causal prefill kernel
+with a 192-wide key (128 nope + 64 rope) and V zero-padded to the same width.
+
+MoE: softmax router over all routed experts, top-k, optional renormalisation; routed experts run through the
+expert-parallel path (`parallel.ep`: dispatch, grouped GEMM, combine) and the shared experts as one fused MLP.
+Under expert parallelism attention is data-parallel: every rank runs all heads on its own requests.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from .. import ops
+from ..ops import reference
+from .config import ModelConfig
+
+
+@dataclass
+class DsLayer:
+    attn_norm: torch.Tensor
+    wq: torch.Tensor          # [H * (nope + rope), hidden]
+    w_kv_a: torch.Tensor      # [kv_lora + rope, hidden]
+    kv_a_norm: torch.Tensor   # [kv_lora]
+    w_uk: torch.Tensor        # [H, nope, kv_lora]
+    w_uv: torch.Tensor        # [H, v_dim, kv_lora]
+    wo: torch.Tensor          # [hidden, H * v_dim]
+    mlp_norm: torch.Tensor
+    # dense FFN layers
+    w_gu: torch.Tensor | None = None      # [2F, hidden] interleaved gate/up
+    w_down: torch.Tensor | None = None
+    # MoE layers
+    w_router: torch.Tensor | None = None  # [E, hidden]
+    w_shared_gu: torch.Tensor | None = None
+    w_shared_down: torch.Tensor | None = None
+    w_exp_gu: torch.Tensor | None = None  # [E_local, 2F_moe, hidden] (gate rows then up rows per expert)
+    w_exp_down: torch.Tensor | None = None  # [E_local, hidden, F_moe]
+
+
+class DeepseekV2Model:
+    def __init__(self, cfg: ModelConfig, device="cpu", dtype=torch.float32, comm=None, ep=None):
+        self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
+        self.comm = comm
+        self.ep = ep                      # expert-parallel communicator (None: all experts local)
+        self.ep_size = ep.world_size if ep is not None else 1
+        self.ep_rank = ep.rank if ep is not None else 0
+        assert cfg.n_routed_experts % self.ep_size == 0
+        self.e_local = cfg.n_routed_experts // self.ep_size
+        self.H = cfg.num_heads
+        self.nope, self.rope, self.vdim, self.lora = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
+        self.scale = 1.0 / math.sqrt(self.nope + self.rope)
+        self.layers: list[DsLayer] = []
+        self.embed = self.final_norm = self.lm_head = None
+        self.cos_sin = reference.rope_table(cfg.max_position_embeddings, self.rope, cfg.rope_theta, None).to(self.device)
+
+    # ------------------------------------------------------------------------------------------------
+    def _put(self, t):
+        return t.to(device=self.device, dtype=self.dtype).contiguous()
+
+    def init_random(self, seed: int = 0, std: float = 0.02) -> "DeepseekV2Model":
+        cfg = self.cfg
+        gen_dev = self.device if self.device.type == "cuda" else torch.device("cpu")
+        g = torch.Generator(device=gen_dev).manual_seed(seed)
+
+        def rnd(*shape):
+            return torch.randn(*shape, generator=g, device=gen_dev, dtype=torch.float32) * std
+
+        h = cfg.hidden_size
+        self.embed = self._put(rnd(cfg.vocab_size, h))
+        for i in range(cfg.num_layers):
+            lw = DsLayer(
+                attn_norm=self._put(torch.ones(h)), wq=self._put(rnd(self.H * (self.nope + self.rope), h)),
+                w_kv_a=self._put(rnd(self.lora + self.rope, h)), kv_a_norm=self._put(torch.ones(self.lora)),
+                w_uk=self._put(rnd(self.H, self.nope, self.lora)), w_uv=self._put(rnd(self.H, self.vdim, self.lora)),
+                wo=self._put(rnd(h, self.H * self.vdim)), mlp_norm=self._put(torch.ones(h)))
+            if i < cfg.first_k_dense_replace:
+                f = cfg.intermediate_size
+                lw.w_gu = self._put(reference.interleave_gate_up(rnd(f, h), rnd(f, h)))
+                lw.w_down = self._put(rnd(h, f))
+            else:
+                fm, fs = cfg.moe_intermediate_size, cfg.moe_intermediate_size * cfg.n_shared_experts
+                lw.w_router = self._put(rnd(cfg.n_routed_experts, h))
+                if fs > 0:
+                    lw.w_shared_gu = self._put(reference.interleave_gate_up(rnd(fs, h), rnd(fs, h)))
+                    lw.w_shared_down = self._put(rnd(h, fs))
+                # every rank draws all experts (same stream on every rank) and keeps its slice
+                e0 = self.ep_rank * self.e_local
+                gu = rnd(cfg.n_routed_experts, 2 * fm, h)
+                dn = rnd(cfg.n_routed_experts, h, fm)
+                lw.w_exp_gu = self._put(gu[e0:e0 + self.e_local])
+                lw.w_exp_down = self._put(dn[e0:e0 + self.e_local])
+                del gu, dn
+            self.layers.append(lw)
+        self.final_norm = self._put(torch.ones(h))
+        self.lm_head = self._put(rnd(cfg.vocab_size, h))
+        return self
+
+    def weight_bytes(self) -> int:
+        n = 0
+        for lw in self.layers:
+            for t in vars(lw).values():
+                if t is not None:
+                    n += t.numel() * t.element_size()
+        return n + sum(t.numel() * t.element_size() for t in (self.embed, self.final_norm, self.lm_head))
+
+    # ------------------------------------------------------------------------------------------------
+    def allocate_kv_cache(self, num_pages: int, page_size: int):
+        return [torch.zeros(num_pages, page_size, self.lora + self.rope, dtype=self.dtype, device=self.device)
+                for _ in range(self.cfg.num_layers)]
+
+    def kv_bytes_per_page(self, page_size: int) -> int:
+        return self.cfg.num_layers * page_size * (self.lora + self.rope) * torch.empty((), dtype=self.dtype).element_size()
+
+    # ------------------------------------------------------------------------------------------------
+    def _attention(self, lw: DsLayer, x: torch.Tensor, positions, slots, meta: ops.AttnMeta, cache: torch.Tensor) -> torch.Tensor:
+        T, H = x.shape[0], self.H
+        q = ops.linear(x, lw.wq).view(T, H, self.nope + self.rope)
+        kv_a = ops.linear(x, lw.w_kv_a)
+        c_kv, _ = ops.rms_norm(kv_a[:, :self.lora].contiguous(), lw.kv_a_norm, self.cfg.rms_norm_eps)
+        k_rope = kv_a[:, self.lora:].contiguous()
+        q_rope = q[:, :, self.nope:].reshape(T, H * self.rope).contiguous()
+        ops.rope_kvwrite(q_rope, k_rope, None, self.cos_sin, positions, None, None, None, self.rope, interleaved=self.cfg.rope_interleaved)
+        # latent cache row = [c_kv | k_rope]; slots < 0 (graph padding) are skipped by the scatter
+        ops.scatter_rows(torch.cat([c_kv, k_rope], dim=1), slots, cache.view(-1, cache.shape[2]))
+        q_nope = q[:, :, :self.nope]
+        q_rope = q_rope.view(T, H, self.rope)
+        out = torch.empty(T, H * self.vdim, dtype=x.dtype, device=x.device)
+        nd = meta.num_decode
+        if nd > 0:
+            # absorbed decode: q_lat[h] = q_nope[h] W_UK[h]; o[h] = o_lat[h] W_UV[h]^T
+            q_lat = torch.einsum("thd,hdc->thc", q_nope[:nd].float(), lw.w_uk.float()).to(x.dtype).contiguous()
+            o_lat = ops.mla_decode(q_lat, q_rope[:nd].contiguous(), cache, meta.ctx_lens[:nd], meta.block_tables[:nd], self.scale,
+                                   meta.max_ctx)
+            o = torch.einsum("thc,hvc->thv", o_lat.float(), lw.w_uv.float()).to(x.dtype)
+            out[:nd] = o.reshape(nd, H * self.vdim)
+        if meta.num_seqs > nd:
+            out[nd:] = self._prefill_rows(lw, q_nope, q_rope, meta, cache, nd)
+        return out
+
+    def _prefill_rows(self, lw, q_nope, q_rope, meta, cache, nd) -> torch.Tensor:
+        """Non-absorbed causal attention for the prefill chunks: expand each sequence's latents to per-head K/V."""
+        H, dq = self.H, self.nope + self.rope
+        cu = meta.cu_q.tolist() if not isinstance(meta.cu_q, list) else meta.cu_q
+        ctx = meta.ctx_lens.tolist()
+        outs = []
+        page_size = cache.shape[1]
+        for b in range(nd, meta.num_seqs):
+            s, e, c = cu[b], cu[b + 1], ctx[b]
+            n_pages = (c + page_size - 1) // page_size
+            lat = cache[meta.block_tables[b, :n_pages].long()].reshape(n_pages * page_size, -1)[:c]
+            c_kv, k_r = lat[:, :self.lora], lat[:, self.lora:]
+            k_nope = torch.einsum("tc,hdc->thd", c_kv.float(), lw.w_uk.float())
+            v = torch.einsum("tc,hvc->thv", c_kv.float(), lw.w_uv.float())
+            k = torch.cat([k_nope, k_r.float().unsqueeze(1).expand(c, H, self.rope)], dim=2)
+            qq = torch.cat([q_nope[s:e].float(), q_rope[s:e].float()], dim=2)
+            sc = torch.einsum("qhd,khd->hqk", qq, k) * self.scale
+            qpos = torch.arange(c - (e - s), c, device=lat.device).unsqueeze(1)
+            kpos = torch.arange(c, device=lat.device).unsqueeze(0)
+            sc = sc.masked_fill(~(kpos <= qpos).unsqueeze(0), float("-inf"))
+            o = torch.einsum("hqk,khv->qhv", torch.softmax(sc, dim=-1), v)
+            outs.append(o.reshape(e - s, H * self.vdim).to(q_nope.dtype))
+        return torch.cat(outs, dim=0)
+
+    def _moe(self, lw: DsLayer, x: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        logits = ops.linear(x, lw.w_router)
+        weights, ids = reference.moe_route(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, cfg.routed_scaling_factor)
+        if self.ep is not None:
+            routed = self.ep.moe(x, weights, ids, lw.w_exp_gu, lw.w_exp_down)
+        elif x.is_cuda:
+            from ..parallel.ep import local_moe
+
+            routed = local_moe(x, weights, ids, lw.w_exp_gu, lw.w_exp_down)
+        else:
+            routed = reference.moe_forward(x, lw.w_exp_gu, lw.w_exp_down, weights, ids).to(x.dtype)
+        if lw.w_shared_gu is not None:
+            routed = routed + ops.linear(ops.linear_swiglu(x, lw.w_shared_gu), lw.w_shared_down)
+        return routed
+
+    def forward(self, token_ids, positions, slots, meta: ops.AttnMeta, kv_caches, sample_rows):
+        cfg = self.cfg
+        h = ops.embedding(token_ids, self.embed)
+        residual = None
+        for li, lw in enumerate(self.layers):
+            x, residual = ops.rms_norm(h, lw.attn_norm, cfg.rms_norm_eps, residual)
+            attn = self._attention(lw, x, positions, slots, meta, kv_caches[li])
+            h = ops.linear(attn, lw.wo)
+            x, residual = ops.rms_norm(h, lw.mlp_norm, cfg.rms_norm_eps, residual)
+            if lw.w_gu is not None:
+                h = ops.linear(ops.linear_swiglu(x, lw.w_gu), lw.w_down)
+            else:
+                h = self._moe(lw, x)
+        x, _ = ops.rms_norm(h, self.final_norm, cfg.rms_norm_eps, residual)
+        if sample_rows is not None:
+            x = ops.gather_rows(x, sample_rows)
+        return ops.linear(x, self.lm_head)

@@ -129,6 +129,17 @@ def gather_rows(src: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def scatter_rows(src: torch.Tensor, slots: torch.Tensor, dst: torch.Tensor) -> None:
+    """dst[slots[i]] = src[i] for slots[i] >= 0 (KV row write for caches with one row per token)."""
+    if not src.is_cuda:
+        valid = slots >= 0
+        dst[slots[valid].long()] = src[valid].to(dst.dtype)
+        return
+    C = _ext.require()
+    C.scatter_rows(src, slots, dst, _state.get(src.device).status)
+    _count()
+
+
 def copy_pages(cache: torch.Tensor, src_pages: torch.Tensor, dst_pages: torch.Tensor) -> None:
     if not cache.is_cuda:
         cache[dst_pages.long()] = cache[src_pages.long()]
@@ -162,6 +173,23 @@ def linear_swiglu(x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tensor | None 
     if out is None:
         out = torch.empty(x.shape[0], w_gu.shape[0] // 2, dtype=x.dtype, device=x.device)
     C.gemm_bf16(x, w_gu, out, None, EPI_SWIGLU, config, st.gemm_ws, st.status)
+    _count()
+    return out
+
+
+def linear_fp8(x, w_q: torch.Tensor, w_scale: torch.Tensor, out: torch.Tensor | None = None, config: int = 0) -> torch.Tensor:
+    """Block-scaled fp8 linear. `x` is either a bf16 [M, K] tensor (quantised here, 1x128 blocks) or a pair
+    (x_q e4m3 [M, K], x_scale f32 [M, K/128]) from `rms_norm_quant`. w_q e4m3 [N, K], w_scale f32 [N/128, K/128]."""
+    if isinstance(x, tuple):
+        xq, xs = x
+    else:
+        xq, xs = quant_e4m3(x)
+    if not xq.is_cuda:
+        return reference.linear_fp8_block(xq, xs, w_q, w_scale).to(torch.bfloat16 if w_q.is_cuda else torch.float32)
+    C = _ext.require()
+    if out is None:
+        out = torch.empty(xq.shape[0], w_q.shape[0], dtype=torch.bfloat16, device=xq.device)
+    C.gemm_fp8(xq, xs, w_q, w_scale, out, config, _state.get(xq.device).status)
     _count()
     return out
 
@@ -218,6 +246,25 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         C.attn_prefill(q, k_cache, v_cache, out, meta.cu_q[nd:], meta.ctx_lens[nd:], meta.block_tables[nd:], head_dim,
                        meta.max_q_len, scale, st.status)
         _count()
+    return out
+
+
+def mla_decode(q_lat: torch.Tensor, q_rope: torch.Tensor, kv_cache: torch.Tensor, ctx_lens: torch.Tensor,
+               block_tables: torch.Tensor, scale: float, max_ctx: int = 0) -> torch.Tensor:
+    """Absorbed multi-head latent attention for one query token per sequence.
+    q_lat [B, H, 512], q_rope [B, H, 64], kv_cache [pages, page_size, 576] -> attention output in latent space [B, H, 512]."""
+    if not q_lat.is_cuda:
+        return reference.mla_decode(q_lat, q_rope, kv_cache, ctx_lens, block_tables, scale).to(q_lat.dtype)
+    C = _ext.require()
+    st = _state.get(q_lat.device)
+    B, H = q_lat.shape[0], q_lat.shape[1]
+    ctas = B * ((H + 15) // 16)
+    splits = 1
+    if ctas < 148 and max_ctx > 256:
+        splits = max(1, min((148 + ctas - 1) // ctas, max_ctx // 128, 16))
+    out = torch.empty_like(q_lat)
+    C.mla_decode(q_lat, q_rope, kv_cache, out, ctx_lens, block_tables, st.attn_ws, splits, scale, st.status)
+    _count(2 if splits > 1 else 1)
     return out
 
 

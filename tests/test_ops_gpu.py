@@ -149,6 +149,24 @@ def test_gemm_swiglu(M, config):
     _close(y, y_ref, 5e-2, 3e-2)
 
 
+@pytest.mark.parametrize("M,N,K,config", [(128, 256, 512, 0), (300, 1280, 1024, 0), (1000, 512, 2048, ops.gemm_config(False, 64)),
+                                          (7, 384, 512, 0), (33, 1024, 4096, 0), (64, 640, 1024, 0), (100, 256, 512, ops.gemm_config(True, 128)),
+                                          (48, 8192, 1024, ops.gemm_config(True, 16))])
+def test_gemm_fp8_block_scaled(M, N, K, config):
+    g = torch.Generator().manual_seed(6)
+    x = (torch.randn(M, K, generator=g) * torch.rand(M, 1, generator=g) * 4).bfloat16()
+    w = torch.randn(N, K, generator=g) * 0.05 * (1 + torch.rand(N, 1, generator=g))
+    wq, ws = ref.quant_e4m3_128x128(w)
+    xq, xs = ref.quant_e4m3_1x128(x)
+    want = ref.linear_fp8_block(xq, xs, wq, ws)             # oracle: dequantise both operands, fp32 matmul
+    y = ops.linear_fp8((xq.to(DEV), xs.to(DEV)), wq.to(DEV), ws.to(DEV), config=config)
+    _close(y, want, 0.02 * want.abs().max().item() + 1e-2, 1.5e-2)
+    # end to end with the device quantiser: compare against the unquantised product with fp8-sized tolerance
+    y2 = ops.linear_fp8(x.to(DEV), wq.to(DEV), ws.to(DEV), config=config)
+    full = x.float() @ ref.dequant_e4m3_128x128(wq, ws).t()
+    assert (y2.float().cpu() - full).abs().max().item() < 0.08 * full.abs().max().item() + 0.05
+
+
 def _attn_case(q_lens, ctx_lens, n_q, n_kv, D, page, seed=0):
     g = torch.Generator().manual_seed(seed)
     B = len(q_lens)
@@ -193,6 +211,28 @@ def test_attention_decode(page):
     _attn_case([1, 1], [300, 31], 4, 2, 64, page)
     _attn_case([1, 1], [64, 2048], 16, 1, 128, page)         # group of 16 heads per kv head
     _attn_case([1, 1, 40, 9], [500, 33, 40, 100], 8, 8, 128, page)  # mixed decode + prefill batch
+
+
+@pytest.mark.parametrize("page", [32, 128])
+@pytest.mark.parametrize("B,H,ctxs", [(3, 16, [1, 33, 700]), (2, 16, [2500, 64]), (5, 16, [31, 32, 95, 128, 129]), (2, 8, [200, 17])])
+def test_mla_decode_absorbed(page, B, H, ctxs):
+    g = torch.Generator().manual_seed(9)
+    pages_per = [(c + page - 1) // page for c in ctxs]
+    total = sum(pages_per) + 2
+    perm = torch.randperm(total, generator=g)
+    bt = torch.zeros(B, max(pages_per), dtype=torch.int32)
+    o = 0
+    for b, n in enumerate(pages_per):
+        bt[b, :n] = perm[o:o + n].int()
+        o += n
+    cache = (torch.randn(total, page, 576, generator=g) * 0.5).bfloat16()
+    q_lat = (torch.randn(B, H, 512, generator=g) * 0.3).bfloat16()
+    q_rope = (torch.randn(B, H, 64, generator=g) * 0.3).bfloat16()
+    cl = torch.tensor(ctxs, dtype=torch.int32)
+    scale = 1.0 / math.sqrt(192)
+    want = ref.mla_decode(q_lat, q_rope, cache, cl, bt, scale)
+    got = ops.mla_decode(q_lat.to(DEV), q_rope.to(DEV), cache.to(DEV), cl.to(DEV), bt.to(DEV), scale, max(ctxs))
+    _close(got, want, 2e-2, 2e-2)
 
 
 def test_argmax_and_sampling():
