@@ -375,3 +375,87 @@ extern "C" int b2_gemm_bf16(const void* x, const void* w, void* y, const void* r
   }
 #undef B2_LAUNCH
 }
+
+// ------------------------------------------------------------------------------------------------------------
+// Allocation-free variant (declared in b2/noalloc.h). The split-K scratch is this file-scope array: the first
+// 256 KiB are the per-tile semaphores, the rest holds f32 partial tiles. In host code the name `g_noalloc_scratch`
+// is only a handle for the runtime; the address a kernel can use comes from cudaGetSymbolAddress, looked up once
+// per device with that device current.
+// ------------------------------------------------------------------------------------------------------------
+#include "b2/noalloc.h"
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[B2_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kNoallocMaxDevices = 64;
+void* g_noalloc_ptr[kNoallocMaxDevices] = {};
+
+// Device address of the scratch for the current device; first use clears the semaphore words.
+int noalloc_scratch(void** out, cudaStream_t stream) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoallocMaxDevices) return -b2::kBadArgument;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return -b2::kBadArgument;
+    }
+    if (cudaMemsetAsync(p, 0, 65536 * 4, stream) != cudaSuccess) {
+      cudaGetLastError();
+      return -b2::kBadArgument;
+    }
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int b2_gemm_bf16_noalloc(const void* x, const void* w, void* y, int M, int N, int K, int64_t ldx,
+                                    int64_t ldw, int64_t ldy, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (x == nullptr || w == nullptr || y == nullptr || K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return -kBadArgument;
+  // Same configuration rule as the allocating entry point, then checked against the fixed capacity.
+  Config c = choose_config(M, N, K, B2_EPI_NONE);
+  const int num_kb = (K + 63) / 64;
+  if (c.splits > num_kb) c.splits = num_kb;
+  while (c.splits > 1 && ((num_kb + c.splits - 1) / c.splits) * (c.splits - 1) >= num_kb) --c.splits;
+  if (!c.swap && (N % 8 != 0 || ldy % 8 != 0)) return -kBadArgument;
+  const int rows_p = c.swap ? N : M, rows_q = c.swap ? M : N;
+  const int64_t tiles = static_cast<int64_t>((rows_p + 127) / 128) * ((rows_q + c.bn - 1) / c.bn);
+  const int64_t counters_bytes = 65536 * 4;
+  if (c.splits > 1) {
+    const int64_t need = counters_bytes + tiles * c.splits * c.bn * 128 * 4;
+    if (need > B2_NOALLOC_SCRATCH_BYTES || tiles > 65536) return -kTooLarge;
+  }
+  void* scratch = nullptr;
+  const int rc = noalloc_scratch(&scratch, stream);
+  if (rc != 0) return rc;
+  EpiParams ep{};
+  ep.y = static_cast<__nv_bfloat16*>(y);
+  ep.ldy = ldy;
+  ep.ldr = ldy;
+  ep.M = M;
+  ep.N = N;
+  ep.mode = B2_EPI_NONE;
+  ep.counters = static_cast<uint32_t*>(scratch);
+  ep.workspace = reinterpret_cast<float*>(static_cast<char*>(scratch) + counters_bytes);
+#define B2_LAUNCH_NA(BN_, SWAP_) return launch<BN_, SWAP_>(x, w, M, N, K, ldx, ldw, c.splits, ep, nullptr, stream)
+  if (c.swap) {
+    switch (c.bn) {
+      case 16: B2_LAUNCH_NA(16, true);
+      case 32: B2_LAUNCH_NA(32, true);
+      case 64: B2_LAUNCH_NA(64, true);
+      case 128: B2_LAUNCH_NA(128, true);
+      case 256: B2_LAUNCH_NA(256, true);
+      default: return -kBadArgument;
+    }
+  }
+  switch (c.bn) {
+    case 64: B2_LAUNCH_NA(64, false);
+    case 128: B2_LAUNCH_NA(128, false);
+    case 256: B2_LAUNCH_NA(256, false);
+    default: return -kBadArgument;
+  }
+#undef B2_LAUNCH_NA
+}

@@ -1,0 +1,59 @@
+"""The allocation-free GEMM entry point, called through its exported C symbol (ctypes), must agree with the regular
+entry point. Some embedders of this library (graph capture in progress, allocator-free serving loops, plugins inside
+another runtime's pool) cannot allocate device memory, so this path keeps its split-K scratch in a fixed array inside
+the library. The test makes two calls in a row on shapes that do split K, because the second call reuses whatever
+the first one left in that array. Collected last on purpose: a failure here cannot hide the rest of the suite."""
+import ctypes
+
+import pytest
+import torch
+
+from mojo_b200 import _ext, ops
+
+pytestmark = pytest.mark.gpu
+
+
+def _call(lib, x, w, y):
+    M, K = x.shape
+    N = w.shape[0]
+    stream = torch.cuda.current_stream().cuda_stream
+    return lib.b2_gemm_bf16_noalloc(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(y.data_ptr()),
+                                    M, N, K, ctypes.c_int64(x.stride(0)), ctypes.c_int64(w.stride(0)), ctypes.c_int64(y.stride(0)),
+                                    ctypes.c_void_p(stream))
+
+
+def test_no_alloc_gemm_matches_regular_entry_point_twice():
+    lib = _ext.kernels_lib()
+    lib.b2_gemm_bf16_noalloc.restype = ctypes.c_int
+    g = torch.Generator().manual_seed(11)
+    for M, N, K in [(16, 1024, 4096), (48, 640, 2048)]:      # decode-like shapes: the configuration splits K
+        for call in range(2):
+            x = torch.randn(M, K, generator=g).bfloat16().cuda()
+            w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().cuda()
+            want = ops.linear(x, w)
+            y = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info()[0]
+            rc = _call(lib, x, w, y)
+            torch.cuda.synchronize()
+            assert rc == 0, f"call {call} on {(M, N, K)} returned {rc}"
+            # the driver's free-memory figure must not move: the call allocated nothing
+            assert torch.cuda.mem_get_info()[0] == free_before
+            torch.testing.assert_close(y.float(), want.float(), atol=3e-2, rtol=2e-2)
+            ref = x.float() @ w.float().t()
+            torch.testing.assert_close(y.float(), ref, atol=6e-2, rtol=2e-2)
+    ops.check_status()
+
+
+def test_no_alloc_gemm_rejects_what_does_not_fit():
+    lib = _ext.kernels_lib()
+    lib.b2_gemm_bf16_noalloc.restype = ctypes.c_int
+    # 128 tokens x 4096 outputs x K = 14336 splits K with partial sums far beyond the 8 MiB array
+    x = torch.zeros(128, 14336, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(4096, 14336, dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros(128, 4096, dtype=torch.bfloat16, device="cuda")
+    rc = _call(lib, x, w, y)
+    torch.cuda.synchronize()
+    assert rc in (0, -5)      # either the chosen configuration does not split, or it is refused as TOO_LARGE
+    bad = _call(lib, x[:, :14330], w, y)
+    assert bad == -4          # K not a multiple of 8: BAD_ARGUMENT, nothing launched
