@@ -38,7 +38,8 @@ def parse_args():
     ap.add_argument("--impl", default="mojo_b200", choices=["mojo_b200", "reference", "torch-baseline"])
     ap.add_argument("--model", default="llama-3.1-8b")
     ap.add_argument("--requests", type=int, default=512)
-    ap.add_argument("--rate", type=float, default=64.0, help="Poisson arrival rate, requests/s")
+    ap.add_argument("--rate", type=float, default=1000.0,
+                    help="Poisson arrival rate, requests/s; the default keeps the queue non-empty at every GPU count, so the number is capacity, not offered load")
     ap.add_argument("--max-num-seqs", type=int, default=256)
     ap.add_argument("--max-batched-tokens", type=int, default=4096)
     ap.add_argument("--page-size", type=int, default=128)
@@ -46,6 +47,7 @@ def parse_args():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--layers", type=int, default=None, help="debug only: marks the result invalid")
+    ap.add_argument("--profile", default=None, help="debug only: write a per-kernel table of a few steps to this file")
     return ap.parse_args()
 
 
@@ -169,6 +171,20 @@ def main() -> None:
         torch.distributed.barrier()
         torch.cuda.synchronize()
     ops.check_status(device)
+
+    if args.profile:
+        # diagnostic only (numbers taken under a profiler are never reported as results)
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            n = 0
+            while n < 6:
+                if one_step(False) is not None:
+                    n += 1
+            torch.cuda.synchronize()
+        if rank == 0:
+            with open(args.profile, "w") as f:
+                f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40, max_name_column_width=90))
 
     # ---- timed region: exactly K engine steps ----
     ops.reset_launch_count()

@@ -5,6 +5,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include "b2/api.h"
 #include "b2/tp.h"
+#include "b2/ep.h"
 namespace py = pybind11;
 
 namespace {
@@ -134,6 +135,84 @@ void bind_ops_extra(py::module_& m) {
                                    status_ptr(status), cur_stream()),
                 "mla_decode");
         });
+
+  py::class_<B2EpLayout>(m, "EpLayout")
+      .def(py::init([]() { return B2EpLayout{}; }))
+      .def_readwrite("off_recv_x", &B2EpLayout::off_recv_x)
+      .def_readwrite("off_recv_meta", &B2EpLayout::off_recv_meta)
+      .def_readwrite("off_recv_count", &B2EpLayout::off_recv_count)
+      .def_readwrite("off_ret_y", &B2EpLayout::off_ret_y)
+      .def_readwrite("off_disp_done", &B2EpLayout::off_disp_done)
+      .def_readwrite("off_comb_done", &B2EpLayout::off_comb_done)
+      .def_readwrite("off_epoch", &B2EpLayout::off_epoch)
+      .def_readwrite("total_bytes", &B2EpLayout::total_bytes)
+      .def_readwrite("cap", &B2EpLayout::cap)
+      .def_readwrite("e_local", &B2EpLayout::e_local)
+      .def_readwrite("hidden", &B2EpLayout::hidden)
+      .def_readwrite("top_k", &B2EpLayout::top_k)
+      .def_readwrite("t_cap", &B2EpLayout::t_cap);
+
+  m.def("ep_dispatch",
+        [](const at::Tensor& x, const at::Tensor& logits, at::Tensor& weights, at::Tensor& ids, int rank, const std::vector<int64_t>& peers,
+           const B2EpLayout& lay, int top_k, bool norm_topk, double route_scale, int slot, uint64_t timeout_ns,
+           c10::optional<at::Tensor> status) {
+          need(is_bf16_2d(x) && x.is_contiguous() && is_bf16_2d(logits) && logits.is_contiguous() && logits.size(0) == x.size(0), "ep_dispatch: x [T, H], logits [T, E] contiguous bf16");
+          need(weights.scalar_type() == at::kFloat && weights.is_contiguous() && ids.scalar_type() == at::kInt && ids.is_contiguous() &&
+                   weights.numel() == x.size(0) * top_k && ids.numel() == x.size(0) * top_k, "ep_dispatch: weights f32 / ids i32 [T, k]");
+          need(x.size(1) == lay.hidden, "ep_dispatch: hidden mismatch");
+          const B2TpRegion reg = make_region(rank, peers);
+          c10::cuda::CUDAGuard g(x.device());
+          check(b2_ep_dispatch(x.data_ptr(), logits.data_ptr(), weights.data_ptr<float>(), ids.data_ptr<int32_t>(), &reg, &lay,
+                               static_cast<int>(x.size(0)), static_cast<int>(logits.size(1)), top_k, norm_topk ? 1 : 0,
+                               static_cast<float>(route_scale), slot, timeout_ns, status_ptr(status), cur_stream()),
+                "ep_dispatch");
+        });
+
+  m.def("moe_grouped_gemm",
+        [](const at::Tensor& x, const at::Tensor& w, const at::Tensor& counts, at::Tensor& y, int cap, bool swiglu, int bn,
+           c10::optional<at::Tensor> status) {
+          need(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.dim() == 2, "moe_grouped_gemm: x bf16 [e_local * cap, K]");
+          need(w.scalar_type() == at::kBFloat16 && w.is_contiguous() && w.dim() == 3 && w.size(2) == x.size(1), "moe_grouped_gemm: w bf16 [e_local, N, K]");
+          need(counts.element_size() == 4 && counts.is_contiguous() && counts.numel() >= w.size(0), "moe_grouped_gemm: counts 32-bit [e_local]");
+          const int e_local = static_cast<int>(w.size(0)), N = static_cast<int>(w.size(1)), K = static_cast<int>(w.size(2));
+          need(x.size(0) == static_cast<int64_t>(e_local) * cap, "moe_grouped_gemm: x rows must be e_local * cap");
+          const int64_t ldy = swiglu ? N / 2 : N;
+          need(y.scalar_type() == at::kBFloat16 && y.is_contiguous() && y.numel() == static_cast<int64_t>(e_local) * cap * ldy, "moe_grouped_gemm: y bf16 [e_local * cap, N or N/2]");
+          c10::cuda::CUDAGuard g(x.device());
+          check(b2_moe_grouped_gemm(x.data_ptr(), w.data_ptr(), reinterpret_cast<const uint32_t*>(counts.data_ptr()), y.data_ptr(), e_local,
+                                    cap, N, K, ldy, swiglu ? 1 : 0, bn, status_ptr(status), cur_stream()),
+                "moe_grouped_gemm");
+        });
+
+  m.def("ep_combine",
+        [](const at::Tensor& y_local, const at::Tensor& weights, c10::optional<at::Tensor> shared, at::Tensor& out, int rank,
+           const std::vector<int64_t>& peers, const B2EpLayout& lay, int top_k, int slot, uint64_t timeout_ns,
+           c10::optional<at::Tensor> status) {
+          need(y_local.is_cuda() && y_local.scalar_type() == at::kBFloat16 && y_local.is_contiguous(), "ep_combine: y_local contiguous bf16");
+          need(weights.scalar_type() == at::kFloat && weights.is_contiguous(), "ep_combine: weights f32 [T, k]");
+          need(is_bf16_2d(out) && out.is_contiguous() && out.size(1) == lay.hidden && weights.numel() == out.size(0) * top_k, "ep_combine: out bf16 [T, H]");
+          if (shared.has_value()) need(is_bf16_2d(*shared) && shared->is_contiguous() && shared->sizes() == out.sizes(), "ep_combine: shared must match out");
+          const B2TpRegion reg = make_region(rank, peers);
+          c10::cuda::CUDAGuard g(out.device());
+          check(b2_ep_combine(y_local.data_ptr(), weights.data_ptr<float>(), shared.has_value() ? shared->data_ptr() : nullptr, out.data_ptr(),
+                              &reg, &lay, static_cast<int>(out.size(0)), top_k, slot, timeout_ns, status_ptr(status), cur_stream()),
+                "ep_combine");
+        });
+
+  m.def("gguf_dequant", [](const at::Tensor& wq, int ggml_type, at::Tensor& out) {
+    need(wq.is_cuda() && wq.element_size() == 1 && wq.is_contiguous(), "gguf_dequant: packed weights as contiguous CUDA bytes");
+    need(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.is_contiguous(), "gguf_dequant: out contiguous bf16");
+    c10::cuda::CUDAGuard g(wq.device());
+    check(b2_dequant_gguf(wq.data_ptr(), ggml_type, out.data_ptr(), out.numel(), cur_stream()), "gguf_dequant");
+  });
+  m.def("gemm_gguf", [](const at::Tensor& x, const at::Tensor& wq, int ggml_type, at::Tensor& y, c10::optional<at::Tensor> status) {
+    need(is_bf16_2d(x) && x.is_contiguous() && is_bf16_2d(y) && y.is_contiguous() && y.size(0) == x.size(0), "gemm_gguf: x [M, K], y [M, N] contiguous bf16");
+    need(wq.is_cuda() && wq.element_size() == 1 && wq.is_contiguous(), "gemm_gguf: packed weights as contiguous CUDA bytes");
+    c10::cuda::CUDAGuard g(x.device());
+    check(b2_gemm_gguf(x.data_ptr(), wq.data_ptr(), ggml_type, y.data_ptr(), static_cast<int>(x.size(0)), static_cast<int>(y.size(1)),
+                       static_cast<int>(x.size(1)), status_ptr(status), cur_stream()),
+          "gemm_gguf");
+  });
 
   m.def("wait_flag", [](const at::Tensor& flag, uint32_t want, uint64_t timeout_ns, c10::optional<at::Tensor> status) {
     need(flag.is_cuda() && flag.element_size() == 4, "wait_flag: 32-bit CUDA flag tensor");

@@ -66,10 +66,25 @@ constexpr int tmem_cols_for() {
 }
 
 // elem_bytes: 2 for bf16/f16 (UMMA K = 16), 1 for fp8 (UMMA K = 32); a k-block is always 128 bytes wide.
-template <int BN, int STAGES, int ELEM_BYTES, class Sched, class Gate, class Epi>
+// Optional fourth role. When PFill::kActive, the P operand does not come from TMA: four extra warps (threads
+// 192..319) write each stage's 128 x 64 P tile themselves (e.g. dequantising packed weights) in the swizzled
+// layout the MMA descriptor expects, then arrive on the stage's full barrier after a proxy fence.
+struct NoFill {
+  static constexpr bool kActive = false;
+  __device__ __forceinline__ void operator()(const WorkUnit&, int, uint8_t*, int, int) const {}
+};
+constexpr int kThreadsWithFill = kThreads + 128;
+
+// Byte offset of 16-byte chunk `c` (0..7) of row `r` (0..127) inside a 128 x 64 bf16 tile stored with the
+// 128-byte swizzle (what TMA SWIZZLE_128B produces and make_smem_desc_sw128 describes).
+__device__ __forceinline__ uint32_t sw128_offset(int r, int c) {
+  return static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
+}
+
+template <int BN, int STAGES, int ELEM_BYTES, class Sched, class Gate, class Epi, class PFill = NoFill>
 __device__ __forceinline__ void run(const CUtensorMap* tmap_p, const CUtensorMap* tmap_q, uint32_t idesc,
-                                    uint64_t policy_p, uint64_t policy_q, Sched sched, Gate gate, Epi epi,
-                                    Status* status, int cta, int num_ctas) {
+                                    uint64_t policy_p, uint64_t policy_q, const Sched& sched, Gate gate, Epi epi,
+                                    Status* status, int cta, int num_ctas, PFill pfill = PFill{}) {
   using L = SmemLayout<BN, STAGES>;
   constexpr int kTmemCols = tmem_cols_for<BN>();
   constexpr int kMmaPerKb = 4;                       // 128 bytes / 32 bytes per instruction
@@ -93,7 +108,7 @@ __device__ __forceinline__ void run(const CUtensorMap* tmap_p, const CUtensorMap
     ptx::prefetch_tensormap(tmap_p);
     ptx::prefetch_tensormap(tmap_q);
     for (int s = 0; s < STAGES; ++s) {
-      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(full_bar(s), PFill::kActive ? 5 : 1);  // TMA thread (+ one arrival per fill warp)
       ptx::mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -131,9 +146,9 @@ __device__ __forceinline__ void run(const CUtensorMap* tmap_p, const CUtensorMap
             break;
           }
           const uint32_t sp = smem_base + stage * L::kStageBytes;
-          ptx::mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
+          ptx::mbar_arrive_expect_tx(full_bar(stage), PFill::kActive ? L::kQBytes : L::kStageBytes);
           const int kx = kb * (128 / ELEM_BYTES);
-          ptx::tma_load_2d(sp, tmap_p, full_bar(stage), kx, u.p_coord, policy_p);
+          if (!PFill::kActive) ptx::tma_load_2d(sp, tmap_p, full_bar(stage), kx, u.p_coord, policy_p);
           ptx::tma_load_2d(sp + L::kPBytes, tmap_q, full_bar(stage), kx, u.q_coord, policy_q);
           ++issued;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -202,6 +217,27 @@ __device__ __forceinline__ void run(const CUtensorMap* tmap_p, const CUtensorMap
       }
     }
     __syncwarp();
+  } else if (PFill::kActive && warp >= 6) {
+    // ------------------------------------------------------------------ P-tile fill warps
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int w = cta; ok && w < total; w += num_ctas) {
+      const WorkUnit u = sched.get(w);
+      for (int kb = u.kb0; kb < u.kb1; ++kb) {
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(empty_bar(stage), phase ^ 1u))) {
+          if (lane == 0) status_record(status, kTimeout, kSiteGemmEmpty, w, kb);
+          ok = false;
+          break;
+        }
+        const uint32_t sp = smem_base + stage * L::kStageBytes;
+        pfill(u, kb, smem_raw + (sp - ptx::smem_u32(smem_raw)), warp - 6, lane);
+        ptx::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(full_bar(stage));
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
   } else {
     // ------------------------------------------------------------------ epilogue warps
     const int quarter = warp & 3;  // TMEM lane quarter this warp may access

@@ -334,6 +334,11 @@ __device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, u
                : "memory");
 }
 
+// Untiled bulk copy shared->global (bulk async-group completion); the destination may be a peer GPU's memory.
+__device__ __forceinline__ void bulk_store(void* gdst, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src), "r"(bytes) : "memory");
+}
+
 // ----------------------------------------------------------------------------------------------
 // tcgen05 / tensor memory
 // ----------------------------------------------------------------------------------------------

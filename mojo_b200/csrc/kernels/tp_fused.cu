@@ -181,30 +181,39 @@ struct RsEpilogue {
   }
 };
 
-// Reduce phase: every thread of the CTA takes part. Returns false when a wait ran out.
+// Reduce phase. Units (output tiles of the rows this rank owns) are claimed from a counter in this rank's
+// memory, in the order in which their contributions are produced, by the dedicated reduce CTAs from the start
+// and by the GEMM CTAs once they run out of tiles. Returns false when a wait ran out.
 template <int BN, bool SWAP>
-__device__ bool reduce_phase(const RsParams& p, Status* status, int cta, int num_ctas) {
+__device__ bool reduce_phase(const RsParams& p, Status* status) {
   __shared__ uint32_t sh_ok;
   __shared__ uint32_t sh_last;
+  __shared__ int sh_unit;
   const int row0 = p.rank * p.R;
   const int rows = max(0, min(p.R, p.M - row0));
   uint8_t* self = p.peer[p.rank];
   const uint32_t* flags = reinterpret_cast<const uint32_t*>(self + p.off_flags);
   const __nv_bfloat16* staging = reinterpret_cast<const __nv_bfloat16*>(self + p.off_staging);
-  uint32_t* done = reinterpret_cast<uint32_t*>(self + p.off_done);
-  // tiles along the row dimension that overlap this rank's rows
+  uint32_t* next_unit = reinterpret_cast<uint32_t*>(self + p.off_done);
+  uint32_t* done = next_unit + 1;
   constexpr int TM = SWAP ? BN : 128;
+  constexpr int TN = SWAP ? 128 : BN;
   const int tm0 = row0 / TM;
   const int tm1 = rows > 0 ? (row0 + rows - 1) / TM + 1 : tm0;
   const int n_tiles_n = SWAP ? p.p_blocks : p.q_blocks;
-  constexpr int TN = SWAP ? 128 : BN;
   const int n_units = (tm1 - tm0) * n_tiles_n;
   bool ok = true;
-  for (int un = cta; un < n_units; un += num_ctas) {
+  while (true) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      sh_unit = static_cast<int>(atomicAdd(next_unit, 1u));
+      sh_ok = 1;
+    }
+    __syncthreads();
+    const int un = sh_unit;
+    if (un >= n_units) break;
     // same enumeration as unit_index(): (tile along m) major, (tile along n) minor
     const int tm = tm0 + un / n_tiles_n, tn = un % n_tiles_n;
-    if (threadIdx.x == 0) sh_ok = 1;
-    __syncthreads();
     if (threadIdx.x < p.tp) {
       if (!ptx::wait_flag_ge_sys(flags + static_cast<int64_t>(un) * p.tp + threadIdx.x, p.epoch, p.timeout_ns)) {
         status_record(status, kTimeout, kSiteRsTile, un, threadIdx.x);
@@ -217,33 +226,53 @@ __device__ bool reduce_phase(const RsParams& p, Status* status, int cta, int num
     const int c_lo = tn * TN, c_hi = min(p.N, tn * TN + TN);
     const int vec_per_row = (c_hi - c_lo) >> 3;
     const int n_vec = (r_hi - r_lo) * vec_per_row;
-    for (int i = threadIdx.x; i < n_vec; i += blockDim.x) {
-      const int m = r_lo + i / vec_per_row;
-      const int col = c_lo + (i % vec_per_row) * 8;
-      const int row_local = m - row0;
-      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll 4
-      for (int s = 0; s < p.tp; ++s) {
-        float v[8];
-        bf16x8_to_f32(ptx::ld_relaxed_sys_v4(staging + (static_cast<int64_t>(s) * p.R + row_local) * p.N + col), v);
+    constexpr int U = 8;  // independent 16-byte vectors per thread per pass: keeps tp * U loads in flight
+    for (int i0 = threadIdx.x; i0 < n_vec; i0 += blockDim.x * U) {
+      uint4 raw[U][kMaxTp];
+      int64_t off[U];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] += v[j];
-      }
-      if (p.residual != nullptr) {
-        float v[8];
-        const int64_t rrow = p.mode == 0 ? row_local : m;
-        bf16x8_to_f32(ptx::ld_v4(p.residual + rrow * p.N + col), v);
+      for (int u = 0; u < U; ++u) {
+        const int i = i0 + u * blockDim.x;
+        const int m = r_lo + (i < n_vec ? i / vec_per_row : 0);
+        const int col = c_lo + (i < n_vec ? (i % vec_per_row) * 8 : 0);
+        off[u] = static_cast<int64_t>(m - row0) * p.N + col;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] += v[j];
+        for (int s2 = 0; s2 < kMaxTp; ++s2)
+          if (s2 < p.tp && i < n_vec) raw[u][s2] = ptx::ld_relaxed_sys_v4(staging + static_cast<int64_t>(s2) * p.R * p.N + off[u]);
       }
-      const uint4 pk = f32_to_bf16x8(acc);
-      if (p.mode == 0) {
-        ptx::st_v4(p.out + static_cast<int64_t>(row_local) * p.N + col, pk);
-      } else {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i >= n_vec) continue;
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int s2 = 0; s2 < kMaxTp; ++s2) {
+          if (s2 < p.tp) {
+            float v[8];
+            bf16x8_to_f32(raw[u][s2], v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += v[j];
+          }
+        }
+        const int row_local = static_cast<int>(off[u] / p.N);
+        const int col = static_cast<int>(off[u] - static_cast<int64_t>(row_local) * p.N);
+        const int m = row0 + row_local;
+        if (p.residual != nullptr) {
+          float v[8];
+          const int64_t rrow = p.mode == 0 ? row_local : m;
+          bf16x8_to_f32(ptx::ld_v4(p.residual + rrow * p.N + col), v);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += v[j];
+        }
+        const uint4 pk = f32_to_bf16x8(acc);
+        if (p.mode == 0) {
+          ptx::st_v4(p.out + off[u], pk);
+        } else {
 #pragma unroll 1
-        for (int d = 0; d < p.tp; ++d) {
-          const int peer = (p.rank + d) % p.tp;  // start with the local copy, then walk the ring
-          ptx::st_v4(reinterpret_cast<__nv_bfloat16*>(p.peer[peer] + p.off_yall) + static_cast<int64_t>(m) * p.N + col, pk);
+          for (int d = 0; d < p.tp; ++d) {
+            const int peer = (p.rank + d) % p.tp;  // local copy first, then around the ring
+            ptx::st_v4(reinterpret_cast<__nv_bfloat16*>(p.peer[peer] + p.off_yall) + static_cast<int64_t>(m) * p.N + col, pk);
+          }
         }
       }
     }
@@ -262,9 +291,10 @@ __device__ bool reduce_phase(const RsParams& p, Status* status, int cta, int num
   }
   if (p.mode == 1) {
     // a rank that owns no rows still announces that it has entered this launch
-    if (n_units == 0 && cta == 0 && threadIdx.x < p.tp)
+    if (n_units == 0 && blockIdx.x == 0 && threadIdx.x < p.tp)
       ptx::st_release_sys(reinterpret_cast<uint32_t*>(p.peer[threadIdx.x] + p.off_resflags) + p.rank, p.epoch);
     // the launch is complete when every rank's rows have landed in this rank's copy
+    __syncthreads();
     if (threadIdx.x == 0) sh_ok = ok ? 1u : 0u;
     __syncthreads();
     if (ok && threadIdx.x < p.tp) {
@@ -280,18 +310,20 @@ __device__ bool reduce_phase(const RsParams& p, Status* status, int cta, int num
   return ok;
 }
 
-// Tile order for the reduce-scatter GEMM: rows owned by rank+1 first, own rows last, so every rank's
-// contributions to its peers are on the wire while it is still computing.
+// Row-tile visiting order of the reduce-scatter GEMM (built on the host): round-robin over the owners starting
+// with rank + 1, one row-tile of each per round. At any moment the ranks are sending to different owners, and
+// every owner's tiles complete at a steady rate, so its reduction overlaps the remaining GEMM work.
+constexpr int kMaxRowTiles = 512;
 struct RsSched {
   int p_blocks, q_blocks, num_kb, bn;
-  int m_tiles;      // tiles along the row (token) dimension
-  int first_tile;   // first row-tile visited: the one after this rank's last own tile
+  int m_tiles;
   bool swap;
+  int16_t order[kMaxRowTiles];
   __device__ __forceinline__ int total() const { return p_blocks * q_blocks; }
   __device__ __forceinline__ WorkUnit get(int w) const {
     WorkUnit u;
     const int n_tiles = swap ? p_blocks : q_blocks;
-    const int mt = (first_tile + w / n_tiles) % m_tiles;
+    const int mt = order[w / n_tiles];
     const int nt = w % n_tiles;
     u.pb = swap ? nt : mt;
     u.qb = swap ? mt : nt;
@@ -307,19 +339,31 @@ struct RsSched {
 
 template <int BN, int STAGES, bool SWAP>
 __global__ void __launch_bounds__(gemm::kThreads, 1)
-gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q, RsSched sched,
-               RsParams prm_in, EpochCtl ectl, Status* status) {
+gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
+               const __grid_constant__ RsSched sched, RsParams prm_in, EpochCtl ectl, int n_gemm, Status* status) {
   constexpr uint32_t idesc = ptx::make_idesc(1, 1, 128, BN);
   RsParams prm = prm_in;
   prm.epoch = epoch_begin(ectl);
-  extern __shared__ uint8_t smem_dyn[];
-  uint8_t* epi_buf = smem_dyn + gemm::SmemLayout<BN, STAGES>::kTotalBytes;
-  epi_buf += (16 - (reinterpret_cast<uintptr_t>(epi_buf) & 15)) & 15;  // 16-byte vector accesses
-  RsEpilogue<BN, SWAP> epi{prm, epi_buf};
-  gemm::run<BN, STAGES, 2>(&tmap_p, &tmap_q, idesc, ptx::kEvictNormal, ptx::kEvictNormal, sched, gemm::NoGate{}, epi, status,
-                           static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
-  reduce_phase<BN, SWAP>(prm, status, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
-  epoch_end(ectl, prm.epoch);
+  if (static_cast<int>(blockIdx.x) < n_gemm) {
+    extern __shared__ uint8_t smem_dyn[];
+    uint8_t* epi_buf = smem_dyn + gemm::SmemLayout<BN, STAGES>::kTotalBytes;
+    epi_buf += (16 - (reinterpret_cast<uintptr_t>(epi_buf) & 15)) & 15;  // 16-byte vector accesses
+    RsEpilogue<BN, SWAP> epi{prm, epi_buf};
+    gemm::run<BN, STAGES, 2>(&tmap_p, &tmap_q, idesc, ptx::kEvictNormal, ptx::kEvictNormal, sched, gemm::NoGate{}, epi, status,
+                             static_cast<int>(blockIdx.x), n_gemm);
+  }
+  reduce_phase<BN, SWAP>(prm, status);
+  // last CTA out: every CTA has made its final (failed) claim, so the unit counter can go back to zero
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(ectl.cta_done, 1u) == gridDim.x - 1) {
+      *ectl.cta_done = 0;
+      *reinterpret_cast<uint32_t*>(prm.peer[prm.rank] + prm.off_done) = 0;
+      *reinterpret_cast<volatile uint32_t*>(ectl.epoch_ptr) = prm.epoch;
+      __threadfence();
+    }
+  }
 }
 
 constexpr int stages_for(int bn) {
@@ -348,7 +392,7 @@ int launch_rs(const void* x, const void* w, int M, int N, int K, int64_t ldx, in
   if (!make_tmap_2d(&tp, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p_ptr, rows_p, K, ldp * 2, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B) ||
       !make_tmap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q_ptr, rows_q, K, ldq * 2, BN, 64, CU_TENSOR_MAP_SWIZZLE_128B))
     return -kBadArgument;
-  RsSched sched;
+  RsSched sched{};
   sched.p_blocks = (rows_p + 127) / 128;
   sched.q_blocks = (rows_q + BN - 1) / BN;
   sched.num_kb = (K + 63) / 64;
@@ -356,8 +400,26 @@ int launch_rs(const void* x, const void* w, int M, int N, int K, int64_t ldx, in
   sched.swap = SWAP;
   constexpr int TM = SWAP ? BN : 128;
   sched.m_tiles = SWAP ? sched.q_blocks : sched.p_blocks;
-  const int own_last_row = min(M, (prm.rank + 1) * prm.R) - 1;
-  sched.first_tile = own_last_row >= prm.rank * prm.R ? (own_last_row / TM + 1) % sched.m_tiles : 0;
+  if (sched.m_tiles > kMaxRowTiles) return -kTooLarge;
+  {
+    // a row-tile belongs to the owner of its first row; visit owners round-robin starting after this rank
+    int next_of[kMaxTp], end_of[kMaxTp];
+    for (int o = 0; o < prm.tp; ++o) {
+      next_of[o] = (o * prm.R + TM - 1) / TM;
+      end_of[o] = ((o + 1) * prm.R + TM - 1) / TM;
+      if (next_of[o] > sched.m_tiles) next_of[o] = sched.m_tiles;
+      if (end_of[o] > sched.m_tiles) end_of[o] = sched.m_tiles;
+    }
+    next_of[0] = 0;
+    end_of[prm.tp - 1] = sched.m_tiles;
+    int n = 0;
+    while (n < sched.m_tiles) {
+      for (int d = 1; d <= prm.tp && n < sched.m_tiles; ++d) {
+        const int o = (prm.rank + d) % prm.tp;
+        if (next_of[o] < end_of[o]) sched.order[n++] = static_cast<int16_t>(next_of[o]++);
+      }
+    }
+  }
   prm.p_blocks = sched.p_blocks;
   prm.q_blocks = sched.q_blocks;
   auto kern = gemm_rs_kernel<BN, STAGES, SWAP>;
@@ -366,8 +428,12 @@ int launch_rs(const void* x, const void* w, int M, int N, int K, int64_t ldx, in
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
     attr_set = true;
   }
-  // Always a full persistent grid: CTAs without GEMM tiles still take part in the reduce phase.
-  kern<<<kNumSMs, gemm::kThreads, SMEM, stream>>>(tp, tq, sched, prm, ectl, status);
+  // Full persistent grid: the last CTAs only reduce from the start, the others join once their tiles are done.
+  const int n_red = prm.tp > 1 ? 8 : 0;
+  const int total = sched.p_blocks * sched.q_blocks;
+  int n_gemm = kNumSMs - n_red;
+  if (total < n_gemm) n_gemm = total;
+  kern<<<kNumSMs, gemm::kThreads, SMEM, stream>>>(tp, tq, sched, prm, ectl, n_gemm, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
 }
 
@@ -487,28 +553,75 @@ struct PlainEpilogue {
 };
 
 // Data-movement CTAs: copy this rank's rows into every peer's gathered buffer, one flag per chunk per peer.
-__device__ void ag_push(const AgParams& p, int comm_cta) {
+// A chunk of rows is one contiguous byte range, so one thread drives it with bulk async copies: local memory ->
+// shared memory (mbarrier completion) -> every peer (bulk store), 32 KB pieces through a 4-deep ring with the
+// loads issued two pieces ahead. `smem` is a 128-byte aligned shared-memory window of kAgRingBytes + 64.
+constexpr int kAgPiece = 32 * 1024;
+constexpr int kAgStages = 4;
+constexpr int kAgRingBytes = kAgPiece * kAgStages;
+
+__device__ void ag_push(const AgParams& p, int comm_cta, uint8_t* smem, Status* status) {
+  if (threadIdx.x != 0) return;
+  const uint32_t ring = ptx::smem_u32(smem);
+  const uint32_t bars = ring + kAgRingBytes;
+  for (int s = 0; s < kAgStages; ++s) ptx::mbar_init(bars + 8 * s, 1);
+  ptx::fence_mbar_init();
   const int row0 = p.rank * p.R;
-  const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.peer[p.rank] + p.off_xall);
-  const int vec_per_row = p.K >> 3;
+  const uint8_t* src = p.peer[p.rank] + p.off_xall;
+  const int64_t row_bytes = static_cast<int64_t>(p.K) * 2;
+  long issued = 0, consumed = 0;  // pieces over the whole kernel (ring positions / phases)
   for (int c = comm_cta; c < p.chunks_per_rank; c += p.n_comm) {
     const int r_lo = row0 + c * p.chunk_rows;
     const int r_hi = min(min(p.M, row0 + p.R), r_lo + p.chunk_rows);
-    const int64_t n_vec = static_cast<int64_t>(max(0, r_hi - r_lo)) * vec_per_row;
-    const int64_t base = static_cast<int64_t>(r_lo) * p.K;
-    for (int d = 1; d < p.tp; ++d) {
-      const int peer = (p.rank + d) % p.tp;
-      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.peer[peer] + p.off_xall);
-      for (int64_t i = threadIdx.x; i < n_vec; i += blockDim.x)
-        ptx::st_v4(dst + base + i * 8, ptx::ld_v4(src + base + i * 8));
+    const int64_t base = static_cast<int64_t>(r_lo) * row_bytes;
+    const int64_t total = static_cast<int64_t>(max(0, r_hi - r_lo)) * row_bytes;
+    const int n_pieces = static_cast<int>((total + kAgPiece - 1) / kAgPiece);
+    int next_load = 0;
+    bool ok = true;
+    for (int i = 0; i < n_pieces && ok; ++i) {
+      // keep two loads in flight; a ring slot is reusable once the stores that read it have finished reading
+      while (next_load < n_pieces && next_load < i + 2) {
+        if (issued >= kAgStages) ptx::tma_store_wait_read<kAgStages - 2>();
+        const int s = static_cast<int>(issued % kAgStages);
+        const int64_t off = static_cast<int64_t>(next_load) * kAgPiece;
+        const uint32_t bytes = static_cast<uint32_t>((total - off < kAgPiece ? total - off : static_cast<int64_t>(kAgPiece)));
+        ptx::mbar_arrive_expect_tx(bars + 8 * s, bytes);
+        ptx::bulk_load(ring + s * kAgPiece, src + base + off, bytes, bars + 8 * s);
+        ++issued;
+        ++next_load;
+      }
+      const int s = static_cast<int>(consumed % kAgStages);
+      if (!ptx::mbar_wait(bars + 8 * s, static_cast<uint32_t>((consumed / kAgStages) & 1))) {
+        status_record(status, kTimeout, kSiteAgChunk, c, i);
+        ok = false;
+        break;
+      }
+      const int64_t off = static_cast<int64_t>(i) * kAgPiece;
+      const uint32_t bytes = static_cast<uint32_t>((total - off < kAgPiece ? total - off : static_cast<int64_t>(kAgPiece)));
+      for (int d = 1; d < p.tp; ++d) {
+        const int peer = (p.rank + d) % p.tp;
+        ptx::bulk_store(p.peer[peer] + p.off_xall + base + off, ring + s * kAgPiece, bytes);
+      }
+      ptx::tma_store_commit();
+      ++consumed;
     }
+    // the chunk is complete on every peer before its flag goes up
+    ptx::tma_store_wait<0>();
+    ptx::fence_proxy_async_all();
     __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x >= 1 && threadIdx.x < p.tp) {
-      const int peer = (p.rank + threadIdx.x) % p.tp;
-      ptx::st_release_sys(reinterpret_cast<uint32_t*>(p.peer[peer] + p.off_flags) + p.rank * p.chunks_per_rank + c, p.epoch);
+    if (ok)
+      for (int d = 1; d < p.tp; ++d) {
+        const int peer = (p.rank + d) % p.tp;
+        ptx::st_release_sys(reinterpret_cast<uint32_t*>(p.peer[peer] + p.off_flags) + p.rank * p.chunks_per_rank + c, p.epoch);
+      }
+    if (!ok) {
+      // let loads that were issued but not consumed land before the shared memory is released
+      while (consumed < issued) {
+        ptx::mbar_wait(bars + 8 * static_cast<int>(consumed % kAgStages), static_cast<uint32_t>((consumed / kAgStages) & 1), 200000000ull);
+        ++consumed;
+      }
+      return;
     }
-    __syncthreads();
   }
 }
 
@@ -520,7 +633,9 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant
   prm.epoch = epoch_begin(ectl);
   const int n_gemm = static_cast<int>(gridDim.x) - prm.n_comm;
   if (static_cast<int>(blockIdx.x) >= n_gemm) {
-    ag_push(prm, static_cast<int>(blockIdx.x) - n_gemm);
+    extern __shared__ uint8_t smem_dyn[];
+    uint8_t* win = smem_dyn + ((128 - (reinterpret_cast<uintptr_t>(smem_dyn) & 127)) & 127);
+    ag_push(prm, static_cast<int>(blockIdx.x) - n_gemm, win, status);
     epoch_end(ectl, prm.epoch);
     return;
   }
@@ -536,7 +651,10 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant
 __global__ void __launch_bounds__(256) ag_push_kernel(AgParams prm_in, EpochCtl ectl, Status* status) {
   AgParams prm = prm_in;
   prm.epoch = epoch_begin(ectl);
-  ag_push(prm, static_cast<int>(blockIdx.x));
+  extern __shared__ uint8_t smem_dyn[];
+  uint8_t* win = smem_dyn + ((128 - (reinterpret_cast<uintptr_t>(smem_dyn) & 127)) & 127);
+  ag_push(prm, static_cast<int>(blockIdx.x), win, status);
+  __syncthreads();
   // wait for every peer's chunks so the gathered buffer is complete when the kernel ends
   if (blockIdx.x == 0) {
     const uint32_t* flags = reinterpret_cast<const uint32_t*>(prm.peer[prm.rank] + prm.off_flags);
@@ -602,6 +720,14 @@ __global__ void wait_flag_kernel(const uint32_t* flag, uint32_t want, uint64_t t
   if (threadIdx.x == 0 && !ptx::wait_flag_ge_sys(flag, want, timeout_ns)) status_record(status, kTimeout, kSiteTest, want, 0);
 }
 
+// rows per all-gather flag chunk: about 16 chunks per rank, at most 128 rows each
+int ag_chunk_rows(int R) {
+  int c = (R + 15) / 16;
+  if (c > 128) c = 128;
+  if (c < 1) c = 1;
+  return c;
+}
+
 int pick_bn_swap(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 
 }  // namespace
@@ -643,7 +769,7 @@ extern "C" int b2_tp_gemm_rs_bf16(const void* x, const void* w, const B2TpRegion
   prm.out = static_cast<__nv_bfloat16*>(out);
   prm.timeout_ns = timeout_ns;
   bool swap = M <= 128;
-  int bn = swap ? pick_bn_swap(M) : ((M + 127) / 128 * ((N + 255) / 256) >= 148 ? 256 : 128);
+  int bn = swap ? pick_bn_swap(M) : 128;
   if (config != 0) {
     swap = (config >> 30) & 1;
     bn = config & 0xffff;
@@ -686,7 +812,7 @@ extern "C" int b2_tp_ag_gemm_bf16(const void* w, const B2TpRegion* reg, const B2
   prm.M = M;
   prm.K = K;
   prm.R = M / tp;
-  prm.chunk_rows = prm.R < 128 ? prm.R : 128;
+  prm.chunk_rows = ag_chunk_rows(prm.R);
   prm.chunks_per_rank = (prm.R + prm.chunk_rows - 1) / prm.chunk_rows;
   prm.epoch = 0;
   const int parity = slot & 1;
@@ -697,7 +823,7 @@ extern "C" int b2_tp_ag_gemm_bf16(const void* w, const B2TpRegion* reg, const B2
   if (static_cast<int64_t>(tp) * prm.chunks_per_rank * 4 > lay->ag_flags_bytes) return -kTooLarge;
   prm.off_xall = lay->off_xall + parity * lay->xall_half_bytes;
   prm.off_flags = lay->off_ag_flags;
-  prm.n_comm = tp > 1 ? (n_comm > 0 ? n_comm : 16) : 0;
+  prm.n_comm = tp > 1 ? (n_comm > 0 ? n_comm : 8) : 0;
   if (prm.n_comm > prm.chunks_per_rank && tp > 1) prm.n_comm = prm.chunks_per_rank;
   prm.timeout_ns = timeout_ns;
   const void* xall_local = prm.peer[prm.rank] + prm.off_xall;
@@ -737,7 +863,7 @@ extern "C" int b2_tp_all_gather(const B2TpRegion* reg, const B2TpLayout* lay, in
   prm.M = M;
   prm.K = K;
   prm.R = M / reg->tp;
-  prm.chunk_rows = prm.R < 128 ? prm.R : 128;
+  prm.chunk_rows = ag_chunk_rows(prm.R);
   prm.chunks_per_rank = (prm.R + prm.chunk_rows - 1) / prm.chunk_rows;
   prm.epoch = 0;
   const int parity = slot & 1;
@@ -750,7 +876,13 @@ extern "C" int b2_tp_all_gather(const B2TpRegion* reg, const B2TpLayout* lay, in
   prm.off_flags = lay->off_ag_flags;
   prm.n_comm = prm.chunks_per_rank < 32 ? prm.chunks_per_rank : 32;
   prm.timeout_ns = timeout_ns;
-  ag_push_kernel<<<prm.n_comm, 256, 0, stream>>>(prm, ectl, status);
+  constexpr int kPushSmem = kAgRingBytes + 64 + 128;
+  static bool push_attr = false;
+  if (!push_attr) {
+    if (cudaFuncSetAttribute(ag_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPushSmem) != cudaSuccess) return -kBadArgument;
+    push_attr = true;
+  }
+  ag_push_kernel<<<prm.n_comm, 256, kPushSmem, stream>>>(prm, ectl, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
 }
 

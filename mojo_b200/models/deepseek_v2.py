@@ -40,6 +40,7 @@ class DsLayer:
     w_shared_down: torch.Tensor | None = None
     w_exp_gu: torch.Tensor | None = None  # [E_local, 2F_moe, hidden] (gate rows then up rows per expert)
     w_exp_down: torch.Tensor | None = None  # [E_local, hidden, F_moe]
+    w_exp_gu_il: torch.Tensor | None = None  # [E_local, 2F_moe, hidden] gate/up interleaved in blocks of 16 (EP kernels)
 
 
 class DeepseekV2Model:
@@ -94,6 +95,9 @@ class DeepseekV2Model:
                 dn = rnd(cfg.n_routed_experts, h, fm)
                 lw.w_exp_gu = self._put(gu[e0:e0 + self.e_local])
                 lw.w_exp_down = self._put(dn[e0:e0 + self.e_local])
+                if self.ep is not None:
+                    lw.w_exp_gu_il = torch.stack([reference.interleave_gate_up(w[:fm], w[fm:]) for w in lw.w_exp_gu])
+                    lw.w_exp_gu = None
                 del gu, dn
             self.layers.append(lw)
         self.final_norm = self._put(torch.ones(h))
@@ -169,18 +173,20 @@ class DeepseekV2Model:
     def _moe(self, lw: DsLayer, x: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
         logits = ops.linear(x, lw.w_router)
-        weights, ids = reference.moe_route(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, cfg.routed_scaling_factor)
+        shared = None
+        if lw.w_shared_gu is not None:
+            shared = ops.linear(ops.linear_swiglu(x, lw.w_shared_gu), lw.w_shared_down)
         if self.ep is not None:
-            routed = self.ep.moe(x, weights, ids, lw.w_exp_gu, lw.w_exp_down)
-        elif x.is_cuda:
+            # fused path: router + dispatch, grouped GEMMs, combine (+ shared) in the expert-parallel kernels
+            return self.ep.moe(x, logits, lw.w_exp_gu_il, lw.w_exp_down, shared, cfg.norm_topk_prob, cfg.routed_scaling_factor)
+        weights, ids = reference.moe_route(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, cfg.routed_scaling_factor)
+        if x.is_cuda:
             from ..parallel.ep import local_moe
 
             routed = local_moe(x, weights, ids, lw.w_exp_gu, lw.w_exp_down)
         else:
             routed = reference.moe_forward(x, lw.w_exp_gu, lw.w_exp_down, weights, ids).to(x.dtype)
-        if lw.w_shared_gu is not None:
-            routed = routed + ops.linear(ops.linear_swiglu(x, lw.w_shared_gu), lw.w_shared_down)
-        return routed
+        return routed + shared if shared is not None else routed
 
     def forward(self, token_ids, positions, slots, meta: ops.AttnMeta, kv_caches, sample_rows):
         cfg = self.cfg

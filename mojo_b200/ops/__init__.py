@@ -194,6 +194,36 @@ def linear_fp8(x, w_q: torch.Tensor, w_scale: torch.Tensor, out: torch.Tensor | 
     return out
 
 
+GGML_Q4_K, GGML_Q6_K = 12, 14
+_GGML_BLOCK_BYTES = {GGML_Q4_K: 144, GGML_Q6_K: 210}
+
+
+def gguf_dequant(w_q: torch.Tensor, ggml_type: int, shape) -> torch.Tensor:
+    """Packed Q4_K / Q6_K super-blocks (uint8) -> bf16 tensor of `shape` (rows x K, K a multiple of 256)."""
+    if not w_q.is_cuda:
+        return reference.gguf_dequant(w_q, ggml_type, shape)
+    C = _ext.require()
+    out = torch.empty(*shape, dtype=torch.bfloat16, device=w_q.device)
+    C.gguf_dequant(w_q, ggml_type, out)
+    _count()
+    return out
+
+
+def linear_gguf(x: torch.Tensor, w_q: torch.Tensor, ggml_type: int, n_out: int) -> torch.Tensor:
+    """y = x @ dequant(w_q).T with the dequantisation fused into the GEMM (decode-sized M); larger M dequantises once
+    and runs the bf16 GEMM."""
+    K = x.shape[1]
+    if not x.is_cuda:
+        return reference.linear(x, reference.gguf_dequant(w_q, ggml_type, (n_out, K))).to(x.dtype)
+    if x.shape[0] > 128:
+        return linear(x, gguf_dequant(w_q, ggml_type, (n_out, K)))
+    C = _ext.require()
+    y = torch.empty(x.shape[0], n_out, dtype=x.dtype, device=x.device)
+    C.gemm_gguf(x, w_q, ggml_type, y, _state.get(x.device).status)
+    _count()
+    return y
+
+
 def gemm_config(swap: bool, bn: int, splits: int = 1) -> int:
     """Encode an explicit GEMM configuration (for tuning sweeps): operand swap, UMMA N, split-K factor."""
     return (int(swap) << 30) | (splits << 16) | bn

@@ -320,3 +320,70 @@ def moe_forward(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
         y = h @ w_down[e].float().t()
         out.index_add_(0, tok, y * weights[tok, slot].unsqueeze(-1).float())
     return out
+
+
+# ------------------------------------------------------------------------------------------------------
+# GGUF k-quants
+# ------------------------------------------------------------------------------------------------------
+
+
+def gguf_dequant(w_q: torch.Tensor, ggml_type: int, shape) -> torch.Tensor:
+    """Q4_K (type 12) / Q6_K (type 14) super-blocks -> fp32, restated from the block layout (256 weights per block:
+    Q4_K = f16 d, f16 dmin, 12 packed 6-bit scales/mins, 128 nibble bytes; Q6_K = 128 low-nibble bytes, 64 bytes of
+    2-bit highs, 16 int8 scales, f16 d)."""
+    import numpy as np
+
+    raw = w_q.detach().cpu().numpy().view(np.uint8).reshape(-1)
+    if ggml_type == 12:
+        b = raw.reshape(-1, 144)
+        d = b[:, 0:2].copy().view(np.float16).astype(np.float32)
+        dmin = b[:, 2:4].copy().view(np.float16).astype(np.float32)
+        sc = b[:, 4:16].astype(np.int32)
+        qs = b[:, 16:144]
+        scales = np.zeros((b.shape[0], 8), np.float32)
+        mins = np.zeros((b.shape[0], 8), np.float32)
+        for j in range(8):
+            if j < 4:
+                scales[:, j] = sc[:, j] & 63
+                mins[:, j] = sc[:, j + 4] & 63
+            else:
+                scales[:, j] = (sc[:, j + 4] & 0xF) | ((sc[:, j - 4] >> 6) << 4)
+                mins[:, j] = (sc[:, j + 4] >> 4) | ((sc[:, j] >> 6) << 4)
+        out = np.zeros((b.shape[0], 256), np.float32)
+        for j in range(8):
+            q = qs[:, (j // 2) * 32:(j // 2) * 32 + 32]
+            q = (q >> 4) if (j & 1) else (q & 0xF)
+            out[:, j * 32:(j + 1) * 32] = d * scales[:, j:j + 1] * q - dmin * mins[:, j:j + 1]
+    elif ggml_type == 14:
+        b = raw.reshape(-1, 210)
+        ql, qh = b[:, :128].astype(np.int32), b[:, 128:192].astype(np.int32)
+        sc = b[:, 192:208].copy().view(np.int8).astype(np.float32)
+        d = b[:, 208:210].copy().view(np.float16).astype(np.float32)
+        out = np.zeros((b.shape[0], 256), np.float32)
+        for half in range(2):
+            for quarter in range(4):
+                l = np.arange(32)
+                lo = ql[:, half * 64 + (quarter & 1) * 32 + l]
+                lo = (lo >> 4) if quarter >= 2 else (lo & 0xF)
+                hi = (qh[:, half * 32 + l] >> (2 * quarter)) & 3
+                q = (lo | (hi << 4)) - 32
+                s_ = sc[:, half * 8 + quarter * 2 + (l >> 4)]
+                out[:, half * 128 + quarter * 32:half * 128 + quarter * 32 + 32] = d * s_ * q
+    else:
+        raise ValueError(f"unsupported ggml type {ggml_type}")
+    return torch.from_numpy(out.reshape(shape))
+
+
+def random_gguf_blocks(n_blocks: int, ggml_type: int, seed: int = 0) -> torch.Tensor:
+    """Random but well-formed super-blocks (finite f16 scales) for tests."""
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    nb = 144 if ggml_type == 12 else 210
+    b = rng.integers(0, 256, size=(n_blocks, nb), dtype=np.uint8)
+    if ggml_type == 12:
+        b[:, 0:2] = rng.uniform(0.001, 0.02, size=(n_blocks, 1)).astype(np.float16).view(np.uint8)
+        b[:, 2:4] = rng.uniform(0.001, 0.02, size=(n_blocks, 1)).astype(np.float16).view(np.uint8)
+    else:
+        b[:, 208:210] = rng.uniform(0.0005, 0.004, size=(n_blocks, 1)).astype(np.float16).view(np.uint8)
+    return torch.from_numpy(b.reshape(-1))

@@ -52,7 +52,7 @@ class FusedTPComm:
         units = ((r_max + 15) // 16 + 2) * ((hidden + 63) // 64)
         lay.rs_flags_bytes = _align(units * tp * 4)
         lay.off_rs_flags = take(lay.rs_flags_bytes)
-        lay.ag_flags_bytes = _align(tp * (r_max // 128 + 2) * 4)
+        lay.ag_flags_bytes = _align(tp * (r_max // 128 + 20) * 4)
         lay.off_ag_flags = take(lay.ag_flags_bytes)
         lay.off_res_flags = take(64)
         lay.off_done = take(64)

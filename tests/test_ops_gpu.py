@@ -235,6 +235,59 @@ def test_mla_decode_absorbed(page, B, H, ctxs):
     _close(got, want, 2e-2, 2e-2)
 
 
+@pytest.mark.parametrize("T,E,k,H,F", [(37, 8, 2, 256, 128), (200, 64, 6, 512, 256), (1, 16, 4, 256, 64), (512, 64, 6, 2048, 1408)])
+def test_moe_dispatch_grouped_gemm_combine_single_rank(T, E, k, H, F):
+    from mojo_b200.parallel.dist import DistInfo
+    from mojo_b200.parallel.ep import EPComm
+
+    g = torch.Generator().manual_seed(10)
+    info = DistInfo(0, 1, 0, torch.device("cuda", torch.cuda.current_device()))
+    ep = EPComm(info, E, H, F, k, max_tokens=max(T, 64), timeout_s=5.0)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    # distinct, bf16-exact logits per row: top-k is then unique (torch.topk and the kernel break ties differently)
+    logits = torch.stack([torch.randperm(E, generator=g) for _ in range(T)]).float().mul(0.125).sub(E / 16).bfloat16()
+    wg = (torch.randn(E, F, H, generator=g) * 0.05).bfloat16()
+    wu = (torch.randn(E, F, H, generator=g) * 0.05).bfloat16()
+    wd = (torch.randn(E, H, F, generator=g) * 0.05).bfloat16()
+    shared = torch.randn(T, H, generator=g).bfloat16()
+    w_ref, id_ref = ref.moe_route(logits, k, norm_topk=True, scale=1.5)
+    want = ref.moe_forward(x, torch.cat([wg, wu], dim=1), wd, w_ref, id_ref) + shared.float()
+    w_il = torch.stack([ref.interleave_gate_up(wg[e], wu[e]) for e in range(E)]).to(DEV)
+    for rep in range(3):            # both counter banks and a reuse
+        got = ep.moe(x.to(DEV), logits.to(DEV), w_il, wd.to(DEV), shared.to(DEV), norm_topk=True, route_scale=1.5)
+        torch.cuda.synchronize()
+        ops.check_status()
+        assert torch.equal(ep.last_ids.cpu().long().sort(dim=1).values, id_ref.sort(dim=1).values)
+        _close(ep.last_weights.cpu().sort(dim=1).values, w_ref.sort(dim=1).values, 2e-3, 2e-3)
+        _close(got, want, 0.03 * want.abs().max().item() + 0.02, 3e-2)
+
+
+@pytest.mark.parametrize("ggml_type", [12, 14])
+def test_gguf_dequant_and_fused_gemm(ggml_type):
+    N, K = 384, 1024
+    wq = ref.random_gguf_blocks(N * K // 256, ggml_type, seed=ggml_type)
+    w_ref = ref.gguf_dequant(wq, ggml_type, (N, K))
+    try:
+        import numpy as np
+        from gguf import GGMLQuantizationType, quants
+
+        nb = 144 if ggml_type == 12 else 210
+        theirs = quants.dequantize(wq.numpy().reshape(N, K // 256 * nb), GGMLQuantizationType(ggml_type))
+        np.testing.assert_allclose(theirs.reshape(N, K), w_ref.numpy(), rtol=1e-5, atol=1e-6)   # oracle vs the gguf package
+    except ImportError:
+        pass
+    w_dev = ops.gguf_dequant(wq.to(DEV), ggml_type, (N, K))
+    _close(w_dev, w_ref, 2e-3 * w_ref.abs().max().item(), 1e-2)
+    g = torch.Generator().manual_seed(12)
+    for M in (1, 16, 40, 100):
+        x = torch.randn(M, K, generator=g).bfloat16()
+        want = x.float() @ w_ref.t()
+        got = ops.linear_gguf(x.to(DEV), wq.to(DEV), ggml_type, N)
+        _close(got, want, 0.02 * want.abs().max().item() + 1e-2, 2e-2)
+    x = torch.randn(300, K, generator=g).bfloat16()        # large M: dequantise once + bf16 GEMM
+    _close(ops.linear_gguf(x.to(DEV), wq.to(DEV), ggml_type, N), x.float() @ w_ref.t(), 0.05, 2e-2)
+
+
 def test_argmax_and_sampling():
     g = torch.Generator().manual_seed(5)
     logits = torch.randn(9, 32003, generator=g) * 3
