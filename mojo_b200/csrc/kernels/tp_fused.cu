@@ -226,7 +226,7 @@ __device__ bool reduce_phase(const RsParams& p, Status* status) {
     const int c_lo = tn * TN, c_hi = min(p.N, tn * TN + TN);
     const int vec_per_row = (c_hi - c_lo) >> 3;
     const int n_vec = (r_hi - r_lo) * vec_per_row;
-    constexpr int U = 8;  // independent 16-byte vectors per thread per pass: keeps tp * U loads in flight
+    constexpr int U = 4;  // independent 16-byte vectors per thread per pass: keeps tp * U loads in flight
     for (int i0 = threadIdx.x; i0 < n_vec; i0 += blockDim.x * U) {
       uint4 raw[U][kMaxTp];
       int64_t off[U];
@@ -429,7 +429,7 @@ int launch_rs(const void* x, const void* w, int M, int N, int K, int64_t ldx, in
     attr_set = true;
   }
   // Full persistent grid: the last CTAs only reduce from the start, the others join once their tiles are done.
-  const int n_red = prm.tp > 1 ? 8 : 0;
+  const int n_red = prm.tp > 1 ? 12 : 0;
   const int total = sched.p_blocks * sched.q_blocks;
   int n_gemm = kNumSMs - n_red;
   if (total < n_gemm) n_gemm = total;

@@ -1,0 +1,213 @@
+"""FastAPI application over the engine.
+
+The engine's hot loop runs in its own thread (`AsyncEngine`): HTTP handlers enqueue requests and receive tokens
+through per-request asyncio queues, the engine thread drains the inbox between steps. This is the product's form of
+the reference's coroutine plumbing (stdlib/src/builtin/coroutine.mojo:83-249): asyncio on the serving side, a plain
+loop on the device side. A watchdog records the time of the last completed step; `/health` turns unhealthy when the
+loop stops making progress while requests are pending, or when a kernel reported an error status.
+"""
+from __future__ import annotations
+
+import asyncio
+import json
+import queue
+import threading
+import time
+import uuid
+
+from ..engine import SamplingParams
+
+
+class AsyncEngine:
+    def __init__(self, llm):
+        self.llm = llm
+        self.engine = llm.engine
+        self.inbox: queue.Queue = queue.Queue()
+        self.streams: dict[int, tuple[asyncio.AbstractEventLoop, asyncio.Queue]] = {}
+        self.last_step = time.time()
+        self.error: str | None = None
+        self._stop = threading.Event()
+        self.thread = threading.Thread(target=self._loop, daemon=True, name="b2-engine")
+        self.thread.start()
+
+    def _loop(self) -> None:
+        eng = self.engine
+        while not self._stop.is_set():
+            try:
+                while True:
+                    kind, payload = self.inbox.get_nowait()
+                    if kind == "add":
+                        rid, ids, sp, loop, q = payload
+                        try:
+                            eng.add_request(ids, sp, request_id=rid)
+                            self.streams[rid] = (loop, q)
+                        except Exception as e:  # noqa: BLE001  (bad request: tell the client, keep serving)
+                            loop.call_soon_threadsafe(q.put_nowait, ("error", str(e)))
+                    elif kind == "abort":
+                        eng.abort_request(payload)
+                        self.streams.pop(payload, None)
+            except queue.Empty:
+                pass
+            if not eng.has_unfinished():
+                self.last_step = time.time()
+                time.sleep(0.001)
+                continue
+            try:
+                outs = eng.step()
+            except Exception as e:  # noqa: BLE001  (kernel status error etc.): fail in-flight requests, stay alive
+                self.error = repr(e)
+                for rid, (loop, q) in list(self.streams.items()):
+                    loop.call_soon_threadsafe(q.put_nowait, ("error", self.error))
+                    eng.abort_request(rid)
+                self.streams.clear()
+                continue
+            self.last_step = time.time()
+            for o in outs:
+                s = self.streams.get(o.request_id)
+                if s is None:
+                    continue
+                loop, q = s
+                loop.call_soon_threadsafe(q.put_nowait, ("token", (o.new_token_ids, o.finished, o.finish_reason)))
+                if o.finished:
+                    self.streams.pop(o.request_id, None)
+
+    _ids = 0
+    _ids_lock = threading.Lock()
+
+    def submit(self, ids, sp: SamplingParams) -> tuple[int, asyncio.Queue]:
+        with AsyncEngine._ids_lock:
+            AsyncEngine._ids += 1
+            rid = AsyncEngine._ids
+        q: asyncio.Queue = asyncio.Queue()
+        self.inbox.put(("add", (rid, list(ids), sp, asyncio.get_running_loop(), q)))
+        return rid, q
+
+    def abort(self, rid: int) -> None:
+        self.inbox.put(("abort", rid))
+
+    def healthy(self) -> bool:
+        stalled = self.engine.has_unfinished() and time.time() - self.last_step > 30.0
+        return self.thread.is_alive() and not stalled
+
+    def shutdown(self) -> None:
+        self._stop.set()
+
+
+def _sampling_from(body: dict, default_max: int = 16) -> SamplingParams:
+    stop_ids = tuple(body.get("stop_token_ids") or ())
+    return SamplingParams(temperature=float(body.get("temperature", 0.0) or 0.0), top_k=int(body.get("top_k", 0) or 0),
+                          top_p=float(body.get("top_p", 1.0) or 1.0), max_tokens=int(body.get("max_tokens") or default_max),
+                          stop_token_ids=stop_ids, ignore_eos=bool(body.get("ignore_eos", False)), seed=body.get("seed"))
+
+
+def build_app(llm, model_name: str = "mojo_b200"):
+    from fastapi import FastAPI, HTTPException
+    from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+
+    app = FastAPI(title="mojo_b200")
+    aeng = AsyncEngine(llm)
+    app.state.engine = aeng
+    tok = llm.tokenizer
+
+    def text_of(ids):
+        t = tok.decode(ids)
+        return t if t is not None else " ".join(str(i) for i in ids)
+
+    async def collect(q):
+        out, reason = [], None
+        while True:
+            kind, payload = await q.get()
+            if kind == "error":
+                raise HTTPException(status_code=500, detail=payload)
+            new, finished, reason = payload
+            out.extend(new)
+            if finished:
+                return out, reason
+
+    async def sse(q, rid, make_chunk, final_chunk):
+        try:
+            while True:
+                kind, payload = await q.get()
+                if kind == "error":
+                    yield f"data: {json.dumps({'error': payload})}\n\n"
+                    break
+                new, finished, reason = payload
+                yield f"data: {json.dumps(make_chunk(new, reason if finished else None))}\n\n"
+                if finished:
+                    if final_chunk is not None:
+                        yield f"data: {json.dumps(final_chunk(reason))}\n\n"
+                    break
+            yield "data: [DONE]\n\n"
+        finally:
+            aeng.abort(rid)
+
+    @app.get("/health")
+    async def health():
+        ok = aeng.healthy()
+        return JSONResponse({"status": "ok" if ok else "unhealthy", "last_error": aeng.error}, status_code=200 if ok else 503)
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": model_name, "object": "model", "owned_by": "mojo_b200"}]}
+
+    @app.get("/metrics")
+    async def metrics():
+        m = aeng.engine.metrics()
+        lines = []
+        for k, v in m.items():
+            if isinstance(v, (int, float)) and v is not None:
+                lines.append(f"# TYPE b2_{k} gauge\nb2_{k} {v}")
+        lines.append(f"# TYPE b2_waiting gauge\nb2_waiting {aeng.engine.scheduler.num_waiting()}")
+        lines.append(f"# TYPE b2_running gauge\nb2_running {aeng.engine.scheduler.num_running()}")
+        return PlainTextResponse("\n".join(lines) + "\n")
+
+    @app.post("/v1/completions")
+    async def completions(body: dict):
+        prompt = body.get("prompt")
+        if prompt is None:
+            raise HTTPException(status_code=400, detail="prompt is required")
+        try:
+            ids = tok.encode(prompt)
+        except ValueError as e:
+            raise HTTPException(status_code=400, detail=str(e))
+        sp = _sampling_from(body)
+        rid, q = aeng.submit(ids, sp)
+        cid = "cmpl-" + uuid.uuid4().hex[:24]
+        created = int(time.time())
+        if body.get("stream"):
+            def chunk(new, reason):
+                return {"id": cid, "object": "text_completion", "created": created, "model": model_name,
+                        "choices": [{"index": 0, "text": text_of(new), "token_ids": new, "finish_reason": reason}]}
+            return StreamingResponse(sse(q, rid, chunk, None), media_type="text/event-stream")
+        out, reason = await collect(q)
+        return {"id": cid, "object": "text_completion", "created": created, "model": model_name,
+                "choices": [{"index": 0, "text": text_of(out), "token_ids": out, "finish_reason": reason}],
+                "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out), "total_tokens": len(ids) + len(out)}}
+
+    @app.post("/v1/chat/completions")
+    async def chat(body: dict):
+        messages = body.get("messages")
+        if not messages:
+            raise HTTPException(status_code=400, detail="messages is required")
+        ids = tok.apply_chat_template(messages)
+        sp = _sampling_from(body, default_max=256)
+        rid, q = aeng.submit(ids, sp)
+        cid = "chatcmpl-" + uuid.uuid4().hex[:24]
+        created = int(time.time())
+        if body.get("stream"):
+            first = {"sent": False}
+
+            def chunk(new, reason):
+                delta = {"content": text_of(new)}
+                if not first["sent"]:
+                    delta["role"] = "assistant"
+                    first["sent"] = True
+                return {"id": cid, "object": "chat.completion.chunk", "created": created, "model": model_name,
+                        "choices": [{"index": 0, "delta": delta, "finish_reason": reason}]}
+            return StreamingResponse(sse(q, rid, chunk, None), media_type="text/event-stream")
+        out, reason = await collect(q)
+        return {"id": cid, "object": "chat.completion", "created": created, "model": model_name,
+                "choices": [{"index": 0, "message": {"role": "assistant", "content": text_of(out)}, "finish_reason": reason}],
+                "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out), "total_tokens": len(ids) + len(out)}}
+
+    return app

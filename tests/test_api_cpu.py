@@ -1,0 +1,96 @@
+"""Pipelines API, loaders and the OpenAI-compatible server on CPU (tiny model, token-id passthrough)."""
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from mojo_b200.pipelines import LLM, PipelineConfig, SamplingParams
+
+
+def tiny_llm(**kw):
+    return LLM(PipelineConfig(model="tiny-llama", random_init=True, device="cpu", page_size=16, num_pages=64, max_num_seqs=8,
+                              max_num_batched_tokens=128, max_model_len=256, **kw))
+
+
+def test_llm_generate_and_stream_agree():
+    llm = tiny_llm()
+    prompt = list(range(100, 130))
+    out = llm.generate([prompt], SamplingParams(max_tokens=8))[0]
+    assert len(out.token_ids) == 8 and out.finish_reason == "length"
+    assert list(tiny_llm().stream(prompt, SamplingParams(max_tokens=8))) == out.token_ids
+    cfg = PipelineConfig.from_json(llm.config.to_json())
+    assert cfg == llm.config
+
+
+def test_safetensors_roundtrip_matches_random_init(tmp_path):
+    from mojo_b200.loaders.safetensors_loader import save_llama_safetensors
+    from mojo_b200.models.config import tiny_llama
+
+    cfg = tiny_llama()
+    g = torch.Generator().manual_seed(0)
+    full = {"model.embed_tokens.weight": torch.randn(cfg.vocab_size, cfg.hidden_size, generator=g) * 0.02,
+            "model.norm.weight": torch.ones(cfg.hidden_size)}
+    d = cfg.head_dim
+    for i in range(cfg.num_layers):
+        p = f"model.layers.{i}."
+        full[p + "input_layernorm.weight"] = torch.ones(cfg.hidden_size)
+        full[p + "post_attention_layernorm.weight"] = torch.ones(cfg.hidden_size)
+        for name, shape in (("self_attn.q_proj", (cfg.num_heads * d, cfg.hidden_size)), ("self_attn.k_proj", (cfg.num_kv_heads * d, cfg.hidden_size)),
+                            ("self_attn.v_proj", (cfg.num_kv_heads * d, cfg.hidden_size)), ("self_attn.o_proj", (cfg.hidden_size, cfg.num_heads * d)),
+                            ("mlp.gate_proj", (cfg.intermediate_size, cfg.hidden_size)), ("mlp.up_proj", (cfg.intermediate_size, cfg.hidden_size)),
+                            ("mlp.down_proj", (cfg.hidden_size, cfg.intermediate_size))):
+            full[p + name + ".weight"] = torch.randn(*shape, generator=g) * 0.02
+    hf_cfg = {"architectures": ["LlamaForCausalLM"], "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers,
+              "num_attention_heads": cfg.num_heads, "num_key_value_heads": cfg.num_kv_heads, "intermediate_size": cfg.intermediate_size,
+              "vocab_size": cfg.vocab_size, "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "max_position_embeddings": 2048,
+              "tie_word_embeddings": True}
+    save_llama_safetensors(full, tmp_path, hf_cfg)
+    llm = LLM(PipelineConfig(model=str(tmp_path), device="cpu", page_size=16, num_pages=32, max_num_seqs=4, max_num_batched_tokens=64, max_model_len=128))
+    assert torch.equal(llm.engine.model.layers[1].wo, full["model.layers.1.self_attn.o_proj.weight"])
+    out = llm.generate([[5, 6, 7, 8, 9]], SamplingParams(max_tokens=4))[0]
+    assert len(out.token_ids) == 4
+
+
+def test_gguf_file_roundtrip(tmp_path):
+    gguf = pytest.importorskip("gguf")
+    from mojo_b200.loaders.gguf_loader import GGUFFile
+    from mojo_b200.ops import reference as ref
+
+    path = tmp_path / "t.gguf"
+    w = gguf.GGUFWriter(str(path), "llama")
+    w.add_uint32("llama.block_count", 1)
+    raw = ref.random_gguf_blocks(4 * 512 // 256, 12, seed=1).numpy().reshape(4, 512 // 256 * 144)
+    w.add_tensor("blk.0.attn_q.weight", raw, raw_dtype=gguf.GGMLQuantizationType.Q4_K)
+    w.add_tensor("output_norm.weight", np.ones(8, dtype=np.float32))
+    w.write_header_to_file(); w.write_kv_data_to_file(); w.write_tensors_to_file(); w.close()
+    gf = GGUFFile(path)
+    kind, (ty, blocks), shape = gf.tensor("blk.0.attn_q.weight")
+    assert kind == "q" and ty == 12 and shape == (4, 512) and blocks.numel() == raw.size
+    assert torch.equal(ref.gguf_dequant(blocks, 12, shape), ref.gguf_dequant(torch.from_numpy(raw.reshape(-1)), 12, shape))
+    assert gf.tensor("output_norm.weight")[0] == "f" and gf.metadata()["llama.block_count"] == 1
+
+
+def test_openai_server_endpoints():
+    from fastapi.testclient import TestClient
+
+    from mojo_b200.serve import build_app
+
+    llm = tiny_llm()
+    want = tiny_llm().generate([[11, 12, 13, 14]], SamplingParams(max_tokens=5))[0].token_ids
+    app = build_app(llm, "tiny-llama")
+    with TestClient(app) as c:
+        assert c.get("/health").json()["status"] == "ok"
+        assert c.get("/v1/models").json()["data"][0]["id"] == "tiny-llama"
+        r = c.post("/v1/completions", json={"prompt": [11, 12, 13, 14], "max_tokens": 5}).json()
+        assert r["choices"][0]["token_ids"] == want and r["usage"]["completion_tokens"] == 5
+        with c.stream("POST", "/v1/completions", json={"prompt": [11, 12, 13, 14], "max_tokens": 5, "stream": True}) as s:
+            lines = [l for l in s.iter_lines() if l.startswith("data: ")]
+        assert lines[-1] == "data: [DONE]"
+        toks = [t for l in lines[:-1] for t in json.loads(l[6:])["choices"][0]["token_ids"]]
+        assert toks == want
+        r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3}).json()
+        assert r["object"] == "chat.completion" and r["usage"]["completion_tokens"] == 3
+        assert c.post("/v1/completions", json={"max_tokens": 3}).status_code == 400
+        assert "b2_output_tokens" in c.get("/metrics").text
+    app.state.engine.shutdown()
