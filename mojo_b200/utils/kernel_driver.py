@@ -1,0 +1,110 @@
+"""Run one hot kernel a handful of times on representative shapes: `python -m mojo_b200.utils.kernel_driver <case>`.
+
+Small, self-terminating workloads (inputs larger than the 126 MB L2, a few GB at most) meant to be wrapped by a
+profiler capture of one kernel; with `--time` the case is timed with CUDA events instead and one JSON line is printed.
+Cases: gemm_large, gemm_prefill, gemm_decode, gemm_swiglu, gemm_fp8, attn_decode, attn_prefill, mla_decode, rmsnorm, sampling.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+
+import torch
+
+from .. import ops
+from ..ops import reference as ref
+
+DEV = "cuda"
+
+
+def _case(name: str):
+    g = torch.Generator(device=DEV).manual_seed(0)
+
+    def rnd(*shape, scale=1.0):
+        return (torch.randn(*shape, generator=g, device=DEV) * scale).bfloat16()
+
+    if name in ("gemm_large", "gemm_prefill", "gemm_decode", "gemm_swiglu"):
+        M, N, K = {"gemm_large": (8192, 8192, 8192), "gemm_prefill": (4096, 6144, 4096), "gemm_decode": (64, 28672, 4096),
+                   "gemm_swiglu": (2048, 28672, 4096)}[name]
+        x, w = rnd(M, K), rnd(N, K, scale=0.02)
+        if name == "gemm_swiglu":
+            y = torch.empty(M, N // 2, device=DEV, dtype=torch.bfloat16)
+            return (lambda: ops.linear_swiglu(x, w, out=y)), 2.0 * M * N * K, (M * K + N * K + M * N // 2) * 2
+        y = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+        return (lambda: ops.linear(x, w, out=y)), 2.0 * M * N * K, (M * K + N * K + M * N) * 2
+    if name == "gemm_fp8":
+        M, N, K = 4096, 8192, 8192
+        xq, xs = ops.quant_e4m3(rnd(M, K))
+        wq, ws = ref.quant_e4m3_128x128(rnd(N, K, scale=0.02).float().cpu())
+        wq, ws = wq.to(DEV), ws.to(DEV)
+        y = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+        return (lambda: ops.linear_fp8((xq, xs), wq, ws, out=y)), 2.0 * M * N * K, M * K + N * K + M * N * 2
+    if name in ("attn_decode", "attn_prefill"):
+        n_q, n_kv, D, page = 32, 8, 128, 128
+        if name == "attn_decode":
+            q_lens, ctx = [1] * 256, [1400] * 256
+        else:
+            q_lens, ctx = [2048, 1024, 1024], [2048, 1024, 1024]
+        B, T = len(q_lens), sum(q_lens)
+        pages_per = [(c + page - 1) // page for c in ctx]
+        bt = torch.zeros(B, max(pages_per), dtype=torch.int32)
+        o = 0
+        for b, n in enumerate(pages_per):
+            bt[b, :n] = torch.arange(o, o + n, dtype=torch.int32)
+            o += n
+        kc, vc = rnd(o + 1, n_kv, page, D), rnd(o + 1, n_kv, page, D)
+        q = rnd(T, n_q * D)
+        cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+        cl = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+        nd = B if name == "attn_decode" else 0
+        meta = ops.AttnMeta(cu, cl, bt.to(DEV), nd, max(q_lens), max(ctx))
+        kv_bytes = sum(ctx) * n_kv * D * 2 * 2
+        flops = sum(4.0 * ql * c * D * n_q * (0.5 if ql > 1 else 1.0) for ql, c in zip(q_lens, ctx))
+        return (lambda: ops.paged_attention(q, kc, vc, meta, 1 / math.sqrt(D), D)), flops, kv_bytes + 2 * T * n_q * D * 2
+    if name == "mla_decode":
+        B, H, ctx, page = 64, 16, 768, 128
+        pages = (ctx + page - 1) // page
+        bt = torch.arange(B * pages, dtype=torch.int32).view(B, pages).to(DEV)
+        cache = rnd(B * pages + 1, page, 576, scale=0.5)
+        ql, qr = rnd(B, H, 512, scale=0.3), rnd(B, H, 64, scale=0.3)
+        cl = torch.full((B,), ctx, dtype=torch.int32, device=DEV)
+        return (lambda: ops.mla_decode(ql, qr, cache, cl, bt, 1 / math.sqrt(192), ctx)), 2.0 * B * H * ctx * (576 + 512), B * ctx * 576 * 2
+    if name == "rmsnorm":
+        rows, h = 65536, 4096
+        x, r, w = rnd(rows, h), rnd(rows, h), torch.ones(h, device=DEV, dtype=torch.bfloat16)
+        return (lambda: ops.rms_norm(x, w, 1e-5, r)), 0.0, rows * h * 2 * 4
+    if name == "sampling":
+        lg = rnd(256, 128256)
+        return (lambda: ops.argmax(lg)), 0.0, lg.numel() * 2
+    raise SystemExit(f"unknown case {name!r}")
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case")
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--time", action="store_true")
+    a = ap.parse_args()
+    fn, flops, nbytes = _case(a.case)
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    if a.time:
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(a.iters):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        us = s.elapsed_time(e) * 1e3 / a.iters
+        print(json.dumps({"case": a.case, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1), "gbs": round(nbytes / us / 1e3, 1)}))
+    else:
+        for _ in range(a.iters):
+            fn()
+        torch.cuda.synchronize()
+    ops.check_status()
+
+
+if __name__ == "__main__":
+    main()
