@@ -87,6 +87,8 @@ def main() -> None:
     if args.layers is not None:
         mcfg.num_layers = args.layers
         debug_invalid = True
+    if args.impl == "torch-baseline":
+        args.comm = "nccl"
     comm = None
     if world > 1:
         if args.comm == "fused" and args.impl == "mojo_b200":
@@ -101,6 +103,8 @@ def main() -> None:
         from mojo_b200.ops import torch_baseline
 
         torch_baseline.enable()
+        args.no_graphs = True
+        args.comm = "nccl"
 
     max_model_len = 2048 + 512 + 128
     ecfg = EngineConfig(model=mcfg, device=str(device), dtype=torch.bfloat16, page_size=args.page_size,

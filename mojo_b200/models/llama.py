@@ -32,6 +32,12 @@ class LayerWeights:
     mlp_norm: torch.Tensor
     w_gu: torch.Tensor
     w_down: torch.Tensor
+    # fp8 block-scaled checkpoints: the four matrices above are float8_e4m3fn and these hold their f32 scales
+    # ([ceil(N/128), ceil(K/128)]); w_gu is then stacked gate-then-up (no interleave: scale blocks stay intact)
+    s_qkv: torch.Tensor | None = None
+    s_o: torch.Tensor | None = None
+    s_gu: torch.Tensor | None = None
+    s_down: torch.Tensor | None = None
 
 
 class NoComm:
@@ -130,6 +136,9 @@ class LlamaModel:
         k = w["wk"][kv_rank * self.n_kv * d:(kv_rank + 1) * self.n_kv * d]
         v = w["wv"][kv_rank * self.n_kv * d:(kv_rank + 1) * self.n_kv * d]
         f = self.ffn_local
+        if cfg.quantization == "fp8_block":
+            self._load_layer_fp8(idx, w, q, k, v)
+            return
         lw = LayerWeights(
             attn_norm=self._put(w["attn_norm"]),
             wqkv=self._put(torch.cat([q, k, v], dim=0)),
@@ -141,8 +150,46 @@ class LlamaModel:
         assert idx == len(self.layers)
         self.layers.append(lw)
 
+    def _load_layer_fp8(self, idx: int, w: dict, q, k, v) -> None:
+        """Keep the four linear weights in e4m3 with one f32 scale per 128x128 block. Checkpoint scales
+        (`w["scales"]`) are sliced with the weights; bf16 / random weights are quantised here."""
+        r, d, f = self.comm.rank, self.cfg.head_dim, self.ffn_local
+        sc = w.get("scales")
+
+        def quant(t):
+            qt, st = reference.quant_e4m3_128x128(t.to(self.device).float())
+            return qt.contiguous(), st.contiguous()
+
+        def put8(t):
+            return t.to(self.device).contiguous()
+
+        if sc is None:
+            wqkv, s_qkv = quant(torch.cat([q, k, v], dim=0))
+            wo, s_o = quant(w["wo"][:, r * self.n_q * d:(r + 1) * self.n_q * d])
+            wgu, s_gu = quant(torch.cat([w["w_gate"][r * f:(r + 1) * f], w["w_up"][r * f:(r + 1) * f]], dim=0))
+            wdn, s_dn = quant(w["w_down"][:, r * f:(r + 1) * f])
+        else:
+            def rows(name, lo, hi):
+                return w[name][lo:hi], sc[name][lo // 128:(hi + 127) // 128]
+
+            def cols(name, lo, hi):
+                return w[name][:, lo:hi], sc[name][:, lo // 128:(hi + 127) // 128]
+
+            kv_rank = r // self.kv_replicas
+            parts = [rows("wq", r * self.n_q * d, (r + 1) * self.n_q * d), rows("wk", kv_rank * self.n_kv * d, (kv_rank + 1) * self.n_kv * d),
+                     rows("wv", kv_rank * self.n_kv * d, (kv_rank + 1) * self.n_kv * d)]
+            wqkv, s_qkv = put8(torch.cat([p[0] for p in parts])), put8(torch.cat([p[1] for p in parts]).float())
+            wo, s_o = (put8(t) for t in cols("wo", r * self.n_q * d, (r + 1) * self.n_q * d))
+            g, u = rows("w_gate", r * f, (r + 1) * f), rows("w_up", r * f, (r + 1) * f)
+            wgu, s_gu = put8(torch.cat([g[0], u[0]])), put8(torch.cat([g[1], u[1]]).float())
+            wdn, s_dn = (put8(t) for t in cols("w_down", r * f, (r + 1) * f))
+        lw = LayerWeights(attn_norm=self._put(w["attn_norm"]), wqkv=wqkv, wo=wo, mlp_norm=self._put(w["mlp_norm"]), w_gu=wgu, w_down=wdn,
+                          s_qkv=s_qkv.float(), s_o=s_o.float(), s_gu=s_gu.float(), s_down=s_dn.float())
+        assert idx == len(self.layers)
+        self.layers.append(lw)
+
     def weight_bytes(self) -> int:
-        n = sum(t.numel() * t.element_size() for lw in self.layers for t in vars(lw).values())
+        n = sum(t.numel() * t.element_size() for lw in self.layers for t in vars(lw).values() if t is not None)
         for t in (self.embed, self.final_norm, self.lm_head):
             if t is not None:
                 n += t.numel() * t.element_size()
@@ -171,6 +218,8 @@ class LlamaModel:
         q_cols, kv_cols = self.n_q * d, self.n_kv * d
         h = ops.embedding(token_ids, self.embed)
         residual = None
+        if cfg.quantization == "fp8_block":
+            return self._forward_fp8(h, positions, slots, meta, kv_caches, sample_rows)
         for li, lw in enumerate(self.layers):
             x, residual = ops.rms_norm(h, lw.attn_norm, cfg.rms_norm_eps, residual)
             qkv = ops.linear(x, lw.wqkv)
@@ -182,6 +231,29 @@ class LlamaModel:
             x, residual = ops.rms_norm(h, lw.mlp_norm, cfg.rms_norm_eps, residual)
             act = ops.linear_swiglu(x, lw.w_gu)
             h = self.comm.linear_all_reduce(act, lw.w_down)
+        x, _ = ops.rms_norm(h, self.final_norm, cfg.rms_norm_eps, residual)
+        if sample_rows is not None:
+            x = ops.gather_rows(x, sample_rows)
+        logits = ops.linear(x, self.lm_head)
+        return self.comm.all_gather_vocab(logits)[:, :cfg.vocab_size]
+
+    def _forward_fp8(self, h, positions, slots, meta, kv_caches, sample_rows):
+        """Same layer structure with block-scaled fp8 linears: RMSNorm emits the e4m3 row + per-128 scales for the
+        column-parallel GEMMs; attention output and the SwiGLU activation are quantised by a small kernel."""
+        cfg, d = self.cfg, self.head_dim
+        q_cols, kv_cols = self.n_q * d, self.n_kv * d
+        residual = None
+        for li, lw in enumerate(self.layers):
+            _, xq, xs, residual = ops.rms_norm_quant(h, lw.attn_norm, cfg.rms_norm_eps, residual)
+            qkv = ops.linear_fp8((xq, xs), lw.wqkv, lw.s_qkv)
+            q, k, v = qkv[:, :q_cols], qkv[:, q_cols:q_cols + kv_cols], qkv[:, q_cols + kv_cols:]
+            kc, vc = kv_caches[li]
+            ops.rope_kvwrite(q, k, v, self.cos_sin, positions, slots, kc, vc, d)
+            attn = ops.paged_attention(q, kc, vc, meta, self.scale, d)
+            h = self.comm.all_reduce(ops.linear_fp8(attn, lw.wo, lw.s_o))
+            _, xq, xs, residual = ops.rms_norm_quant(h, lw.mlp_norm, cfg.rms_norm_eps, residual)
+            act = ops.swiglu(ops.linear_fp8((xq, xs), lw.w_gu, lw.s_gu))
+            h = self.comm.all_reduce(ops.linear_fp8(act, lw.w_down, lw.s_down))
         x, _ = ops.rms_norm(h, self.final_norm, cfg.rms_norm_eps, residual)
         if sample_rows is not None:
             x = ops.gather_rows(x, sample_rows)

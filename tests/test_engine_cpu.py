@@ -102,3 +102,29 @@ def test_sampling_params_and_metrics():
     assert a == b, "sampling must be reproducible for a fixed seed"
     m = eng.metrics()
     assert m["requests"] == 3 and m["output_tokens"] == 18 and m["ttft_p50_ms"] > 0
+
+
+def test_fp8_block_quantised_llama_runs_and_tracks_the_bf16_model():
+    """fp8 (128x128 block-scaled) weights through the same engine: on CPU the linears dequantise to fp32, so the
+    logits must stay close to the unquantised model's and generation must be deterministic."""
+    import copy
+
+    from mojo_b200.models import build_model
+    from mojo_b200 import ops
+
+    cfg = tiny_llama()
+    cfg.hidden_size, cfg.intermediate_size, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim = 256, 768, 4, 2, 64
+    qcfg = copy.deepcopy(cfg)
+    qcfg.quantization = "fp8_block"
+    full = build_model(cfg, "cpu", torch.float32).init_random(0, std=0.05)
+    quant = build_model(qcfg, "cpu", torch.float32).init_random(0, std=0.05)
+    T = 40
+    ids = torch.randint(0, 32000, (T,), generator=torch.Generator().manual_seed(1))
+    pos, slots = torch.arange(T, dtype=torch.int32), torch.arange(T, dtype=torch.int64)
+    meta = ops.AttnMeta(torch.tensor([0, T], dtype=torch.int32), torch.tensor([T], dtype=torch.int32),
+                        torch.arange(3, dtype=torch.int32).unsqueeze(0), 0, T, T)
+    a = full.forward(ids, pos, slots, meta, full.allocate_kv_cache(4, 16), None).float()
+    b = quant.forward(ids, pos, slots, meta, quant.allocate_kv_cache(4, 16), None).float()
+    assert quant.layers[0].wqkv.dtype == torch.float8_e4m3fn and quant.layers[0].s_qkv.shape == (4, 2)
+    rel = (a - b).norm() / a.norm()
+    assert rel < 0.2, rel       # e4m3 keeps 3 mantissa bits on both operands; K = 256 averages little
