@@ -69,6 +69,28 @@ void bind_ops_extra(py::module_& m) {
         py::arg("x"), py::arg("w"), py::arg("rank"), py::arg("peers"), py::arg("layout"), py::arg("out"), py::arg("residual"),
         py::arg("mode"), py::arg("slot"), py::arg("timeout_ns"), py::arg("config") = 0, py::arg("status") = py::none());
 
+  m.def("tp_gemm_rs_fp8",
+        [](const at::Tensor& xq, const at::Tensor& xs, const at::Tensor& wq, const at::Tensor& ws, int rank,
+           const std::vector<int64_t>& peers, const B2TpLayout& lay, c10::optional<at::Tensor> out,
+           c10::optional<at::Tensor> residual, int mode, int slot, uint64_t timeout_ns, c10::optional<at::Tensor> status) {
+          need(xq.is_cuda() && xq.element_size() == 1 && wq.element_size() == 1 && xq.dim() == 2 && wq.dim() == 2 && xq.is_contiguous() && wq.is_contiguous(),
+               "tp_gemm_rs_fp8: xq [M, K/tp], wq [N, K/tp] contiguous 8-bit");
+          const int M = static_cast<int>(xq.size(0)), K = static_cast<int>(xq.size(1)), N = static_cast<int>(wq.size(0));
+          need(wq.size(1) == K && K % 128 == 0, "tp_gemm_rs_fp8: K must match and be a multiple of 128");
+          need(xs.scalar_type() == at::kFloat && xs.is_contiguous() && xs.numel() == static_cast<int64_t>(M) * (K / 128), "tp_gemm_rs_fp8: xs f32 [M, K/128]");
+          need(ws.scalar_type() == at::kFloat && ws.is_contiguous() && ws.numel() == static_cast<int64_t>((N + 127) / 128) * (K / 128), "tp_gemm_rs_fp8: ws f32 [ceil(N/128), K/128]");
+          const B2TpRegion reg = make_region(rank, peers);
+          if (mode == 0) need(out.has_value() && is_bf16_2d(*out) && out->is_contiguous() && out->size(0) * reg.tp == M && out->size(1) == N, "tp_gemm_rs_fp8: out must be contiguous [M/tp, N]");
+          if (residual.has_value()) need(is_bf16_2d(*residual) && residual->is_contiguous() && residual->size(1) == N, "tp_gemm_rs_fp8: residual must be contiguous [rows, N]");
+          c10::cuda::CUDAGuard g(xq.device());
+          check(b2_tp_gemm_rs_fp8(xq.data_ptr(), xs.data_ptr<float>(), wq.data_ptr(), ws.data_ptr<float>(), &reg, &lay,
+                                  out.has_value() ? out->data_ptr() : nullptr, residual.has_value() ? residual->data_ptr() : nullptr, M, N,
+                                  K, mode, slot, timeout_ns, status_ptr(status), cur_stream()),
+                "tp_gemm_rs_fp8");
+        },
+        py::arg("xq"), py::arg("xs"), py::arg("wq"), py::arg("ws"), py::arg("rank"), py::arg("peers"), py::arg("layout"), py::arg("out"),
+        py::arg("residual"), py::arg("mode"), py::arg("slot"), py::arg("timeout_ns"), py::arg("status") = py::none());
+
   m.def("tp_ag_gemm",
         [](const at::Tensor& w, int rank, const std::vector<int64_t>& peers, const B2TpLayout& lay, at::Tensor& y, int M,
            int slot, uint64_t timeout_ns, int n_comm, int config, c10::optional<at::Tensor> status) {

@@ -36,6 +36,10 @@ struct B2TpLayout {
 int b2_tp_gemm_rs_bf16(const void* x, const void* w, const struct B2TpRegion* reg, const struct B2TpLayout* lay, void* out,
                        const void* residual, int M, int N, int K, int64_t ldx, int64_t ldw, int mode, int slot,
                        uint64_t timeout_ns, int config, b2::Status* status, cudaStream_t stream);
+// Same fused reduction with the block-scaled fp8 mainloop (xq/wq e4m3, xs [M, K/128], ws [N/128, K/128] f32 scales).
+int b2_tp_gemm_rs_fp8(const void* xq, const float* xs, const void* wq, const float* ws, const struct B2TpRegion* reg,
+                      const struct B2TpLayout* lay, void* out, const void* residual, int M, int N, int K, int mode, int slot,
+                      uint64_t timeout_ns, b2::Status* status, cudaStream_t stream);
 // X rows of this rank must already be in its own xall half at rows [rank * M/tp, (rank + 1) * M/tp).
 int b2_tp_ag_gemm_bf16(const void* w, const struct B2TpRegion* reg, const struct B2TpLayout* lay, void* y, int M, int N, int K,
                        int64_t ldw, int64_t ldy, int slot, uint64_t timeout_ns, int n_comm, int config,

@@ -250,7 +250,7 @@ Config choose_config(int M, int N, int K, int epilogue) {
     }
   }
   if (M > 64) {
-    static const int kBn[] = {64, 128, 256};
+    static const int kBn[] = {64, 96, 128, 160, 192, 224, 256};
     for (int bn : kBn) {
       if (N % 8 != 0) continue;
       for (int sp : kSplits) consider(false, bn, sp);
@@ -368,7 +368,11 @@ extern "C" int b2_gemm_bf16(const void* x, const void* w, void* y, const void* r
   } else {
     switch (c.bn) {
       case 64: B2_LAUNCH(64, false);
+      case 96: B2_LAUNCH(96, false);
       case 128: B2_LAUNCH(128, false);
+      case 160: B2_LAUNCH(160, false);
+      case 192: B2_LAUNCH(192, false);
+      case 224: B2_LAUNCH(224, false);
       case 256: B2_LAUNCH(256, false);
       default: return -kBadArgument;
     }
@@ -453,7 +457,11 @@ extern "C" int b2_gemm_bf16_noalloc(const void* x, const void* w, void* y, int M
   }
   switch (c.bn) {
     case 64: B2_LAUNCH_NA(64, false);
+    case 96: B2_LAUNCH_NA(96, false);
     case 128: B2_LAUNCH_NA(128, false);
+    case 160: B2_LAUNCH_NA(160, false);
+    case 192: B2_LAUNCH_NA(192, false);
+    case 224: B2_LAUNCH_NA(224, false);
     case 256: B2_LAUNCH_NA(256, false);
     default: return -kBadArgument;
   }

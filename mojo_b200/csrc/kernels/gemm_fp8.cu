@@ -19,6 +19,8 @@
 #include "b2/gemm_tc.cuh"
 #include "b2/ptx.cuh"
 #include "b2/tma.h"
+#include "b2/tp.h"
+#include "b2/tp_rs.cuh"
 
 namespace b2 {
 namespace {
@@ -34,13 +36,31 @@ struct Fp8Params {
   int p_blocks, q_blocks;
 };
 
-template <int BN, int STAGES, int SLABS, bool SWAP>
+// RS = true: row-parallel GEMM fused with reduce-scatter / all-reduce (see tp_fused.cu): finished tiles go to the
+// owner rank's staging buffer, CTAs >= n_gemm only reduce, the others join the reduction after their tiles.
+template <int BN, int STAGES, int SLABS, bool SWAP, bool RS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q, Fp8Params prm,
-                Status* status) {
+                const __grid_constant__ tp::RsSched rs_sched, tp::RsParams rs_in, tp::EpochCtl ectl, int n_gemm, Status* status) {
+  tp::RsParams rs = rs_in;
+  if (RS) rs.epoch = tp::epoch_begin(ectl);
+  const int my_cta = static_cast<int>(blockIdx.x);
+  const int n_ctas = RS ? n_gemm : static_cast<int>(gridDim.x);
+  auto tile_of = [&](int w, int& pb, int& qb) {
+    if (RS) {
+      const gemm::WorkUnit u = rs_sched.get(w);
+      pb = u.pb;
+      qb = u.qb;
+    } else {
+      pb = w / prm.q_blocks;
+      qb = w % prm.q_blocks;
+    }
+  };
+  if (!RS || my_cta < n_gemm) {
   constexpr int kPBytes = 128 * 128, kQBytes = BN * 128, kStageBytes = kPBytes + kQBytes;
   constexpr int kTmemCols = (SLABS * BN <= 32) ? 32 : (SLABS * BN <= 64) ? 64 : (SLABS * BN <= 128) ? 128 : (SLABS * BN <= 256) ? 256 : 512;
   constexpr int CH = BN >= 32 ? 32 : 16;
+  constexpr int kRingAndBarriers = STAGES * kStageBytes + (2 * STAGES + 2 * SLABS + 1) * 8 + 16 + 4 * BN * 4 + 1024 + 64;
   constexpr uint32_t idesc = ptx::make_idesc(0, 0, 128, BN);  // e4m3 x e4m3 -> f32
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -86,8 +106,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
       uint32_t phase = 0;
       long issued = 0;
       bool ok = true;
-      for (int w = blockIdx.x; ok && w < total; w += gridDim.x) {
-        const int pb = w / prm.q_blocks, qb = w % prm.q_blocks;
+      for (int w = my_cta; ok && w < total; w += n_ctas) {
+        int pb, qb;
+        tile_of(w, pb, qb);
         for (int kb = 0; kb < KB; ++kb) {
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u)) {
             status_record(status, kTimeout, kSiteGemmEmpty, w, kb);
@@ -118,7 +139,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
       int stage = 0, slab = 0;
       uint32_t phase = 0, slab_phase = 0;
       bool ok = true;
-      for (int w = blockIdx.x; ok && w < total; w += gridDim.x) {
+      for (int w = my_cta; ok && w < total; w += n_ctas) {
         for (int kb = 0; kb < KB; ++kb) {
           if (!ptx::mbar_wait(slab_empty(slab), slab_phase ^ 1u)) {
             status_record(status, kTimeout, kSiteGemmTmemEmpty, w, kb);
@@ -156,8 +177,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
     int slab = 0;
     uint32_t slab_phase = 0;
     bool ok = true;
-    for (int w = blockIdx.x; ok && w < total; w += gridDim.x) {
-      const int pb = w / prm.q_blocks, qb = w % prm.q_blocks;
+    for (int w = my_cta; ok && w < total; w += n_ctas) {
+      int pb, qb;
+      tile_of(w, pb, qb);
       float acc[BN];
 #pragma unroll
       for (int j = 0; j < BN; ++j) acc[j] = 0.0f;
@@ -209,9 +231,23 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
         if (lane == 0) ptx::mbar_arrive(slab_empty(slab));
         if (++slab == SLABS) { slab = 0; slab_phase ^= 1u; }
       }
+      // the fused epilogue below synchronises the four warps, so they must agree on whether it runs
+      if constexpr (RS) ok = ptx::named_barrier_and(3, 128, ok);
       if (!ok) break;
       // ---- store ----
-      if constexpr (!SWAP) {
+      if constexpr (RS) {
+        extern __shared__ uint8_t smem_dyn[];
+        uint8_t* epi_buf = smem_dyn + kRingAndBarriers;
+        epi_buf += (16 - (reinterpret_cast<uintptr_t>(epi_buf) & 15)) & 15;
+        tp::RsEpilogue<BN, SWAP> writer{rs, epi_buf};
+        gemm::WorkUnit u{};
+        u.pb = pb;
+        u.qb = qb;
+        writer.write_tile(u, quarter, lane, [&](int col0, uint32_t (&r)[CH]) {
+#pragma unroll
+          for (int j = 0; j < CH; ++j) r[j] = __float_as_uint(acc[col0 + j]);
+        });
+      } else if constexpr (!SWAP) {
         if (row < prm.M) {
           __nv_bfloat16* dst = prm.y + static_cast<int64_t>(row) * prm.ldy + qb * BN;
 #pragma unroll
@@ -243,6 +279,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
+  }  // GEMM CTAs
+  if constexpr (RS) {
+    tp::reduce_phase<BN, SWAP>(rs, status);
+    tp::rs_epoch_end(ectl, rs);
+  }
 }
 
 template <int BN, bool SWAP>
@@ -269,14 +310,61 @@ int launch_fp8(const void* xq, const float* xs, const void* wq, const float* ws,
   prm.KB = K / 128;
   prm.p_blocks = (rows_p + 127) / 128;
   prm.q_blocks = (rows_q + BN - 1) / BN;
-  auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP>;
+  auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP, false>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
     attr_set = true;
   }
   const int total = prm.p_blocks * prm.q_blocks;
-  kern<<<total < kNumSMs ? total : kNumSMs, kThreads, SMEM, stream>>>(tp, tq, prm, status);
+  static const tp::RsSched no_sched{};
+  kern<<<total < kNumSMs ? total : kNumSMs, kThreads, SMEM, stream>>>(tp, tq, prm, no_sched, tp::RsParams{}, tp::EpochCtl{}, 0, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+}
+
+template <int BN, bool SWAP>
+int launch_fp8_rs(const void* xq, const float* xs, const void* wq, const float* ws, int M, int N, int K, tp::RsParams rs,
+                  tp::EpochCtl ectl, Status* status, cudaStream_t stream) {
+  constexpr int kStageBytes = 128 * 128 + BN * 128;
+  constexpr int STAGES = (150 * 1024 / kStageBytes) > 8 ? 8 : (150 * 1024 / kStageBytes);
+  constexpr int SLABS = BN <= 128 ? 4 : 2;
+  constexpr int SMEM = STAGES * kStageBytes + (2 * STAGES + 2 * SLABS + 1) * 8 + 16 + 4 * BN * 4 + 1024 + 64 + tp::rs_epi_bytes<BN, SWAP>() + 16;
+  const void* p_ptr = SWAP ? wq : xq;
+  const void* q_ptr = SWAP ? xq : wq;
+  const int rows_p = SWAP ? N : M, rows_q = SWAP ? M : N;
+  CUtensorMap tmp, tmq;
+  if (!make_tmap_2d(&tmp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p_ptr, rows_p, K, K, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !make_tmap_2d(&tmq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q_ptr, rows_q, K, K, BN, 128, CU_TENSOR_MAP_SWIZZLE_128B))
+    return -kBadArgument;
+  Fp8Params prm{};
+  prm.sx = xs;
+  prm.sw = ws;
+  prm.M = M;
+  prm.N = N;
+  prm.KB = K / 128;
+  prm.p_blocks = (rows_p + 127) / 128;
+  prm.q_blocks = (rows_q + BN - 1) / BN;
+  tp::RsSched sched{};
+  sched.p_blocks = prm.p_blocks;
+  sched.q_blocks = prm.q_blocks;
+  sched.num_kb = prm.KB;
+  sched.bn = BN;
+  sched.swap = SWAP;
+  constexpr int TM = SWAP ? BN : 128;
+  sched.m_tiles = SWAP ? sched.q_blocks : sched.p_blocks;
+  if (!tp::build_rs_order(sched, rs.tp, rs.rank, rs.R, TM)) return -kTooLarge;
+  rs.p_blocks = prm.p_blocks;
+  rs.q_blocks = prm.q_blocks;
+  auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP, true>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
+    attr_set = true;
+  }
+  const int total = prm.p_blocks * prm.q_blocks;
+  int n_gemm = kNumSMs - (rs.tp > 1 ? 12 : 0);
+  if (total < n_gemm) n_gemm = total;
+  kern<<<kNumSMs, kThreads, SMEM, stream>>>(tmp, tmq, prm, sched, rs, ectl, n_gemm, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
 }
 
@@ -310,4 +398,48 @@ extern "C" int b2_gemm_fp8_block(const void* xq, const float* xs, const void* wq
     case 128: return launch_fp8<128, false>(xq, xs, wq, ws, y, M, N, K, ldy, status, stream);
     default: return -kBadArgument;
   }
+}
+
+extern "C" int b2_tp_gemm_rs_fp8(const void* xq, const float* xs, const void* wq, const float* ws, const B2TpRegion* reg,
+                                 const B2TpLayout* lay, void* out, const void* residual, int M, int N, int K, int mode, int slot,
+                                 uint64_t timeout_ns, b2::Status* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (reg == nullptr || lay == nullptr || reg->tp < 1 || reg->tp > tp::kMaxTp || K % 128 != 0 || N % 8 != 0) return -kBadArgument;
+  const int ntp = reg->tp;
+  const int R = (M + ntp - 1) / ntp;
+  if (mode == 0 && M % ntp != 0) return -kBadArgument;
+  tp::RsParams rs{};
+  rs.rank = reg->rank;
+  rs.tp = ntp;
+  rs.M = M;
+  rs.N = N;
+  rs.R = R;
+  rs.mode = mode;
+  const int parity = slot & 1;
+  for (int i = 0; i < ntp; ++i) rs.peer[i] = static_cast<uint8_t*>(reg->peer[i]);
+  tp::EpochCtl ectl{reinterpret_cast<uint32_t*>(rs.peer[rs.rank] + lay->off_epoch_rs),
+                    reinterpret_cast<uint32_t*>(rs.peer[rs.rank] + lay->off_epoch_rs + 4)};
+  if (static_cast<int64_t>(ntp) * R * N * 2 > lay->staging_half_bytes || (mode == 1 && static_cast<int64_t>(M) * N * 2 > lay->yall_half_bytes))
+    return -kTooLarge;
+  rs.off_staging = lay->off_staging + parity * lay->staging_half_bytes;
+  rs.off_yall = lay->off_yall + parity * lay->yall_half_bytes;
+  rs.off_flags = lay->off_rs_flags;
+  rs.off_resflags = lay->off_res_flags;
+  rs.off_done = lay->off_done;
+  rs.residual = static_cast<const __nv_bfloat16*>(residual);
+  rs.out = static_cast<__nv_bfloat16*>(out);
+  rs.timeout_ns = timeout_ns;
+  const bool swap = M <= 64;
+  const int bn = swap ? (M <= 16 ? 16 : M <= 32 ? 32 : 64) : 128;
+  const int tm = swap ? bn : 128;
+  const int64_t units = static_cast<int64_t>((R + tm - 1) / tm + 1) * (swap ? (N + 127) / 128 : (N + bn - 1) / bn);
+  if (units * ntp * 4 > lay->rs_flags_bytes) return -kTooLarge;
+  if (swap) {
+    switch (bn) {
+      case 16: return launch_fp8_rs<16, true>(xq, xs, wq, ws, M, N, K, rs, ectl, status, stream);
+      case 32: return launch_fp8_rs<32, true>(xq, xs, wq, ws, M, N, K, rs, ectl, status, stream);
+      default: return launch_fp8_rs<64, true>(xq, xs, wq, ws, M, N, K, rs, ectl, status, stream);
+    }
+  }
+  return launch_fp8_rs<128, false>(xq, xs, wq, ws, M, N, K, rs, ectl, status, stream);
 }

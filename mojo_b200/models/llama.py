@@ -52,6 +52,10 @@ class NoComm:
     def linear_all_reduce(self, x, w, residual=None):
         return ops.linear(x, w, residual)
 
+    def linear_fp8_all_reduce(self, x, w_q, w_scale, residual=None):
+        y = ops.linear_fp8(x, w_q, w_scale)
+        return y if residual is None else y + residual
+
     def all_gather_vocab(self, logits: torch.Tensor) -> torch.Tensor:
         return logits
 
@@ -250,10 +254,10 @@ class LlamaModel:
             kc, vc = kv_caches[li]
             ops.rope_kvwrite(q, k, v, self.cos_sin, positions, slots, kc, vc, d)
             attn = ops.paged_attention(q, kc, vc, meta, self.scale, d)
-            h = self.comm.all_reduce(ops.linear_fp8(attn, lw.wo, lw.s_o))
+            h = self.comm.linear_fp8_all_reduce(attn, lw.wo, lw.s_o)
             _, xq, xs, residual = ops.rms_norm_quant(h, lw.mlp_norm, cfg.rms_norm_eps, residual)
             act = ops.swiglu(ops.linear_fp8((xq, xs), lw.w_gu, lw.s_gu))
-            h = self.comm.all_reduce(ops.linear_fp8(act, lw.w_down, lw.s_down))
+            h = self.comm.linear_fp8_all_reduce(act, lw.w_down, lw.s_down)
         x, _ = ops.rms_norm(h, self.final_norm, cfg.rms_norm_eps, residual)
         if sample_rows is not None:
             x = ops.gather_rows(x, sample_rows)

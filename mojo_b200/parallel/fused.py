@@ -95,6 +95,35 @@ class FusedTPComm:
         ops._count()
         return out
 
+    def linear_fp8_all_reduce(self, x, w_q: torch.Tensor, w_scale: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """Block-scaled fp8 row-parallel linear fused with the all-reduce. `x` is bf16 [M, K/tp] (quantised here) or a
+        pair (x_q, x_scale); w_q e4m3 [N, K/tp], w_scale f32 [N/128, K/tp/128]. Same result buffer as `linear_all_reduce`."""
+        xq, xs = x if isinstance(x, tuple) else ops.quant_e4m3(x)
+        M, N = xq.shape[0], w_q.shape[0]
+        if self.world_size == 1:
+            y = ops.linear_fp8((xq, xs), w_q, w_scale)
+            return y if residual is None else y + residual
+        slot = self._rs_calls & 1
+        self._rs_calls += 1
+        self.C.tp_gemm_rs_fp8(xq, xs, w_q, w_scale, self.rank, self.peers, self.layout, None, residual, 1, slot, self.timeout_ns, self.status)
+        ops._count()
+        return self.region.view(self.layout.off_yall + slot * self.layout.yall_half_bytes, (M, N), torch.bfloat16)
+
+    def linear_fp8_reduce_scatter(self, x, w_q: torch.Tensor, w_scale: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """Rows [rank * M/tp, (rank+1) * M/tp) of reduce(dequant(x) @ dequant(w).T) (+ residual rows of that shard)."""
+        xq, xs = x if isinstance(x, tuple) else ops.quant_e4m3(x)
+        M, N = xq.shape[0], w_q.shape[0]
+        if self.world_size == 1:
+            y = ops.linear_fp8((xq, xs), w_q, w_scale)
+            return y if residual is None else y + residual
+        assert M % self.world_size == 0, "reduce-scatter needs a token count divisible by tp"
+        out = torch.empty(M // self.world_size, N, dtype=torch.bfloat16, device=xq.device)
+        slot = self._rs_calls & 1
+        self._rs_calls += 1
+        self.C.tp_gemm_rs_fp8(xq, xs, w_q, w_scale, self.rank, self.peers, self.layout, out, residual, 0, slot, self.timeout_ns, self.status)
+        ops._count()
+        return out
+
     def gather_input(self, M: int, K: int) -> torch.Tensor:
         """The [M/tp, K] slice of the next all-gather's buffer that this rank must fill with its rows."""
         assert M % self.world_size == 0

@@ -33,6 +33,13 @@ class NcclTPComm:
             y = y + residual
         return y
 
+    def linear_fp8_all_reduce(self, x, w_q: torch.Tensor, w_scale: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """Row-parallel block-scaled fp8 linear followed by an all-reduce of the partial sums."""
+        y = self.all_reduce(ops.linear_fp8(x, w_q, w_scale))
+        if residual is not None:
+            y = y + residual
+        return y
+
     def all_gather_vocab(self, logits: torch.Tensor) -> torch.Tensor:
         """[S, V/tp] per rank -> [S, V] on every rank."""
         if self.world_size == 1:

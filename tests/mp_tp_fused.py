@@ -107,6 +107,28 @@ def main():
     close(b, want_b, "graph replay chained all-reduce")
     ops.check_status(dev)
 
+    # ---- block-scaled fp8 GEMM -> all-reduce / reduce-scatter ----
+    from mojo_b200.ops import reference
+
+    for i, M in enumerate([8, 48, 256, 1024]):
+        N = hidden
+        x = mk((M, k_local), 7000 + 10 * i + rank)
+        w = mk((N, k_local), 7500 + 10 * i + rank, 0.05)
+        res = mk((M, N), 7900 + i)
+        xq, xs = ops.quant_e4m3(x)
+        wq, ws = reference.quant_e4m3_128x128(w)
+        want = reference.linear_fp8_block(xq, xs, wq, ws).float()
+        dist.all_reduce(want)
+        for rep in range(2):
+            y = comm.linear_fp8_all_reduce((xq, xs), wq, ws, residual=res if rep else None)
+            close(y, want + res.float() if rep else want, f"fp8 all-reduce M={M} rep={rep}")
+        if M % tp == 0:
+            r = M // tp
+            y3 = comm.linear_fp8_reduce_scatter(x, wq, ws)
+            close(y3, want[rank * r:(rank + 1) * r], f"fp8 reduce-scatter M={M}")
+    torch.cuda.synchronize()
+    ops.check_status(dev)
+
     # ---- timeout path: a wait nobody satisfies returns a TIMEOUT status and leaves the context usable ----
     flag = torch.zeros(1, dtype=torch.int32, device=dev)
     comm.C.wait_flag(flag, 1, 50_000_000, comm.status)

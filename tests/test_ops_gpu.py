@@ -117,7 +117,7 @@ def test_gemm_large_m(M, N, K):
     _gemm_case(M, N, K, config=ops.gemm_config(False, 128))
 
 
-@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("bn", [64, 96, 128, 160, 192, 224, 256])
 def test_gemm_normal_tiles(bn):
     _gemm_case(300, 1280, 768, config=ops.gemm_config(False, bn), residual=True)
 

@@ -29,3 +29,9 @@ def test_fused_tp_kernels_all_gpus():
     n = 8 if torch.cuda.device_count() >= 8 else 4
     p = _run("mp_tp_fused.py", n, 29612)
     assert f"TP_FUSED_OK {n}" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_moe_two_gpus():
+    p = _run("mp_ep.py", 2, 29613)
+    assert "EP_OK 2" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
