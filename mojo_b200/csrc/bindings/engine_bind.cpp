@@ -4,6 +4,7 @@
 #include <pybind11/stl.h>
 #include "b2/dtype.h"
 #include "b2/engine.h"
+#include "b2/symm_sim.h"
 
 namespace py = pybind11;
 using namespace b2::engine;
@@ -18,6 +19,40 @@ py::array_t<T> to_array(const std::vector<T>& v) {
 }  // namespace
 
 void bind_engine(py::module_& m) {
+  // CPU-rank simulator of the symmetric-memory collective protocol, with host-side fault injection
+  m.def(
+      "symm_sim_run",
+      [](int world, int n, int steps, const std::string& algo, const std::string& fault, int timeout_ms) {
+        b2::sim::Fault f;
+        if (!b2::sim::parse_fault(fault, &f)) throw std::invalid_argument("mojo_b200: malformed fault spec '" + fault + "'");
+        b2::sim::Algo a;
+        if (algo == "one_shot") a = b2::sim::Algo::kOneShot;
+        else if (algo == "two_shot") a = b2::sim::Algo::kTwoShot;
+        else if (algo == "all_to_all") a = b2::sim::Algo::kAllToAll;
+        else throw std::invalid_argument("mojo_b200: symm_sim_run: algo must be one_shot, two_shot or all_to_all");
+        if (world < 1 || world > 8 || n < 1 || steps < 0 || timeout_ms < 1) throw std::invalid_argument("mojo_b200: symm_sim_run: bad sizes");
+        b2::sim::SimResult r;
+        {
+          py::gil_scoped_release nogil;
+          r = b2::sim::run(world, n, steps, a, f, timeout_ms);
+        }
+        py::list ranks;
+        for (const auto& rr : r.ranks) {
+          py::dict d;
+          d["code"] = rr.code;
+          d["step"] = rr.step;
+          d["peer"] = rr.peer;
+          d["which"] = rr.which;
+          d["wrong_steps"] = rr.wrong_steps;
+          d["timeouts"] = rr.timeouts;
+          ranks.append(d);
+        }
+        py::dict out;
+        out["ranks"] = ranks;
+        out["elapsed_ms"] = r.elapsed_ms;
+        return out;
+      },
+      py::arg("world"), py::arg("n"), py::arg("steps"), py::arg("algo") = "one_shot", py::arg("fault") = "", py::arg("timeout_ms") = 2000);
   m.def("hash_page", [](uint64_t parent, py::array_t<int32_t, py::array::c_style | py::array::forcecast> tokens) {
     return hash_page(parent, tokens.data(), static_cast<int>(tokens.size()));
   });

@@ -246,6 +246,7 @@ py::dict device_caps(int device) {
 }  // namespace
 
 void bind_ops_extra(py::module_& m);
+void bind_coll(py::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "mojo_b200 native extension: sm_100a kernels + engine runtime";
@@ -276,4 +277,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_decode_workspace_bytes", [](int batch, int n_q, int d, int splits) { return b2_attn_decode_workspace(batch, n_q, d, splits); });
   m.def("device_caps", &device_caps, py::arg("device") = 0);
   bind_ops_extra(m);
+  bind_coll(m);
 }

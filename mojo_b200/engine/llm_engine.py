@@ -88,8 +88,17 @@ class LLMEngine:
         sc.enable_chunked_prefill = cfg.enable_chunked_prefill
         self.scheduler = self.C.Scheduler(sc, self.kv)
         self.requests: dict[int, RequestState] = {}
+        self._prompts: dict[int, np.ndarray] = {}
         self._next_id = 0
         self.step_count = 0
+        # failure detection (all optional, all on the host): see engine/watchdog.py and utils/fault.py
+        from ..utils import fault as _fault
+
+        rank = getattr(comm, "rank", 0) if comm is not None else 0
+        self.fault = _fault.FaultInjector(_fault.from_env(), rank)
+        self.watchdog = None
+        self.heartbeat = None
+        self.skipped_launches = 0
         from .model_runner import ModelRunner
 
         self.runner = ModelRunner(self.model, self.kv_caches, cfg)
@@ -117,7 +126,31 @@ class LLMEngine:
         now = time.perf_counter() if arrival is None else arrival
         self.scheduler.add_request(rid, prompt, max_new, now)
         self.requests[rid] = RequestState(rid, len(prompt), params, now)
+        self._prompts[rid] = prompt
         return rid
+
+    def prompt_of(self, rid: int) -> np.ndarray:
+        return self._prompts[rid]
+
+    def readmit(self, rid: int, prompt_ids, max_new: int, state: RequestState) -> None:
+        """Put an aborted request back in the queue under its old id (recovery: recompute from the prompt plus
+        the tokens already produced). The request's state object, and with it its output so far, is kept."""
+        prompt = np.asarray(prompt_ids, dtype=np.int32)
+        max_new = max(1, min(max_new, self.cfg.max_model_len - len(prompt)))
+        self.scheduler.add_request(rid, prompt, max_new, state.arrival)
+        self.requests[rid] = state
+
+    def attach_watchdog(self, limit_s: float = 60.0, on_stall=None):
+        from .watchdog import Watchdog
+
+        self.watchdog = Watchdog(limit_s, on_stall).start()
+        return self.watchdog
+
+    def attach_heartbeat(self, store, rank: int, world_size: int, limit_s: float = 30.0):
+        from .watchdog import Heartbeat
+
+        self.heartbeat = Heartbeat(store, rank, world_size, limit_s)
+        return self.heartbeat
 
     def abort_request(self, rid: int) -> None:
         if rid in self.requests:
@@ -130,13 +163,29 @@ class LLMEngine:
 
     # ------------------------------------------------------------------------------------------------
     def step(self) -> list[RequestOutput]:
-        """One engine iteration. Returns outputs for every sequence that produced a token."""
+        """One engine iteration. Returns outputs for every sequence that produced a token.
+
+        Before anything is launched the host-side failure hooks run: an injected fault may raise, sleep or skip the
+        launch, and the heartbeat check raises `WorkerLost` when a peer rank has left or gone silent."""
+        skip = self.fault.before_step(self.step_count)
+        if self.heartbeat is not None:
+            self.heartbeat.check()
+        if skip:
+            self.skipped_launches += 1
+            self.step_count += 1
+            return []
         batch = self.scheduler.step()
         if batch.num_seqs == 0:
             return []
         sample_ids = batch.sample_seq_ids
         states = [self.requests[int(r)] for r in sample_ids]
+        if self.watchdog is not None:
+            self.watchdog.begin_step()
         tokens = self.runner.execute(batch, states, self.step_count)
+        if self.watchdog is not None:
+            self.watchdog.end_step(self.step_count)
+        if self.heartbeat is not None:
+            self.heartbeat.beat(self.step_count)
         self.step_count += 1
         now = time.perf_counter()
         outs = []

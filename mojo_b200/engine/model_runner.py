@@ -121,8 +121,14 @@ class ModelRunner:
                 self.step_events[1].record()
             self.d2h_bytes = 0
             return []
-        logits = self.model.forward(token_ids, positions, slots, meta, self.kv_caches, rows)
-        if greedy:
+        fused_greedy = greedy and getattr(self.model, "greedy_in_forward", False)
+        if fused_greedy:
+            ids = self.model.forward(token_ids, positions, slots, meta, self.kv_caches, rows, greedy=True)
+        else:
+            logits = self.model.forward(token_ids, positions, slots, meta, self.kv_caches, rows)
+        if fused_greedy:
+            pass
+        elif greedy:
             ids = ops.argmax(logits)
         else:
             seed = self.cfg.seed if states[0].params.seed is None else states[0].params.seed
@@ -207,6 +213,8 @@ class _DecodeGraph:
         def run():
             if comm is not None and hasattr(comm, "begin_graph"):
                 comm.begin_graph()
+            if getattr(model, "greedy_in_forward", False):
+                return model.forward(self.tok, self.pos, self.slot, self.meta, caches, None, greedy=True)
             logits = model.forward(self.tok, self.pos, self.slot, self.meta, caches, None)
             return ops.argmax(logits)
 

@@ -65,7 +65,9 @@ class DeepseekV2Model:
 
     def init_random(self, seed: int = 0, std: float = 0.02) -> "DeepseekV2Model":
         cfg = self.cfg
-        gen_dev = self.device if self.device.type == "cuda" else torch.device("cpu")
+        # small models draw on the CPU so that CPU and GPU instances of one seed hold the same weights
+        big = cfg.hidden_size * cfg.vocab_size > (1 << 27)
+        gen_dev = self.device if (big and self.device.type == "cuda") else torch.device("cpu")
         g = torch.Generator(device=gen_dev).manual_seed(seed)
 
         def rnd(*shape):

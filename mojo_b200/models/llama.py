@@ -215,15 +215,16 @@ class LlamaModel:
     # forward
     # ------------------------------------------------------------------------------------------------
     def forward(self, token_ids: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, meta: ops.AttnMeta,
-                kv_caches, sample_rows: torch.Tensor | None) -> torch.Tensor:
+                kv_caches, sample_rows: torch.Tensor | None, greedy: bool = False) -> torch.Tensor:
         """Returns logits [len(sample_rows), vocab] (fp32 on CPU, bf16 on CUDA). With sample_rows None, logits
-        for every token are returned."""
+        for every token are returned. `greedy=True` on a model whose `greedy_in_forward` is set returns int64
+        token ids instead (arg-max merged across the vocabulary shards without gathering the logits)."""
         cfg, d = self.cfg, self.head_dim
         q_cols, kv_cols = self.n_q * d, self.n_kv * d
         h = ops.embedding(token_ids, self.embed)
         residual = None
         if cfg.quantization == "fp8_block":
-            return self._forward_fp8(h, positions, slots, meta, kv_caches, sample_rows)
+            return self._forward_fp8(h, positions, slots, meta, kv_caches, sample_rows, greedy)
         for li, lw in enumerate(self.layers):
             x, residual = ops.rms_norm(h, lw.attn_norm, cfg.rms_norm_eps, residual)
             qkv = ops.linear(x, lw.wqkv)
@@ -235,13 +236,26 @@ class LlamaModel:
             x, residual = ops.rms_norm(h, lw.mlp_norm, cfg.rms_norm_eps, residual)
             act = ops.linear_swiglu(x, lw.w_gu)
             h = self.comm.linear_all_reduce(act, lw.w_down)
+        return self._head(h, residual, sample_rows, greedy)
+
+    def _head(self, h, residual, sample_rows, greedy: bool):
+        """Final norm, row gather and the vocabulary-parallel LM head. `greedy` on a tensor-parallel communicator
+        that can merge arg-maxes returns int64 token ids instead of gathered logits."""
+        cfg = self.cfg
         x, _ = ops.rms_norm(h, self.final_norm, cfg.rms_norm_eps, residual)
         if sample_rows is not None:
             x = ops.gather_rows(x, sample_rows)
         logits = ops.linear(x, self.lm_head)
+        if greedy and self.greedy_in_forward:
+            valid = max(1, min(self.vocab_local, cfg.vocab_size - self.vocab_start))
+            return self.comm.vocab_argmax(logits[:, :valid], self.vocab_local)
         return self.comm.all_gather_vocab(logits)[:, :cfg.vocab_size]
 
-    def _forward_fp8(self, h, positions, slots, meta, kv_caches, sample_rows):
+    @property
+    def greedy_in_forward(self) -> bool:
+        return self.tp > 1 and hasattr(self.comm, "vocab_argmax")
+
+    def _forward_fp8(self, h, positions, slots, meta, kv_caches, sample_rows, greedy=False):
         """Same layer structure with block-scaled fp8 linears: RMSNorm emits the e4m3 row + per-128 scales for the
         column-parallel GEMMs; attention output and the SwiGLU activation are quantised by a small kernel."""
         cfg, d = self.cfg, self.head_dim
@@ -258,8 +272,4 @@ class LlamaModel:
             _, xq, xs, residual = ops.rms_norm_quant(h, lw.mlp_norm, cfg.rms_norm_eps, residual)
             act = ops.swiglu(ops.linear_fp8((xq, xs), lw.w_gu, lw.s_gu))
             h = self.comm.linear_fp8_all_reduce(act, lw.w_down, lw.s_down)
-        x, _ = ops.rms_norm(h, self.final_norm, cfg.rms_norm_eps, residual)
-        if sample_rows is not None:
-            x = ops.gather_rows(x, sample_rows)
-        logits = ops.linear(x, self.lm_head)
-        return self.comm.all_gather_vocab(logits)[:, :cfg.vocab_size]
+        return self._head(h, residual, sample_rows, greedy)

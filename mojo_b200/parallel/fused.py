@@ -67,6 +67,8 @@ class FusedTPComm:
         self.timeout_ns = int(timeout_s * 1e9)
         self._rs_calls = 0
         self._ag_calls = 0
+        self._coll = None
+        self._coll_bytes = 16 << 20
         self.status = _state.get(info.device).status
 
     # -- fused ops ---------------------------------------------------------------------------------
@@ -166,9 +168,26 @@ class FusedTPComm:
             dist.all_reduce(x, group=self.group)
         return x
 
+    def _collectives(self):
+        """Standalone symmetric-memory collectives for what is not fused into a GEMM (logits gather, greedy merge)."""
+        if self._coll is None:
+            from .coll import SymmCollectives
+
+            self._coll = SymmCollectives(self.info, max_bytes=self._coll_bytes, timeout_s=self.timeout_ns / 1e9)
+        return self._coll
+
     def all_gather_vocab(self, logits: torch.Tensor) -> torch.Tensor:
+        """[S, V/tp] per rank -> [S, V] on every rank, pushed over NVLink by one kernel."""
         if self.world_size == 1:
             return logits
-        out = torch.empty(self.world_size, *logits.shape, dtype=logits.dtype, device=logits.device)
-        dist.all_gather_into_tensor(out, logits.contiguous(), group=self.group)
+        nbytes = logits.numel() * logits.element_size()
+        if nbytes % 16 != 0 or nbytes > self._coll_bytes:
+            out = torch.empty(self.world_size, *logits.shape, dtype=logits.dtype, device=logits.device)
+            dist.all_gather_into_tensor(out, logits.contiguous(), group=self.group)
+        else:
+            out = self._collectives().all_gather(logits)
         return out.permute(1, 0, 2).reshape(logits.shape[0], -1)
+
+    def vocab_argmax(self, logits: torch.Tensor, vocab_stride: int) -> torch.Tensor:
+        """Greedy tokens from vocabulary-sharded logits without gathering them (one small merge kernel)."""
+        return self._collectives().vocab_argmax(logits, vocab_stride)

@@ -35,3 +35,18 @@ def test_fused_tp_kernels_all_gpus():
 def test_expert_parallel_moe_two_gpus():
     p = _run("mp_ep.py", 2, 29613)
     assert "EP_OK 2" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_symmetric_collectives_two_gpus():
+    p = _run("mp_coll.py", 2, 29614)
+    assert "COLL_OK 2" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_symmetric_collectives_and_moe_all_gpus():
+    n = 8 if torch.cuda.device_count() >= 8 else 4
+    p = _run("mp_coll.py", n, 29615)
+    assert f"COLL_OK {n}" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+    p = _run("mp_ep.py", n, 29616)
+    assert f"EP_OK {n}" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
