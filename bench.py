@@ -45,6 +45,7 @@ def parse_args():
     ap.add_argument("--page-size", type=int, default=128)
     ap.add_argument("--max-ramp-steps", type=int, default=400)
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--no-autotune", action="store_true", help="skip the start-up measurement of GEMM configurations")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--layers", type=int, default=None, help="debug only: marks the result invalid")
     ap.add_argument("--profile", default=None, help="debug only: write a per-kernel table of a few steps to this file")
@@ -109,7 +110,8 @@ def main() -> None:
     max_model_len = 2048 + 512 + 128
     ecfg = EngineConfig(model=mcfg, device=str(device), dtype=torch.bfloat16, page_size=args.page_size,
                         max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_batched_tokens,
-                        max_model_len=max_model_len, seed=0, use_cuda_graphs=not args.no_graphs, tp_size=world)
+                        max_model_len=max_model_len, seed=0, use_cuda_graphs=not args.no_graphs, tp_size=world,
+                        autotune=(args.impl == "mojo_b200" and not args.no_autotune and device.type == "cuda"))
     model = build_model(mcfg, device, torch.bfloat16, comm=comm).init_random(0)
     engine = LLMEngine(ecfg, model=model, comm=comm)
 
@@ -237,7 +239,7 @@ def main() -> None:
                 "parallelism": f"tp{world}", "requests": args.requests, "poisson_rate_per_s": args.rate,
                 "max_num_batched_tokens": args.max_batched_tokens, "page_size": args.page_size, "ramp_steps": ramp,
                 "l2": "inputs larger than L2: every step streams the full weight set (16 GB / tp) through the 126 MB L2",
-                "cuda_graphs": not args.no_graphs, "comm": args.comm if world > 1 else "none",
+                "cuda_graphs": not args.no_graphs, "gemm_autotune": bool(ecfg.autotune), "comm": args.comm if world > 1 else "none",
                 "prefill_tokens_in_timed_region": prefill_tokens, "output_tokens_in_timed_region": tokens,
             },
             "clocks": {k: clocks.summary().get(k) for k in ("sm_mhz", "sm_max_mhz", "reasons", "power_w_max")},

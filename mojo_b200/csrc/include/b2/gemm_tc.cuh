@@ -40,7 +40,8 @@ struct WorkUnit {
   int kb0;      // first 64-wide k-block
   int kb1;      // one past the last k-block
   int split;    // split-K index
-  int tile;     // linear output tile id (pb, qb) for split-K bookkeeping
+  int tile;     // split-K bookkeeping slot (partials and semaphore): the linear tile id, or the stream-K slot
+  int nsplit;   // how many work units contribute to this output tile (1 = the unit owns the tile)
   int p_coord;  // TMA row coordinate of the P tile (normally pb * 128)
   int q_coord;  // TMA row coordinate of the Q tile (normally qb * BN)
 };
@@ -138,6 +139,7 @@ __device__ __forceinline__ void run(const CUtensorMap* tmap_p, const CUtensorMap
       bool ok = true;
       for (int w = cta; ok && w < total; w += num_ctas) {
         const WorkUnit u = sched.get(w);
+        if (u.kb0 >= u.kb1) continue;  // empty unit (stream-K padding); every role skips it alike
         if (!gate(u, status)) { ok = false; break; }
         for (int kb = u.kb0; kb < u.kb1; ++kb) {
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u)) {
@@ -176,6 +178,7 @@ __device__ __forceinline__ void run(const CUtensorMap* tmap_p, const CUtensorMap
       bool ok = true;
       for (int w = cta; ok && w < total; w += num_ctas) {
         const WorkUnit u = sched.get(w);
+        if (u.kb0 >= u.kb1) continue;
         if (!ptx::mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u)) {
           status_record(status, kTimeout, kSiteGemmTmemEmpty, w, acc);
           ok = false;
@@ -224,7 +227,7 @@ __device__ __forceinline__ void run(const CUtensorMap* tmap_p, const CUtensorMap
     bool ok = true;
     for (int w = cta; ok && w < total; w += num_ctas) {
       const WorkUnit u = sched.get(w);
-      for (int kb = u.kb0; kb < u.kb1; ++kb) {
+      for (int kb = u.kb0; kb < u.kb1; ++kb) {  // an empty unit has no k-blocks
         if (!__all_sync(0xffffffffu, ptx::mbar_wait(empty_bar(stage), phase ^ 1u))) {
           if (lane == 0) status_record(status, kTimeout, kSiteGemmEmpty, w, kb);
           ok = false;
@@ -246,6 +249,7 @@ __device__ __forceinline__ void run(const CUtensorMap* tmap_p, const CUtensorMap
     bool ok = true;
     for (int w = cta; ok && w < total; w += num_ctas) {
       const WorkUnit u = sched.get(w);
+      if (u.kb0 >= u.kb1) continue;
       // The four epilogue warps must take the same decision: epilogues synchronise among themselves with
       // barriers that have no deadline, so a lone warp giving up would strand the other three.
       const bool arrived = ptx::mbar_wait(tmem_full_bar(acc), acc_phase);
@@ -275,13 +279,22 @@ __device__ __forceinline__ void run(const CUtensorMap* tmap_p, const CUtensorMap
 
 // Default scheduler: tiles rastered in groups of 8 P-blocks so that one wave of CTAs shares Q tiles in L2;
 // the `splits` K-slices of a tile are adjacent work units.
+//
+// Stream-K mode (sk_tiles > 0, splits == 1): the first `sk_tiles` tiles (the ragged part of the last wave) are cut
+// along K into `num_ctas` equal runs of `sk_per` k-blocks, one run per CTA, so that every CTA gets the same
+// amount of tensor work whatever the tile count; a tile whose k-range spans several CTAs is summed through the
+// split-K workspace by whichever contributor arrives last. The remaining tiles, a multiple of the grid size,
+// follow as whole tiles. CTA c's units are w = c, c + num_ctas, ...: first its `sk_units` stream-K units (some
+// may be empty), then its whole tiles.
 struct TileSched {
   int p_blocks, q_blocks, splits, num_kb, kb_per_split, bn;
-  __device__ __forceinline__ int total() const { return p_blocks * q_blocks * splits; }
-  __device__ __forceinline__ WorkUnit get(int w) const {
-    WorkUnit u;
-    u.split = w % splits;
-    const int t = w / splits;
+  int sk_tiles, sk_per, sk_units, num_ctas;
+  __device__ __forceinline__ int total() const {
+    if (sk_tiles == 0) return p_blocks * q_blocks * splits;
+    const int dp_waves = (p_blocks * q_blocks - sk_tiles + num_ctas - 1) / num_ctas;
+    return num_ctas * (sk_units + dp_waves);
+  }
+  __device__ __forceinline__ void place(WorkUnit& u, int t) const {
     const int group_size = 8 * q_blocks;
     const int group = t / group_size;
     const int first_p = group * 8;
@@ -289,11 +302,49 @@ struct TileSched {
     const int r = t - group * group_size;
     u.pb = first_p + r % gp;
     u.qb = r / gp;
-    u.tile = u.pb * q_blocks + u.qb;
-    u.kb0 = u.split * kb_per_split;
-    u.kb1 = min(num_kb, u.kb0 + kb_per_split);
     u.p_coord = u.pb * kBlockP;
     u.q_coord = u.qb * bn;
+  }
+  __device__ __forceinline__ WorkUnit get(int w) const {
+    WorkUnit u;
+    if (sk_tiles == 0) {
+      u.split = w % splits;
+      place(u, w / splits);
+      u.tile = u.pb * q_blocks + u.qb;
+      u.nsplit = splits;
+      u.kb0 = u.split * kb_per_split;
+      u.kb1 = min(num_kb, u.kb0 + kb_per_split);
+      return u;
+    }
+    const int cta = w % num_ctas, j = w / num_ctas;
+    u.split = 0;
+    u.nsplit = 1;
+    u.tile = 0;
+    if (j < sk_units) {
+      const int start = cta * sk_per, end = min(start + sk_per, sk_tiles * num_kb);
+      const int t = start / num_kb + j;
+      const int lo = max(start, t * num_kb), hi = min(end, (t + 1) * num_kb);
+      if (t >= sk_tiles || lo >= hi) {
+        u.pb = u.qb = u.kb0 = u.kb1 = u.p_coord = u.q_coord = 0;
+        return u;
+      }
+      place(u, t);
+      u.kb0 = lo - t * num_kb;
+      u.kb1 = hi - t * num_kb;
+      const int first = (t * num_kb) / sk_per, last = ((t + 1) * num_kb - 1) / sk_per;
+      u.nsplit = last - first + 1;
+      u.split = cta - first;
+      u.tile = first;  // a CTA is the first contributor of at most one tile: its index names the workspace slot
+      return u;
+    }
+    const int t = sk_tiles + (j - sk_units) * num_ctas + cta;
+    if (t >= p_blocks * q_blocks) {
+      u.pb = u.qb = u.kb0 = u.kb1 = u.p_coord = u.q_coord = 0;
+      return u;
+    }
+    place(u, t);
+    u.kb0 = 0;
+    u.kb1 = num_kb;
     return u;
   }
 };

@@ -27,7 +27,7 @@ struct EpiParams {
   int64_t ldy;
   int64_t ldr;
   int M, N;          // logical output shape before any SwiGLU halving
-  int splits;
+  int splits;        // slots per tile in the workspace (split-K: the split count; stream-K: the most contributors a tile can have)
   float* workspace;  // [tiles][splits][BN][128] f32 partials
   uint32_t* counters;  // [tiles], zero on entry and on exit
   int mode;          // B2Epilogue
@@ -143,8 +143,8 @@ struct Epilogue {
   __device__ __forceinline__ void operator()(const WorkUnit& u, uint32_t taddr, int quarter, int lane,
                                              uint32_t* flag, Status* status) const {
     const int p_local = quarter * 32 + lane;
-    AccSource<BN, CH> src{false, taddr, nullptr, p.splits, p_local};
-    if (p.splits > 1) {
+    AccSource<BN, CH> src{false, taddr, nullptr, u.nsplit, p_local};
+    if (u.nsplit > 1) {
       // 1. publish this CTA's partial
       float* ws_tile = p.workspace + static_cast<size_t>(u.tile) * p.splits * BN * 128;
       float* mine = ws_tile + static_cast<size_t>(u.split) * BN * 128 + p_local;
@@ -159,7 +159,7 @@ struct Epilogue {
       ptx::named_barrier_sync(1, gemm::kEpiThreads);
       if (threadIdx.x == 64) {  // first epilogue thread
         const uint32_t old = atomicAdd(p.counters + u.tile, 1u);
-        const bool last = old == static_cast<uint32_t>(p.splits - 1);
+        const bool last = old == static_cast<uint32_t>(u.nsplit - 1);
         if (last) p.counters[u.tile] = 0;  // leave the counter ready for the next launch
         __threadfence();
         *flag = last ? 1u : 0u;
@@ -200,27 +200,56 @@ struct Config {
   bool swap;
   int bn;
   int splits;
+  bool stream_k;   // cut the ragged last wave along K instead (splits == 1)
 };
+
+// Stream-K geometry for `tiles` output tiles of `num_kb` k-blocks on a grid of kNumSMs CTAs.
+struct StreamK {
+  int sk_tiles, per, units, max_nsplit;
+};
+StreamK stream_k_plan(long tiles, int num_kb) {
+  StreamK s{};
+  int rem = static_cast<int>(tiles % kNumSMs);
+  if (tiles >= 2 * kNumSMs && rem > 0 && rem * 2 < kNumSMs) rem += kNumSMs;  // short runs cost more fix-up than they balance
+  s.sk_tiles = rem;
+  if (rem == 0) return s;
+  const long iters = static_cast<long>(rem) * num_kb;
+  s.per = static_cast<int>((iters + kNumSMs - 1) / kNumSMs);
+  s.units = (s.per + num_kb - 1) / num_kb + 1;
+  s.max_nsplit = (num_kb + s.per - 1) / s.per + 1;
+  return s;
+}
 
 // Cost model behind the automatic configuration (cycles at SM clock; constants fitted to a sweep of the four
 // Llama-8B layer GEMMs at M = 16 ... 1024 on a B200):
 //   one work unit = k-blocks * max(tensor time, shared-memory fill time) + fixed epilogue cost
 //   tensor time of a 128 x bn x 64 block  = 2 * bn / 0.75   (8192 dense bf16 FLOP/clk/SM nominal, ~75 % reachable)
 //   fill time of the same block           = (128 + bn) * 128 B at ~128 B/clk from L2
+//   a unit can go no faster than its share of the operand bytes at one SM's share of HBM bandwidth (decode shapes)
 //   split-K adds a semaphore round trip and a pass over splits * bn * 128 f32 partials
 //   the kernel is persistent over 148 SMs, so the total is waves * unit + launch/prologue cost,
 //   and never less than streaming every operand once from HBM.
-double model_cycles(int M, int N, int K, bool swap, int bn, int splits) {
+double model_cycles(int M, int N, int K, bool swap, int bn, int splits, bool stream_k = false) {
   const int num_kb = (K + 63) / 64;
   const int rows_p = swap ? N : M, rows_q = swap ? M : N;
   const long units = static_cast<long>((rows_p + 127) / 128) * ((rows_q + bn - 1) / bn) * splits;
   const double kb = (num_kb + splits - 1) / splits;
   const double mma = kb * 2.0 * bn / 0.75;
   const double fill = kb * (128.0 + bn);
-  double unit = (mma > fill ? mma : fill) + 600.0;
+  // each unit's share of the bytes that must come from HBM, at one SM's share of the HBM bandwidth
+  const double dram = (static_cast<double>(N) * K + static_cast<double>(M) * K) * 2.0 / units / (3300.0 / kNumSMs);
+  double unit = (mma > fill ? mma : fill);
+  unit = (unit > dram ? unit : dram) + 600.0;
   if (splits > 1) unit += 2500.0 + splits * bn * 128.0 * 4.0 / 48.0;
-  const double waves = static_cast<double>((units + kNumSMs - 1) / kNumSMs);
-  const double total = waves * unit + 7000.0;
+  double waves = static_cast<double>((units + kNumSMs - 1) / kNumSMs);
+  double extra = 0.0;
+  if (stream_k) {
+    // every CTA gets the same number of k-blocks; each pays the epilogue of the tiles it touches and one fix-up
+    const StreamK sk = stream_k_plan(units, num_kb);
+    waves = static_cast<double>(units) / kNumSMs;
+    if (sk.sk_tiles > 0) extra = 600.0 * sk.units + 2500.0 + sk.max_nsplit * bn * 128.0 * 4.0 / 48.0;
+  }
+  const double total = waves * unit + extra + 7000.0;
   const double hbm = (static_cast<double>(N) * K + static_cast<double>(M) * K + static_cast<double>(M) * N) * 2.0 / 3300.0 + 5000.0;
   return total > hbm ? total : hbm;
 }
@@ -238,13 +267,24 @@ Config choose_config(int M, int N, int K, int epilogue) {
     const double t = model_cycles(M, N, K, swap, bn, splits);
     if (t < best_t) {
       best_t = t;
-      best = Config{swap, bn, splits};
+      best = Config{swap, bn, splits, false};
+    }
+    // Stream-K staggers the CTAs along K, which breaks the lock-step in which CTAs that share an operand tile
+    // fetch it (measured: up to 1.5x slower once operands are shared). It pays where nothing is shared: the
+    // swapped layout with a single token tile, where every weight byte is read by exactly one CTA.
+    if (splits == 1 && swap && M <= bn && num_kb >= 8 && tiles % kNumSMs != 0) {
+      const double ts = model_cycles(M, N, K, swap, bn, 1, true);
+      if (ts < best_t) {
+        best_t = ts;
+        best = Config{swap, bn, 1, true};
+      }
     }
   };
   static const int kSplits[] = {1, 2, 4, 8};
-  if (M <= 128) {
-    static const int kBn[] = {16, 32, 64, 128};
+  if (M <= 256) {
+    static const int kBn[] = {16, 32, 64, 128, 256};
     for (int bn : kBn) {
+      if (bn == 256 && M <= 128) continue;
       if (bn * 4 < M || (bn >= 2 * M && bn > 16)) continue;  // neither many token tiles nor mostly padding
       for (int sp : kSplits) consider(true, bn, sp);
     }
@@ -256,12 +296,12 @@ Config choose_config(int M, int N, int K, int epilogue) {
       for (int sp : kSplits) consider(false, bn, sp);
     }
   }
-  if (best_t == 1e300) best = Config{true, 16, 1};
+  if (best_t == 1e300) best = Config{true, 16, 1, false};
   return best;
 }
 
 template <int BN, bool SWAP>
-int launch(const void* x, const void* w, int M, int N, int K, int64_t ldx, int64_t ldw, int splits, EpiParams ep,
+int launch(const void* x, const void* w, int M, int N, int K, int64_t ldx, int64_t ldw, int splits, bool stream_k, EpiParams ep,
            Status* status, cudaStream_t stream) {
   constexpr int STAGES = stages_for(BN);
   using L = gemm::SmemLayout<BN, STAGES>;
@@ -275,7 +315,7 @@ int launch(const void* x, const void* w, int M, int N, int K, int64_t ldx, int64
       !make_tmap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q_ptr, rows_q, K, ldq * 2, BN, 64,
                     CU_TENSOR_MAP_SWIZZLE_128B))
     return -kBadArgument;
-  gemm::TileSched sched;
+  gemm::TileSched sched{};
   sched.p_blocks = (rows_p + 127) / 128;
   sched.q_blocks = (rows_q + BN - 1) / BN;
   sched.splits = splits;
@@ -283,6 +323,16 @@ int launch(const void* x, const void* w, int M, int N, int K, int64_t ldx, int64
   sched.kb_per_split = (sched.num_kb + splits - 1) / splits;
   sched.bn = BN;
   ep.splits = splits;
+  if (stream_k && splits == 1) {
+    const StreamK sk = stream_k_plan(static_cast<long>(sched.p_blocks) * sched.q_blocks, sched.num_kb);
+    if (sk.sk_tiles > 0) {
+      sched.sk_tiles = sk.sk_tiles;
+      sched.sk_per = sk.per;
+      sched.sk_units = sk.units;
+      sched.num_ctas = kNumSMs;
+      ep.splits = sk.max_nsplit;
+    }
+  }
   auto kern = gemm_bf16_kernel<BN, STAGES, SWAP>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -291,7 +341,7 @@ int launch(const void* x, const void* w, int M, int N, int K, int64_t ldx, int64
     attr_set = true;
   }
   const int total = sched.p_blocks * sched.q_blocks * splits;
-  const int grid = total < kNumSMs ? total : kNumSMs;
+  const int grid = (total < kNumSMs && sched.sk_tiles == 0) ? total : kNumSMs;
   // Weights are read once per step: stream them; activations are re-read by every weight tile: keep them.
   const uint64_t pol_w = ptx::kEvictFirst, pol_x = ptx::kEvictLast;
   const uint64_t pol_p = SWAP ? pol_w : (M <= 1024 ? pol_x : ptx::kEvictNormal);
@@ -320,9 +370,11 @@ extern "C" int b2_gemm_bf16(const void* x, const void* w, void* y, const void* r
   Config c = choose_config(M, N, K, epilogue);
   if (config != 0) {
     c.swap = (config >> 30) & 1;
+    c.stream_k = (config >> 29) & 1;
     c.splits = (config >> 16) & 0xff;
     c.bn = config & 0xffff;
     if (c.splits < 1) c.splits = 1;
+    if (c.stream_k) c.splits = 1;
   }
   const int num_kb = (K + 63) / 64;
   if (c.splits > num_kb) c.splits = num_kb;
@@ -353,9 +405,21 @@ extern "C" int b2_gemm_bf16(const void* x, const void* w, void* y, const void* r
     if (workspace == nullptr || workspace_bytes < need || tiles > 65536) return -kTooLarge;
     ep.counters = static_cast<uint32_t*>(workspace);
     ep.workspace = reinterpret_cast<float*>(static_cast<char*>(workspace) + counters_bytes);
+  } else if (c.stream_k) {
+    const int64_t counters_bytes = 65536 * 4;
+    const int rows_p = c.swap ? N : M, rows_q = c.swap ? M : N;
+    const int64_t tiles = static_cast<int64_t>((rows_p + 127) / 128) * ((rows_q + c.bn - 1) / c.bn);
+    const StreamK sk = stream_k_plan(tiles, num_kb);
+    const int64_t need = counters_bytes + static_cast<int64_t>(kNumSMs) * sk.max_nsplit * c.bn * 128 * 4;
+    if (sk.sk_tiles == 0 || workspace == nullptr || workspace_bytes < need) {
+      c.stream_k = false;  // nothing ragged to balance, or no room for the partials: plain tile loop
+    } else {
+      ep.counters = static_cast<uint32_t*>(workspace);
+      ep.workspace = reinterpret_cast<float*>(static_cast<char*>(workspace) + counters_bytes);
+    }
   }
 #define B2_LAUNCH(BN_, SWAP_) \
-  return launch<BN_, SWAP_>(x, w, M, N, K, ldx, ldw, c.splits, ep, status, stream)
+  return launch<BN_, SWAP_>(x, w, M, N, K, ldx, ldw, c.splits, c.stream_k, ep, status, stream)
   if (c.swap) {
     switch (c.bn) {
       case 16: B2_LAUNCH(16, true);
@@ -444,7 +508,7 @@ extern "C" int b2_gemm_bf16_noalloc(const void* x, const void* w, void* y, int M
   ep.mode = B2_EPI_NONE;
   ep.counters = static_cast<uint32_t*>(scratch);
   ep.workspace = reinterpret_cast<float*>(static_cast<char*>(scratch) + counters_bytes);
-#define B2_LAUNCH_NA(BN_, SWAP_) return launch<BN_, SWAP_>(x, w, M, N, K, ldx, ldw, c.splits, ep, nullptr, stream)
+#define B2_LAUNCH_NA(BN_, SWAP_) return launch<BN_, SWAP_>(x, w, M, N, K, ldx, ldw, c.splits, false, ep, nullptr, stream)
   if (c.swap) {
     switch (c.bn) {
       case 16: B2_LAUNCH_NA(16, true);
@@ -466,4 +530,11 @@ extern "C" int b2_gemm_bf16_noalloc(const void* x, const void* w, void* y, int M
     default: return -kBadArgument;
   }
 #undef B2_LAUNCH_NA
+}
+
+// The configuration the automatic rule picks for a shape, encoded like the `config` argument
+// ((swap << 30) | (stream_k << 29) | (splits << 16) | bn): for tuning sweeps and tests. Host only, no launch.
+extern "C" int b2_gemm_auto_config(int M, int N, int K, int epilogue) {
+  const Config c = choose_config(M, N, K, epilogue);
+  return (static_cast<int>(c.swap) << 30) | (static_cast<int>(c.stream_k) << 29) | (c.splits << 16) | c.bn;
 }

@@ -362,7 +362,7 @@ int launch_fp8_rs(const void* xq, const float* xs, const void* wq, const float* 
     attr_set = true;
   }
   const int total = prm.p_blocks * prm.q_blocks;
-  int n_gemm = kNumSMs - (rs.tp > 1 ? 12 : 0);
+  int n_gemm = kNumSMs - (rs.tp > 1 ? (M >= 2048 ? 4 : 12) : 0);
   if (total < n_gemm) n_gemm = total;
   kern<<<kNumSMs, kThreads, SMEM, stream>>>(tmp, tmq, prm, sched, rs, ectl, n_gemm, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;

@@ -117,7 +117,7 @@ int launch_gguf(const void* x, const void* wq, int ggml_type, void* y, int M, in
   CUtensorMap tx;
   if (!make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, M, K, static_cast<uint64_t>(K) * 2, BN, 64, CU_TENSOR_MAP_SWIZZLE_128B))
     return -kBadArgument;
-  gemm::TileSched sched;
+  gemm::TileSched sched{};
   sched.p_blocks = (N + 127) / 128;
   sched.q_blocks = (M + BN - 1) / BN;
   sched.splits = 1;

@@ -98,7 +98,8 @@ int launch_rs(const void* x, const void* w, int M, int N, int K, int64_t ldx, in
     attr_set = true;
   }
   // Full persistent grid: the last CTAs only reduce from the start, the others join once their tiles are done.
-  const int n_red = prm.tp > 1 ? 12 : 0;
+  // large M is GEMM-bound and the reduction of the last units is a short tail: give the GEMM more CTAs
+  const int n_red = prm.tp > 1 ? (M >= 2048 ? 4 : 12) : 0;
   const int total = sched.p_blocks * sched.q_blocks;
   int n_gemm = kNumSMs - n_red;
   if (total < n_gemm) n_gemm = total;
@@ -438,7 +439,7 @@ extern "C" int b2_tp_gemm_rs_bf16(const void* x, const void* w, const B2TpRegion
   prm.out = static_cast<__nv_bfloat16*>(out);
   prm.timeout_ns = timeout_ns;
   bool swap = M <= 128;
-  int bn = swap ? pick_bn_swap(M) : 128;
+  int bn = swap ? pick_bn_swap(M) : (M >= 2048 ? 256 : 128);
   if (config != 0) {
     swap = (config >> 30) & 1;
     bn = config & 0xffff;

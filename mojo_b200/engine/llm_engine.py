@@ -47,6 +47,7 @@ class EngineConfig:
     use_cuda_graphs: bool = True
     tp_size: int = 1
     ep_size: int = 1
+    autotune: bool = False                # measure GEMM configurations for this model's shapes at start-up
 
 
 @dataclass
@@ -102,6 +103,8 @@ class LLMEngine:
         from .model_runner import ModelRunner
 
         self.runner = ModelRunner(self.model, self.kv_caches, cfg)
+        if cfg.autotune:
+            self.runner.autotune()
 
     def _auto_num_pages(self) -> int:
         cfg = self.cfg

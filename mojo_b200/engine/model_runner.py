@@ -80,6 +80,23 @@ class ModelRunner:
             b = b * 2 if b < 16 else b + max(16, b // 4) // 16 * 16
         self.buckets.append(cfg.max_num_seqs)
 
+    def autotune(self, verbose: bool = False) -> dict:
+        """Measure the GEMM configurations of this model's weight shapes at the token counts the engine produces
+        (decode graph buckets, then multiples of 128 up to the token budget). A second or two, once, before serving."""
+        if not self.cuda or not hasattr(self.model, "gemm_shapes"):
+            return {}
+        counts = ops.autotune.default_token_counts(self.cfg.max_num_batched_tokens, self.buckets)
+        report = {}
+        for N, K, epi, max_m in self.model.gemm_shapes():
+            ms = [m for m in counts if not max_m or m <= max_m]
+            report[(N, K, epi)] = ops.autotune.tune(N, K, epi, ms, self.device)
+            if verbose:
+                for m, (cfg, us, us_auto) in report[(N, K, epi)].items():
+                    print(f"[autotune] N={N} K={K} epi={epi} M={m}: {ops.autotune.describe(cfg)} {us:.1f} us (rule: {us_auto:.1f} us)")
+        torch.cuda.synchronize(self.device)
+        ops.check_status(self.device)
+        return report
+
     # ------------------------------------------------------------------------------------------------
     def execute(self, batch, states, step: int) -> list[int]:
         self.last_num_tokens = int(batch.num_tokens)

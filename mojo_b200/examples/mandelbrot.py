@@ -5,6 +5,8 @@ from __future__ import annotations
 
 import time
 
+import ctypes
+
 import numpy as np
 import torch
 
@@ -17,7 +19,7 @@ MIN_X, MAX_X, MIN_Y, MAX_Y = -2.0, 0.6, -1.5, 1.5
 
 def gpu() -> torch.Tensor:
     out = torch.empty(ROWS, COLS, dtype=torch.int32, device="cuda")
-    assert lib().b2_ex_mandelbrot(ptr(out), ROWS, COLS, MAX_ITERS, *(torch.tensor(v).float().item() for v in (MIN_X, MAX_X, MIN_Y, MAX_Y)), stream()) == 0
+    assert lib().b2_ex_mandelbrot(ptr(out), ROWS, COLS, MAX_ITERS, *(ctypes.c_float(v) for v in (MIN_X, MAX_X, MIN_Y, MAX_Y)), stream()) == 0
     return out
 
 

@@ -8,7 +8,7 @@ from __future__ import annotations
 import torch
 
 from .. import _ext
-from . import _state, reference
+from . import _state, autotune, reference
 from ._state import KernelError, check_status
 
 EPI_NONE, EPI_ADD_RESIDUAL, EPI_SWIGLU = 0, 1, 2
@@ -158,7 +158,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = Non
     st = _state.get(x.device)
     if out is None:
         out = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
-    C.gemm_bf16(x, w, out, residual, EPI_ADD_RESIDUAL if residual is not None else EPI_NONE, config, st.gemm_ws, st.status)
+    epi = EPI_ADD_RESIDUAL if residual is not None else EPI_NONE
+    if config == 0:
+        config = autotune.lookup(x.shape[0], w.shape[0], w.shape[1], epi, x.device.index or 0)
+    C.gemm_bf16(x, w, out, residual, epi, config, st.gemm_ws, st.status)
     _count()
     return out
 
@@ -172,6 +175,8 @@ def linear_swiglu(x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tensor | None 
     st = _state.get(x.device)
     if out is None:
         out = torch.empty(x.shape[0], w_gu.shape[0] // 2, dtype=x.dtype, device=x.device)
+    if config == 0:
+        config = autotune.lookup(x.shape[0], w_gu.shape[0], w_gu.shape[1], EPI_SWIGLU, x.device.index or 0)
     C.gemm_bf16(x, w_gu, out, None, EPI_SWIGLU, config, st.gemm_ws, st.status)
     _count()
     return out
@@ -224,9 +229,10 @@ def linear_gguf(x: torch.Tensor, w_q: torch.Tensor, ggml_type: int, n_out: int) 
     return y
 
 
-def gemm_config(swap: bool, bn: int, splits: int = 1) -> int:
-    """Encode an explicit GEMM configuration (for tuning sweeps): operand swap, UMMA N, split-K factor."""
-    return (int(swap) << 30) | (splits << 16) | bn
+def gemm_config(swap: bool, bn: int, splits: int = 1, stream_k: bool = False) -> int:
+    """Encode an explicit GEMM configuration (for tuning sweeps): operand swap, UMMA N, split-K factor, or
+    stream-K balancing of the ragged last wave (excludes split-K)."""
+    return (int(swap) << 30) | (int(stream_k) << 29) | ((1 if stream_k else splits) << 16) | bn
 
 
 class AttnMeta:

@@ -112,20 +112,20 @@ def main():
 
     for i, M in enumerate([8, 48, 256, 1024]):
         N = hidden
-        x = mk((M, k_local), 7000 + 10 * i + rank)
-        w = mk((N, k_local), 7500 + 10 * i + rank, 0.05)
+        x8 = mk((M, k_local), 7000 + 10 * i + rank)
+        w8 = mk((N, k_local), 7500 + 10 * i + rank, 0.05)
         res = mk((M, N), 7900 + i)
-        xq, xs = ops.quant_e4m3(x)
-        wq, ws = reference.quant_e4m3_128x128(w)
-        want = reference.linear_fp8_block(xq, xs, wq, ws).float()
-        dist.all_reduce(want)
+        xq, xs = ops.quant_e4m3(x8)
+        wq, ws = reference.quant_e4m3_128x128(w8)
+        want8 = reference.linear_fp8_block(xq, xs, wq, ws).float()
+        dist.all_reduce(want8)
         for rep in range(2):
             y = comm.linear_fp8_all_reduce((xq, xs), wq, ws, residual=res if rep else None)
-            close(y, want + res.float() if rep else want, f"fp8 all-reduce M={M} rep={rep}")
+            close(y, want8 + res.float() if rep else want8, f"fp8 all-reduce M={M} rep={rep}")
         if M % tp == 0:
             r = M // tp
-            y3 = comm.linear_fp8_reduce_scatter(x, wq, ws)
-            close(y3, want[rank * r:(rank + 1) * r], f"fp8 reduce-scatter M={M}")
+            y3 = comm.linear_fp8_reduce_scatter(x8, wq, ws)
+            close(y3, want8[rank * r:(rank + 1) * r], f"fp8 reduce-scatter M={M}")
     torch.cuda.synchronize()
     ops.check_status(dev)
 

@@ -122,6 +122,16 @@ def test_gemm_normal_tiles(bn):
     _gemm_case(300, 1280, 768, config=ops.gemm_config(False, bn), residual=True)
 
 
+@pytest.mark.parametrize("M,N,K,swap,bn", [(300, 1280, 768, False, 128), (1100, 4096, 1024, False, 256), (2500, 3072, 512, False, 128),
+                                          (4200, 8192, 1024, False, 256), (64, 6144, 4096, True, 64), (100, 30000, 1024, True, 128),
+                                          (777, 1000, 8192, False, 64)])
+def test_gemm_stream_k(M, N, K, swap, bn):
+    """Ragged last wave cut along K: fewer tiles than CTAs, a little over one wave, many waves plus a remainder."""
+    cfg = ops.gemm_config(swap, bn, stream_k=True)
+    _gemm_case(M, N, K, config=cfg, residual=True)
+    _gemm_case(M, N, K, config=cfg, seed=1)   # twice in a row: the fix-up counters must come back to zero
+
+
 @pytest.mark.parametrize("M", [1, 7, 16, 33, 64, 100, 128, 200, 256])
 def test_gemm_small_m_auto(M):
     _gemm_case(M, 1024, 2048, residual=(M % 2 == 0))
@@ -346,3 +356,22 @@ def test_status_word_reports_bad_index():
         ops.check_status()
     assert e.value.code == 2 and e.value.a == 9
     ops.check_status()  # cleared
+
+
+def test_gemm_autotune_table_picks_valid_faster_or_equal_configs():
+    """The measured table only ever holds configurations the kernel accepts, and looking one up gives the same
+    numbers as the analytic rule's choice."""
+    from mojo_b200.ops import autotune
+
+    autotune.clear()
+    N, K = 1536, 2048
+    rep = autotune.tune(N, K, ops.EPI_NONE, [8, 64, 200, 640], torch.device(DEV))
+    assert set(rep) == {8, 64, 200, 640}
+    for m, (cfg, us, us_rule) in rep.items():
+        assert us <= us_rule * 1.001 and (cfg == 0 or cfg in autotune.candidates(m, N, K, ops.EPI_NONE))
+    assert autotune.lookup(50, N, K, ops.EPI_NONE) == rep[64][0] and autotune.lookup(5000, N, K, ops.EPI_NONE) == 0
+    try:
+        _gemm_case(50, N, K)     # goes through the table
+        _gemm_case(600, N, K, residual=True)   # residual epilogue has no table: analytic rule
+    finally:
+        autotune.clear()
