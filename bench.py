@@ -30,6 +30,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 
+METRIC_NAMES = {"llama-3.1-8b": "Llama-3.1-8B bf16", "llama-3.3-70b-fp8": "Llama-3.3-70B fp8 block-scaled",
+                "deepseek-v2-lite": "DeepSeek-V2-Lite bf16 (MLA + MoE)"}
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -47,6 +51,7 @@ def parse_args():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--no-autotune", action="store_true", help="skip the start-up measurement of GEMM configurations")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--sp", action="store_true", help="sequence-parallel dataflow: all-gather -> GEMM and GEMM -> reduce-scatter kernels")
     ap.add_argument("--layers", type=int, default=None, help="debug only: marks the result invalid")
     ap.add_argument("--profile", default=None, help="debug only: write a per-kernel table of a few steps to this file")
     return ap.parse_args()
@@ -90,12 +95,22 @@ def main() -> None:
         debug_invalid = True
     if args.impl == "torch-baseline":
         args.comm = "nccl"
+    # Named configurations: the Llama models are tensor-parallel over all GPUs; the DeepSeek MoE model runs
+    # data-parallel attention (every rank serves its own requests from its own KV cache) with the routed experts
+    # spread over all GPUs (expert parallelism) and every rank in lock-step through the MoE layers.
+    ep_mode = mcfg.architecture == "deepseek_v2"
     comm = None
-    if world > 1:
+    ep = None
+    if ep_mode:
+        from mojo_b200.parallel.ep import EPComm
+
+        ep = EPComm(info, mcfg.n_routed_experts, mcfg.hidden_size, mcfg.moe_intermediate_size, mcfg.num_experts_per_tok,
+                    max_tokens=args.max_batched_tokens, timeout_s=30.0)
+    elif world > 1:
         if args.comm == "fused" and args.impl == "mojo_b200":
             from mojo_b200.parallel.fused import FusedTPComm
 
-            comm = FusedTPComm(info, max_tokens=args.max_batched_tokens, hidden=mcfg.hidden_size)
+            comm = FusedTPComm(info, max_tokens=args.max_batched_tokens, hidden=mcfg.hidden_size, max_k=mcfg.hidden_size)
         else:
             from mojo_b200.parallel.tp import NcclTPComm
 
@@ -107,15 +122,29 @@ def main() -> None:
         args.no_graphs = True
         args.comm = "nccl"
 
-    max_model_len = 2048 + 512 + 128
+    fixed = {"llama-3.3-70b-fp8": (256, 1024, 256), "deepseek-v2-lite": (512, 512, 256), "tiny-deepseek": (64, 64, 16)}.get(args.model)
+    max_model_len = 2048 + 512 + 128 if fixed is None else fixed[1] + fixed[2] + 128
+    if fixed is not None:
+        args.max_num_seqs = max(1, fixed[0] // (world if ep_mode else 1))
+        args.requests = fixed[0]
     ecfg = EngineConfig(model=mcfg, device=str(device), dtype=torch.bfloat16, page_size=args.page_size,
                         max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_batched_tokens,
-                        max_model_len=max_model_len, seed=0, use_cuda_graphs=not args.no_graphs, tp_size=world,
+                        max_model_len=max_model_len, seed=0, use_cuda_graphs=not args.no_graphs, tp_size=1 if ep_mode else world,
+                        ep_size=world if ep_mode else 1, lockstep=ep_mode and world > 1,
                         autotune=(args.impl == "mojo_b200" and not args.no_autotune and device.type == "cuda"))
-    model = build_model(mcfg, device, torch.bfloat16, comm=comm).init_random(0)
+    model = build_model(mcfg, device, torch.bfloat16, comm=comm, ep=ep).init_random(0)
+    if args.sp and world > 1 and args.comm == "fused":
+        model.sequence_parallel = True
     engine = LLMEngine(ecfg, model=model, comm=comm)
 
-    trace = poisson_trace(args.requests, args.rate, (128, 2048), (64, 512), mcfg.vocab_size, seed=1)
+    if fixed is None:
+        trace = poisson_trace(args.requests, args.rate, (128, 2048), (64, 512), mcfg.vocab_size, seed=1)
+    else:
+        from mojo_b200.utils.workload import fixed_batch
+
+        trace = fixed_batch(fixed[0], fixed[1], fixed[2], mcfg.vocab_size, seed=1)   # one batch, all present at t = 0
+    if ep_mode and world > 1:
+        trace = trace[rank::world]      # data-parallel attention: every rank serves its own share of the requests
     state = {"next": 0, "epoch": 0, "t0": None, "offset": 0.0}
 
     def feed() -> None:
@@ -143,10 +172,20 @@ def main() -> None:
 
     def one_step(timed: bool):
         feed()
-        if not engine.has_unfinished():
+        if not engine.has_unfinished() and not (ep_mode and world > 1):
             # idle gap in the arrival process: wait for the next arrival without burning a step
+            # (expert-parallel ranks never skip: a rank without work still joins every MoE layer of the step)
             time.sleep(0.0005)
             return None
+        if timed and ep_mode:
+            # a rank may have an idle step (it only serves peers' tokens in the MoE layers): bracket the whole step
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            engine.runner.step_events = None
+            s.record()
+            outs = engine.step()
+            e.record()
+            ev_pairs.append((s, e))
+            return outs
         if timed:
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             engine.runner.step_events = (s, e)
@@ -167,6 +206,13 @@ def main() -> None:
             continue
         ramp += 1
         finished += sum(o.finished for o in outs)
+        if ramp % 8 == 1:
+            ops.check_status(device)   # a kernel that gave up (bounded wait) ends the run here instead of after every step
+        if ep_mode and world > 1:
+            # ranks serve different requests: agree on when the ramp ends so that all take the same number of steps
+            flag = torch.tensor([finished], dtype=torch.int64)
+            torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MAX, group=info.host_group)
+            finished = int(flag[0])
     # ---- warm-up ----
     w = 0
     while w < args.warmup:
@@ -217,29 +263,35 @@ def main() -> None:
         t_wall = time.perf_counter() - t_start
     launches = ops.reset_launch_count() + engine.runner.graph_kernel_launches
     ops.check_status(device)
-    dev_ms = sum(s.elapsed_time(e) for s, e in ev_pairs)
+    dev_ms = sum(s.elapsed_time(e) for s, e in ev_pairs if s is not None)
     times = torch.tensor([dev_ms, t_wall * 1e3], dtype=torch.float64, device=device)
     if world > 1:
         torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
     dev_ms, wall_ms = float(times[0]), float(times[1])
+    if ep_mode and world > 1:
+        # data-parallel ranks produce different tokens: the job's output is their sum
+        counts = torch.tensor([tokens, prefill_tokens, h2d, d2h, launches], dtype=torch.float64, device=device)
+        torch.distributed.all_reduce(counts)
+        tokens, prefill_tokens, h2d, d2h, launches = (int(c) for c in counts.tolist())
 
     if rank == 0:
         m = engine.metrics()
         value = tokens / (dev_ms / 1e3)
         e2e = tokens / (wall_ms / 1e3)
         line = {
-            "metric": "output tok/s/box, Llama-3.1-8B bf16, continuous batching (paged KV, page 128)",
+            "metric": f"output tok/s/box, {METRIC_NAMES.get(args.model, args.model)}, continuous batching (paged KV, page {args.page_size})",
             "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(dev_ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16",
+            "vs_baseline": None, "dtype": "fp8 block-scaled weights and GEMMs, bf16 activations" if mcfg.quantization == "fp8_block" else "bf16",
             "data": "synthetic: uniform-random token ids, random-init N(0,0.02) weights of the named architecture",
             "impl": args.impl,
             "config": {
-                "model": args.model, "global_batch": args.max_num_seqs, "seq_len": "prompt U[128,2048] + output U[64,512]",
-                "parallelism": f"tp{world}", "requests": args.requests, "poisson_rate_per_s": args.rate,
+                "model": args.model, "global_batch": args.max_num_seqs * (world if ep_mode else 1),
+                "seq_len": "prompt U[128,2048] + output U[64,512]" if fixed is None else f"prompt {fixed[1]} + output {fixed[2]}",
+                "parallelism": (f"dp{world}-attention + ep{world}-experts" if ep_mode else f"tp{world}"), "requests": args.requests, "poisson_rate_per_s": args.rate,
                 "max_num_batched_tokens": args.max_batched_tokens, "page_size": args.page_size, "ramp_steps": ramp,
-                "l2": "inputs larger than L2: every step streams the full weight set (16 GB / tp) through the 126 MB L2",
-                "cuda_graphs": not args.no_graphs, "gemm_autotune": bool(ecfg.autotune), "comm": args.comm if world > 1 else "none",
+                "l2": "inputs larger than L2: every step streams this rank's full weight set (GBs) through the 126 MB L2",
+                "cuda_graphs": not args.no_graphs, "gemm_autotune": bool(ecfg.autotune), "comm": args.comm if world > 1 else "none", "sequence_parallel": bool(getattr(model, "sequence_parallel", False)),
                 "prefill_tokens_in_timed_region": prefill_tokens, "output_tokens_in_timed_region": tokens,
             },
             "clocks": {k: clocks.summary().get(k) for k in ("sm_mhz", "sm_max_mhz", "reasons", "power_w_max")},

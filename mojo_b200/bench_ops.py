@@ -41,6 +41,7 @@ def timed(fn, iters: int, warm: int, info) -> float:
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
+    ops.check_status(info.device)   # a wait that ran out in the warm-up ends the sweep here, not after every timed launch
     if info.world_size > 1:
         dist.barrier()
     torch.cuda.synchronize()
@@ -56,6 +57,93 @@ def timed(fn, iters: int, warm: int, info) -> float:
     return float(t)
 
 
+def _hbm_gbs() -> float:
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(p))["hbm_gbs"])
+    except Exception:  # noqa: BLE001
+        return 6650.0
+
+
+def fp8_sweep(a, info, comm, ms, peak_bf16) -> None:
+    """Block-scaled fp8 variant of the sweep. The unfused arm is this library's own fp8 GEMM followed by the NCCL
+    collective (torch has no block-scaled fp8 matmul to stand in for the library GEMM). There is no measured fp8
+    GEMM peak on file: the compute roof uses twice the measured bf16 peak, the ratio of the nominal figures."""
+    from .ops import reference
+
+    tp, rank, dev = info.world_size, info.rank, info.device
+    k_local, n_ag_local = a.inner // tp, a.cols_ag // tp
+    peak = 2.0 * peak_bf16
+    rows = []
+    for M in ms:
+        Mp = (M + tp - 1) // tp * tp
+        x = torch.randn(Mp, k_local, device=dev).bfloat16()
+        xq, xs = ops.quant_e4m3(x)
+        wq, ws = reference.quant_e4m3_128x128(torch.randn(a.cols, k_local, device=dev) * 0.02)
+        y_full = torch.empty(Mp, a.cols, device=dev, dtype=torch.bfloat16)
+        y_shard = torch.empty(Mp // tp, a.cols, device=dev, dtype=torch.bfloat16)
+
+        def base_rs():
+            ops.linear_fp8((xq, xs), wq, ws, out=y_full)
+            if tp > 1:
+                dist.reduce_scatter_tensor(y_shard, y_full)
+
+        t_base_rs = timed(base_rs, a.iters, 3, info)
+        t_rs = timed(lambda: comm.linear_fp8_reduce_scatter((xq, xs), wq, ws), a.iters, 3, info)
+        t_gemm = timed(lambda: ops.linear_fp8((xq, xs), wq, ws, out=y_full), a.iters, 3, info)
+        flops = 2.0 * Mp * a.cols * k_local
+        rs_bytes = (tp - 1) / tp * Mp * a.cols * 2
+        roof_rs = max(flops / (peak * 1e6), rs_bytes / (NVLINK_GBS * 1e3))
+        # all-gather GEMM: quantised rows + scales are gathered
+        xfull = torch.randn(Mp, a.inner_ag, device=dev).bfloat16()
+        waq, was = reference.quant_e4m3_128x128(torch.randn(n_ag_local, a.inner_ag, device=dev) * 0.02)
+        r = Mp // tp
+        x_r = xfull[rank * r:(rank + 1) * r].contiguous()
+        xq_r, xs_r = ops.quant_e4m3(x_r)
+        xq_all = torch.empty(Mp, a.inner_ag, device=dev, dtype=torch.float8_e4m3fn)
+        xs_all = torch.empty(Mp, a.inner_ag // 128, device=dev, dtype=torch.float32)
+        y_ag = torch.empty(Mp, n_ag_local, device=dev, dtype=torch.bfloat16)
+
+        def base_ag():
+            if tp > 1:
+                dist.all_gather_into_tensor(xq_all.view(torch.uint8), xq_r.view(torch.uint8))
+                dist.all_gather_into_tensor(xs_all, xs_r)
+            else:
+                xq_all.copy_(xq_r)
+                xs_all.copy_(xs_r)
+            ops.linear_fp8((xq_all, xs_all), waq, was, out=y_ag)
+
+        def fused_ag():
+            qv, sv = comm.gather_input_fp8(Mp, a.inner_ag)
+            qv.copy_(xq_r)
+            sv.copy_(xs_r)
+            comm.all_gather_linear_fp8(waq, was, Mp, out=y_ag)
+
+        t_base_ag = timed(base_ag, a.iters, 3, info)
+        t_ag = timed(fused_ag, a.iters, 3, info)
+        flops_ag = 2.0 * Mp * n_ag_local * a.inner_ag
+        ag_bytes = (tp - 1) / tp * Mp * (a.inner_ag + a.inner_ag // 32)
+        roof_ag = max(flops_ag / (peak * 1e6), ag_bytes / (NVLINK_GBS * 1e3))
+        torch.cuda.synchronize()
+        ops.check_status(dev)
+        row = {
+            "M": M, "tp": tp, "N": a.cols, "K_local": k_local, "dtype": "fp8 block-scaled", "gemm_only_us": round(t_gemm, 1),
+            "gemm_rs": {"fused_us": round(t_rs, 1), "gemm_nccl_us": round(t_base_rs, 1), "roofline_us": round(roof_rs, 1),
+                        "pct_roofline": round(100 * roof_rs / t_rs, 1)},
+            "ag_gemm": {"fused_us": round(t_ag, 1), "all_gather_gemm_us": round(t_base_ag, 1), "roofline_us": round(roof_ag, 1),
+                        "pct_roofline": round(100 * roof_ag / t_ag, 1), "N_local": n_ag_local, "K": a.inner_ag},
+        }
+        rows.append(row)
+        if rank == 0:
+            print(json.dumps(row), flush=True)
+    if rank == 0 and a.out:
+        json.dump({"peak_tflops_assumed_fp8": peak, "nvlink_gbs": NVLINK_GBS, "rows": rows}, open(a.out, "w"), indent=1)
+    if tp > 1:
+        dist.barrier()
+    sys.stdout.flush()
+    os._exit(0)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--sizes", default="64,256,1024,4096,16384")
@@ -65,6 +153,8 @@ def main() -> None:
     ap.add_argument("--cols-ag", type=int, default=28672, help="N of the all-gather GEMM before sharding")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--rs-bn", type=int, default=0, help="force the UMMA N of the fused reduce-scatter GEMM (0 = automatic)")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"],
+                    help="fp8: e4m3 operands with 1x128 activation and 128x128 weight scales (block-scaled), bf16 out")
     ap.add_argument("--out", default=None)
     a = ap.parse_args()
     info = init_distributed("cuda")
@@ -72,9 +162,12 @@ def main() -> None:
     ms = [int(x) for x in a.sizes.split(",")]
     k_local = a.inner // tp
     n_ag_local = a.cols_ag // tp
-    comm = FusedTPComm(info, max_tokens=max(ms), hidden=a.cols, max_k=a.inner_ag, timeout_s=10.0)
+    comm = FusedTPComm(info, max_tokens=max(ms), hidden=a.cols, max_k=a.inner_ag, timeout_s=3.0)
     peak = _peak_tflops()
     rows = []
+    if a.dtype == "fp8":
+        fp8_sweep(a, info, comm, ms, peak)
+        return
     for M in ms:
         Mp = (M + tp - 1) // tp * tp
         x = torch.randn(Mp, k_local, device=dev).bfloat16()
@@ -129,9 +222,14 @@ def main() -> None:
         roof_ag = max(flops_ag / (peak * 1e6), ag_bytes / (NVLINK_GBS * 1e3))
         torch.cuda.synchronize()
         ops.check_status(dev)
+        # the same roofs with the operand traffic over HBM included (what bounds the decode-sized rows)
+        hbm = _hbm_gbs() * 1e3
+        roof_rs_hbm = max(roof_rs, (a.cols * k_local + Mp * k_local + Mp * a.cols) * 2 / hbm)
+        roof_ag_hbm = max(roof_ag, (n_ag_local * a.inner_ag + Mp * a.inner_ag + Mp * n_ag_local) * 2 / hbm)
         row = {
             "M": M, "tp": tp, "N": a.cols, "K_local": k_local,
             "gemm_only_us": round(t_gemm, 1),
+            "pct_roofline_with_hbm": {"gemm_rs": round(100 * roof_rs_hbm / t_rs, 1), "ag_gemm": round(100 * roof_ag_hbm / t_ag, 1)},
             "gemm_rs": {"fused_us": round(t_rs, 1), "matmul_nccl_us": round(t_base_rs, 1), "roofline_us": round(roof_rs, 1),
                         "pct_roofline": round(100 * roof_rs / t_rs, 1)},
             "gemm_ar": {"fused_us": round(t_ar, 1), "matmul_nccl_us": round(t_base_ar, 1), "roofline_us": round(roof_ar, 1),

@@ -81,12 +81,12 @@ void rope_kvwrite(at::Tensor& q, at::Tensor& k, c10::optional<at::Tensor> v, con
         "rope_kvwrite");
 }
 
-void swiglu(const at::Tensor& gate_up, at::Tensor& out) {
+void swiglu(const at::Tensor& gate_up, at::Tensor& out, bool interleaved) {
   need(gate_up.is_cuda() && is_bf16(gate_up) && gate_up.is_contiguous() && out.is_contiguous() && is_bf16(out), "swiglu: contiguous CUDA bf16 required");
   const int ffn = static_cast<int>(out.size(-1));
   need(gate_up.size(-1) == 2 * ffn, "swiglu: gate_up last dim must be 2 * ffn");
   c10::cuda::CUDAGuard g(out.device());
-  check(b2_swiglu_bf16(gate_up.data_ptr(), out.data_ptr(), static_cast<int>(out.numel() / ffn), ffn, cur_stream()), "swiglu");
+  check(b2_swiglu_bf16(gate_up.data_ptr(), out.data_ptr(), static_cast<int>(out.numel() / ffn), ffn, interleaved ? 1 : 0, cur_stream()), "swiglu");
 }
 
 void embedding(const at::Tensor& ids, const at::Tensor& table, at::Tensor& out, int64_t vocab_start) {
@@ -257,7 +257,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rope_kvwrite", &rope_kvwrite, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("cos_sin"), py::arg("positions"),
         py::arg("slots"), py::arg("k_cache"), py::arg("v_cache"), py::arg("head_dim"), py::arg("interleaved") = false,
         py::arg("status") = py::none());
-  m.def("swiglu", &swiglu);
+  m.def("swiglu", &swiglu, py::arg("gate_up"), py::arg("out"), py::arg("interleaved") = false);
   m.def("embedding", &embedding, py::arg("ids"), py::arg("table"), py::arg("out"), py::arg("vocab_start") = 0);
   m.def("gather_rows", &gather_rows, py::arg("src"), py::arg("index"), py::arg("out"), py::arg("status") = py::none());
   m.def("scatter_rows", &scatter_rows, py::arg("src"), py::arg("slots"), py::arg("dst"), py::arg("status") = py::none());

@@ -104,6 +104,22 @@ void bind_ops_extra(py::module_& m) {
         py::arg("w"), py::arg("rank"), py::arg("peers"), py::arg("layout"), py::arg("y"), py::arg("M"), py::arg("slot"),
         py::arg("timeout_ns"), py::arg("n_comm") = 0, py::arg("config") = 0, py::arg("status") = py::none());
 
+  m.def("tp_ag_gemm_fp8",
+        [](const at::Tensor& wq, const at::Tensor& ws, int rank, const std::vector<int64_t>& peers, const B2TpLayout& lay, at::Tensor& y,
+           int M, int slot, uint64_t timeout_ns, int n_comm, c10::optional<at::Tensor> status) {
+          need(wq.is_cuda() && wq.element_size() == 1 && wq.dim() == 2 && wq.is_contiguous(), "tp_ag_gemm_fp8: wq [N/tp, K] contiguous 8-bit");
+          const int N = static_cast<int>(wq.size(0)), K = static_cast<int>(wq.size(1));
+          need(ws.scalar_type() == at::kFloat && ws.is_contiguous() && ws.numel() == static_cast<int64_t>((N + 127) / 128) * (K / 128), "tp_ag_gemm_fp8: ws f32 [ceil(N/128), K/128]");
+          need(is_bf16_2d(y) && y.size(0) == M && y.size(1) == N, "tp_ag_gemm_fp8: y bf16 [M, N/tp]");
+          const B2TpRegion reg = make_region(rank, peers);
+          c10::cuda::CUDAGuard g(wq.device());
+          check(b2_tp_ag_gemm_fp8(wq.data_ptr(), ws.data_ptr<float>(), &reg, &lay, y.data_ptr(), M, N, K, y.stride(0), slot, timeout_ns, n_comm,
+                                  status_ptr(status), cur_stream()),
+                "tp_ag_gemm_fp8");
+        },
+        py::arg("wq"), py::arg("ws"), py::arg("rank"), py::arg("peers"), py::arg("layout"), py::arg("y"), py::arg("M"), py::arg("slot"),
+        py::arg("timeout_ns"), py::arg("n_comm") = 0, py::arg("status") = py::none());
+
   m.def("tp_all_gather",
         [](int rank, const std::vector<int64_t>& peers, const B2TpLayout& lay, int M, int K, int slot, uint64_t timeout_ns,
            c10::optional<at::Tensor> status) {

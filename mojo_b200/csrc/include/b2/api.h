@@ -31,7 +31,7 @@ int b2_rope_kvwrite_bf16(void* q, void* k, const void* v, const float* cos_sin, 
                          int64_t v_stride, int page_size, int64_t num_slots, int max_pos, b2::Status* status,
                          cudaStream_t stream);
 // out[t, j] = silu(gate_up[t, j]) * gate_up[t, F + j]
-int b2_swiglu_bf16(const void* gate_up, void* out, int rows, int ffn, cudaStream_t stream);
+int b2_swiglu_bf16(const void* gate_up, void* out, int rows, int ffn, int interleaved, cudaStream_t stream);
 // out[t, :] = table[ids[t] - vocab_start, :] for ids inside [vocab_start, vocab_start + vocab_rows), else 0.
 int b2_embedding_bf16(const int64_t* ids, const void* table, void* out, int tokens, int hidden, int64_t vocab_start,
                       int64_t vocab_rows, cudaStream_t stream);

@@ -76,16 +76,26 @@ struct NoFill {
 };
 constexpr int kThreadsWithFill = kThreads + 128;
 
+// Optional side role. When Side::kWarps > 0 (and no fill warps are present), warps 6 .. 6 + kWarps - 1 of the CTA
+// run `side(warp - 6, lane)` next to the GEMM roles and rejoin at the CTA's final barrier: work that belongs to
+// the same kernel but not to the tile pipeline (pushing this rank's rows to peers, reducing finished tiles).
+// Side warps must not use __syncthreads(); named barriers 4 and up are theirs.
+struct NoSide {
+  static constexpr int kWarps = 0;
+  __device__ __forceinline__ void operator()(int, int) const {}
+};
+
 // Byte offset of 16-byte chunk `c` (0..7) of row `r` (0..127) inside a 128 x 64 bf16 tile stored with the
 // 128-byte swizzle (what TMA SWIZZLE_128B produces and make_smem_desc_sw128 describes).
 __device__ __forceinline__ uint32_t sw128_offset(int r, int c) {
   return static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
 }
 
-template <int BN, int STAGES, int ELEM_BYTES, class Sched, class Gate, class Epi, class PFill = NoFill>
+template <int BN, int STAGES, int ELEM_BYTES, class Sched, class Gate, class Epi, class PFill = NoFill, class Side = NoSide>
 __device__ __forceinline__ void run(const CUtensorMap* tmap_p, const CUtensorMap* tmap_q, uint32_t idesc,
                                     uint64_t policy_p, uint64_t policy_q, const Sched& sched, Gate gate, Epi epi,
-                                    Status* status, int cta, int num_ctas, PFill pfill = PFill{}) {
+                                    Status* status, int cta, int num_ctas, PFill pfill = PFill{}, Side side = Side{}) {
+  static_assert(!(PFill::kActive && Side::kWarps > 0), "fill warps and side warps share warp indices 6 and up");
   using L = SmemLayout<BN, STAGES>;
   constexpr int kTmemCols = tmem_cols_for<BN>();
   constexpr int kMmaPerKb = 4;                       // 128 bytes / 32 bytes per instruction
@@ -220,6 +230,9 @@ __device__ __forceinline__ void run(const CUtensorMap* tmap_p, const CUtensorMap
       }
     }
     __syncwarp();
+  } else if (Side::kWarps > 0 && warp >= 6) {
+    // ------------------------------------------------------------------ side warps
+    side(warp - 6, lane);
   } else if (PFill::kActive && warp >= 6) {
     // ------------------------------------------------------------------ P-tile fill warps
     int stage = 0;

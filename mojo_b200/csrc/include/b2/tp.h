@@ -44,6 +44,9 @@ int b2_tp_gemm_rs_fp8(const void* xq, const float* xs, const void* wq, const flo
 int b2_tp_ag_gemm_bf16(const void* w, const struct B2TpRegion* reg, const struct B2TpLayout* lay, void* y, int M, int N, int K,
                        int64_t ldw, int64_t ldy, int slot, uint64_t timeout_ns, int n_comm, int config,
                        b2::Status* status, cudaStream_t stream);
+// fp8 variant: the gathered half holds e4m3 rows [M][K], then (next 1024-byte boundary) f32 scales [M][K/128].
+int b2_tp_ag_gemm_fp8(const void* wq, const float* ws, const struct B2TpRegion* reg, const struct B2TpLayout* lay, void* y, int M, int N,
+                      int K, int64_t ldy, int slot, uint64_t timeout_ns, int n_comm, b2::Status* status, cudaStream_t stream);
 int b2_tp_all_gather(const struct B2TpRegion* reg, const struct B2TpLayout* lay, int M, int K, int slot,
                      uint64_t timeout_ns, b2::Status* status, cudaStream_t stream);
 int b2_symm_barrier(const struct B2TpRegion* reg, const struct B2TpLayout* lay, uint64_t timeout_ns, b2::Status* status,

@@ -67,8 +67,9 @@ __device__ __forceinline__ int unit_index(const RsParams& p, int owner, int pb, 
 constexpr int kRsRowPad = 16;
 template <int BN, bool SWAP>
 constexpr int rs_epi_bytes() {
-  // normal: two buffers of [128 rows][64 cols] bf16; swapped: two buffers of [32 tokens][128 cols] bf16
-  return SWAP ? 2 * 32 * (256 + kRsRowPad) : 2 * 128 * (128 + kRsRowPad);
+  // normal: one buffer of [128 rows][64 cols] bf16 (a second one would cost the 256-wide tile a pipeline stage);
+  // swapped: two buffers of [32 tokens][128 cols] bf16
+  return SWAP ? 2 * 32 * (256 + kRsRowPad) : 128 * (128 + kRsRowPad);
 }
 
 // Epilogue of the reduce-scatter GEMM. NVLink moves small scattered writes badly, so the accumulator is first
@@ -108,7 +109,8 @@ struct RsEpilogue {
       static_assert(BN % 64 == 0, "normal layout stages 64 columns at a time");
 #pragma unroll
       for (int cg = 0; cg < BN / 64; ++cg) {
-        uint8_t* buf = epi_smem + (cg & 1) * 128 * ROW;
+        uint8_t* buf = epi_smem;
+        if (cg > 0) ptx::named_barrier_sync(1, gemm::kEpiThreads);  // the previous group's rows have been read out
 #pragma unroll
         for (int c2 = 0; c2 < 2; ++c2) {
           uint32_t r[32];
@@ -174,7 +176,20 @@ struct RsEpilogue {
 // Reduce phase. Units (output tiles of the rows this rank owns) are claimed from a counter in this rank's
 // memory, in the order in which their contributions are produced, by the dedicated reduce CTAs from the start
 // and by the GEMM CTAs once they run out of tiles. Returns false when a wait ran out.
-template <int BN, bool SWAP>
+// `Team` says which threads of the CTA do the reducing: the whole CTA, or the two side warps of a GEMM CTA.
+struct CtaTeam {
+  static __device__ __forceinline__ int tid() { return static_cast<int>(threadIdx.x); }
+  static __device__ __forceinline__ int size() { return static_cast<int>(blockDim.x); }
+  static __device__ __forceinline__ void sync() { __syncthreads(); }
+};
+struct SideTeam {  // warps 6..7 of a CTA whose warps 0..5 run the GEMM roles (8 warps keep 255 registers per thread)
+  static constexpr int kThreads = 64;
+  static __device__ __forceinline__ int tid() { return static_cast<int>(threadIdx.x) - gemm::kThreads; }
+  static __device__ __forceinline__ int size() { return kThreads; }
+  static __device__ __forceinline__ void sync() { ptx::named_barrier_sync(4, kThreads); }
+};
+
+template <int BN, bool SWAP, class Team = CtaTeam>
 __device__ inline bool reduce_phase(const RsParams& p, Status* status) {
   __shared__ uint32_t sh_ok;
   __shared__ uint32_t sh_last;
@@ -194,35 +209,35 @@ __device__ inline bool reduce_phase(const RsParams& p, Status* status) {
   const int n_units = (tm1 - tm0) * n_tiles_n;
   bool ok = true;
   while (true) {
-    __syncthreads();
-    if (threadIdx.x == 0) {
+    Team::sync();
+    if (Team::tid() == 0) {
       sh_unit = static_cast<int>(atomicAdd(next_unit, 1u));
       sh_ok = 1;
     }
-    __syncthreads();
+    Team::sync();
     const int un = sh_unit;
     if (un >= n_units) break;
     // same enumeration as unit_index(): (tile along m) major, (tile along n) minor
     const int tm = tm0 + un / n_tiles_n, tn = un % n_tiles_n;
-    if (threadIdx.x < p.tp) {
-      if (!ptx::wait_flag_ge_sys(flags + static_cast<int64_t>(un) * p.tp + threadIdx.x, p.epoch, p.timeout_ns)) {
-        status_record(status, kTimeout, kSiteRsTile, un, threadIdx.x);
+    if (Team::tid() < p.tp) {
+      if (!ptx::wait_flag_ge_sys(flags + static_cast<int64_t>(un) * p.tp + Team::tid(), p.epoch, p.timeout_ns)) {
+        status_record(status, kTimeout, kSiteRsTile, un, Team::tid());
         sh_ok = 0;
       }
     }
-    __syncthreads();
+    Team::sync();
     if (sh_ok == 0) { ok = false; break; }
     const int r_lo = max(row0, tm * TM), r_hi = min(row0 + rows, tm * TM + TM);
     const int c_lo = tn * TN, c_hi = min(p.N, tn * TN + TN);
     const int vec_per_row = (c_hi - c_lo) >> 3;
     const int n_vec = (r_hi - r_lo) * vec_per_row;
     constexpr int U = 4;  // independent 16-byte vectors per thread per pass: keeps tp * U loads in flight
-    for (int i0 = threadIdx.x; i0 < n_vec; i0 += blockDim.x * U) {
+    for (int i0 = Team::tid(); i0 < n_vec; i0 += Team::size() * U) {
       uint4 raw[U][kMaxTp];
       int64_t off[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        const int i = i0 + u * blockDim.x;
+        const int i = i0 + u * Team::size();
         const int m = r_lo + (i < n_vec ? i / vec_per_row : 0);
         const int col = c_lo + (i < n_vec ? (i % vec_per_row) * 8 : 0);
         off[u] = static_cast<int64_t>(m - row0) * p.N + col;
@@ -232,7 +247,7 @@ __device__ inline bool reduce_phase(const RsParams& p, Status* status) {
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        const int i = i0 + u * blockDim.x;
+        const int i = i0 + u * Team::size();
         if (i >= n_vec) continue;
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
@@ -268,33 +283,33 @@ __device__ inline bool reduce_phase(const RsParams& p, Status* status) {
     }
     if (p.mode == 1) {
       __threadfence_system();
-      __syncthreads();
-      if (threadIdx.x == 0) {
+      Team::sync();
+      if (Team::tid() == 0) {
         const uint32_t old = atomicAdd(done, 1u);
         sh_last = (old == static_cast<uint32_t>(n_units - 1)) ? 1u : 0u;
         if (sh_last) *done = 0;
       }
-      __syncthreads();
-      if (sh_last && threadIdx.x < p.tp)
-        ptx::st_release_sys(reinterpret_cast<uint32_t*>(p.peer[threadIdx.x] + p.off_resflags) + p.rank, p.epoch);
+      Team::sync();
+      if (sh_last && Team::tid() < p.tp)
+        ptx::st_release_sys(reinterpret_cast<uint32_t*>(p.peer[Team::tid()] + p.off_resflags) + p.rank, p.epoch);
     }
   }
   if (p.mode == 1) {
     // a rank that owns no rows still announces that it has entered this launch
-    if (n_units == 0 && blockIdx.x == 0 && threadIdx.x < p.tp)
-      ptx::st_release_sys(reinterpret_cast<uint32_t*>(p.peer[threadIdx.x] + p.off_resflags) + p.rank, p.epoch);
+    if (n_units == 0 && blockIdx.x == 0 && Team::tid() < p.tp)
+      ptx::st_release_sys(reinterpret_cast<uint32_t*>(p.peer[Team::tid()] + p.off_resflags) + p.rank, p.epoch);
     // the launch is complete when every rank's rows have landed in this rank's copy
-    __syncthreads();
-    if (threadIdx.x == 0) sh_ok = ok ? 1u : 0u;
-    __syncthreads();
-    if (ok && threadIdx.x < p.tp) {
-      const uint32_t* rf = reinterpret_cast<const uint32_t*>(self + p.off_resflags) + threadIdx.x;
+    Team::sync();
+    if (Team::tid() == 0) sh_ok = ok ? 1u : 0u;
+    Team::sync();
+    if (ok && Team::tid() < p.tp) {
+      const uint32_t* rf = reinterpret_cast<const uint32_t*>(self + p.off_resflags) + Team::tid();
       if (!ptx::wait_flag_ge_sys(rf, p.epoch, p.timeout_ns)) {
-        status_record(status, kTimeout, kSitePeerSignal, threadIdx.x, p.epoch);
+        status_record(status, kTimeout, kSitePeerSignal, Team::tid(), p.epoch);
         sh_ok = 0;
       }
     }
-    __syncthreads();
+    Team::sync();
     ok = sh_ok != 0;
   }
   return ok;

@@ -214,15 +214,19 @@ __global__ void rope_kvwrite_kernel(__nv_bfloat16* __restrict__ q, __nv_bfloat16
   }
 }
 
-__global__ void swiglu_kernel(const uint4* __restrict__ gate_up, uint4* __restrict__ out, int rows, int ffn_vecs) {
+// interleaved = false: row = [gate (ffn) | up (ffn)]. interleaved = true: alternating blocks of 16 gate and 16 up
+// columns (the output of a plain GEMM against a weight stacked for the SwiGLU GEMM epilogue).
+__global__ void swiglu_kernel(const uint4* __restrict__ gate_up, uint4* __restrict__ out, int rows, int ffn_vecs, bool interleaved) {
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t total = static_cast<int64_t>(rows) * ffn_vecs;
   if (idx >= total) return;
   const int64_t r = idx / ffn_vecs;
   const int c = static_cast<int>(idx % ffn_vecs);
   float g[8], u[8], o[8];
-  bf16x8_to_f32(ptx::ld_nc_v4(gate_up + r * 2 * ffn_vecs + c), g);
-  bf16x8_to_f32(ptx::ld_nc_v4(gate_up + r * 2 * ffn_vecs + ffn_vecs + c), u);
+  const int gv = interleaved ? 4 * (c >> 1) + (c & 1) : c;       // 16 columns = 2 vectors per block half
+  const int uv = interleaved ? gv + 2 : ffn_vecs + c;
+  bf16x8_to_f32(ptx::ld_nc_v4(gate_up + r * 2 * ffn_vecs + gv), g);
+  bf16x8_to_f32(ptx::ld_nc_v4(gate_up + r * 2 * ffn_vecs + uv), u);
 #pragma unroll
   for (int j = 0; j < 8; ++j) o[j] = ptx::silu(g[j]) * u[j];
   out[idx] = f32_to_bf16x8(o);
@@ -335,13 +339,13 @@ extern "C" int b2_rope_kvwrite_bf16(void* q, void* k, const void* v, const float
   return 0;
 }
 
-extern "C" int b2_swiglu_bf16(const void* gate_up, void* out, int rows, int ffn, cudaStream_t stream) {
+extern "C" int b2_swiglu_bf16(const void* gate_up, void* out, int rows, int ffn, int interleaved, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (ffn % 8 != 0) return -kBadArgument;
+  if (ffn % 8 != 0 || (interleaved && ffn % 16 != 0)) return -kBadArgument;
   const int64_t total = static_cast<int64_t>(rows) * (ffn / 8);
   const int threads = 256;
   swiglu_kernel<<<static_cast<unsigned>((total + threads - 1) / threads), threads, 0, stream>>>(
-      static_cast<const uint4*>(gate_up), static_cast<uint4*>(out), rows, ffn / 8);
+      static_cast<const uint4*>(gate_up), static_cast<uint4*>(out), rows, ffn / 8, interleaved != 0);
   return 0;
 }
 

@@ -20,6 +20,7 @@
 #include "b2/ptx.cuh"
 #include "b2/tma.h"
 #include "b2/tp.h"
+#include "b2/tp_ag.cuh"
 #include "b2/tp_rs.cuh"
 
 namespace b2 {
@@ -36,19 +37,52 @@ struct Fp8Params {
   int p_blocks, q_blocks;
 };
 
-// RS = true: row-parallel GEMM fused with reduce-scatter / all-reduce (see tp_fused.cu): finished tiles go to the
-// owner rank's staging buffer, CTAs >= n_gemm only reduce, the others join the reduction after their tiles.
-template <int BN, int STAGES, int SLABS, bool SWAP, bool RS>
+// What the tensor-parallel variants add to the plain kernel (see tp_fused.cu for the protocols).
+struct Fp8Fused {
+  tp::RsParams rs;     // kModeRs
+  tp::AgParams ag;     // kModeAg
+  tp::AgSched ag_sched;
+  tp::EpochCtl ectl;
+  int n_gemm;          // CTAs [0, n_gemm) run the GEMM; the rest only reduce (RS) or only move data (AG)
+};
+constexpr int kModePlain = 0;
+// Row-parallel GEMM fused with reduce-scatter / all-reduce: finished tiles go to the owner rank's staging buffer,
+// CTAs >= n_gemm only reduce, the others join the reduction after their tiles.
+constexpr int kModeRs = 1;
+// All-gather fused with the column-parallel GEMM: CTAs >= n_gemm push this rank's quantised rows and their scales
+// to every peer chunk by chunk; the GEMM producer waits for the chunks a tile needs before its first load.
+constexpr int kModeAg = 2;
+
+template <int BN, int STAGES, int SLABS, bool SWAP, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q, Fp8Params prm,
-                const __grid_constant__ tp::RsSched rs_sched, tp::RsParams rs_in, tp::EpochCtl ectl, int n_gemm, Status* status) {
-  tp::RsParams rs = rs_in;
-  if (RS) rs.epoch = tp::epoch_begin(ectl);
+                const __grid_constant__ tp::RsSched rs_sched, const __grid_constant__ Fp8Fused fz, Status* status) {
+  constexpr bool RS = MODE == kModeRs;
+  constexpr bool AG = MODE == kModeAg;
+  tp::RsParams rs = fz.rs;
+  tp::AgParams ag = fz.ag;
+  const tp::EpochCtl ectl = fz.ectl;
+  const int n_gemm = fz.n_gemm;
+  uint32_t epoch = 0;
+  if (RS || AG) epoch = tp::epoch_begin(ectl);
+  rs.epoch = epoch;
+  ag.epoch = epoch;
   const int my_cta = static_cast<int>(blockIdx.x);
-  const int n_ctas = RS ? n_gemm : static_cast<int>(gridDim.x);
+  const int n_ctas = (RS || AG) ? n_gemm : static_cast<int>(gridDim.x);
+  if (AG && my_cta >= n_gemm) {
+    extern __shared__ uint8_t smem_comm[];
+    uint8_t* win = smem_comm + ((128 - (reinterpret_cast<uintptr_t>(smem_comm) & 127)) & 127);
+    tp::ag_push(ag, my_cta - n_gemm, win, status);
+    tp::epoch_end(ectl, epoch);
+    return;
+  }
   auto tile_of = [&](int w, int& pb, int& qb) {
     if (RS) {
       const gemm::WorkUnit u = rs_sched.get(w);
+      pb = u.pb;
+      qb = u.qb;
+    } else if (AG) {
+      const gemm::WorkUnit u = fz.ag_sched.get(w);
       pb = u.pb;
       qb = u.qb;
     } else {
@@ -109,6 +143,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
       for (int w = my_cta; ok && w < total; w += n_ctas) {
         int pb, qb;
         tile_of(w, pb, qb);
+        if constexpr (AG) {
+          gemm::WorkUnit u{};
+          u.pb = pb;
+          u.qb = qb;
+          if (!tp::AgGate{ag, SWAP, BN}(u, status)) { ok = false; break; }
+        }
         for (int kb = 0; kb < KB; ++kb) {
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u)) {
             status_record(status, kTimeout, kSiteGemmEmpty, w, kb);
@@ -185,29 +225,36 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
       for (int j = 0; j < BN; ++j) acc[j] = 0.0f;
       const int row = pb * 128 + p_local;  // m (normal) or n (swapped)
       for (int kb = 0; kb < KB; ++kb) {
-        // scale(s) for this k-block
+        // scale(s) for this k-block. With the fused all-gather the token scales of a tile arrive from peers and
+        // are only known to be in place once the tile's first slab is full (the producer passed the chunk gate
+        // before it loaded the operands), so they are read after the wait, past L1.
         float s_row = 0.0f, s_blk0 = 0.0f, s_blk1 = 0.0f;
-        if constexpr (!SWAP) {
-          s_row = row < prm.M ? prm.sx[static_cast<int64_t>(row) * KB + kb] : 0.0f;
-          const int nb = (qb * BN) >> 7;
-          s_blk0 = prm.sw[static_cast<int64_t>(nb) * KB + kb];
-          if (BN > 128) s_blk1 = ((qb * BN + 128) < prm.N) ? prm.sw[static_cast<int64_t>(nb + 1) * KB + kb] : 0.0f;
-        } else {
-          s_row = prm.sw[static_cast<int64_t>(pb) * KB + kb];  // 128 weight rows = one scale block
-          // each warp stages the token scales it needs itself: no barrier that a failed warp could strand
-          float* cs = col_scale + quarter * BN;
-          __syncwarp();
-          for (int j = lane; j < BN; j += 32) {
-            const int m = qb * BN + j;
-            cs[j] = m < prm.M ? prm.sx[static_cast<int64_t>(m) * KB + kb] : 0.0f;
+        auto load_scales = [&]() {
+          if constexpr (!SWAP) {
+            if (row < prm.M) s_row = AG ? __ldcg(prm.sx + static_cast<int64_t>(row) * KB + kb) : prm.sx[static_cast<int64_t>(row) * KB + kb];
+            const int nb = (qb * BN) >> 7;
+            s_blk0 = prm.sw[static_cast<int64_t>(nb) * KB + kb];
+            if (BN > 128) s_blk1 = ((qb * BN + 128) < prm.N) ? prm.sw[static_cast<int64_t>(nb + 1) * KB + kb] : 0.0f;
+          } else {
+            s_row = prm.sw[static_cast<int64_t>(pb) * KB + kb];  // 128 weight rows = one scale block
+            // each warp stages the token scales it needs itself: no barrier that a failed warp could strand
+            float* cs = col_scale + quarter * BN;
+            __syncwarp();
+            for (int j = lane; j < BN; j += 32) {
+              const int m = qb * BN + j;
+              const float* src = prm.sx + static_cast<int64_t>(m) * KB + kb;
+              cs[j] = m < prm.M ? (AG ? __ldcg(src) : *src) : 0.0f;
+            }
+            __syncwarp();
           }
-          __syncwarp();
-        }
+        };
+        if constexpr (!AG) load_scales();
         if (!__all_sync(0xffffffffu, ptx::mbar_wait(slab_full(slab), slab_phase))) {
           if (lane == 0) status_record(status, kTimeout, kSiteGemmTmemFull, w, kb);
           ok = false;
           break;
         }
+        if constexpr (AG) load_scales();
         ptx::tc_fence_after();
         const uint32_t taddr = tmem_base + slab * BN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll
@@ -284,6 +331,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
     tp::reduce_phase<BN, SWAP>(rs, status);
     tp::rs_epoch_end(ectl, rs);
   }
+  if constexpr (AG) tp::epoch_end(ectl, epoch);
 }
 
 template <int BN, bool SWAP>
@@ -310,7 +358,7 @@ int launch_fp8(const void* xq, const float* xs, const void* wq, const float* ws,
   prm.KB = K / 128;
   prm.p_blocks = (rows_p + 127) / 128;
   prm.q_blocks = (rows_q + BN - 1) / BN;
-  auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP, false>;
+  auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP, kModePlain>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
@@ -318,7 +366,8 @@ int launch_fp8(const void* xq, const float* xs, const void* wq, const float* ws,
   }
   const int total = prm.p_blocks * prm.q_blocks;
   static const tp::RsSched no_sched{};
-  kern<<<total < kNumSMs ? total : kNumSMs, kThreads, SMEM, stream>>>(tp, tq, prm, no_sched, tp::RsParams{}, tp::EpochCtl{}, 0, status);
+  static const Fp8Fused no_fused{};
+  kern<<<total < kNumSMs ? total : kNumSMs, kThreads, SMEM, stream>>>(tp, tq, prm, no_sched, no_fused, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
 }
 
@@ -355,7 +404,7 @@ int launch_fp8_rs(const void* xq, const float* xs, const void* wq, const float* 
   if (!tp::build_rs_order(sched, rs.tp, rs.rank, rs.R, TM)) return -kTooLarge;
   rs.p_blocks = prm.p_blocks;
   rs.q_blocks = prm.q_blocks;
-  auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP, true>;
+  auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP, kModeRs>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
@@ -364,7 +413,63 @@ int launch_fp8_rs(const void* xq, const float* xs, const void* wq, const float* 
   const int total = prm.p_blocks * prm.q_blocks;
   int n_gemm = kNumSMs - (rs.tp > 1 ? (M >= 2048 ? 4 : 12) : 0);
   if (total < n_gemm) n_gemm = total;
-  kern<<<kNumSMs, kThreads, SMEM, stream>>>(tmp, tmq, prm, sched, rs, ectl, n_gemm, status);
+  Fp8Fused fz{};
+  fz.rs = rs;
+  fz.ectl = ectl;
+  fz.n_gemm = n_gemm;
+  kern<<<kNumSMs, kThreads, SMEM, stream>>>(tmp, tmq, prm, sched, fz, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+}
+
+template <int BN, bool SWAP>
+int launch_fp8_ag(const void* xq_all, const float* xs_all, const void* wq, const float* ws, void* y, int M, int N, int K, int64_t ldy,
+                  tp::AgParams ag, tp::EpochCtl ectl, Status* status, cudaStream_t stream) {
+  constexpr int kStageBytes = 128 * 128 + BN * 128;
+  constexpr int STAGES = (190 * 1024 / kStageBytes) > 8 ? 8 : (190 * 1024 / kStageBytes);
+  constexpr int SLABS = BN <= 128 ? 4 : 2;
+  constexpr int SMEM_GEMM = STAGES * kStageBytes + (2 * STAGES + 2 * SLABS + 1) * 8 + 16 + 4 * BN * 4 + 1024 + 64;
+  constexpr int SMEM_COMM = tp::kAgRingBytes + 64 + 128;
+  constexpr int SMEM = SMEM_GEMM > SMEM_COMM ? SMEM_GEMM : SMEM_COMM;
+  const void* p_ptr = SWAP ? wq : xq_all;
+  const void* q_ptr = SWAP ? xq_all : wq;
+  const int rows_p = SWAP ? N : M, rows_q = SWAP ? M : N;
+  CUtensorMap tmp, tmq;
+  if (!make_tmap_2d(&tmp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p_ptr, rows_p, K, K, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !make_tmap_2d(&tmq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q_ptr, rows_q, K, K, BN, 128, CU_TENSOR_MAP_SWIZZLE_128B))
+    return -kBadArgument;
+  Fp8Params prm{};
+  prm.y = static_cast<__nv_bfloat16*>(y);
+  prm.ldy = ldy;
+  prm.sx = xs_all;
+  prm.sw = ws;
+  prm.M = M;
+  prm.N = N;
+  prm.KB = K / 128;
+  prm.p_blocks = (rows_p + 127) / 128;
+  prm.q_blocks = (rows_q + BN - 1) / BN;
+  Fp8Fused fz{};
+  fz.ag = ag;
+  fz.ectl = ectl;
+  fz.ag_sched.p_blocks = prm.p_blocks;
+  fz.ag_sched.q_blocks = prm.q_blocks;
+  fz.ag_sched.num_kb = prm.KB;
+  fz.ag_sched.bn = BN;
+  fz.ag_sched.swap = SWAP;
+  constexpr int TM = SWAP ? BN : 128;
+  fz.ag_sched.m_tiles = SWAP ? prm.q_blocks : prm.p_blocks;
+  fz.ag_sched.first_tile = (ag.rank * ag.R / TM) % fz.ag_sched.m_tiles;
+  const int total = prm.p_blocks * prm.q_blocks;
+  int n_gemm = kNumSMs - ag.n_comm;
+  if (total < n_gemm) n_gemm = total;
+  fz.n_gemm = n_gemm;
+  auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP, kModeAg>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
+    attr_set = true;
+  }
+  static const tp::RsSched no_sched{};
+  kern<<<n_gemm + ag.n_comm, kThreads, SMEM, stream>>>(tmp, tmq, prm, no_sched, fz, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
 }
 
@@ -442,4 +547,54 @@ extern "C" int b2_tp_gemm_rs_fp8(const void* xq, const float* xs, const void* wq
     }
   }
   return launch_fp8_rs<128, false>(xq, xs, wq, ws, M, N, K, rs, ectl, status, stream);
+}
+
+// All-gather fused with the block-scaled fp8 column-parallel GEMM. The gathered buffer of this parity holds the
+// e4m3 rows [M][K] followed (at the next 1024-byte boundary) by their f32 scales [M][K / 128]; this rank's rows
+// and scales must already be there. K must be a multiple of 512 so that a chunk of scale rows is a whole number
+// of 16-byte units.
+extern "C" int b2_tp_ag_gemm_fp8(const void* wq, const float* ws, const B2TpRegion* reg, const B2TpLayout* lay, void* y, int M, int N,
+                                 int K, int64_t ldy, int slot, uint64_t timeout_ns, int n_comm, b2::Status* status,
+                                 cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (reg == nullptr || lay == nullptr || reg->tp < 1 || reg->tp > tp::kMaxTp || K % 512 != 0 || N % 8 != 0 || ldy % 8 != 0 ||
+      M % reg->tp != 0)
+    return -kBadArgument;
+  const int ntp = reg->tp;
+  tp::AgParams ag{};
+  ag.rank = reg->rank;
+  ag.tp = ntp;
+  ag.M = M;
+  ag.K = K;
+  ag.R = M / ntp;
+  ag.chunk_rows = tp::ag_chunk_rows(ag.R);
+  ag.chunks_per_rank = (ag.R + ag.chunk_rows - 1) / ag.chunk_rows;
+  const int parity = slot & 1;
+  for (int i = 0; i < ntp; ++i) ag.peer[i] = static_cast<uint8_t*>(reg->peer[i]);
+  tp::EpochCtl ectl{reinterpret_cast<uint32_t*>(ag.peer[ag.rank] + lay->off_epoch_ag),
+                    reinterpret_cast<uint32_t*>(ag.peer[ag.rank] + lay->off_epoch_ag + 4)};
+  const int64_t q_bytes = (static_cast<int64_t>(M) * K + 1023) / 1024 * 1024;
+  const int64_t s_bytes = static_cast<int64_t>(M) * (K / 128) * 4;
+  if (q_bytes + s_bytes > lay->xall_half_bytes) return -kTooLarge;
+  if (static_cast<int64_t>(ntp) * ag.chunks_per_rank * 4 > lay->ag_flags_bytes) return -kTooLarge;
+  ag.off_xall = lay->off_xall + parity * lay->xall_half_bytes;
+  ag.row_bytes = K;
+  ag.off_aux = ag.off_xall + q_bytes;
+  ag.aux_row_bytes = static_cast<int64_t>(K / 128) * 4;
+  ag.off_flags = lay->off_ag_flags;
+  ag.n_comm = ntp > 1 ? (n_comm > 0 ? n_comm : 8) : 0;
+  if (ag.n_comm > ag.chunks_per_rank && ntp > 1) ag.n_comm = ag.chunks_per_rank;
+  ag.timeout_ns = timeout_ns;
+  const void* xq_all = ag.peer[ag.rank] + ag.off_xall;
+  const float* xs_all = reinterpret_cast<const float*>(ag.peer[ag.rank] + ag.off_aux);
+  const bool swap = M <= 64;
+  const int bn = swap ? (M <= 16 ? 16 : M <= 32 ? 32 : 64) : 128;
+  if (swap) {
+    switch (bn) {
+      case 16: return launch_fp8_ag<16, true>(xq_all, xs_all, wq, ws, y, M, N, K, ldy, ag, ectl, status, stream);
+      case 32: return launch_fp8_ag<32, true>(xq_all, xs_all, wq, ws, y, M, N, K, ldy, ag, ectl, status, stream);
+      default: return launch_fp8_ag<64, true>(xq_all, xs_all, wq, ws, y, M, N, K, ldy, ag, ectl, status, stream);
+    }
+  }
+  return launch_fp8_ag<128, false>(xq_all, xs_all, wq, ws, y, M, N, K, ldy, ag, ectl, status, stream);
 }

@@ -27,6 +27,7 @@
 #include "b2/ptx.cuh"
 #include "b2/tma.h"
 #include "b2/tp.h"
+#include "b2/tp_ag.cuh"
 #include "b2/tp_rs.cuh"
 #include "b2/vec.cuh"
 
@@ -35,8 +36,19 @@ namespace {
 
 using gemm::WorkUnit;
 using namespace b2::tp;
+// The reduction runs next to the GEMM in every CTA: two side warps claim finished units of this rank's rows and
+// sum the ranks' contributions while warps 0-5 keep the tile pipeline going, so all SMs do tensor work.
+constexpr int kRsThreads = gemm::kThreads + SideTeam::kThreads;
+template <int BN, bool SWAP>
+struct RsSideReduce {
+  static constexpr int kWarps = SideTeam::kThreads / 32;
+  RsParams p;
+  Status* status;
+  __device__ __forceinline__ void operator()(int, int) const { reduce_phase<BN, SWAP, SideTeam>(p, status); }
+};
+
 template <int BN, int STAGES, bool SWAP>
-__global__ void __launch_bounds__(gemm::kThreads, 1)
+__global__ void __launch_bounds__(kRsThreads, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
                const __grid_constant__ RsSched sched, RsParams prm_in, EpochCtl ectl, int n_gemm, Status* status) {
   constexpr uint32_t idesc = ptx::make_idesc(1, 1, 128, BN);
@@ -48,9 +60,10 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant
     epi_buf += (16 - (reinterpret_cast<uintptr_t>(epi_buf) & 15)) & 15;  // 16-byte vector accesses
     RsEpilogue<BN, SWAP> epi{prm, epi_buf};
     gemm::run<BN, STAGES, 2>(&tmap_p, &tmap_q, idesc, ptx::kEvictNormal, ptx::kEvictNormal, sched, gemm::NoGate{}, epi, status,
-                             static_cast<int>(blockIdx.x), n_gemm);
+                             static_cast<int>(blockIdx.x), n_gemm, gemm::NoFill{}, RsSideReduce<BN, SWAP>{prm, status});
+  } else {
+    reduce_phase<BN, SWAP, CtaTeam>(prm, status);  // fewer tiles than SMs: the spare CTAs reduce with all their threads
   }
-  reduce_phase<BN, SWAP>(prm, status);
   rs_epoch_end(ectl, prm);
 }
 
@@ -62,7 +75,7 @@ constexpr int stages_for(int bn) {
 // the reduce-scatter kernel gives part of its shared memory to the staged epilogue
 constexpr int rs_stages_for(int bn) {
   const int stage = 128 * 64 * 2 + bn * 64 * 2;
-  int s = (176 * 1024) / stage;
+  int s = (192 * 1024) / stage;
   return s > 10 ? 10 : s;
 }
 
@@ -97,85 +110,17 @@ int launch_rs(const void* x, const void* w, int M, int N, int K, int64_t ldx, in
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
     attr_set = true;
   }
-  // Full persistent grid: the last CTAs only reduce from the start, the others join once their tiles are done.
-  // large M is GEMM-bound and the reduction of the last units is a short tail: give the GEMM more CTAs
-  const int n_red = prm.tp > 1 ? (M >= 2048 ? 4 : 12) : 0;
+  // Full persistent grid: every CTA that has tiles runs the GEMM with its reduction side warps; CTAs beyond the
+  // tile count only reduce.
   const int total = sched.p_blocks * sched.q_blocks;
-  int n_gemm = kNumSMs - n_red;
-  if (total < n_gemm) n_gemm = total;
-  kern<<<kNumSMs, gemm::kThreads, SMEM, stream>>>(tp, tq, sched, prm, ectl, n_gemm, status);
+  const int n_gemm = total < kNumSMs ? total : kNumSMs;
+  kern<<<kNumSMs, kRsThreads, SMEM, stream>>>(tp, tq, sched, prm, ectl, n_gemm, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
 }
 
 // ------------------------------------------------------------------------------------------------
 // all-gather -> GEMM
 // ------------------------------------------------------------------------------------------------
-struct AgParams {
-  int rank, tp;
-  int M, K;           // gathered rows, columns of X
-  int R;              // rows per rank (M = R * tp)
-  int chunk_rows;     // rows per flag chunk
-  int chunks_per_rank;
-  uint32_t epoch;
-  uint8_t* peer[kMaxTp];
-  int64_t off_xall;   // bf16 [M][K] of the current parity
-  int64_t off_flags;  // u32 [tp][chunks_per_rank]
-  int n_comm;         // CTAs that only move data
-  uint64_t timeout_ns;
-};
-
-// Producer gate: before the first load of a tile, wait until every chunk of X rows it covers has arrived.
-struct AgGate {
-  AgParams p;
-  bool swap;
-  int bn;
-  __device__ __forceinline__ bool operator()(const WorkUnit& u, Status* status) const {
-    const int m_lo = swap ? u.qb * bn : u.pb * 128;
-    const int m_hi = min(p.M, m_lo + (swap ? bn : 128)) - 1;
-    if (m_hi < m_lo) return true;
-    const uint32_t* flags = reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.off_flags);
-    bool waited = false;
-    for (int m = m_lo; m <= m_hi;) {
-      const int src = m / p.R;
-      const int c = (m - src * p.R) / p.chunk_rows;
-      if (src != p.rank) {
-        if (!ptx::wait_flag_ge_sys(flags + src * p.chunks_per_rank + c, p.epoch, p.timeout_ns)) {
-          status_record(status, kTimeout, kSiteAgChunk, src, c);
-          return false;
-        }
-        waited = true;
-      }
-      m = src * p.R + (c + 1) * p.chunk_rows;  // first row of the next chunk
-    }
-    // the rows were written by peers' ordinary stores; the loads that follow go through the async proxy
-    if (waited) ptx::fence_proxy_async_all();
-    return true;
-  }
-};
-
-// Row-tile order: own rows first, then the peers' in ring order (rank + 1, rank + 2, ...).
-struct AgSched {
-  int p_blocks, q_blocks, num_kb, bn;
-  int m_tiles, first_tile;
-  bool swap;
-  __device__ __forceinline__ int total() const { return p_blocks * q_blocks; }
-  __device__ __forceinline__ WorkUnit get(int w) const {
-    WorkUnit u;
-    const int n_tiles = swap ? p_blocks : q_blocks;
-    const int mt = (first_tile + w / n_tiles) % m_tiles;
-    const int nt = w % n_tiles;
-    u.pb = swap ? nt : mt;
-    u.qb = swap ? mt : nt;
-    u.split = 0;
-    u.tile = u.pb * q_blocks + u.qb;
-    u.kb0 = 0;
-    u.kb1 = num_kb;
-    u.p_coord = u.pb * 128;
-    u.q_coord = u.qb * bn;
-    return u;
-  }
-};
-
 struct PlainEpiParams {
   __nv_bfloat16* y;
   int64_t ldy;
@@ -222,98 +167,21 @@ struct PlainEpilogue {
   }
 };
 
-// Data-movement CTAs: copy this rank's rows into every peer's gathered buffer, one flag per chunk per peer.
-// A chunk of rows is one contiguous byte range, so one thread drives it with bulk async copies: local memory ->
-// shared memory (mbarrier completion) -> every peer (bulk store), 32 KB pieces through a 4-deep ring with the
-// loads issued two pieces ahead. `smem` is a 128-byte aligned shared-memory window of kAgRingBytes + 64.
-constexpr int kAgPiece = 32 * 1024;
-constexpr int kAgStages = 4;
-constexpr int kAgRingBytes = kAgPiece * kAgStages;
-
-__device__ void ag_push(const AgParams& p, int comm_cta, uint8_t* smem, Status* status) {
-  if (threadIdx.x != 0) return;
-  const uint32_t ring = ptx::smem_u32(smem);
-  const uint32_t bars = ring + kAgRingBytes;
-  for (int s = 0; s < kAgStages; ++s) ptx::mbar_init(bars + 8 * s, 1);
-  ptx::fence_mbar_init();
-  const int row0 = p.rank * p.R;
-  const uint8_t* src = p.peer[p.rank] + p.off_xall;
-  const int64_t row_bytes = static_cast<int64_t>(p.K) * 2;
-  long issued = 0, consumed = 0;  // pieces over the whole kernel (ring positions / phases)
-  for (int c = comm_cta; c < p.chunks_per_rank; c += p.n_comm) {
-    const int r_lo = row0 + c * p.chunk_rows;
-    const int r_hi = min(min(p.M, row0 + p.R), r_lo + p.chunk_rows);
-    const int64_t base = static_cast<int64_t>(r_lo) * row_bytes;
-    const int64_t total = static_cast<int64_t>(max(0, r_hi - r_lo)) * row_bytes;
-    const int n_pieces = static_cast<int>((total + kAgPiece - 1) / kAgPiece);
-    int next_load = 0;
-    bool ok = true;
-    for (int i = 0; i < n_pieces && ok; ++i) {
-      // keep two loads in flight; a ring slot is reusable once the stores that read it have finished reading
-      while (next_load < n_pieces && next_load < i + 2) {
-        if (issued >= kAgStages) ptx::tma_store_wait_read<kAgStages - 2>();
-        const int s = static_cast<int>(issued % kAgStages);
-        const int64_t off = static_cast<int64_t>(next_load) * kAgPiece;
-        const uint32_t bytes = static_cast<uint32_t>((total - off < kAgPiece ? total - off : static_cast<int64_t>(kAgPiece)));
-        ptx::mbar_arrive_expect_tx(bars + 8 * s, bytes);
-        ptx::bulk_load(ring + s * kAgPiece, src + base + off, bytes, bars + 8 * s);
-        ++issued;
-        ++next_load;
-      }
-      const int s = static_cast<int>(consumed % kAgStages);
-      if (!ptx::mbar_wait(bars + 8 * s, static_cast<uint32_t>((consumed / kAgStages) & 1))) {
-        status_record(status, kTimeout, kSiteAgChunk, c, i);
-        ok = false;
-        break;
-      }
-      const int64_t off = static_cast<int64_t>(i) * kAgPiece;
-      const uint32_t bytes = static_cast<uint32_t>((total - off < kAgPiece ? total - off : static_cast<int64_t>(kAgPiece)));
-      for (int d = 1; d < p.tp; ++d) {
-        const int peer = (p.rank + d) % p.tp;
-        ptx::bulk_store(p.peer[peer] + p.off_xall + base + off, ring + s * kAgPiece, bytes);
-      }
-      ptx::tma_store_commit();
-      ++consumed;
-    }
-    // the chunk is complete on every peer before its flag goes up
-    ptx::tma_store_wait<0>();
-    ptx::fence_proxy_async_all();
-    __threadfence_system();
-    if (ok)
-      for (int d = 1; d < p.tp; ++d) {
-        const int peer = (p.rank + d) % p.tp;
-        ptx::st_release_sys(reinterpret_cast<uint32_t*>(p.peer[peer] + p.off_flags) + p.rank * p.chunks_per_rank + c, p.epoch);
-      }
-    if (!ok) {
-      // let loads that were issued but not consumed land before the shared memory is released
-      while (consumed < issued) {
-        ptx::mbar_wait(bars + 8 * static_cast<int>(consumed % kAgStages), static_cast<uint32_t>((consumed / kAgStages) & 1), 200000000ull);
-        ++consumed;
-      }
-      return;
-    }
-  }
-}
-
+// Every CTA runs the GEMM; one side warp per CTA pushes its share of this rank's row chunks to the peers with
+// plain 16-byte loads and stores at kernel start, so no SM is set aside for communication.
+constexpr int kAgThreads = gemm::kThreads + 32;
 template <int BN, int STAGES, bool SWAP>
-__global__ void __launch_bounds__(gemm::kThreads, 1)
+__global__ void __launch_bounds__(kAgThreads, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q, AgSched sched,
                AgParams prm_in, PlainEpiParams ep, EpochCtl ectl, Status* status) {
   AgParams prm = prm_in;
   prm.epoch = epoch_begin(ectl);
-  const int n_gemm = static_cast<int>(gridDim.x) - prm.n_comm;
-  if (static_cast<int>(blockIdx.x) >= n_gemm) {
-    extern __shared__ uint8_t smem_dyn[];
-    uint8_t* win = smem_dyn + ((128 - (reinterpret_cast<uintptr_t>(smem_dyn) & 127)) & 127);
-    ag_push(prm, static_cast<int>(blockIdx.x) - n_gemm, win, status);
-    epoch_end(ectl, prm.epoch);
-    return;
-  }
   constexpr uint32_t idesc = ptx::make_idesc(1, 1, 128, BN);
   PlainEpilogue<BN, SWAP> epi{ep};
   AgGate gate{prm, SWAP, BN};
+  AgSidePush push{prm, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x)};
   gemm::run<BN, STAGES, 2>(&tmap_p, &tmap_q, idesc, ptx::kEvictNormal, ptx::kEvictNormal, sched, gate, epi, status,
-                           static_cast<int>(blockIdx.x), n_gemm);
+                           static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), gemm::NoFill{}, push);
   epoch_end(ectl, prm.epoch);
 }
 
@@ -367,9 +235,8 @@ int launch_ag(const void* xall_local, const void* w, void* y, int M, int N, int 
     attr_set = true;
   }
   const int total = sched.p_blocks * sched.q_blocks;
-  int n_gemm = kNumSMs - prm.n_comm;
-  if (total < n_gemm) n_gemm = total;
-  kern<<<n_gemm + prm.n_comm, gemm::kThreads, L::kTotalBytes, stream>>>(tp, tq, sched, prm, ep, ectl, status);
+  const int grid = total < kNumSMs ? total : kNumSMs;
+  kern<<<grid, kAgThreads, L::kTotalBytes, stream>>>(tp, tq, sched, prm, ep, ectl, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
 }
 
@@ -388,14 +255,6 @@ __global__ void symm_barrier_kernel(B2TpRegion reg, int64_t off_flags, EpochCtl 
 // Test hook for the timeout path: wait on a flag that nothing raises, with a short deadline.
 __global__ void wait_flag_kernel(const uint32_t* flag, uint32_t want, uint64_t timeout_ns, Status* status) {
   if (threadIdx.x == 0 && !ptx::wait_flag_ge_sys(flag, want, timeout_ns)) status_record(status, kTimeout, kSiteTest, want, 0);
-}
-
-// rows per all-gather flag chunk: about 16 chunks per rank, at most 128 rows each
-int ag_chunk_rows(int R) {
-  int c = (R + 15) / 16;
-  if (c > 128) c = 128;
-  if (c < 1) c = 1;
-  return c;
 }
 
 int pick_bn_swap(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
@@ -439,7 +298,7 @@ extern "C" int b2_tp_gemm_rs_bf16(const void* x, const void* w, const B2TpRegion
   prm.out = static_cast<__nv_bfloat16*>(out);
   prm.timeout_ns = timeout_ns;
   bool swap = M <= 128;
-  int bn = swap ? pick_bn_swap(M) : (M >= 2048 ? 256 : 128);
+  int bn = swap ? pick_bn_swap(M) : (M >= 512 ? 256 : 128);
   if (config != 0) {
     swap = (config >> 30) & 1;
     bn = config & 0xffff;
@@ -492,6 +351,7 @@ extern "C" int b2_tp_ag_gemm_bf16(const void* w, const B2TpRegion* reg, const B2
   if (static_cast<int64_t>(M) * K * 2 > lay->xall_half_bytes) return -kTooLarge;
   if (static_cast<int64_t>(tp) * prm.chunks_per_rank * 4 > lay->ag_flags_bytes) return -kTooLarge;
   prm.off_xall = lay->off_xall + parity * lay->xall_half_bytes;
+  prm.row_bytes = static_cast<int64_t>(K) * 2;
   prm.off_flags = lay->off_ag_flags;
   prm.n_comm = tp > 1 ? (n_comm > 0 ? n_comm : 8) : 0;
   if (prm.n_comm > prm.chunks_per_rank && tp > 1) prm.n_comm = prm.chunks_per_rank;
@@ -543,6 +403,7 @@ extern "C" int b2_tp_all_gather(const B2TpRegion* reg, const B2TpLayout* lay, in
   if (static_cast<int64_t>(M) * K * 2 > lay->xall_half_bytes) return -kTooLarge;
   if (static_cast<int64_t>(reg->tp) * prm.chunks_per_rank * 4 > lay->ag_flags_bytes) return -kTooLarge;
   prm.off_xall = lay->off_xall + parity * lay->xall_half_bytes;
+  prm.row_bytes = static_cast<int64_t>(K) * 2;
   prm.off_flags = lay->off_ag_flags;
   prm.n_comm = prm.chunks_per_rank < 32 ? prm.chunks_per_rank : 32;
   prm.timeout_ns = timeout_ns;

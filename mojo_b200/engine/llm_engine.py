@@ -47,6 +47,7 @@ class EngineConfig:
     use_cuda_graphs: bool = True
     tp_size: int = 1
     ep_size: int = 1
+    lockstep: bool = False                # data-parallel attention + expert parallelism: a rank without work still joins every MoE layer
     autotune: bool = False                # measure GEMM configurations for this model's shapes at start-up
 
 
@@ -179,6 +180,9 @@ class LLMEngine:
             return []
         batch = self.scheduler.step()
         if batch.num_seqs == 0:
+            if self.cfg.lockstep and hasattr(self.model, "forward_idle"):
+                self.model.forward_idle()
+                self.step_count += 1
             return []
         sample_ids = batch.sample_seq_ids
         states = [self.requests[int(r)] for r in sample_ids]

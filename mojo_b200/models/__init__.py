@@ -6,7 +6,7 @@ import torch
 from .config import ModelConfig, get_config, PRESETS  # noqa: F401
 
 
-def build_model(cfg: ModelConfig, device="cpu", dtype=torch.float32, comm=None):
+def build_model(cfg: ModelConfig, device="cpu", dtype=torch.float32, comm=None, ep=None):
     if cfg.architecture == "llama":
         from .llama import LlamaModel
 
@@ -14,5 +14,5 @@ def build_model(cfg: ModelConfig, device="cpu", dtype=torch.float32, comm=None):
     if cfg.architecture == "deepseek_v2":
         from .deepseek_v2 import DeepseekV2Model
 
-        return DeepseekV2Model(cfg, device, dtype, comm=comm)
+        return DeepseekV2Model(cfg, device, dtype, comm=comm, ep=ep)
     raise ValueError(f"unsupported architecture {cfg.architecture!r}")

@@ -190,7 +190,20 @@ class DeepseekV2Model:
             routed = reference.moe_forward(x, lw.w_exp_gu, lw.w_exp_down, weights, ids).to(x.dtype)
         return routed + shared if shared is not None else routed
 
-    def forward(self, token_ids, positions, slots, meta: ops.AttnMeta, kv_caches, sample_rows):
+    def forward_idle(self) -> None:
+        """A step without tokens on this rank. With data-parallel attention and expert-parallel MoE every rank must
+        still take part in each MoE layer's dispatch / combine, so that peers' tokens routed to this rank's experts
+        are computed and returned."""
+        if self.ep is None or self.ep_size == 1:
+            return
+        cfg = self.cfg
+        x = torch.empty(0, cfg.hidden_size, dtype=self.dtype, device=self.device)
+        logits = torch.empty(0, cfg.n_routed_experts, dtype=self.dtype, device=self.device)
+        for lw in self.layers:
+            if lw.w_gu is None:
+                self.ep.moe(x, logits, lw.w_exp_gu_il, lw.w_exp_down, None, cfg.norm_topk_prob, cfg.routed_scaling_factor)
+
+    def forward(self, token_ids, positions, slots, meta: ops.AttnMeta, kv_caches, sample_rows, greedy: bool = False):
         cfg = self.cfg
         h = ops.embedding(token_ids, self.embed)
         residual = None

@@ -82,6 +82,9 @@ class LlamaModel:
         self.final_norm: torch.Tensor | None = None
         self.lm_head: torch.Tensor | None = None     # [V / tp, H]
         self.cos_sin = reference.rope_table(cfg.max_position_embeddings, cfg.head_dim, cfg.rope_theta, cfg.rope_scaling).to(self.device)
+        # Sequence-parallel dataflow between the tensor-parallel regions (activations sharded by token): needs a
+        # communicator with the fused all-gather -> GEMM and GEMM -> reduce-scatter kernels. Off by default.
+        self.sequence_parallel = False
 
     # ------------------------------------------------------------------------------------------------
     # weights
@@ -221,6 +224,8 @@ class LlamaModel:
         token ids instead (arg-max merged across the vocabulary shards without gathering the logits)."""
         cfg, d = self.cfg, self.head_dim
         q_cols, kv_cols = self.n_q * d, self.n_kv * d
+        if self.sequence_parallel and self.tp > 1 and hasattr(self.comm, "all_gather_linear"):
+            return self._forward_sp(token_ids, positions, slots, meta, kv_caches, sample_rows, greedy)
         h = ops.embedding(token_ids, self.embed)
         residual = None
         if cfg.quantization == "fp8_block":
@@ -237,6 +242,57 @@ class LlamaModel:
             act = ops.linear_swiglu(x, lw.w_gu)
             h = self.comm.linear_all_reduce(act, lw.w_down)
         return self._head(h, residual, sample_rows, greedy)
+
+    def _forward_sp(self, token_ids, positions, slots, meta, kv_caches, sample_rows, greedy=False):
+        """Sequence-parallel layer structure: the residual stream and the norms live on T / tp token rows per rank;
+        every column-parallel GEMM is `all-gather -> GEMM` in one kernel and every row-parallel GEMM is
+        `GEMM -> reduce-scatter` in one kernel, in bf16 or block-scaled fp8. Tokens are padded to a multiple of tp
+        (padding rows carry slot -1 and feed nothing that is read)."""
+        cfg, d, comm = self.cfg, self.head_dim, self.comm
+        tp, rank, H = self.tp, comm.rank, cfg.hidden_size
+        q_cols, kv_cols = self.n_q * d, self.n_kv * d
+        fp8 = cfg.quantization == "fp8_block"
+        T = token_ids.shape[0]
+        Tp = (T + tp - 1) // tp * tp
+        r = Tp // tp
+        if Tp != T:
+            pad = Tp - T
+            token_ids = torch.nn.functional.pad(token_ids, (0, pad))
+            positions = torch.nn.functional.pad(positions, (0, pad))
+            slots = torch.nn.functional.pad(slots, (0, pad), value=-1)
+        h = ops.embedding(token_ids[rank * r:(rank + 1) * r], self.embed)
+        residual = None
+
+        def norm_gather_linear(h, residual, norm_w, w, w_scale):
+            if fp8:
+                qv, sv = comm.gather_input_fp8(Tp, H)
+                _, _, _, residual = ops.rms_norm_quant(h, norm_w, cfg.rms_norm_eps, residual, out_q=qv, out_s=sv)
+                return comm.all_gather_linear_fp8(w, w_scale, Tp), residual
+            _, residual = ops.rms_norm(h, norm_w, cfg.rms_norm_eps, residual, out=comm.gather_input(Tp, H))
+            return comm.all_gather_linear(w, Tp), residual
+
+        for li, lw in enumerate(self.layers):
+            qkv, residual = norm_gather_linear(h, residual, lw.attn_norm, lw.wqkv, getattr(lw, "s_qkv", None))
+            q, k, v = qkv[:, :q_cols], qkv[:, q_cols:q_cols + kv_cols], qkv[:, q_cols + kv_cols:]
+            kc, vc = kv_caches[li]
+            ops.rope_kvwrite(q, k, v, self.cos_sin, positions, slots, kc, vc, d)
+            attn = ops.paged_attention(q[:T], kc, vc, meta, self.scale, d)
+            if Tp != T:
+                attn = torch.nn.functional.pad(attn, (0, 0, 0, Tp - T))
+            h = comm.linear_fp8_reduce_scatter(attn, lw.wo, lw.s_o) if fp8 else comm.linear_reduce_scatter(attn, lw.wo)
+            gu, residual = norm_gather_linear(h, residual, lw.mlp_norm, lw.w_gu, getattr(lw, "s_gu", None))
+            act = ops.swiglu(gu, interleaved=not fp8)   # bf16 gate/up weights are stacked for the SwiGLU GEMM epilogue
+            h = comm.linear_fp8_reduce_scatter(act, lw.w_down, lw.s_down) if fp8 else comm.linear_reduce_scatter(act, lw.w_down)
+        # final norm on the local rows, then gather the hidden states for the LM head
+        ops.rms_norm(h, self.final_norm, cfg.rms_norm_eps, residual, out=comm.gather_input(Tp, H))
+        x = comm.all_gather_rows(Tp, H)[:T]
+        if sample_rows is not None:
+            x = ops.gather_rows(x, sample_rows)
+        logits = ops.linear(x, self.lm_head)
+        if greedy and self.greedy_in_forward:
+            valid = max(1, min(self.vocab_local, cfg.vocab_size - self.vocab_start))
+            return comm.vocab_argmax(logits[:, :valid], self.vocab_local)
+        return comm.all_gather_vocab(logits)[:, :cfg.vocab_size]
 
     def gemm_shapes(self) -> list[tuple[int, int, int, int]]:
         """(N, K, epilogue, max tokens or 0) of every weight that goes through `ops.linear` / `ops.linear_swiglu` on

@@ -48,9 +48,11 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, residual:
     return out, (residual if residual is not None else x)
 
 
-def rms_norm_quant(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, residual: torch.Tensor | None = None):
+def rms_norm_quant(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, residual: torch.Tensor | None = None,
+                   out_q: torch.Tensor | None = None, out_s: torch.Tensor | None = None):
     """RMSNorm that also emits the row as e4m3 with one f32 scale per 128 columns.
-    Returns (normed bf16, q e4m3, scales f32 [rows, H/128], residual_stream)."""
+    Returns (normed bf16, q e4m3, scales f32 [rows, H/128], residual_stream). `out_q` / `out_s` (contiguous, CUDA
+    only) let the quantised row land where a fused all-gather will pick it up."""
     if not x.is_cuda:
         y, r = reference.rms_norm(x, weight, eps, residual)
         if residual is not None:
@@ -61,20 +63,20 @@ def rms_norm_quant(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, res
     C = _ext.require()
     out = torch.empty_like(x)
     rows = x.numel() // x.shape[-1]
-    q = torch.empty(rows, x.shape[-1], dtype=torch.float8_e4m3fn, device=x.device)
-    s = torch.empty(rows, x.shape[-1] // 128, dtype=torch.float32, device=x.device)
+    q = out_q if out_q is not None else torch.empty(rows, x.shape[-1], dtype=torch.float8_e4m3fn, device=x.device)
+    s = out_s if out_s is not None else torch.empty(rows, x.shape[-1] // 128, dtype=torch.float32, device=x.device)
     C.rmsnorm(x, residual, weight, out, q, s, eps)
     _count()
     return out, q, s, (residual if residual is not None else x)
 
 
-def quant_e4m3(x: torch.Tensor):
+def quant_e4m3(x: torch.Tensor, out_q: torch.Tensor | None = None, out_s: torch.Tensor | None = None):
     """Per-row 1x128 dynamic e4m3 quantisation of a [M, K] bf16 matrix."""
     if not x.is_cuda:
         return reference.quant_e4m3_1x128(x)
     C = _ext.require()
-    q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
-    s = torch.empty(x.shape[0], x.shape[1] // 128, dtype=torch.float32, device=x.device)
+    q = out_q if out_q is not None else torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    s = out_s if out_s is not None else torch.empty(x.shape[0], x.shape[1] // 128, dtype=torch.float32, device=x.device)
     C.quant_e4m3(x, q, s)
     _count()
     return q, s
@@ -98,13 +100,19 @@ def rope_kvwrite(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor | None, cos_s
     _count()
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None, interleaved: bool = False) -> torch.Tensor:
+    """silu(gate) * up. Row layout [gate | up], or with `interleaved` alternating blocks of 16 gate and 16 up
+    columns (what a plain GEMM against an `interleave_gate_up` weight produces)."""
     if not gate_up.is_cuda:
+        if interleaved:
+            m = gate_up.shape[0]
+            y = gate_up.float().reshape(m, -1, 2, 16)
+            return (reference.silu(y[:, :, 0]) * y[:, :, 1]).reshape(m, -1).to(gate_up.dtype)
         return reference.swiglu(gate_up).to(gate_up.dtype)
     C = _ext.require()
     if out is None:
         out = torch.empty(*gate_up.shape[:-1], gate_up.shape[-1] // 2, dtype=gate_up.dtype, device=gate_up.device)
-    C.swiglu(gate_up, out)
+    C.swiglu(gate_up, out, interleaved)
     _count()
     return out
 

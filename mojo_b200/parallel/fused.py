@@ -52,7 +52,7 @@ class FusedTPComm:
         units = ((r_max + 15) // 16 + 2) * ((hidden + 63) // 64)
         lay.rs_flags_bytes = _align(units * tp * 4)
         lay.off_rs_flags = take(lay.rs_flags_bytes)
-        lay.ag_flags_bytes = _align(tp * (r_max // 128 + 20) * 4)
+        lay.ag_flags_bytes = _align(tp * max(r_max // 128 + 20, 72) * 4)
         lay.off_ag_flags = take(lay.ag_flags_bytes)
         lay.off_res_flags = take(64)
         lay.off_done = take(64)
@@ -141,6 +141,29 @@ class FusedTPComm:
         slot = self._ag_calls & 1
         self._ag_calls += 1
         self.C.tp_ag_gemm(w, self.rank, self.peers, self.layout, out, M, slot, self.timeout_ns, n_comm, config, self.status)
+        ops._count()
+        return out
+
+    def gather_input_fp8(self, M: int, K: int):
+        """(e4m3 [M/tp, K], f32 [M/tp, K/128]) slices of the next fp8 all-gather's buffer that this rank must fill
+        (e.g. by passing them as `out_q` / `out_s` to `ops.rms_norm_quant`). K must be a multiple of 512."""
+        assert M % self.world_size == 0 and K % 512 == 0
+        slot = self._ag_calls & 1
+        r = M // self.world_size
+        base = self.layout.off_xall + slot * self.layout.xall_half_bytes
+        q_bytes = (M * K + 1023) // 1024 * 1024
+        assert q_bytes + M * (K // 128) * 4 <= self.layout.xall_half_bytes, "fp8 gather larger than the gathered buffer"
+        q = self.region.view(base, (M, K), torch.float8_e4m3fn)
+        s = self.region.view(base + q_bytes, (M, K // 128), torch.float32)
+        return q[self.rank * r:(self.rank + 1) * r], s[self.rank * r:(self.rank + 1) * r]
+
+    def all_gather_linear_fp8(self, w_q: torch.Tensor, w_scale: torch.Tensor, M: int, out: torch.Tensor | None = None, n_comm: int = 0) -> torch.Tensor:
+        """y = dequant(all_gather(x_q, x_s)) @ dequant(w).T where this rank's rows were written into `gather_input_fp8`."""
+        if out is None:
+            out = torch.empty(M, w_q.shape[0], dtype=torch.bfloat16, device=w_q.device)
+        slot = self._ag_calls & 1
+        self._ag_calls += 1
+        self.C.tp_ag_gemm_fp8(w_q, w_scale, self.rank, self.peers, self.layout, out, M, slot, self.timeout_ns, n_comm, self.status)
         ops._count()
         return out
 

@@ -129,6 +129,23 @@ def main():
     torch.cuda.synchronize()
     ops.check_status(dev)
 
+    # ---- fp8 all-gather -> GEMM: every rank quantises its own rows straight into the gathered buffer ----
+    for i, M in enumerate([tp * 4, tp * 24, 512, 2048]):
+        K, n_local = 2048, 768
+        r = M // tp
+        x_full = mk((M, K), 8000 + i)
+        w8 = mk((n_local, K), 8100 + 10 * i + rank, 0.05)
+        wq, ws = reference.quant_e4m3_128x128(w8)
+        xq_full, xs_full = ops.quant_e4m3(x_full)
+        want8 = reference.linear_fp8_block(xq_full, xs_full, wq, ws).float()
+        for rep in range(3):
+            q_view, s_view = comm.gather_input_fp8(M, K)
+            ops.quant_e4m3(x_full[rank * r:(rank + 1) * r].contiguous(), out_q=q_view, out_s=s_view)
+            y = comm.all_gather_linear_fp8(wq, ws, M)
+            close(y, want8, f"fp8 all-gather GEMM M={M} rep={rep}")
+    torch.cuda.synchronize()
+    ops.check_status(dev)
+
     # ---- timeout path: a wait nobody satisfies returns a TIMEOUT status and leaves the context usable ----
     flag = torch.zeros(1, dtype=torch.int32, device=dev)
     comm.C.wait_flag(flag, 1, 50_000_000, comm.status)

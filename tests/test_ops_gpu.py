@@ -81,6 +81,7 @@ def test_swiglu_embedding_gather():
     g = torch.Generator().manual_seed(3)
     gu = torch.randn(19, 2 * 1408, generator=g).bfloat16()
     _close(ops.swiglu(gu.to(DEV)), ref.swiglu(gu), 2e-2, 2e-2)
+    _close(ops.swiglu(gu.to(DEV), interleaved=True), ops.swiglu(gu, interleaved=True), 2e-2, 2e-2)
     table = torch.randn(1000, 256, generator=g).bfloat16()
     ids = torch.randint(0, 1000, (29,), generator=g)
     _close(ops.embedding(ids.to(DEV), table.to(DEV)), table[ids], 0, 0)

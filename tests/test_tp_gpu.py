@@ -10,7 +10,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(script, nproc, port, timeout=600, extra_env=None):
+def _run(script, nproc, port, timeout=240, extra_env=None):
     env = dict(os.environ)
     env.update(extra_env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
@@ -50,3 +50,10 @@ def test_symmetric_collectives_and_moe_all_gpus():
     assert f"COLL_OK {n}" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
     p = _run("mp_ep.py", n, 29616)
     assert f"EP_OK {n}" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tensor_parallel_llama_matches_single_process_model():
+    n = 2
+    p = _run("mp_tp_engine.py", n, 29617)
+    assert f"TP_ENGINE_OK {n}" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
