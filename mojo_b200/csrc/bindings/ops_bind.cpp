@@ -183,6 +183,25 @@ void attn_prefill(const at::Tensor& q, const at::Tensor& k_cache, const at::Tens
         "attn_prefill");
 }
 
+void attn_prefill_tc(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache, at::Tensor& out,
+                     const at::Tensor& cu_q, const at::Tensor& ctx_lens, const at::Tensor& block_tables, int64_t max_q_len,
+                     double scale, int64_t variant, c10::optional<at::Tensor> status) {
+  check_cache(q, k_cache, v_cache, 128);
+  need(k_cache.size(2) == 128 && k_cache.size(3) == 128, "attn_prefill_tc: head_dim 128 and page_size 128 only");
+  need(out.dim() == 2 && out.stride(1) == 1 && is_bf16(out) && out.size(0) == q.size(0), "attention: bad out");
+  need(cu_q.scalar_type() == at::kInt && ctx_lens.scalar_type() == at::kInt && block_tables.scalar_type() == at::kInt, "attention: metadata must be int32");
+  need(block_tables.dim() == 2 && block_tables.is_contiguous() && cu_q.is_contiguous() && ctx_lens.is_contiguous(), "attention: metadata must be contiguous");
+  const int batch = static_cast<int>(ctx_lens.numel());
+  need(cu_q.numel() == batch + 1 && block_tables.size(0) == batch, "attention: metadata batch mismatch");
+  c10::cuda::CUDAGuard g(q.device());
+  check(b2_attn_prefill_tc_bf16(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), cu_q.data_ptr<int32_t>(),
+                                ctx_lens.data_ptr<int32_t>(), block_tables.data_ptr<int32_t>(), batch,
+                                static_cast<int>(block_tables.size(1)), static_cast<int>(q.size(1) / 128),
+                                static_cast<int>(k_cache.size(1)), static_cast<int>(max_q_len), static_cast<float>(scale), q.size(0),
+                                q.stride(0), out.stride(0), k_cache.size(0), static_cast<int>(variant), status_ptr(status), cur_stream()),
+        "attn_prefill_tc");
+}
+
 void attn_decode(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache, at::Tensor& out,
                  const at::Tensor& ctx_lens, const at::Tensor& block_tables, c10::optional<at::Tensor> workspace,
                  int64_t head_dim, int64_t num_splits, double scale, c10::optional<at::Tensor> status) {
@@ -267,6 +286,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("top_p") = py::none(), py::arg("uniforms") = py::none(), py::arg("seed") = 0, py::arg("step") = 0);
   m.def("attn_prefill", &attn_prefill, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("out"), py::arg("cu_q"),
         py::arg("ctx_lens"), py::arg("block_tables"), py::arg("head_dim"), py::arg("max_q_len"), py::arg("scale"),
+        py::arg("status") = py::none());
+  m.def("attn_prefill_tc", &attn_prefill_tc, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("out"), py::arg("cu_q"),
+        py::arg("ctx_lens"), py::arg("block_tables"), py::arg("max_q_len"), py::arg("scale"), py::arg("variant") = 0,
         py::arg("status") = py::none());
   m.def("attn_decode", &attn_decode, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("out"), py::arg("ctx_lens"),
         py::arg("block_tables"), py::arg("workspace"), py::arg("head_dim"), py::arg("num_splits"), py::arg("scale"),

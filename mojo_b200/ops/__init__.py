@@ -267,6 +267,11 @@ def _decode_splits(batch: int, n_kv: int, max_ctx: int) -> int:
     return max(1, min(want, max_ctx // 128, 32))
 
 
+# Prefill attention on tcgen05 for head_dim 128 and 128-token pages (False: the mma.sync kernel for every shape).
+prefill_tensor_core = False
+prefill_tc_variant = 0
+
+
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, meta: AttnMeta, scale: float,
                     head_dim: int, out: torch.Tensor | None = None) -> torch.Tensor:
     """Causal GQA attention over the paged cache. q, out: [T, n_q * D]."""
@@ -287,8 +292,13 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _count(2 if splits > 1 else 1)
     if ns > nd:
         # cu_q offsets are absolute token rows, so q/out are passed whole
-        C.attn_prefill(q, k_cache, v_cache, out, meta.cu_q[nd:], meta.ctx_lens[nd:], meta.block_tables[nd:], head_dim,
-                       meta.max_q_len, scale, st.status)
+        if prefill_tensor_core and head_dim == 128 and k_cache.shape[2] == 128:
+            # tcgen05 / TMEM kernel: one KV tile = one 128-token page
+            C.attn_prefill_tc(q, k_cache, v_cache, out, meta.cu_q[nd:], meta.ctx_lens[nd:], meta.block_tables[nd:],
+                              meta.max_q_len, scale, prefill_tc_variant, st.status)
+        else:
+            C.attn_prefill(q, k_cache, v_cache, out, meta.cu_q[nd:], meta.ctx_lens[nd:], meta.block_tables[nd:], head_dim,
+                           meta.max_q_len, scale, st.status)
         _count()
     return out
 

@@ -376,3 +376,19 @@ def test_gemm_autotune_table_picks_valid_faster_or_equal_configs():
         _gemm_case(600, N, K, residual=True)   # residual epilogue has no table: analytic rule
     finally:
         autotune.clear()
+
+
+def test_attention_prefill_tcgen05():
+    """The tcgen05 / TMEM prefill kernel (head_dim 128, 128-token pages) against the fp32 reference: single tile,
+    ragged tails, several KV tiles, a cached prefix before the chunk, GQA, a mixed decode + prefill batch."""
+    ops.prefill_tensor_core = True
+    try:
+        _attn_case([64], [64], 8, 2, 128, 128)
+        _attn_case([128], [128], 4, 4, 128, 128)
+        _attn_case([5, 127, 300], [5, 127, 300], 8, 2, 128, 128)
+        _attn_case([17, 129], [200, 257], 32, 8, 128, 128)      # chunked: cached prefix + chunk
+        _attn_case([700, 260], [700, 1000], 8, 1, 128, 128, seed=2)
+        _attn_case([1, 1, 40, 9], [500, 33, 40, 100], 8, 8, 128, 128)  # decode rows go to the decode kernel
+        ops.check_status()
+    finally:
+        ops.prefill_tensor_core = False
