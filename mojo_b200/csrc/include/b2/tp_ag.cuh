@@ -201,10 +201,9 @@ struct AgSidePush {
   }
 };
 
-// rows per all-gather flag chunk: about 64 chunks per rank (fine enough to spread the push over many CTAs and to
-// let the first tiles start early), at most 128 rows each
+// rows per all-gather flag chunk: about 16 chunks per rank, at most 128 rows each
 inline int ag_chunk_rows(int R) {
-  int c = (R + 63) / 64;
+  int c = (R + 15) / 16;
   if (c > 128) c = 128;
   if (c < 1) c = 1;
   return c;

@@ -54,7 +54,14 @@ struct RsParams {
   const __nv_bfloat16* residual;  // reduce-scatter: [R, N] local rows; all-reduce: [M, N]
   __nv_bfloat16* out;             // reduce-scatter result [R, N]
   uint64_t timeout_ns;
+  int64_t region_bytes;    // size of every rank's symmetric region: accesses into it are checked against this bound
+  Status* status;          // where a failed bounds check is recorded (the access is skipped)
 };
+
+// Bounds check of a 16-byte access at byte offset `off` of a symmetric region; `what` names the access in the record.
+__device__ __forceinline__ bool rs_in_region(const RsParams& p, int64_t off, int what) {
+  return B2_ASSERT(p.status, p.region_bytes == 0 || (off >= 0 && off + 16 <= p.region_bytes), kSiteRsTile, what, off);
+}
 
 // Index of tile (pb, qb) among the units of `owner` (tiles that overlap the owner's rows).
 template <bool SWAP, int BN>
@@ -67,9 +74,8 @@ __device__ __forceinline__ int unit_index(const RsParams& p, int owner, int pb, 
 constexpr int kRsRowPad = 16;
 template <int BN, bool SWAP>
 constexpr int rs_epi_bytes() {
-  // normal: one buffer of [128 rows][64 cols] bf16 (a second one would cost the 256-wide tile a pipeline stage);
-  // swapped: two buffers of [32 tokens][128 cols] bf16
-  return SWAP ? 2 * 32 * (256 + kRsRowPad) : 128 * (128 + kRsRowPad);
+  // normal: two buffers of [128 rows][64 cols] bf16; swapped: two buffers of [32 tokens][128 cols] bf16
+  return SWAP ? 2 * 32 * (256 + kRsRowPad) : 2 * 128 * (128 + kRsRowPad);
 }
 
 // Epilogue of the reduce-scatter GEMM. NVLink moves small scattered writes badly, so the accumulator is first
@@ -85,6 +91,12 @@ struct RsEpilogue {
     const int owner = m / p.R;
     return reinterpret_cast<__nv_bfloat16*>(p.peer[owner] + p.off_staging) +
            (static_cast<int64_t>(p.rank) * p.R + (m - owner * p.R)) * p.N;
+  }
+
+  // byte offset inside the owner's region of column n of row m as written by this rank
+  __device__ __forceinline__ int64_t staging_off(int m, int n) const {
+    const int owner = m / p.R;
+    return p.off_staging + ((static_cast<int64_t>(p.rank) * p.R + (m - owner * p.R)) * p.N + n) * 2;
   }
 
   // TMEM-backed epilogue (bf16 GEMM core)
@@ -109,8 +121,7 @@ struct RsEpilogue {
       static_assert(BN % 64 == 0, "normal layout stages 64 columns at a time");
 #pragma unroll
       for (int cg = 0; cg < BN / 64; ++cg) {
-        uint8_t* buf = epi_smem;
-        if (cg > 0) ptx::named_barrier_sync(1, gemm::kEpiThreads);  // the previous group's rows have been read out
+        uint8_t* buf = epi_smem + (cg & 1) * 128 * ROW;
 #pragma unroll
         for (int c2 = 0; c2 < 2; ++c2) {
           uint32_t r[32];
@@ -132,7 +143,7 @@ struct RsEpilogue {
           const int v = t + 128 * i;
           const int row = v >> 3, cv = v & 7;
           const int m = u.pb * 128 + row;
-          if (m < p.M && n0 + cv * 8 < p.N)
+          if (m < p.M && n0 + cv * 8 < p.N && rs_in_region(p, staging_off(m, n0 + cv * 8), 1))
             ptx::st_v4(staging_row(m) + n0 + cv * 8, *reinterpret_cast<const uint4*>(buf + row * ROW + cv * 16));
         }
       }
@@ -153,7 +164,7 @@ struct RsEpilogue {
           const int v = t + 128 * i;
           const int j = v >> 4, cv = v & 15;
           const int m = m0 + j, n = u.pb * 128 + cv * 8;
-          if (m < p.M && n < p.N)
+          if (m < p.M && n < p.N && rs_in_region(p, staging_off(m, n), 2))
             ptx::st_v4(staging_row(m) + n, *reinterpret_cast<const uint4*>(buf + j * ROW + cv * 16));
         }
       }
@@ -168,7 +179,7 @@ struct RsEpilogue {
       const int owner = o_lo + t;
       const int unit = unit_index<SWAP, BN>(p, owner, u.pb, u.qb);
       uint32_t* f = reinterpret_cast<uint32_t*>(p.peer[owner] + p.off_flags) + static_cast<int64_t>(unit) * p.tp + p.rank;
-      ptx::st_release_sys(f, p.epoch);
+      if (rs_in_region(p, p.off_flags + (static_cast<int64_t>(unit) * p.tp + p.rank) * 4 - 12, 6)) ptx::st_release_sys(f, p.epoch);
     }
   }
 };
@@ -220,7 +231,9 @@ __device__ inline bool reduce_phase(const RsParams& p, Status* status) {
     // same enumeration as unit_index(): (tile along m) major, (tile along n) minor
     const int tm = tm0 + un / n_tiles_n, tn = un % n_tiles_n;
     if (Team::tid() < p.tp) {
-      if (!ptx::wait_flag_ge_sys(flags + static_cast<int64_t>(un) * p.tp + Team::tid(), p.epoch, p.timeout_ns)) {
+      if (!rs_in_region(p, p.off_flags + (static_cast<int64_t>(un) * p.tp + Team::tid()) * 4 - 12, 5)) {
+        sh_ok = 0;
+      } else if (!ptx::wait_flag_ge_sys(flags + static_cast<int64_t>(un) * p.tp + Team::tid(), p.epoch, p.timeout_ns)) {
         status_record(status, kTimeout, kSiteRsTile, un, Team::tid());
         sh_ok = 0;
       }
@@ -243,7 +256,10 @@ __device__ inline bool reduce_phase(const RsParams& p, Status* status) {
         off[u] = static_cast<int64_t>(m - row0) * p.N + col;
 #pragma unroll
         for (int s2 = 0; s2 < kMaxTp; ++s2)
-          if (s2 < p.tp && i < n_vec) raw[u][s2] = ptx::ld_relaxed_sys_v4(staging + static_cast<int64_t>(s2) * p.R * p.N + off[u]);
+          if (s2 < p.tp && i < n_vec && rs_in_region(p, p.off_staging + (static_cast<int64_t>(s2) * p.R * p.N + off[u]) * 2, 3))
+            raw[u][s2] = ptx::ld_relaxed_sys_v4(staging + static_cast<int64_t>(s2) * p.R * p.N + off[u]);
+          else if (s2 < p.tp)
+            raw[u][s2] = make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
@@ -276,6 +292,7 @@ __device__ inline bool reduce_phase(const RsParams& p, Status* status) {
 #pragma unroll 1
           for (int d = 0; d < p.tp; ++d) {
             const int peer = (p.rank + d) % p.tp;  // local copy first, then around the ring
+            if (!rs_in_region(p, p.off_yall + (static_cast<int64_t>(m) * p.N + col) * 2, 4)) continue;
             ptx::st_v4(reinterpret_cast<__nv_bfloat16*>(p.peer[peer] + p.off_yall) + static_cast<int64_t>(m) * p.N + col, pk);
           }
         }

@@ -534,6 +534,8 @@ extern "C" int b2_tp_gemm_rs_fp8(const void* xq, const float* xs, const void* wq
   rs.residual = static_cast<const __nv_bfloat16*>(residual);
   rs.out = static_cast<__nv_bfloat16*>(out);
   rs.timeout_ns = timeout_ns;
+  rs.region_bytes = lay->total_bytes;
+  rs.status = status;
   const bool swap = M <= 64;
   const int bn = swap ? (M <= 16 ? 16 : M <= 32 ? 32 : 64) : 128;
   const int tm = swap ? bn : 128;

@@ -27,6 +27,7 @@
 #include "b2/ptx.cuh"
 #include "b2/tma.h"
 #include "b2/tp.h"
+#include <cstdlib>
 #include "b2/tp_ag.cuh"
 #include "b2/tp_rs.cuh"
 #include "b2/vec.cuh"
@@ -47,23 +48,32 @@ struct RsSideReduce {
   __device__ __forceinline__ void operator()(int, int) const { reduce_phase<BN, SWAP, SideTeam>(p, status); }
 };
 
-template <int BN, int STAGES, bool SWAP>
-__global__ void __launch_bounds__(kRsThreads, 1)
+// SIDE = true: the side-warp scheme above (every CTA runs the GEMM). SIDE = false: CTAs [n_gemm, grid) only reduce
+// from the start and the GEMM CTAs join the reduction after their last tile; kept as the fallback the launch
+// uses unless B2_RS_SIDE=1.
+template <int BN, int STAGES, bool SWAP, bool SIDE>
+__global__ void __launch_bounds__(SIDE ? kRsThreads : gemm::kThreads, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
                const __grid_constant__ RsSched sched, RsParams prm_in, EpochCtl ectl, int n_gemm, Status* status) {
   constexpr uint32_t idesc = ptx::make_idesc(1, 1, 128, BN);
   RsParams prm = prm_in;
   prm.epoch = epoch_begin(ectl);
-  if (static_cast<int>(blockIdx.x) < n_gemm) {
+  prm.status = status;
+  const bool has_tiles = static_cast<int>(blockIdx.x) < n_gemm;
+  if (has_tiles) {
     extern __shared__ uint8_t smem_dyn[];
     uint8_t* epi_buf = smem_dyn + gemm::SmemLayout<BN, STAGES>::kTotalBytes;
     epi_buf += (16 - (reinterpret_cast<uintptr_t>(epi_buf) & 15)) & 15;  // 16-byte vector accesses
     RsEpilogue<BN, SWAP> epi{prm, epi_buf};
-    gemm::run<BN, STAGES, 2>(&tmap_p, &tmap_q, idesc, ptx::kEvictNormal, ptx::kEvictNormal, sched, gemm::NoGate{}, epi, status,
-                             static_cast<int>(blockIdx.x), n_gemm, gemm::NoFill{}, RsSideReduce<BN, SWAP>{prm, status});
-  } else {
-    reduce_phase<BN, SWAP, CtaTeam>(prm, status);  // fewer tiles than SMs: the spare CTAs reduce with all their threads
+    if constexpr (SIDE) {
+      gemm::run<BN, STAGES, 2>(&tmap_p, &tmap_q, idesc, ptx::kEvictNormal, ptx::kEvictNormal, sched, gemm::NoGate{}, epi, status,
+                               static_cast<int>(blockIdx.x), n_gemm, gemm::NoFill{}, RsSideReduce<BN, SWAP>{prm, status});
+    } else {
+      gemm::run<BN, STAGES, 2>(&tmap_p, &tmap_q, idesc, ptx::kEvictNormal, ptx::kEvictNormal, sched, gemm::NoGate{}, epi, status,
+                               static_cast<int>(blockIdx.x), n_gemm);
+    }
   }
+  if (!SIDE || !has_tiles) reduce_phase<BN, SWAP, CtaTeam>(prm, status);
   rs_epoch_end(ectl, prm);
 }
 
@@ -75,7 +85,7 @@ constexpr int stages_for(int bn) {
 // the reduce-scatter kernel gives part of its shared memory to the staged epilogue
 constexpr int rs_stages_for(int bn) {
   const int stage = 128 * 64 * 2 + bn * 64 * 2;
-  int s = (192 * 1024) / stage;
+  int s = (176 * 1024) / stage;
   return s > 10 ? 10 : s;
 }
 
@@ -104,17 +114,35 @@ int launch_rs(const void* x, const void* w, int M, int N, int K, int64_t ldx, in
   if (!build_rs_order(sched, prm.tp, prm.rank, prm.R, TM)) return -kTooLarge;
   prm.p_blocks = sched.p_blocks;
   prm.q_blocks = sched.q_blocks;
-  auto kern = gemm_rs_kernel<BN, STAGES, SWAP>;
+  static const bool side = [] {
+    const char* e = std::getenv("B2_RS_SIDE");
+    return e != nullptr && e[0] == '1';
+  }();
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
+    if (cudaFuncSetAttribute(gemm_rs_kernel<BN, STAGES, SWAP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_rs_kernel<BN, STAGES, SWAP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+      return -kBadArgument;
     attr_set = true;
   }
-  // Full persistent grid: every CTA that has tiles runs the GEMM with its reduction side warps; CTAs beyond the
-  // tile count only reduce.
   const int total = sched.p_blocks * sched.q_blocks;
-  const int n_gemm = total < kNumSMs ? total : kNumSMs;
-  kern<<<kNumSMs, kRsThreads, SMEM, stream>>>(tp, tq, sched, prm, ectl, n_gemm, status);
+  if (side) {
+    // Full persistent grid: every CTA that has tiles runs the GEMM with its reduction side warps; CTAs beyond the
+    // tile count only reduce.
+    const int n_gemm = total < kNumSMs ? total : kNumSMs;
+    gemm_rs_kernel<BN, STAGES, SWAP, true><<<kNumSMs, kRsThreads, SMEM, stream>>>(tp, tq, sched, prm, ectl, n_gemm, status);
+  } else {
+    // CTAs that only reduce are kept only if they do not cost the GEMM an extra wave.
+    int n_red = 0;
+    if (prm.tp > 1) {
+      const int waves_all = (total + kNumSMs - 1) / kNumSMs;
+      n_red = (total + kNumSMs - 13) / (kNumSMs - 12) == waves_all ? 12 : (total + kNumSMs - 5) / (kNumSMs - 4) == waves_all ? 4 : 0;
+      if (total <= kNumSMs - 12) n_red = 12;
+    }
+    int n_gemm = kNumSMs - n_red;
+    if (total < n_gemm) n_gemm = total;
+    gemm_rs_kernel<BN, STAGES, SWAP, false><<<kNumSMs, gemm::kThreads, SMEM, stream>>>(tp, tq, sched, prm, ectl, n_gemm, status);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
 }
 
@@ -167,11 +195,13 @@ struct PlainEpilogue {
   }
 };
 
-// Every CTA runs the GEMM; one side warp per CTA pushes its share of this rank's row chunks to the peers with
-// plain 16-byte loads and stores at kernel start, so no SM is set aside for communication.
+// SIDE = false: the last n_comm CTAs of the grid only move data (bulk async copies through shared memory), the
+// others run the GEMM. SIDE = true: every CTA runs the GEMM and one side warp per CTA pushes its share of this
+// rank's row chunks with plain 16-byte loads and stores at kernel start, so no SM is set aside for communication;
+// selected with B2_AG_SIDE=1.
 constexpr int kAgThreads = gemm::kThreads + 32;
-template <int BN, int STAGES, bool SWAP>
-__global__ void __launch_bounds__(kAgThreads, 1)
+template <int BN, int STAGES, bool SWAP, bool SIDE>
+__global__ void __launch_bounds__(SIDE ? kAgThreads : gemm::kThreads, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q, AgSched sched,
                AgParams prm_in, PlainEpiParams ep, EpochCtl ectl, Status* status) {
   AgParams prm = prm_in;
@@ -179,9 +209,22 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant
   constexpr uint32_t idesc = ptx::make_idesc(1, 1, 128, BN);
   PlainEpilogue<BN, SWAP> epi{ep};
   AgGate gate{prm, SWAP, BN};
-  AgSidePush push{prm, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x)};
-  gemm::run<BN, STAGES, 2>(&tmap_p, &tmap_q, idesc, ptx::kEvictNormal, ptx::kEvictNormal, sched, gate, epi, status,
-                           static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), gemm::NoFill{}, push);
+  if constexpr (SIDE) {
+    AgSidePush push{prm, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x)};
+    gemm::run<BN, STAGES, 2>(&tmap_p, &tmap_q, idesc, ptx::kEvictNormal, ptx::kEvictNormal, sched, gate, epi, status,
+                             static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), gemm::NoFill{}, push);
+  } else {
+    const int n_gemm = static_cast<int>(gridDim.x) - prm.n_comm;
+    if (static_cast<int>(blockIdx.x) >= n_gemm) {
+      extern __shared__ uint8_t smem_dyn[];
+      uint8_t* win = smem_dyn + ((128 - (reinterpret_cast<uintptr_t>(smem_dyn) & 127)) & 127);
+      ag_push(prm, static_cast<int>(blockIdx.x) - n_gemm, win, status);
+      epoch_end(ectl, prm.epoch);
+      return;
+    }
+    gemm::run<BN, STAGES, 2>(&tmap_p, &tmap_q, idesc, ptx::kEvictNormal, ptx::kEvictNormal, sched, gate, epi, status,
+                             static_cast<int>(blockIdx.x), n_gemm);
+  }
   epoch_end(ectl, prm.epoch);
 }
 
@@ -228,15 +271,26 @@ int launch_ag(const void* xall_local, const void* w, void* y, int M, int N, int 
   sched.m_tiles = SWAP ? sched.q_blocks : sched.p_blocks;
   sched.first_tile = (prm.rank * prm.R / TM) % sched.m_tiles;
   PlainEpiParams ep{static_cast<__nv_bfloat16*>(y), ldy, M, N};
-  auto kern = ag_gemm_kernel<BN, STAGES, SWAP>;
+  static const bool side = [] {
+    const char* e = std::getenv("B2_AG_SIDE");
+    return e != nullptr && e[0] == '1';
+  }();
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes) != cudaSuccess) return -kBadArgument;
+    if (cudaFuncSetAttribute(ag_gemm_kernel<BN, STAGES, SWAP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(ag_gemm_kernel<BN, STAGES, SWAP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes) != cudaSuccess)
+      return -kBadArgument;
     attr_set = true;
   }
   const int total = sched.p_blocks * sched.q_blocks;
-  const int grid = total < kNumSMs ? total : kNumSMs;
-  kern<<<grid, kAgThreads, L::kTotalBytes, stream>>>(tp, tq, sched, prm, ep, ectl, status);
+  if (side) {
+    const int grid = total < kNumSMs ? total : kNumSMs;
+    ag_gemm_kernel<BN, STAGES, SWAP, true><<<grid, kAgThreads, L::kTotalBytes, stream>>>(tp, tq, sched, prm, ep, ectl, status);
+  } else {
+    int n_gemm = kNumSMs - prm.n_comm;
+    if (total < n_gemm) n_gemm = total;
+    ag_gemm_kernel<BN, STAGES, SWAP, false><<<n_gemm + prm.n_comm, gemm::kThreads, L::kTotalBytes, stream>>>(tp, tq, sched, prm, ep, ectl, status);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
 }
 
@@ -297,8 +351,10 @@ extern "C" int b2_tp_gemm_rs_bf16(const void* x, const void* w, const B2TpRegion
   prm.residual = static_cast<const __nv_bfloat16*>(residual);
   prm.out = static_cast<__nv_bfloat16*>(out);
   prm.timeout_ns = timeout_ns;
+  prm.region_bytes = lay->total_bytes;
   bool swap = M <= 128;
-  int bn = swap ? pick_bn_swap(M) : (M >= 512 ? 256 : 128);
+  // 256-wide tiles faulted here with a residual at M = 2048 (cause not found by reading): they stay off until it is.
+  int bn = swap ? pick_bn_swap(M) : 128;
   if (config != 0) {
     swap = (config >> 30) & 1;
     bn = config & 0xffff;

@@ -30,6 +30,11 @@ def main():
         ref = b.float().abs().max().item()
         assert err <= 0.02 * ref + 0.05, f"{what}: max err {err} (ref max {ref}) on rank {rank}"
 
+    def progress(what):
+        # one line per finished section on stderr: tells which section a failure belongs to
+        torch.cuda.synchronize()
+        print(f"[rank {rank}] ok: {what}", file=sys.stderr, flush=True)
+
     k_local = 512
     # ---- GEMM -> all-reduce and -> reduce-scatter (row-parallel: every rank has its own K shard) ----
     for i, M in enumerate([8, 64, 136, 512, 1024, 16, 2048]):
@@ -47,8 +52,10 @@ def main():
             r = M // tp
             y3 = comm.linear_reduce_scatter(x, w, residual=res[rank * r:(rank + 1) * r].contiguous())
             close(y3, (want + res.float())[rank * r:(rank + 1) * r], f"reduce-scatter M={M}")
+        progress(f"row-parallel M={M}")
     torch.cuda.synchronize()
     ops.check_status(dev)
+    progress("row-parallel GEMM + all-reduce / reduce-scatter")
 
     # ---- back-to-back launches without host syncs (epochs + double buffering) ----
     x = mk((256, k_local), 1000 + rank)
@@ -62,6 +69,7 @@ def main():
     for o in outs:
         close(o, want, "back-to-back all-reduce")
     ops.check_status(dev)
+    progress("back-to-back launches")
 
     # ---- all-gather -> GEMM (column-parallel: every rank has its own rows of X and its own N shard) ----
     for i, M in enumerate([tp * 4, tp * 32, 512, 2048]):
@@ -78,8 +86,10 @@ def main():
         full = comm.all_gather_rows(M, K)
         torch.cuda.synchronize()
         assert torch.equal(full, x_full), f"standalone all-gather M={M}"
+        progress(f"all-gather M={M}")
     torch.cuda.synchronize()
     ops.check_status(dev)
+    progress("all-gather GEMM")
 
     # ---- the same launches replayed from a CUDA graph ----
     x = mk((64, k_local), 5000 + rank)
@@ -106,6 +116,7 @@ def main():
     dist.all_reduce(want_b)
     close(b, want_b, "graph replay chained all-reduce")
     ops.check_status(dev)
+    progress("graph replay")
 
     # ---- block-scaled fp8 GEMM -> all-reduce / reduce-scatter ----
     from mojo_b200.ops import reference
@@ -128,6 +139,7 @@ def main():
             close(y3, want8[rank * r:(rank + 1) * r], f"fp8 reduce-scatter M={M}")
     torch.cuda.synchronize()
     ops.check_status(dev)
+    progress("fp8 GEMM + all-reduce / reduce-scatter")
 
     # ---- fp8 all-gather -> GEMM: every rank quantises its own rows straight into the gathered buffer ----
     for i, M in enumerate([tp * 4, tp * 24, 512, 2048]):
@@ -145,6 +157,7 @@ def main():
             close(y, want8, f"fp8 all-gather GEMM M={M} rep={rep}")
     torch.cuda.synchronize()
     ops.check_status(dev)
+    progress("fp8 all-gather GEMM")
 
     # ---- timeout path: a wait nobody satisfies returns a TIMEOUT status and leaves the context usable ----
     flag = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -159,6 +172,7 @@ def main():
     torch.cuda.synchronize()
     close(y, want, "all-reduce after a timeout")
     ops.check_status(dev)
+    progress("timeout path")
     dist.barrier()
     if rank == 0:
         print(f"TP_FUSED_OK {tp}", flush=True)
