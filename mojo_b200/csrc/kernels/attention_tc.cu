@@ -362,7 +362,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 using namespace b2;
 
 // Same contract as b2_attn_prefill_bf16 with head_dim = 128 and page_size = 128 fixed; out rows 16-byte aligned.
-// `variant` selects the descriptor of the MN-major V operand: 0 = the layout described at the top of this file.
+// `variant` is reserved (0).
 extern "C" int b2_attn_prefill_tc_bf16(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* cu_q,
                                        const int32_t* ctx_lens, const int32_t* block_tables, int batch, int max_blocks, int n_q,
                                        int n_kv, int max_q_len, float scale, int64_t q_rows, int64_t q_stride, int64_t out_stride,
@@ -391,7 +391,7 @@ extern "C" int b2_attn_prefill_tc_bf16(const void* q, const void* k_cache, const
   prm.scale_log2 = scale * 1.4426950408889634f;
   prm.v_lbo = kHalfBytes;   // the second 64 columns of the head dimension are the second TMA box
   prm.v_sbo = 1024;         // 8 KV rows of 128 bytes
-  if (variant == 1) { prm.v_lbo = 1024; prm.v_sbo = kHalfBytes; }
+  (void)variant;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttn) != cudaSuccess)

@@ -268,8 +268,7 @@ def _decode_splits(batch: int, n_kv: int, max_ctx: int) -> int:
 
 
 # Prefill attention on tcgen05 for head_dim 128 and 128-token pages (False: the mma.sync kernel for every shape).
-prefill_tensor_core = False
-prefill_tc_variant = 0
+prefill_tensor_core = True
 
 
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, meta: AttnMeta, scale: float,
@@ -295,7 +294,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         if prefill_tensor_core and head_dim == 128 and k_cache.shape[2] == 128:
             # tcgen05 / TMEM kernel: one KV tile = one 128-token page
             C.attn_prefill_tc(q, k_cache, v_cache, out, meta.cu_q[nd:], meta.ctx_lens[nd:], meta.block_tables[nd:],
-                              meta.max_q_len, scale, prefill_tc_variant, st.status)
+                              meta.max_q_len, scale, 0, st.status)
         else:
             C.attn_prefill(q, k_cache, v_cache, out, meta.cu_q[nd:], meta.ctx_lens[nd:], meta.block_tables[nd:], head_dim,
                            meta.max_q_len, scale, st.status)

@@ -381,7 +381,7 @@ def test_gemm_autotune_table_picks_valid_faster_or_equal_configs():
 def test_attention_prefill_tcgen05():
     """The tcgen05 / TMEM prefill kernel (head_dim 128, 128-token pages) against the fp32 reference: single tile,
     ragged tails, several KV tiles, a cached prefix before the chunk, GQA, a mixed decode + prefill batch."""
-    ops.prefill_tensor_core = True
+    assert ops.prefill_tensor_core
     try:
         _attn_case([64], [64], 8, 2, 128, 128)
         _attn_case([128], [128], 4, 4, 128, 128)
@@ -390,5 +390,8 @@ def test_attention_prefill_tcgen05():
         _attn_case([700, 260], [700, 1000], 8, 1, 128, 128, seed=2)
         _attn_case([1, 1, 40, 9], [500, 33, 40, 100], 8, 8, 128, 128)  # decode rows go to the decode kernel
         ops.check_status()
-    finally:
+        # and the mma.sync kernel on the same shapes stays correct
         ops.prefill_tensor_core = False
+        _attn_case([5, 127, 300], [5, 127, 300], 8, 2, 128, 128)
+    finally:
+        ops.prefill_tensor_core = True
