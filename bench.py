@@ -51,6 +51,9 @@ def parse_args():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--no-autotune", action="store_true", help="skip the start-up measurement of GEMM configurations")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--ar-mode", default="auto", choices=["auto", "fused", "split"],
+                    help="row-parallel linear + all-reduce: the single fused kernel, GEMM -> symmetric-memory all-reduce kernel, "
+                         "or whichever was measured faster per token count at start-up (no NCCL in any of them)")
     ap.add_argument("--sp", action="store_true", help="sequence-parallel dataflow: all-gather -> GEMM and GEMM -> reduce-scatter kernels")
     ap.add_argument("--layers", type=int, default=None, help="debug only: marks the result invalid")
     ap.add_argument("--profile", default=None, help="debug only: write a per-kernel table of a few steps to this file")
@@ -111,6 +114,7 @@ def main() -> None:
             from mojo_b200.parallel.fused import FusedTPComm
 
             comm = FusedTPComm(info, max_tokens=args.max_batched_tokens, hidden=mcfg.hidden_size, max_k=mcfg.hidden_size)
+            comm.ar_mode = args.ar_mode
         else:
             from mojo_b200.parallel.tp import NcclTPComm
 
@@ -291,7 +295,7 @@ def main() -> None:
                 "parallelism": (f"dp{world}-attention + ep{world}-experts" if ep_mode else f"tp{world}"), "requests": args.requests, "poisson_rate_per_s": args.rate,
                 "max_num_batched_tokens": args.max_batched_tokens, "page_size": args.page_size, "ramp_steps": ramp,
                 "l2": "inputs larger than L2: every step streams this rank's full weight set (GBs) through the 126 MB L2",
-                "cuda_graphs": not args.no_graphs, "gemm_autotune": bool(ecfg.autotune), "comm": args.comm if world > 1 else "none", "sequence_parallel": bool(getattr(model, "sequence_parallel", False)),
+                "cuda_graphs": not args.no_graphs, "gemm_autotune": bool(ecfg.autotune), "comm": args.comm if world > 1 else "none", "all_reduce_form": (args.ar_mode if world > 1 and args.comm == "fused" and not ep_mode else None), "sequence_parallel": bool(getattr(model, "sequence_parallel", False)),
                 "prefill_tokens_in_timed_region": prefill_tokens, "output_tokens_in_timed_region": tokens,
             },
             "clocks": {k: clocks.summary().get(k) for k in ("sm_mhz", "sm_max_mhz", "reasons", "power_w_max")},

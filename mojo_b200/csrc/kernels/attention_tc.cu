@@ -10,11 +10,12 @@
 //                 S_j   = Q K_j^T    A = Q  (K-major, 128-byte swizzle), B = K_j (K-major: head dim is contiguous)
 //                 O_j   = P_j V_j    A = P_j (K-major, written by the softmax warps), B = V_j (MN-major: V rows are
 //                                    KV tokens, so the N = head-dim index is the contiguous one)
-//   warps 2-5   softmax: one query row per thread; tcgen05.ld the S row, scale, causal mask, running max, exp2,
-//               row sum; write P_j as bf16 into shared memory in the swizzled operand layout; publish the factor
-//               by which the running maximum moved (alpha_j)
-//   warps 6-9   accumulate: one query row per thread; O = O * alpha_j + O_j (tcgen05.ld), final O / l, bf16 store
-// S_{j+1} is issued before P_j V_j, so the softmax of tile j + 1 overlaps the second MMA of tile j.
+//   warps 2-9   compute, two threads per query row (64 columns each): tcgen05.ld the half row of S_j, causal mask,
+//               running max (halves exchanged through shared memory), exp2, row sum; write P_j as bf16 into shared
+//               memory in the swizzled operand layout; then O = O * alpha_{j-1} + O_{j-1} for their 64 columns of
+//               the accumulator (tcgen05.ld); at the end O / l as bf16
+// S_{j+1} is issued before P_j V_j, so the softmax of tile j + 1 overlaps the second MMA of tile j, and the
+// accumulation of O_j runs after the softmax of tile j + 1.
 // Every mbarrier wait is bounded; a role that gives up records TIMEOUT, raises a CTA-wide flag and leaves its
 // loop, the others follow at their next wait, and the CTA still frees TMEM and exits.
 #include <cstdint>
@@ -45,9 +46,9 @@ constexpr int kOffK = kOffP + kTileBytes;
 constexpr int kOffV = kOffK + kStages * kTileBytes;
 constexpr int kOffBar = kOffV + kStages * kTileBytes;      // 192 KB
 constexpr int kNumBars = 1 + 4 * kStages + 2 + 2 + 2 + 2 + 1;  // q_full, k/v full+empty, s full/empty, p full/empty, o full/empty, drain
-constexpr int kOffAlpha = kOffBar + 8 * kNumBars + 16;     // float [4][128]
-constexpr int kOffL = kOffAlpha + 4 * kTile * 4;           // float [128]
-constexpr int kOffFlags = kOffL + kTile * 4;               // tmem holder, fail flag
+constexpr int kOffAlpha = kOffBar + 8 * kNumBars + 16;     // float [2][2][128]: partial row maxima
+constexpr int kOffL = kOffAlpha + 4 * kTile * 4;           // float [2][128]
+constexpr int kOffFlags = kOffL + 2 * kTile * 4;           // tmem holder, fail flag
 constexpr int kSmemAttn = kOffFlags + 16 + 1024;           // + alignment slack
 
 struct AttnTcParams {
@@ -120,11 +121,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(s_full(a), 1);
-      ptx::mbar_init(s_empty(a), 4);
+      ptx::mbar_init(s_empty(a), 8);
       ptx::mbar_init(o_full(a), 1);
-      ptx::mbar_init(o_empty(a), 4);
+      ptx::mbar_init(o_empty(a), 8);
     }
-    ptx::mbar_init(p_full, 4);
+    ptx::mbar_init(p_full, 8);
     ptx::mbar_init(p_empty, 1);
     ptx::mbar_init(drain_bar, 1);
     ptx::fence_mbar_init();
@@ -230,98 +231,39 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       }
     }
     __syncwarp();
-  } else if (warp < 6) {
-    // ------------------------------------------------------------------ softmax warps (one query row per thread)
-    const int quarter = warp & 3;
+  } else {
+    // ------------------------------------------------------------------ compute warps
+    // Eight warps, two threads per query row: thread (r, g) owns columns [64 g, 64 g + 64) of the row's S tile and
+    // the same columns of its O accumulator. Two warps per scheduler hide each other's dependency stalls, which one
+    // warp per scheduler cannot. Per KV tile: softmax of S_j and the write of P_j, then (software pipelining) the
+    // accumulation of O_{j-1}, whose MMA ran while this tile's softmax did.
+    const int g = (warp - 2) >> 2;          // column half
+    const int quarter = warp & 3;           // TMEM lane quarter this warp may access
     const int r = quarter * 32 + lane;
     const int qpos = pos0 + r;
-    float m_run = -INFINITY, l_run = 0.0f;
+    const uint32_t lane_bits = static_cast<uint32_t>(quarter * 32) << 16;
+    float* pmax = alpha_ring;               // [2 tiles in flight][2 halves][128 rows]
+    float m_run = -INFINITY, l_part = 0.0f, alpha_prev = 1.0f;
+    float o[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) o[i] = 0.0f;
+    // A warp that gives up keeps walking the loop (every compute warp must reach the named barrier of every tile)
+    // but no longer waits, reads TMEM or arrives anywhere; the other roles then run into their own limits.
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
+    auto wait_all = [&](uint32_t bar_addr, uint32_t parity, int code, int j) -> bool {
+      if (!ok || *fail != 0) return false;
+      if (__all_sync(0xffffffffu, ptx::mbar_wait(bar_addr, parity))) return true;
+      if (lane == 0) give_up(code, j);
+      return false;
+    };
+    auto accumulate = [&](int j, float alpha) {
       const int a = j & 1;
-      if (!__all_sync(0xffffffffu, ptx::mbar_wait(s_full(a), (j >> 1) & 1))) {
-        if (lane == 0) give_up(9, j);
-        ok = false;
-        break;
-      }
+      ok = wait_all(o_full(a), (j >> 1) & 1, 11, j);
+      if (!ok) return;
       ptx::tc_fence_after();
-      const uint32_t taddr = tmem_base + a * 128 + (static_cast<uint32_t>(quarter * 32) << 16);
-      float s[128];
+      const uint32_t taddr = tmem_base + 256 + a * 128 + g * 64 + lane_bits;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        ptx::tmem_ld_32x32(taddr + c * 32, v);
-        ptx::tc_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(v[i]);
-      }
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(s_empty(a));     // S buffer free for tile j + 2
-      const int kv0 = j * kTile;
-      const bool diag = kv0 + kTile - 1 > pos0;        // some row of this tile masks some column
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 128; ++c) {
-        float v = s[c] * prm.scale_log2;
-        if (diag && kv0 + c > qpos) v = -INFINITY;
-        s[c] = v;
-        mx = fmaxf(mx, v);
-      }
-      const float m_new = fmaxf(m_run, mx);
-      const float m_use = m_new == -INFINITY ? 0.0f : m_new;   // a row with nothing visible yet
-      const float alpha = exp2f(m_run - m_use);
-      m_run = m_new;
-      alpha_ring[(j & 3) * kTile + r] = alpha;
-      if (j > 0 && !__all_sync(0xffffffffu, ptx::mbar_wait(p_empty, (j - 1) & 1))) {
-        if (lane == 0) give_up(10, j);
-        ok = false;
-        break;
-      }
-      float sum = 0.0f;
-#pragma unroll
-      for (int ch = 0; ch < 16; ++ch) {
-        float p[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          p[i] = exp2f(s[ch * 8 + i] - m_use);
-          sum += p[i];
-        }
-        uint4 pk;
-        pk.x = ptx::pack_bf16x2(p[0], p[1]);
-        pk.y = ptx::pack_bf16x2(p[2], p[3]);
-        pk.z = ptx::pack_bf16x2(p[4], p[5]);
-        pk.w = ptx::pack_bf16x2(p[6], p[7]);
-        *reinterpret_cast<uint4*>(smem + kOffP + (ch >> 3) * kHalfBytes + gemm::sw128_offset(r, ch & 7)) = pk;
-      }
-      l_run = l_run * alpha + sum;
-      ptx::fence_proxy_async_smem();   // generic-proxy writes of P -> visible to the tensor core's async proxy
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(p_full);
-    }
-    (void)ok;
-    l_final[r] = l_run;
-    ptx::named_barrier_sync(5, 256);
-  } else {
-    // ------------------------------------------------------------------ accumulate warps (one query row per thread)
-    const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;
-    float o[128];
-#pragma unroll
-    for (int i = 0; i < 128; ++i) o[i] = 0.0f;
-    bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int a = j & 1;
-      if (!__all_sync(0xffffffffu, ptx::mbar_wait(o_full(a), (j >> 1) & 1))) {
-        if (lane == 0) give_up(11, j);
-        ok = false;
-        break;
-      }
-      ptx::tc_fence_after();
-      const float alpha = alpha_ring[(j & 3) * kTile + r];
-      const uint32_t taddr = tmem_base + 256 + a * 128 + (static_cast<uint32_t>(quarter * 32) << 16);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
         ptx::tmem_ld_32x32(taddr + c * 32, v);
         ptx::tc_wait_ld();
@@ -331,20 +273,91 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(o_empty(a));
+    };
+    for (int j = 0; j < n_tiles; ++j) {
+      const int a = j & 1;
+      float s[64];
+      ok = wait_all(s_full(a), (j >> 1) & 1, 9, j);
+      if (ok) {
+        ptx::tc_fence_after();
+        const uint32_t taddr = tmem_base + a * 128 + g * 64 + lane_bits;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32(taddr + c * 32, v);
+          ptx::tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(v[i]);
+        }
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(s_empty(a));     // S buffer free for tile j + 2
+      } else {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) s[c] = 0.0f;
+      }
+      const int kv0 = j * kTile + g * 64;
+      if (kv0 + 63 > pos0) {                             // some row of this tile masks some of these columns
+#pragma unroll
+        for (int c = 0; c < 64; ++c)
+          if (kv0 + c > qpos) s[c] = -INFINITY;
+      }
+      // row maximum of the raw scores: eight independent chains, then the partner's half through shared memory
+      float mx[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx[i] = s[i];
+#pragma unroll
+      for (int c = 8; c < 64; ++c) mx[c & 7] = fmaxf(mx[c & 7], s[c]);
+      const float mloc = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+      pmax[(a * 2 + g) * kTile + r] = mloc;
+      ptx::named_barrier_sync(5, 256);
+      const float m_new = fmaxf(m_run, fmaxf(mloc, pmax[(a * 2 + (g ^ 1)) * kTile + r]));
+      const float m_use = m_new == -INFINITY ? 0.0f : m_new;   // a row with nothing visible yet
+      const float alpha = ptx::ex2((m_run - m_use) * prm.scale_log2);
+      const float neg_m = -m_use * prm.scale_log2;
+      m_run = m_new;
+      if (j > 0) ok = wait_all(p_empty, (j - 1) & 1, 10, j);
+      if (ok) {
+        float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          float p[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            p[i] = ptx::ex2(fmaf(s[ch * 8 + i], prm.scale_log2, neg_m));
+            sum[i & 3] += p[i];
+          }
+          uint4 pk;
+          pk.x = ptx::pack_bf16x2(p[0], p[1]);
+          pk.y = ptx::pack_bf16x2(p[2], p[3]);
+          pk.z = ptx::pack_bf16x2(p[4], p[5]);
+          pk.w = ptx::pack_bf16x2(p[6], p[7]);
+          *reinterpret_cast<uint4*>(smem + kOffP + g * kHalfBytes + gemm::sw128_offset(r, ch)) = pk;
+        }
+        l_part = l_part * alpha + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
+        ptx::fence_proxy_async_smem();   // generic-proxy writes of P -> visible to the tensor core's async proxy
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(p_full);
+      }
+      // O_{j-1} = P_{j-1} V_{j-1} has had this tile's softmax to finish in
+      if (j > 0) accumulate(j - 1, alpha_prev);
+      alpha_prev = alpha;
     }
+    if (n_tiles > 0) accumulate(n_tiles - 1, alpha_prev);
+    l_final[g * kTile + r] = l_part;
     ptx::named_barrier_sync(5, 256);
     if (ok && *fail == 0 && r < rows) {
-      const float l = l_final[r];
+      const float l = l_final[r] + l_final[kTile + r];
       const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-      __nv_bfloat16* dst = prm.out + static_cast<int64_t>(q_begin + qt * kTile + r) * prm.ld_out + head * kD;
+      __nv_bfloat16* dst = prm.out + static_cast<int64_t>(q_begin + qt * kTile + r) * prm.ld_out + head * kD + g * 64;
 #pragma unroll
-      for (int g = 0; g < 16; ++g) {
+      for (int c = 0; c < 8; ++c) {
         uint4 pk;
-        pk.x = ptx::pack_bf16x2(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv);
-        pk.y = ptx::pack_bf16x2(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv);
-        pk.z = ptx::pack_bf16x2(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv);
-        pk.w = ptx::pack_bf16x2(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv);
-        ptx::st_v4(dst + g * 8, pk);
+        pk.x = ptx::pack_bf16x2(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv);
+        pk.y = ptx::pack_bf16x2(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
+        pk.z = ptx::pack_bf16x2(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv);
+        pk.w = ptx::pack_bf16x2(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
+        ptx::st_v4(dst + c * 8, pk);
       }
     }
   }

@@ -93,6 +93,11 @@ class ModelRunner:
             if verbose:
                 for m, (cfg, us, us_auto) in report[(N, K, epi)].items():
                     print(f"[autotune] N={N} K={K} epi={epi} M={m}: {ops.autotune.describe(cfg)} {us:.1f} us (rule: {us_auto:.1f} us)")
+        comm = getattr(self.model, "comm", None)
+        if comm is not None and hasattr(comm, "tune_all_reduce") and hasattr(self.model, "row_parallel_shapes"):
+            # fused GEMM+all-reduce kernel or GEMM -> symmetric all-reduce kernel: whichever is faster per token count
+            for N, K in self.model.row_parallel_shapes():
+                report[("all_reduce", N, K)] = comm.tune_all_reduce(N, K, [m for m in counts if m >= 8])
         torch.cuda.synchronize(self.device)
         ops.check_status(self.device)
         return report
@@ -131,6 +136,11 @@ class ModelRunner:
         rows = st.view(seg_rows, torch.int64)
         if self.step_events is not None:
             self.step_events[0].record()
+        comm = getattr(self.model, "comm", None)
+        if comm is not None and hasattr(comm, "begin_graph"):
+            # cross-rank barrier kernel: eager steps and graph replays interleave, and each keeps its own count of
+            # double-buffer halves; after the barrier no peer is still reading a half this step overwrites
+            comm.begin_graph()
         if S == 0:
             # pure mid-prompt chunks: run the layers for their KV side effect, nothing to sample
             self.model.forward(token_ids, positions, slots, meta, self.kv_caches, rows)

@@ -296,16 +296,22 @@ class LlamaModel:
 
     def gemm_shapes(self) -> list[tuple[int, int, int, int]]:
         """(N, K, epilogue, max tokens or 0) of every weight that goes through `ops.linear` / `ops.linear_swiglu` on
-        this rank, for the measured GEMM configuration tables. Row-parallel weights under a fused tensor-parallel
-        communicator are left out: they run in the fused GEMM+collective kernels."""
+        this rank, for the measured GEMM configuration tables (the row-parallel weights too: under tensor
+        parallelism they run either in the fused GEMM+all-reduce kernel or as plain GEMM -> all-reduce kernel)."""
         if self.cfg.quantization == "fp8_block" or not self.layers:
             return []
         lw = self.layers[0]
         shapes = [(lw.wqkv.shape[0], lw.wqkv.shape[1], ops.EPI_NONE, 0), (lw.w_gu.shape[0], lw.w_gu.shape[1], ops.EPI_SWIGLU, 0),
-                  (self.lm_head.shape[0], self.lm_head.shape[1], ops.EPI_NONE, 256)]
-        if self.tp == 1:
-            shapes += [(lw.wo.shape[0], lw.wo.shape[1], ops.EPI_NONE, 0), (lw.w_down.shape[0], lw.w_down.shape[1], ops.EPI_NONE, 0)]
+                  (self.lm_head.shape[0], self.lm_head.shape[1], ops.EPI_NONE, 256),
+                  (lw.wo.shape[0], lw.wo.shape[1], ops.EPI_NONE, 0), (lw.w_down.shape[0], lw.w_down.shape[1], ops.EPI_NONE, 0)]
         return shapes
+
+    def row_parallel_shapes(self) -> list[tuple[int, int]]:
+        """(N, K per rank) of the row-parallel bf16 linears (attention output, FFN down) under tensor parallelism."""
+        if self.tp == 1 or self.cfg.quantization == "fp8_block" or not self.layers:
+            return []
+        lw = self.layers[0]
+        return [(lw.wo.shape[0], lw.wo.shape[1]), (lw.w_down.shape[0], lw.w_down.shape[1])]
 
     def _head(self, h, residual, sample_rows, greedy: bool):
         """Final norm, row gather and the vocabulary-parallel LM head. `greedy` on a tensor-parallel communicator

@@ -76,6 +76,33 @@ class SymmCollectives:
             buf[n:].zero_()
         return n_pad
 
+    def staging_view(self, shape, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        """The input half of the NEXT collective as a tensor of `shape`: a producer (e.g. a GEMM) can write its result
+        straight into it and call `all_reduce_staged(shape)` instead of `all_reduce(x)`, saving the staging copy."""
+        n = 1
+        for d in shape:
+            n *= int(d)
+        assert n * torch.empty((), dtype=dtype).element_size() <= self.max_bytes, "message larger than the collective buffer"
+        slot = self._calls & 1
+        return self.region.view(self.layout.off_buf + slot * self.layout.buf_half_bytes, tuple(shape), dtype)
+
+    def all_reduce_staged(self, shape, algo: str = "auto") -> torch.Tensor:
+        """All-reduce of what was written into `staging_view(shape)` (bf16; numel a multiple of 8 * world size)."""
+        n = 1
+        for d in shape:
+            n *= int(d)
+        assert n % (8 * self.world_size) == 0
+        slot = self._slot()
+        if algo == "auto":
+            algo = "one_shot" if n * 2 <= self.ONE_SHOT_MAX_BYTES else ("nvls" if self.mc_ptr else "two_shot")
+        code = {"one_shot": 0, "two_shot": 1, "nvls": 2}[algo]
+        out = torch.empty(n, dtype=torch.bfloat16, device=self.info.device) if code == 0 else None
+        self.C.coll_all_reduce(self.rank, self.peers, self.layout, self.mc_ptr, out, n, code, slot, self.timeout_ns, self.status)
+        ops._count()
+        if out is None:
+            out = self.region.view(self.layout.off_out + slot * self.layout.out_half_bytes, (n,), torch.bfloat16)
+        return out.view(*shape)
+
     def all_reduce(self, x: torch.Tensor, algo: str = "auto") -> torch.Tensor:
         if self.world_size == 1:
             return x

@@ -68,16 +68,69 @@ class FusedTPComm:
         self._rs_calls = 0
         self._ag_calls = 0
         self._coll = None
-        self._coll_bytes = 16 << 20
+        self._coll_bytes = max(16 << 20, self.max_tokens * hidden * 2)
+        self.ar_mode = "auto"
+        self._ar_table: dict = {}
         self.status = _state.get(info.device).status
 
     # -- fused ops ---------------------------------------------------------------------------------
+    def _split_all_reduce(self, M: int, N: int, K: int) -> bool:
+        """Whether the row-parallel linear of this shape runs as GEMM -> symmetric-memory all-reduce kernel (two
+        launches, the GEMM writing straight into the all-reduce's input buffer) instead of the single fused kernel.
+        `ar_mode`: "fused", "split", or "auto" = per token-count table measured by `tune_all_reduce`, fused if untuned."""
+        if self.ar_mode != "auto":
+            return self.ar_mode == "split"
+        table = self._ar_table.get((N, K))
+        if not table or (M * N) % (8 * self.world_size) != 0 or M * N * 2 > self._coll_bytes:
+            return False
+        for bound, split in table:
+            if M <= bound:
+                return split
+        return table[-1][1]
+
+    def tune_all_reduce(self, N: int, K: int, token_counts, iters: int = 3) -> dict:
+        """Time both forms of the row-parallel linear + all-reduce at each token count (all ranks call this
+        together; the slower rank decides) and remember the faster one. Returns {M: (fused us, split us)}."""
+        dev = self.info.device
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+        report, table = {}, []
+        saved = self.ar_mode
+        for M in sorted(set(int(m) for m in token_counts)):
+            if (M * N) % (8 * self.world_size) != 0 or M * N * 2 > self._coll_bytes:
+                continue
+            x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+            times = []
+            for mode in ("fused", "split"):
+                self.ar_mode = mode
+                self.linear_all_reduce(x, w)
+                torch.cuda.synchronize(dev)
+                dist.barrier(group=self.group)
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                for _ in range(iters):
+                    self.linear_all_reduce(x, w)
+                e.record()
+                e.synchronize()
+                t = torch.tensor([s.elapsed_time(e) * 1e3 / iters], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+                times.append(float(t))
+            report[M] = tuple(times)
+            table.append((M, times[1] < times[0]))
+        self.ar_mode = saved
+        self._ar_table[(N, K)] = table
+        ops.check_status(dev)
+        return report
+
     def linear_all_reduce(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None, config: int = 0) -> torch.Tensor:
-        """y = all_reduce(x @ w.T) (+ residual), replicated on every rank. Returns a view into the symmetric
-        result buffer that stays valid until the second fused reduce launch after this one."""
+        """y = all_reduce(x @ w.T) (+ residual), replicated on every rank. Returns a view into a symmetric
+        result buffer (or a fresh tensor) that stays valid until the second reduce launch after this one."""
         M, N = x.shape[0], w.shape[0]
         if self.world_size == 1:
             return ops.linear(x, w, residual)
+        if residual is None and config == 0 and self._split_all_reduce(M, N, x.shape[1]):
+            coll = self._collectives()
+            ops.linear(x, w, out=coll.staging_view((M, N)))
+            return coll.all_reduce_staged((M, N))
         slot = self._rs_calls & 1
         self._rs_calls += 1
         self.C.tp_gemm_rs(x, w, self.rank, self.peers, self.layout, None, residual, 1, slot, self.timeout_ns, config, self.status)

@@ -118,6 +118,23 @@ def main():
     ops.check_status(dev)
     progress("graph replay")
 
+    # ---- the two-launch form: GEMM writing into the all-reduce kernel's input buffer, one-shot and two-shot ----
+    comm.ar_mode = "split"
+    for i, M in enumerate([8, 64, 512, 2048]):
+        x = mk((M, k_local), 6500 + 10 * i + rank)
+        w = mk((hidden, k_local), 6600 + 10 * i + rank, 0.05)
+        want = x.float() @ w.float().t()
+        dist.all_reduce(want)
+        for rep in range(3):
+            close(comm.linear_all_reduce(x, w), want, f"split all-reduce M={M} rep={rep}")
+    comm.ar_mode = "auto"
+    rep = comm.tune_all_reduce(hidden, k_local, [16, 256, 1024])
+    assert set(rep) == {16, 256, 1024} and all(a > 0 and b > 0 for a, b in rep.values())
+    close(comm.linear_all_reduce(x, w), want, "all-reduce after tuning")
+    torch.cuda.synchronize()
+    ops.check_status(dev)
+    progress("split all-reduce")
+
     # ---- block-scaled fp8 GEMM -> all-reduce / reduce-scatter ----
     from mojo_b200.ops import reference
 
