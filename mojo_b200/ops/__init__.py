@@ -174,6 +174,18 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = Non
     return out
 
 
+def linear_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """y = x @ w.T on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles): the large-M form of `linear`."""
+    if not x.is_cuda:
+        return reference.linear(x, w, None).to(x.dtype)
+    C = _ext.require()
+    if out is None:
+        out = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
+    C.gemm_bf16_pair(x, w, out, _state.get(x.device).status)
+    _count()
+    return out
+
+
 def linear_swiglu(x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tensor | None = None, config: int = 0) -> torch.Tensor:
     """silu(x Wg^T) * (x Wu^T) in one GEMM; `w_gu` is the 16-row interleaved stack from
     `reference.interleave_gate_up`."""
