@@ -41,7 +41,20 @@ struct PairParams {
   int64_t ldy;
   int M, N, num_kb;
   int m_tiles, n_tiles;   // 256-row and 256-column tiles
+  int swiglu;             // 1: W rows alternate 16 gate / 16 up rows; y[M, N / 2] = silu(gate) * up
 };
+
+// Tile order: groups of 8 row tiles, column tiles varying slowest inside a group, so that the pairs running at the
+// same time share W tiles (8 pairs each) and X tiles through L2.
+__device__ __forceinline__ void pair_tile(const PairParams& p, int t, int& mt, int& nt) {
+  const int group_size = 8 * p.n_tiles;
+  const int group = t / group_size;
+  const int first = group * 8;
+  const int gm = min(p.m_tiles - first, 8);
+  const int r = t - group * group_size;
+  mt = first + r % gm;
+  nt = r / gm;
+}
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, PairParams p,
@@ -92,7 +105,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       long issued = 0;
       bool ok = true;
       for (int t = pair; ok && t < total; t += num_pairs) {
-        const int mt = t / p.n_tiles, nt = t % p.n_tiles;
+        int mt, nt;
+        pair_tile(p, t, mt, nt);
         const int row_x = mt * 256 + static_cast<int>(rank) * 128;
         const int row_w = nt * kPairBN + static_cast<int>(rank) * (kPairBN / 2);
         for (int kb = 0; kb < p.num_kb; ++kb) {
@@ -163,7 +177,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = pair; t < total; t += num_pairs) {
-      const int mt = t / p.n_tiles, nt = t % p.n_tiles;
+      int mt, nt;
+      pair_tile(p, t, mt, nt);
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(tmem_full(acc), acc_phase))) {
         if (lane == 0) status_record(status, kTimeout, kSiteGemmTmemFull, t, acc);
         break;
@@ -177,7 +192,24 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
         ptx::tmem_ld_32x32(taddr + c * 32, r);
         ptx::tc_wait_ld();
         const int n0 = nt * kPairBN + c * 32;
-        if (m < p.M) {
+        if (p.swiglu) {
+          // columns [n0, n0 + 16) are gate values, [n0 + 16, n0 + 32) the matching up values: 16 outputs
+          if (m < p.M && n0 < p.N) {
+            __nv_bfloat16* dst = p.y + static_cast<int64_t>(m) * p.ldy + (n0 >> 1);
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+              float o[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o[i] = ptx::silu(__uint_as_float(r[g * 8 + i])) * __uint_as_float(r[16 + g * 8 + i]);
+              uint4 pk;
+              pk.x = ptx::pack_bf16x2(o[0], o[1]);
+              pk.y = ptx::pack_bf16x2(o[2], o[3]);
+              pk.z = ptx::pack_bf16x2(o[4], o[5]);
+              pk.w = ptx::pack_bf16x2(o[6], o[7]);
+              ptx::st_v4(dst + g * 8, pk);
+            }
+          }
+        } else if (m < p.M) {
           __nv_bfloat16* dst = p.y + static_cast<int64_t>(m) * p.ldy + n0;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
@@ -213,12 +245,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
 
 using namespace b2;
 
-// Y = X W^T on CTA pairs. K a multiple of 8; N a multiple of 8; ldx, ldw, ldy multiples of 8 elements. Best for
+// Y = X W^T on CTA pairs (epilogue B2_EPI_NONE, or B2_EPI_SWIGLU with the 16-row interleaved gate/up weight and
+// y [M, N / 2]). K a multiple of 8; N a multiple of 8; ldx, ldw, ldy multiples of 8 elements. Best for
 // M >= 512 (tiles are 256 x 256); any M and N are accepted (edges are zero-filled on load and clipped on store).
 extern "C" int b2_gemm_bf16_pair(const void* x, const void* w, void* y, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldy,
-                                 Status* status, cudaStream_t stream) {
+                                 int epilogue, Status* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || N % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ldy % 8 != 0) return -kBadArgument;
+  if (epilogue != B2_EPI_NONE && epilogue != B2_EPI_SWIGLU) return -kBadArgument;
+  if (epilogue == B2_EPI_SWIGLU && N % 32 != 0) return -kBadArgument;
   CUtensorMap tx, tw;
   if (!make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, M, K, ldx * 2, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B) ||
       !make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, N, K, ldw * 2, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
@@ -231,6 +266,7 @@ extern "C" int b2_gemm_bf16_pair(const void* x, const void* w, void* y, int M, i
   p.num_kb = (K + 63) / 64;
   p.m_tiles = (M + 255) / 256;
   p.n_tiles = (N + kPairBN - 1) / kPairBN;
+  p.swiglu = epilogue == B2_EPI_SWIGLU ? 1 : 0;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem) != cudaSuccess)

@@ -157,6 +157,18 @@ def copy_pages(cache: torch.Tensor, src_pages: torch.Tensor, dst_pages: torch.Te
     _count()
 
 
+PAIR_CONFIG = 1 << 28   # configuration word that selects the CTA-pair (cta_group::2) GEMM kernel
+
+
+def _launch_gemm(C, x, w, out, residual, epi, config, st) -> None:
+    """One bf16 GEMM launch: the CTA-pair kernel when `config` says so (plain and SwiGLU epilogues only), else the
+    single-CTA kernel family with `config` as its tile / split / layout word."""
+    if config & PAIR_CONFIG and residual is None and epi != EPI_ADD_RESIDUAL:
+        C.gemm_bf16_pair(x, w, out, epi, st.status)
+    else:
+        C.gemm_bf16(x, w, out, residual, epi, config & ~PAIR_CONFIG, st.gemm_ws, st.status)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
            config: int = 0) -> torch.Tensor:
     """y = x @ w.T (+ residual) on the tcgen05 GEMM. x [M, K], w [N, K], both bf16."""
@@ -169,21 +181,14 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = Non
     epi = EPI_ADD_RESIDUAL if residual is not None else EPI_NONE
     if config == 0:
         config = autotune.lookup(x.shape[0], w.shape[0], w.shape[1], epi, x.device.index or 0)
-    C.gemm_bf16(x, w, out, residual, epi, config, st.gemm_ws, st.status)
+    _launch_gemm(C, x, w, out, residual, epi, config, st)
     _count()
     return out
 
 
 def linear_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """y = x @ w.T on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles): the large-M form of `linear`."""
-    if not x.is_cuda:
-        return reference.linear(x, w, None).to(x.dtype)
-    C = _ext.require()
-    if out is None:
-        out = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
-    C.gemm_bf16_pair(x, w, out, _state.get(x.device).status)
-    _count()
-    return out
+    return linear(x, w, out=out, config=PAIR_CONFIG)
 
 
 def linear_swiglu(x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tensor | None = None, config: int = 0) -> torch.Tensor:
@@ -197,7 +202,7 @@ def linear_swiglu(x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tensor | None 
         out = torch.empty(x.shape[0], w_gu.shape[0] // 2, dtype=x.dtype, device=x.device)
     if config == 0:
         config = autotune.lookup(x.shape[0], w_gu.shape[0], w_gu.shape[1], EPI_SWIGLU, x.device.index or 0)
-    C.gemm_bf16(x, w_gu, out, None, EPI_SWIGLU, config, st.gemm_ws, st.status)
+    _launch_gemm(C, x, w_gu, out, None, EPI_SWIGLU, config, st)
     _count()
     return out
 

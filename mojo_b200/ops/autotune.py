@@ -15,6 +15,7 @@ import bisect
 import torch
 
 EPI_NONE, EPI_ADD_RESIDUAL, EPI_SWIGLU = 0, 1, 2
+PAIR_CONFIG = 1 << 28
 L2_BYTES = 126 << 20
 
 # (N, K, epilogue, device index) -> (sorted list of bucket upper bounds, configs)
@@ -29,6 +30,8 @@ def _encode(swap: bool, bn: int, splits: int = 1, stream_k: bool = False) -> int
 def describe(config: int) -> str:
     if config == 0:
         return "auto"
+    if config & PAIR_CONFIG:
+        return "CTA pair 256x256"
     return f"{'swap' if (config >> 30) & 1 else 'normal'} bn={config & 0xffff} splits={(config >> 16) & 0xff}" + (" stream-k" if (config >> 29) & 1 else "")
 
 
@@ -60,6 +63,8 @@ def candidates(M: int, N: int, K: int, epilogue: int) -> list[int]:
                 if sp > 1 and (num_kb // sp < 4 or not ws_ok(tiles, sp, bn) or tiles * sp > 4 * 148):
                     continue
                 out.append(_encode(False, bn, sp))
+    if M >= 384 and N >= 256 and N % 8 == 0 and epilogue != EPI_ADD_RESIDUAL:
+        out.append(PAIR_CONFIG)   # 256 x 256 tiles on CTA pairs
     return out
 
 
@@ -78,6 +83,7 @@ def tune(N: int, K: int, epilogue: int, token_counts, device=None, iters: int = 
     """Time all candidates for weight shape [N, K] at each token count; fill the lookup table. Returns
     {M: (config, microseconds, microseconds of the analytic rule's choice)}."""
     from .. import _ext
+    from . import _launch_gemm as _launch
     from . import _state
 
     C = _ext.require()
@@ -100,7 +106,7 @@ def tune(N: int, K: int, epilogue: int, token_counts, device=None, iters: int = 
         def run(cfg):
             w = ws[turn[0] % len(ws)]
             turn[0] += 1
-            C.gemm_bf16(x, w, y, res, epilogue, cfg, st.gemm_ws, st.status)
+            _launch(C, x, w, y, res, epilogue, cfg, st)
 
         best_cfg, best_t = 0, _time(lambda: run(0), iters)
         t_auto = best_t

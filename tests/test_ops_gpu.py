@@ -359,6 +359,24 @@ def test_status_word_reports_bad_index():
     ops.check_status()  # cleared
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 1024), (1000, 1280, 2048), (300, 520, 200), (2048, 4096, 4096)])
+def test_gemm_cta_pair(M, N, K):
+    """tcgen05 cta_group::2: two CTAs per 256 x 256 tile; edges clipped in M and N, K tail zero-filled."""
+    _gemm_case(M, N, K, config=ops.PAIR_CONFIG)
+    _gemm_case(M, N, K, config=ops.PAIR_CONFIG, seed=1)
+
+
+def test_gemm_cta_pair_swiglu():
+    g = torch.Generator().manual_seed(4)
+    M, K, F = 700, 1024, 1408
+    x = torch.randn(M, K, generator=g).bfloat16()
+    wg = (torch.randn(F, K, generator=g) * 0.05).bfloat16()
+    wu = (torch.randn(F, K, generator=g) * 0.05).bfloat16()
+    y_ref = ref.swiglu(torch.cat([ref.linear(x, wg), ref.linear(x, wu)], dim=1))
+    y = ops.linear_swiglu(x.to(DEV), ref.interleave_gate_up(wg, wu).to(DEV), config=ops.PAIR_CONFIG)
+    _close(y, y_ref, 5e-2, 3e-2)
+
+
 def test_gemm_autotune_table_picks_valid_faster_or_equal_configs():
     """The measured table only ever holds configurations the kernel accepts, and looking one up gives the same
     numbers as the analytic rule's choice."""
