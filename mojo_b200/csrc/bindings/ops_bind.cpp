@@ -183,14 +183,14 @@ void attn_prefill(const at::Tensor& q, const at::Tensor& k_cache, const at::Tens
         "attn_prefill");
 }
 
-void gemm_bf16_pair(const at::Tensor& x, const at::Tensor& w, at::Tensor& y, int64_t epilogue, c10::optional<at::Tensor> status) {
+void gemm_bf16_pair(const at::Tensor& x, const at::Tensor& w, at::Tensor& y, int64_t epilogue, int64_t bn, c10::optional<at::Tensor> status) {
   need(x.is_cuda() && is_bf16(x) && is_bf16(w) && is_bf16(y) && x.dim() == 2 && w.dim() == 2 && y.dim() == 2, "gemm_bf16_pair: 2-D CUDA bf16 tensors");
   need(x.stride(1) == 1 && w.stride(1) == 1 && y.stride(1) == 1 && x.size(1) == w.size(1) && y.size(0) == x.size(0) &&
            y.size(1) == (epilogue == B2_EPI_SWIGLU ? w.size(0) / 2 : w.size(0)),
        "gemm_bf16_pair: x [M, K], w [N, K], y [M, N] (or [M, N / 2] with the SwiGLU epilogue), unit inner strides");
   c10::cuda::CUDAGuard g(x.device());
   check(b2_gemm_bf16_pair(x.data_ptr(), w.data_ptr(), y.data_ptr(), static_cast<int>(x.size(0)), static_cast<int>(w.size(0)),
-                          static_cast<int>(x.size(1)), x.stride(0), w.stride(0), y.stride(0), static_cast<int>(epilogue), status_ptr(status), cur_stream()),
+                          static_cast<int>(x.size(1)), x.stride(0), w.stride(0), y.stride(0), static_cast<int>(epilogue), static_cast<int>(bn), status_ptr(status), cur_stream()),
         "gemm_bf16_pair");
 }
 
@@ -298,7 +298,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_prefill", &attn_prefill, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("out"), py::arg("cu_q"),
         py::arg("ctx_lens"), py::arg("block_tables"), py::arg("head_dim"), py::arg("max_q_len"), py::arg("scale"),
         py::arg("status") = py::none());
-  m.def("gemm_bf16_pair", &gemm_bf16_pair, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("epilogue") = 0, py::arg("status") = py::none());
+  m.def("gemm_bf16_pair", &gemm_bf16_pair, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("epilogue") = 0, py::arg("bn") = 256, py::arg("status") = py::none());
   m.def("attn_prefill_tc", &attn_prefill_tc, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("out"), py::arg("cu_q"),
         py::arg("ctx_lens"), py::arg("block_tables"), py::arg("max_q_len"), py::arg("scale"), py::arg("variant") = 0,
         py::arg("status") = py::none());

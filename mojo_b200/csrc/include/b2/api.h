@@ -65,7 +65,7 @@ int b2_attn_prefill_bf16(const void* q, const void* k_cache, const void* v_cache
                          int64_t out_stride, int64_t num_pages, b2::Status* status, cudaStream_t stream);
 // bf16 GEMM on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles; csrc/kernels/gemm_bf16_pair.cu). Epilogue NONE or SWIGLU.
 int b2_gemm_bf16_pair(const void* x, const void* w, void* y, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldy,
-                      int epilogue, b2::Status* status, cudaStream_t stream);
+                      int epilogue, int bn, b2::Status* status, cudaStream_t stream);
 // The same attention on tcgen05 / TMEM (csrc/kernels/attention_tc.cu): head_dim 128 and page_size 128 only.
 // q_rows = rows of the q matrix (for the tensor map); variant = descriptor variant of the V operand (0 = default).
 int b2_attn_prefill_tc_bf16(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* cu_q,

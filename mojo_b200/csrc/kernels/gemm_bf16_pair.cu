@@ -28,13 +28,18 @@ namespace b2 {
 namespace {
 
 constexpr int kPairThreads = 192;
-constexpr int kPairBN = 256;                    // UMMA N of the pair; each CTA stages kPairBN / 2 rows of W
-constexpr int kPairStages = 6;
-constexpr int kPairABytes = 128 * 64 * 2;       // 16 KB
-constexpr int kPairStageBytes = 2 * kPairABytes;  // A half + B half
-constexpr int kPairRing = kPairStages * kPairStageBytes;   // 192 KB
-constexpr int kPairBars = 2 * kPairStages + 4;  // full, empty, tmem_full[2], tmem_empty[2]
-constexpr int kPairSmem = kPairRing + 8 * kPairBars + 16 + 1024;
+constexpr int kPairABytes = 128 * 64 * 2;       // 16 KB: this CTA's 128 rows of X for one k-block
+// BN = UMMA N of the pair (256 or 128); each CTA stages BN / 2 rows of W per k-block.
+template <int BN>
+struct PairCfg {
+  static constexpr int kBBytes = (BN / 2) * 64 * 2;
+  static constexpr int kStageBytes = kPairABytes + kBBytes;
+  static constexpr int kStages = (192 * 1024) / kStageBytes;          // 6 (BN 256) or 8 (BN 128)
+  static constexpr int kRing = kStages * kStageBytes;
+  static constexpr int kBars = 2 * kStages + 4;                        // full, empty, tmem_full[2], tmem_empty[2]
+  static constexpr int kSmem = kRing + 8 * kBars + 16 + 1024;
+  static constexpr int kTmemCols = 2 * BN;                             // two accumulators
+};
 
 struct PairParams {
   __nv_bfloat16* y;
@@ -56,9 +61,16 @@ __device__ __forceinline__ void pair_tile(const PairParams& p, int t, int& mt, i
   nt = r / gm;
 }
 
+template <int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, PairParams p,
                       Status* status) {
+  using Cfg = PairCfg<BN>;
+  constexpr int kPairBN = BN;
+  constexpr int kPairStages = Cfg::kStages;
+  constexpr int kPairStageBytes = Cfg::kStageBytes;
+  constexpr int kPairRing = Cfg::kRing;
+  constexpr int kPairBars = Cfg::kBars;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - ptx::smem_u32(smem_raw));
@@ -88,7 +100,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
     ptx::fence_mbar_init();
   }
   if (warp == 1) {
-    ptx::tmem_alloc_pair(ptx::smem_u32(holder), 512);
+    ptx::tmem_alloc_pair(ptx::smem_u32(holder), Cfg::kTmemCols);
     ptx::tmem_relinquish_pair();
   }
   ptx::tc_fence_before();
@@ -236,27 +248,17 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   ptx::cluster_sync();   // neither CTA frees TMEM or leaves while the other may still read its shared memory / TMEM
   if (warp == 1) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc_pair(tmem_base, 512);
+    ptx::tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
   }
 }
 
-}  // namespace
-}  // namespace b2
-
-using namespace b2;
-
-// Y = X W^T on CTA pairs (epilogue B2_EPI_NONE, or B2_EPI_SWIGLU with the 16-row interleaved gate/up weight and
-// y [M, N / 2]). K a multiple of 8; N a multiple of 8; ldx, ldw, ldy multiples of 8 elements. Best for
-// M >= 512 (tiles are 256 x 256); any M and N are accepted (edges are zero-filled on load and clipped on store).
-extern "C" int b2_gemm_bf16_pair(const void* x, const void* w, void* y, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldy,
-                                 int epilogue, Status* status, cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || K % 8 != 0 || N % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ldy % 8 != 0) return -kBadArgument;
-  if (epilogue != B2_EPI_NONE && epilogue != B2_EPI_SWIGLU) return -kBadArgument;
-  if (epilogue == B2_EPI_SWIGLU && N % 32 != 0) return -kBadArgument;
+template <int BN>
+int launch_pair(const void* x, const void* w, void* y, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldy, int epilogue,
+                Status* status, cudaStream_t stream) {
+  using Cfg = PairCfg<BN>;
   CUtensorMap tx, tw;
   if (!make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, M, K, ldx * 2, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B) ||
-      !make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, N, K, ldw * 2, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+      !make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, N, K, ldw * 2, BN / 2, 64, CU_TENSOR_MAP_SWIZZLE_128B))
     return -kBadArgument;
   PairParams p{};
   p.y = static_cast<__nv_bfloat16*>(y);
@@ -265,16 +267,35 @@ extern "C" int b2_gemm_bf16_pair(const void* x, const void* w, void* y, int M, i
   p.N = N;
   p.num_kb = (K + 63) / 64;
   p.m_tiles = (M + 255) / 256;
-  p.n_tiles = (N + kPairBN - 1) / kPairBN;
+  p.n_tiles = (N + BN - 1) / BN;
   p.swiglu = epilogue == B2_EPI_SWIGLU ? 1 : 0;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_bf16_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem) != cudaSuccess)
       return -kBadArgument;
     attr_set = true;
   }
   const int total = p.m_tiles * p.n_tiles;
   const int pairs = total < kNumSMs / 2 ? total : kNumSMs / 2;
-  gemm_bf16_pair_kernel<<<2 * pairs, kPairThreads, kPairSmem, stream>>>(tx, tw, p, status);
+  gemm_bf16_pair_kernel<BN><<<2 * pairs, kPairThreads, Cfg::kSmem, stream>>>(tx, tw, p, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+}
+
+}  // namespace
+}  // namespace b2
+
+using namespace b2;
+
+// Y = X W^T on CTA pairs (epilogue B2_EPI_NONE, or B2_EPI_SWIGLU with the 16-row interleaved gate/up weight and
+// y [M, N / 2]); tiles of 256 rows x `bn` columns, bn = 256 or 128. K a multiple of 8; N a multiple of 8; ldx, ldw,
+// ldy multiples of 8 elements. Any M and N are accepted (edges are zero-filled on load and clipped on store).
+extern "C" int b2_gemm_bf16_pair(const void* x, const void* w, void* y, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldy,
+                                 int epilogue, int bn, Status* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 != 0 || N % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ldy % 8 != 0) return -kBadArgument;
+  if (epilogue != B2_EPI_NONE && epilogue != B2_EPI_SWIGLU) return -kBadArgument;
+  if (epilogue == B2_EPI_SWIGLU && N % 32 != 0) return -kBadArgument;
+  if (bn == 128) return launch_pair<128>(x, w, y, M, N, K, ldx, ldw, ldy, epilogue, status, stream);
+  if (bn == 0 || bn == 256) return launch_pair<256>(x, w, y, M, N, K, ldx, ldw, ldy, epilogue, status, stream);
+  return -kBadArgument;
 }

@@ -157,14 +157,14 @@ def copy_pages(cache: torch.Tensor, src_pages: torch.Tensor, dst_pages: torch.Te
     _count()
 
 
-PAIR_CONFIG = 1 << 28   # configuration word that selects the CTA-pair (cta_group::2) GEMM kernel
+PAIR_CONFIG = 1 << 28   # configuration word that selects the CTA-pair (cta_group::2) GEMM kernel; low bits = tile width (256 default, 128)
 
 
 def _launch_gemm(C, x, w, out, residual, epi, config, st) -> None:
     """One bf16 GEMM launch: the CTA-pair kernel when `config` says so (plain and SwiGLU epilogues only), else the
     single-CTA kernel family with `config` as its tile / split / layout word."""
     if config & PAIR_CONFIG and residual is None and epi != EPI_ADD_RESIDUAL:
-        C.gemm_bf16_pair(x, w, out, epi, st.status)
+        C.gemm_bf16_pair(x, w, out, epi, (config & 0xffff) or 256, st.status)
     else:
         C.gemm_bf16(x, w, out, residual, epi, config & ~PAIR_CONFIG, st.gemm_ws, st.status)
 

@@ -31,7 +31,7 @@ def describe(config: int) -> str:
     if config == 0:
         return "auto"
     if config & PAIR_CONFIG:
-        return "CTA pair 256x256"
+        return f"CTA pair 256x{(config & 0xffff) or 256}"
     return f"{'swap' if (config >> 30) & 1 else 'normal'} bn={config & 0xffff} splits={(config >> 16) & 0xff}" + (" stream-k" if (config >> 29) & 1 else "")
 
 
@@ -64,7 +64,8 @@ def candidates(M: int, N: int, K: int, epilogue: int) -> list[int]:
                     continue
                 out.append(_encode(False, bn, sp))
     if M >= 384 and N >= 256 and N % 8 == 0 and epilogue != EPI_ADD_RESIDUAL:
-        out.append(PAIR_CONFIG)   # 256 x 256 tiles on CTA pairs
+        out.append(PAIR_CONFIG | 256)   # 256 x 256 tiles on CTA pairs
+        out.append(PAIR_CONFIG | 128)   # 256 x 128
     return out
 
 
