@@ -50,6 +50,20 @@ void bind_coll(py::module_& m) {
                                         timeout_ns, status_ptr(status), cur_stream()),
                 "coll_all_reduce");
         });
+  m.def("coll_all_reduce_rmsnorm",
+        [](int rank, const std::vector<int64_t>& peers, const B2CollLayout& lay, c10::optional<at::Tensor> residual, const at::Tensor& weight,
+           at::Tensor& out, double eps, int slot, uint64_t timeout_ns, c10::optional<at::Tensor> status) {
+          const B2TpRegion reg = make_region(rank, peers);
+          need(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.is_contiguous() && out.dim() == 2, "coll_all_reduce_rmsnorm: out bf16 [rows, hidden]");
+          need(weight.scalar_type() == at::kBFloat16 && weight.is_contiguous() && weight.numel() == out.size(1), "coll_all_reduce_rmsnorm: weight bf16 [hidden]");
+          if (residual.has_value())
+            need(residual->scalar_type() == at::kBFloat16 && residual->is_contiguous() && residual->sizes() == out.sizes(), "coll_all_reduce_rmsnorm: residual bf16 [rows, hidden]");
+          c10::cuda::CUDAGuard g(out.device());
+          check(b2_coll_all_reduce_rmsnorm_bf16(&reg, &lay, residual.has_value() ? residual->data_ptr() : nullptr, weight.data_ptr(), out.data_ptr(),
+                                                static_cast<int>(out.size(0)), static_cast<int>(out.size(1)), static_cast<float>(eps), slot,
+                                                timeout_ns, status_ptr(status), cur_stream()),
+                "coll_all_reduce_rmsnorm");
+        });
   m.def("coll_reduce_scatter",
         [](int rank, const std::vector<int64_t>& peers, const B2CollLayout& lay, at::Tensor& out, int64_t n, int slot, uint64_t timeout_ns,
            c10::optional<at::Tensor> status) {

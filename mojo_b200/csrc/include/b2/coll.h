@@ -30,6 +30,11 @@ struct B2CollLayout {
 // it into every peer's `out` half; result is read there), 2 two-shot through the multicast mapping `mc_base`.
 int b2_coll_all_reduce_bf16(const struct B2TpRegion* reg, const struct B2CollLayout* lay, void* mc_base, void* out, int64_t n,
                             int algo, int slot, uint64_t timeout_ns, b2::Status* status, cudaStream_t stream);
+// One-shot all-reduce of the [rows, hidden] partials in `buf`, fused with the layer's residual add and RMSNorm:
+// residual (bf16 [rows, hidden], may be null) += bf16(sum); out = rmsnorm(residual) * weight. hidden <= 16384.
+int b2_coll_all_reduce_rmsnorm_bf16(const struct B2TpRegion* reg, const struct B2CollLayout* lay, void* residual, const void* weight,
+                                    void* out, int rows, int hidden, float eps, int slot, uint64_t timeout_ns, b2::Status* status,
+                                    cudaStream_t stream);
 // out = this rank's n / tp elements of the sum.
 int b2_coll_reduce_scatter_bf16(const struct B2TpRegion* reg, const struct B2CollLayout* lay, void* out, int64_t n, int slot,
                                 uint64_t timeout_ns, b2::Status* status, cudaStream_t stream);

@@ -112,6 +112,62 @@ __global__ void __launch_bounds__(kCollThreads) all_reduce_kernel(CollParams p, 
   tp::epoch_end(ectl, epoch);
 }
 
+// One-shot all-reduce fused with the residual add and the RMSNorm that follow it in a transformer layer:
+//   h = bf16(sum over ranks of the partial rows);  residual += h (stored in bf16);  out = rmsnorm(residual) * weight
+// One CTA per row at a time; the row stays in registers between the reduction and the scaling (VPT 16-byte
+// vectors per thread). Numerics match `all_reduce` followed by the rmsnorm kernel with a residual.
+template <int VPT>
+__global__ void __launch_bounds__(kCollThreads) all_reduce_rmsnorm_kernel(CollParams p, EpochCtl ectl, uint4* __restrict__ residual,
+                                                                          const uint4* __restrict__ weight, uint4* __restrict__ out, int rows,
+                                                                          int hidden, float eps, Status* status) {
+  __shared__ float scratch[33];
+  const uint32_t epoch = tp::epoch_begin(ectl);
+  const bool ok = arrive_and_wait(p, p.off_flags_a, epoch, blockIdx.x == 0, status);
+  const int nvec = hidden >> 3;
+  if (ok) {
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+      const int64_t base = static_cast<int64_t>(row) * nvec;
+      float v[VPT][8];
+      float ss = 0.0f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * kCollThreads;
+        if (c < nvec) {
+          bf16x8_to_f32(sum_peers(p, (base + c) * 16), v[i]);   // rounded to bf16 like the stand-alone all-reduce
+          if (residual != nullptr) {
+            float r[8];
+            bf16x8_to_f32(residual[base + c], r);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[i][j] += r[j];
+            const uint4 packed = f32_to_bf16x8(v[i]);
+            residual[base + c] = packed;                        // the stream is stored in bf16: normalise what is stored
+            bf16x8_to_f32(packed, v[i]);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
+        }
+      }
+      ss = block_sum(ss, scratch);
+      const float rstd = ptx::rsqrt(ss / static_cast<float>(hidden) + eps);
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * kCollThreads;
+        if (c < nvec) {
+          float w[8];
+          bf16x8_to_f32(weight[c], w);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] = v[i][j] * rstd * w[j];
+          out[base + c] = f32_to_bf16x8(v[i]);
+        }
+      }
+    }
+  }
+  tp::epoch_end(ectl, epoch);
+}
+
 __global__ void __launch_bounds__(kCollThreads) reduce_scatter_kernel(CollParams p, EpochCtl ectl, uint4* out, int64_t n_vec_per_rank,
                                                                       Status* status) {
   const uint32_t epoch = tp::epoch_begin(ectl);
@@ -248,6 +304,28 @@ extern "C" int b2_coll_all_reduce_bf16(const B2TpRegion* reg, const B2CollLayout
   if (algo == 0) all_reduce_kernel<0><<<grid, kCollThreads, 0, stream>>>(p, ectl, nullptr, static_cast<uint4*>(out), n_vec, status);
   else if (algo == 1) all_reduce_kernel<1><<<grid, kCollThreads, 0, stream>>>(p, ectl, nullptr, nullptr, n_vec, status);
   else all_reduce_kernel<2><<<grid, kCollThreads, 0, stream>>>(p, ectl, static_cast<uint8_t*>(mc_base), nullptr, n_vec, status);
+  return launched();
+}
+
+extern "C" int b2_coll_all_reduce_rmsnorm_bf16(const B2TpRegion* reg, const B2CollLayout* lay, void* residual, const void* weight,
+                                               void* out, int rows, int hidden, float eps, int slot, uint64_t timeout_ns,
+                                               Status* status, cudaStream_t stream) {
+  CollParams p{};
+  EpochCtl ectl{};
+  if (!fill(p, ectl, reg, lay, slot, timeout_ns) || rows <= 0 || hidden <= 0 || hidden % 8 != 0 || hidden > 8 * kCollThreads * 8 ||
+      weight == nullptr || out == nullptr)
+    return -kBadArgument;
+  if (static_cast<int64_t>(rows) * hidden * 2 > lay->buf_half_bytes) return -kTooLarge;
+  const int nvec = hidden / 8;
+  const int vpt = (nvec + kCollThreads - 1) / kCollThreads;
+  const int grid = rows < 4 * kNumSMs ? rows : 4 * kNumSMs;
+  uint4* res = static_cast<uint4*>(residual);
+  const uint4* w = static_cast<const uint4*>(weight);
+  uint4* o = static_cast<uint4*>(out);
+  if (vpt <= 1) all_reduce_rmsnorm_kernel<1><<<grid, kCollThreads, 0, stream>>>(p, ectl, res, w, o, rows, hidden, eps, status);
+  else if (vpt <= 2) all_reduce_rmsnorm_kernel<2><<<grid, kCollThreads, 0, stream>>>(p, ectl, res, w, o, rows, hidden, eps, status);
+  else if (vpt <= 4) all_reduce_rmsnorm_kernel<4><<<grid, kCollThreads, 0, stream>>>(p, ectl, res, w, o, rows, hidden, eps, status);
+  else all_reduce_rmsnorm_kernel<8><<<grid, kCollThreads, 0, stream>>>(p, ectl, res, w, o, rows, hidden, eps, status);
   return launched();
 }
 

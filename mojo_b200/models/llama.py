@@ -230,17 +230,31 @@ class LlamaModel:
         residual = None
         if cfg.quantization == "fp8_block":
             return self._forward_fp8(h, positions, slots, meta, kv_caches, sample_rows, greedy)
+        fuse_norm = hasattr(self.comm, "linear_all_reduce_norm") and self.tp > 1
+        x = None   # normed input of the next block when the previous all-reduce kernel already produced it
         for li, lw in enumerate(self.layers):
-            x, residual = ops.rms_norm(h, lw.attn_norm, cfg.rms_norm_eps, residual)
+            if x is None:
+                x, residual = ops.rms_norm(h, lw.attn_norm, cfg.rms_norm_eps, residual)
             qkv = ops.linear(x, lw.wqkv)
             q, k, v = qkv[:, :q_cols], qkv[:, q_cols:q_cols + kv_cols], qkv[:, q_cols + kv_cols:]
             kc, vc = kv_caches[li]
             ops.rope_kvwrite(q, k, v, self.cos_sin, positions, slots, kc, vc, d)
             attn = ops.paged_attention(q, kc, vc, meta, self.scale, d)
-            h = self.comm.linear_all_reduce(attn, lw.wo)
-            x, residual = ops.rms_norm(h, lw.mlp_norm, cfg.rms_norm_eps, residual)
+            if fuse_norm:
+                # all-reduce + residual add + the MLP norm in one kernel after the GEMM (decode-sized token counts)
+                x, residual = self.comm.linear_all_reduce_norm(attn, lw.wo, lw.mlp_norm, cfg.rms_norm_eps, residual)
+            else:
+                h = self.comm.linear_all_reduce(attn, lw.wo)
+                x, residual = ops.rms_norm(h, lw.mlp_norm, cfg.rms_norm_eps, residual)
             act = ops.linear_swiglu(x, lw.w_gu)
-            h = self.comm.linear_all_reduce(act, lw.w_down)
+            if fuse_norm:
+                next_norm = self.layers[li + 1].attn_norm if li + 1 < len(self.layers) else self.final_norm
+                x, residual = self.comm.linear_all_reduce_norm(act, lw.w_down, next_norm, cfg.rms_norm_eps, residual)
+            else:
+                h = self.comm.linear_all_reduce(act, lw.w_down)
+                x = None
+        if fuse_norm and self.layers:
+            return self._head(None, residual, sample_rows, greedy, normed=x)
         return self._head(h, residual, sample_rows, greedy)
 
     def _forward_sp(self, token_ids, positions, slots, meta, kv_caches, sample_rows, greedy=False):
@@ -313,11 +327,11 @@ class LlamaModel:
         lw = self.layers[0]
         return [(lw.wo.shape[0], lw.wo.shape[1]), (lw.w_down.shape[0], lw.w_down.shape[1])]
 
-    def _head(self, h, residual, sample_rows, greedy: bool):
-        """Final norm, row gather and the vocabulary-parallel LM head. `greedy` on a tensor-parallel communicator
-        that can merge arg-maxes returns int64 token ids instead of gathered logits."""
+    def _head(self, h, residual, sample_rows, greedy: bool, normed: torch.Tensor | None = None):
+        """Final norm (unless `normed` already holds it), row gather and the vocabulary-parallel LM head. `greedy`
+        on a tensor-parallel communicator that can merge arg-maxes returns int64 token ids instead of gathered logits."""
         cfg = self.cfg
-        x, _ = ops.rms_norm(h, self.final_norm, cfg.rms_norm_eps, residual)
+        x = normed if normed is not None else ops.rms_norm(h, self.final_norm, cfg.rms_norm_eps, residual)[0]
         if sample_rows is not None:
             x = ops.gather_rows(x, sample_rows)
         logits = ops.linear(x, self.lm_head)

@@ -103,6 +103,17 @@ class SymmCollectives:
             out = self.region.view(self.layout.off_out + slot * self.layout.out_half_bytes, (n,), torch.bfloat16)
         return out.view(*shape)
 
+    def all_reduce_rmsnorm_staged(self, shape, weight: torch.Tensor, eps: float, residual: torch.Tensor | None):
+        """One kernel for all-reduce + residual add + RMSNorm of the [rows, hidden] partials written into
+        `staging_view(shape)`: `residual` (bf16 [rows, hidden], updated in place; None = no residual) += sum;
+        returns (rmsnorm(residual) * weight, residual or the reduced rows)."""
+        rows, hidden = int(shape[0]), int(shape[1])
+        slot = self._slot()
+        out = torch.empty(rows, hidden, dtype=torch.bfloat16, device=self.info.device)
+        self.C.coll_all_reduce_rmsnorm(self.rank, self.peers, self.layout, residual, weight, out, eps, slot, self.timeout_ns, self.status)
+        ops._count()
+        return out, residual
+
     def all_reduce(self, x: torch.Tensor, algo: str = "auto") -> torch.Tensor:
         if self.world_size == 1:
             return x

@@ -137,6 +137,24 @@ class FusedTPComm:
         ops._count()
         return self.region.view(self.layout.off_yall + slot * self.layout.yall_half_bytes, (M, N), torch.bfloat16)
 
+    # largest reduction (bytes per rank) that goes through the one-shot all-reduce + residual + RMSNorm kernel
+    FUSED_NORM_MAX_BYTES = 4 << 20
+
+    def linear_all_reduce_norm(self, x: torch.Tensor, w: torch.Tensor, norm_weight: torch.Tensor, eps: float,
+                               residual: torch.Tensor):
+        """The row-parallel linear, its all-reduce, the residual add and the next RMSNorm:
+        residual += all_reduce(x @ w.T); returns (rmsnorm(residual) * norm_weight, residual). For decode-sized
+        token counts this is GEMM -> one kernel (all-reduce + add + norm); larger ones take `linear_all_reduce`
+        followed by the norm kernel."""
+        M, N = x.shape[0], w.shape[0]
+        if (self.world_size > 1 and self.ar_mode != "fused" and M * N * 2 <= self.FUSED_NORM_MAX_BYTES and N % 8 == 0 and N <= 16384
+                and M * N * 2 <= self._coll_bytes):
+            coll = self._collectives()
+            ops.linear(x, w, out=coll.staging_view((M, N)))
+            return coll.all_reduce_rmsnorm_staged((M, N), norm_weight, eps, residual)
+        h = self.linear_all_reduce(x, w)
+        return ops.rms_norm(h, norm_weight, eps, residual)
+
     def linear_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None, config: int = 0) -> torch.Tensor:
         """Rows [rank * M/tp, (rank+1) * M/tp) of reduce(x @ w.T) (+ residual rows of the same shard)."""
         M, N = x.shape[0], w.shape[0]

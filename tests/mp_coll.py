@@ -53,6 +53,26 @@ def main():
     torch.cuda.synchronize()
     ops.check_status(dev)
 
+    # all-reduce + residual add + RMSNorm in one kernel, against the separate ops
+    from mojo_b200.ops import reference
+
+    for i, (rows, hidden) in enumerate([(1, 512), (37, 4096), (256, 8192), (130, 1024)]):
+        part = mk((rows, hidden), 700 + 10 * i + rank)
+        res0 = mk((rows, hidden), 760 + i)
+        wn = mk((hidden,), 780 + i) * 0.1 + 1.0
+        want_sum = part.float().clone()
+        dist.all_reduce(want_sum)
+        h = want_sum.bfloat16()
+        want_x, want_res = reference.rms_norm(h.cpu(), wn.cpu(), 1e-5, res0.clone().cpu())
+        for rep in range(2):
+            res = res0.clone()
+            coll.staging_view((rows, hidden)).copy_(part)
+            x, res_out = coll.all_reduce_rmsnorm_staged((rows, hidden), wn, 1e-5, res)
+            torch.cuda.synchronize()
+            close(res_out, want_res.to(dev), f"fused all-reduce+norm residual {rows}x{hidden}")
+            close(x, want_x.to(dev), f"fused all-reduce+norm output {rows}x{hidden}")
+    ops.check_status(dev)
+
     # all-to-all with per-peer row counts (zero rows to some peers)
     max_rows, row = 64, 256
     for it in range(3):
