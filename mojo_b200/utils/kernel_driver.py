@@ -2,7 +2,8 @@
 
 Small, self-terminating workloads (inputs larger than the 126 MB L2, a few GB at most) meant to be wrapped by a
 profiler capture of one kernel; with `--time` the case is timed with CUDA events instead and one JSON line is printed.
-Cases: gemm_large, gemm_prefill, gemm_decode, gemm_swiglu, gemm_fp8, attn_decode, attn_prefill, mla_decode, rmsnorm, sampling.
+Cases: gemm_large, gemm_pair (the same product on CTA pairs), gemm_prefill, gemm_decode, gemm_swiglu, gemm_fp8,
+attn_decode, attn_prefill, mla_decode, rmsnorm, sampling.
 """
 from __future__ import annotations
 
@@ -24,15 +25,16 @@ def _case(name: str):
     def rnd(*shape, scale=1.0):
         return (torch.randn(*shape, generator=g, device=DEV) * scale).bfloat16()
 
-    if name in ("gemm_large", "gemm_prefill", "gemm_decode", "gemm_swiglu"):
-        M, N, K = {"gemm_large": (8192, 8192, 8192), "gemm_prefill": (4096, 6144, 4096), "gemm_decode": (64, 28672, 4096),
+    if name in ("gemm_large", "gemm_pair", "gemm_prefill", "gemm_decode", "gemm_swiglu"):
+        M, N, K = {"gemm_large": (8192, 8192, 8192), "gemm_pair": (8192, 8192, 8192), "gemm_prefill": (4096, 6144, 4096), "gemm_decode": (64, 28672, 4096),
                    "gemm_swiglu": (2048, 28672, 4096)}[name]
         x, w = rnd(M, K), rnd(N, K, scale=0.02)
         if name == "gemm_swiglu":
             y = torch.empty(M, N // 2, device=DEV, dtype=torch.bfloat16)
             return (lambda: ops.linear_swiglu(x, w, out=y)), 2.0 * M * N * K, (M * K + N * K + M * N // 2) * 2
         y = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
-        return (lambda: ops.linear(x, w, out=y)), 2.0 * M * N * K, (M * K + N * K + M * N) * 2
+        cfg = ops.PAIR_CONFIG if name == "gemm_pair" else 0
+        return (lambda: ops.linear(x, w, out=y, config=cfg)), 2.0 * M * N * K, (M * K + N * K + M * N) * 2
     if name == "gemm_fp8":
         M, N, K = 4096, 8192, 8192
         xq, xs = ops.quant_e4m3(rnd(M, K))
