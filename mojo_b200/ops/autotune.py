@@ -63,7 +63,7 @@ def candidates(M: int, N: int, K: int, epilogue: int) -> list[int]:
                 if sp > 1 and (num_kb // sp < 4 or not ws_ok(tiles, sp, bn) or tiles * sp > 4 * 148):
                     continue
                 out.append(_encode(False, bn, sp))
-    if M >= 384 and N >= 256 and N % 8 == 0 and epilogue != EPI_ADD_RESIDUAL:
+    if M >= 192 and N >= 256 and N % 8 == 0 and epilogue != EPI_ADD_RESIDUAL:
         out.append(PAIR_CONFIG | 256)   # 256 x 256 tiles on CTA pairs
         out.append(PAIR_CONFIG | 128)   # 256 x 128
     return out
