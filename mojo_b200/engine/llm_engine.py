@@ -16,6 +16,7 @@ import torch
 from .. import _ext, ops
 from ..models import build_model
 from ..models.config import ModelConfig
+from ..utils import trace
 
 
 @dataclass
@@ -178,7 +179,8 @@ class LLMEngine:
             self.skipped_launches += 1
             self.step_count += 1
             return []
-        batch = self.scheduler.step()
+        with trace.span("engine.schedule"):
+            batch = self.scheduler.step()
         if batch.num_seqs == 0:
             if self.cfg.lockstep and hasattr(self.model, "forward_idle"):
                 self.model.forward_idle()
@@ -188,7 +190,8 @@ class LLMEngine:
         states = [self.requests[int(r)] for r in sample_ids]
         if self.watchdog is not None:
             self.watchdog.begin_step()
-        tokens = self.runner.execute(batch, states, self.step_count)
+        with trace.span("engine.execute"):
+            tokens = self.runner.execute(batch, states, self.step_count)
         if self.watchdog is not None:
             self.watchdog.end_step(self.step_count)
         if self.heartbeat is not None:

@@ -128,3 +128,25 @@ def test_fp8_block_quantised_llama_runs_and_tracks_the_bf16_model():
     assert quant.layers[0].wqkv.dtype == torch.float8_e4m3fn and quant.layers[0].s_qkv.shape == (4, 2)
     rel = (a - b).norm() / a.norm()
     assert rel < 0.2, rel       # e4m3 keeps 3 mantissa bits on both operands; K = 256 averages little
+
+
+def test_trace_spans_and_request_timeline(monkeypatch):
+    from mojo_b200.utils import trace
+
+    monkeypatch.setattr(trace, "TRACE", True)
+    trace.reset()
+    eng = _engine() if "_engine" in globals() else None
+    if eng is None:
+        from mojo_b200.engine.llm_engine import EngineConfig, LLMEngine
+        from mojo_b200.models.config import tiny_llama
+
+        eng = LLMEngine(EngineConfig(model=tiny_llama(), device="cpu", dtype=torch.float32, page_size=16, num_pages=64, max_num_seqs=8,
+                                     max_num_batched_tokens=64, max_model_len=256))
+    from mojo_b200.engine.llm_engine import SamplingParams
+
+    eng.generate([[1, 2, 3], list(range(5, 30))], SamplingParams(max_tokens=5))
+    s = trace.summary()
+    assert s["engine.schedule"]["calls"] >= 5 and s["engine.execute"]["calls"] >= 5 and s["engine.execute"]["total_ms"] > 0
+    tl = trace.timeline(eng)
+    assert len(tl) == 2 and all(len(r["token_times_s"]) == 5 and r["ttft_s"] is not None and r["ttft_s"] >= 0 for r in tl)
+    trace.reset()
