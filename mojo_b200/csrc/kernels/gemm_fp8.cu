@@ -53,12 +53,19 @@ constexpr int kModeRs = 1;
 // to every peer chunk by chunk; the GEMM producer waits for the chunks a tile needs before its first load.
 constexpr int kModeAg = 2;
 
-template <int BN, int STAGES, int SLABS, bool SWAP, int MODE>
-__global__ void __launch_bounds__(kThreads, 1)
+// WG2 = true: eight promotion warps, two threads per accumulator row, each owning BN / 2 columns of every slab.
+// Two warps per scheduler hide each other's tcgen05.ld and FMA latency, which one warp per scheduler cannot
+// (measured: with four warps the tensor pipe idles 58 % of the time waiting for slabs to be promoted).
+template <int BN, int STAGES, int SLABS, bool SWAP, int MODE, bool WG2>
+__global__ void __launch_bounds__(WG2 ? kThreads + 128 : kThreads, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q, Fp8Params prm,
                 const __grid_constant__ tp::RsSched rs_sched, const __grid_constant__ Fp8Fused fz, Status* status) {
   constexpr bool RS = MODE == kModeRs;
   constexpr bool AG = MODE == kModeAg;
+  static_assert(!(RS && WG2), "the fused reduce-scatter epilogue is written for four epilogue warps");
+  static_assert(!WG2 || BN >= 64, "column halves must be whole tcgen05.ld chunks");
+  constexpr int NW = WG2 ? 8 : 4;            // promotion warps
+  constexpr int COLS = WG2 ? BN / 2 : BN;    // accumulator columns per thread
   tp::RsParams rs = fz.rs;
   tp::AgParams ag = fz.ag;
   const tp::EpochCtl ectl = fz.ectl;
@@ -94,7 +101,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
   constexpr int kPBytes = 128 * 128, kQBytes = BN * 128, kStageBytes = kPBytes + kQBytes;
   constexpr int kTmemCols = (SLABS * BN <= 32) ? 32 : (SLABS * BN <= 64) ? 64 : (SLABS * BN <= 128) ? 128 : (SLABS * BN <= 256) ? 256 : 512;
   constexpr int CH = BN >= 32 ? 32 : 16;
-  constexpr int kRingAndBarriers = STAGES * kStageBytes + (2 * STAGES + 2 * SLABS + 1) * 8 + 16 + 4 * BN * 4 + 1024 + 64;
+  constexpr int kRingAndBarriers = STAGES * kStageBytes + (2 * STAGES + 2 * SLABS + 1) * 8 + 16 + NW * BN * 4 + 1024 + 64;
   constexpr uint32_t idesc = ptx::make_idesc(0, 0, 128, BN);  // e4m3 x e4m3 -> f32
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -118,7 +125,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
     }
     for (int s = 0; s < SLABS; ++s) {
       ptx::mbar_init(slab_full(s), 1);
-      ptx::mbar_init(slab_empty(s), 4);
+      ptx::mbar_init(slab_empty(s), NW);
     }
     ptx::mbar_init(drain_bar, 1);
     ptx::fence_mbar_init();
@@ -214,15 +221,16 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
     // ---- promotion + epilogue warps ----
     const int quarter = warp & 3;
     const int p_local = quarter * 32 + lane;
+    const int col_base = WG2 ? ((warp - 2) >> 2) * COLS : 0;   // first accumulator column of this thread
     int slab = 0;
     uint32_t slab_phase = 0;
     bool ok = true;
     for (int w = my_cta; ok && w < total; w += n_ctas) {
       int pb, qb;
       tile_of(w, pb, qb);
-      float acc[BN];
+      float acc[COLS];
 #pragma unroll
-      for (int j = 0; j < BN; ++j) acc[j] = 0.0f;
+      for (int j = 0; j < COLS; ++j) acc[j] = 0.0f;
       const int row = pb * 128 + p_local;  // m (normal) or n (swapped)
       for (int kb = 0; kb < KB; ++kb) {
         // scale(s) for this k-block. With the fused all-gather the token scales of a tile arrive from peers and
@@ -238,7 +246,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
           } else {
             s_row = prm.sw[static_cast<int64_t>(pb) * KB + kb];  // 128 weight rows = one scale block
             // each warp stages the token scales it needs itself: no barrier that a failed warp could strand
-            float* cs = col_scale + quarter * BN;
+            float* cs = col_scale + (warp - 2) * BN;
             __syncwarp();
             for (int j = lane; j < BN; j += 32) {
               const int m = qb * BN + j;
@@ -258,17 +266,17 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
         ptx::tc_fence_after();
         const uint32_t taddr = tmem_base + slab * BN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll
-        for (int c = 0; c < BN / CH; ++c) {
+        for (int c = 0; c < COLS / CH; ++c) {
           uint32_t r[CH];
-          if constexpr (CH == 32) ptx::tmem_ld_32x32(taddr + c * CH, r);
-          else ptx::tmem_ld_32x16(taddr + c * CH, r);
+          if constexpr (CH == 32) ptx::tmem_ld_32x32(taddr + col_base + c * CH, r);
+          else ptx::tmem_ld_32x16(taddr + col_base + c * CH, r);
           ptx::tc_wait_ld();
           if constexpr (!SWAP) {
-            const float s = s_row * ((c * CH) < 128 ? s_blk0 : s_blk1);
+            const float s = s_row * ((col_base + c * CH) < 128 ? s_blk0 : s_blk1);
 #pragma unroll
             for (int j = 0; j < CH; ++j) acc[c * CH + j] = fmaf(__uint_as_float(r[j]), s, acc[c * CH + j]);
           } else {
-            const float* cs = col_scale + quarter * BN + c * CH;
+            const float* cs = col_scale + (warp - 2) * BN + col_base + c * CH;
 #pragma unroll
             for (int j = 0; j < CH; ++j) acc[c * CH + j] = fmaf(__uint_as_float(r[j]), s_row * cs[j], acc[c * CH + j]);
           }
@@ -296,10 +304,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
         });
       } else if constexpr (!SWAP) {
         if (row < prm.M) {
-          __nv_bfloat16* dst = prm.y + static_cast<int64_t>(row) * prm.ldy + qb * BN;
+          __nv_bfloat16* dst = prm.y + static_cast<int64_t>(row) * prm.ldy + qb * BN + col_base;
 #pragma unroll
-          for (int g = 0; g < BN / 8; ++g) {
-            if (qb * BN + g * 8 >= prm.N) break;
+          for (int g = 0; g < COLS / 8; ++g) {
+            if (qb * BN + col_base + g * 8 >= prm.N) break;
             uint4 pk;
             pk.x = ptx::pack_bf16x2(acc[g * 8 + 0], acc[g * 8 + 1]);
             pk.y = ptx::pack_bf16x2(acc[g * 8 + 2], acc[g * 8 + 3]);
@@ -311,8 +319,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
       } else {
         if (row < prm.N) {
 #pragma unroll
-          for (int j = 0; j < BN; ++j) {
-            const int m = qb * BN + j;
+          for (int j = 0; j < COLS; ++j) {
+            const int m = qb * BN + col_base + j;
             if (m >= prm.M) break;
             prm.y[static_cast<int64_t>(m) * prm.ldy + row] = __float2bfloat16(acc[j]);
           }
@@ -340,7 +348,8 @@ int launch_fp8(const void* xq, const float* xs, const void* wq, const float* ws,
   constexpr int kStageBytes = 128 * 128 + BN * 128;
   constexpr int STAGES = (190 * 1024 / kStageBytes) > 8 ? 8 : (190 * 1024 / kStageBytes);
   constexpr int SLABS = BN <= 128 ? 4 : 2;
-  constexpr int SMEM = STAGES * kStageBytes + (2 * STAGES + 2 * SLABS + 1) * 8 + 16 + 4 * BN * 4 + 1024 + 64;
+  constexpr bool WG2 = BN >= 64;
+  constexpr int SMEM = STAGES * kStageBytes + (2 * STAGES + 2 * SLABS + 1) * 8 + 16 + (WG2 ? 8 : 4) * BN * 4 + 1024 + 64;
   const void* p_ptr = SWAP ? wq : xq;
   const void* q_ptr = SWAP ? xq : wq;
   const int rows_p = SWAP ? N : M, rows_q = SWAP ? M : N;
@@ -358,7 +367,7 @@ int launch_fp8(const void* xq, const float* xs, const void* wq, const float* ws,
   prm.KB = K / 128;
   prm.p_blocks = (rows_p + 127) / 128;
   prm.q_blocks = (rows_q + BN - 1) / BN;
-  auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP, kModePlain>;
+  auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP, kModePlain, WG2>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
@@ -367,7 +376,7 @@ int launch_fp8(const void* xq, const float* xs, const void* wq, const float* ws,
   const int total = prm.p_blocks * prm.q_blocks;
   static const tp::RsSched no_sched{};
   static const Fp8Fused no_fused{};
-  kern<<<total < kNumSMs ? total : kNumSMs, kThreads, SMEM, stream>>>(tp, tq, prm, no_sched, no_fused, status);
+  kern<<<total < kNumSMs ? total : kNumSMs, WG2 ? kThreads + 128 : kThreads, SMEM, stream>>>(tp, tq, prm, no_sched, no_fused, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
 }
 
@@ -404,7 +413,7 @@ int launch_fp8_rs(const void* xq, const float* xs, const void* wq, const float* 
   if (!tp::build_rs_order(sched, rs.tp, rs.rank, rs.R, TM)) return -kTooLarge;
   rs.p_blocks = prm.p_blocks;
   rs.q_blocks = prm.q_blocks;
-  auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP, kModeRs>;
+  auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP, kModeRs, false>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
@@ -427,7 +436,8 @@ int launch_fp8_ag(const void* xq_all, const float* xs_all, const void* wq, const
   constexpr int kStageBytes = 128 * 128 + BN * 128;
   constexpr int STAGES = (190 * 1024 / kStageBytes) > 8 ? 8 : (190 * 1024 / kStageBytes);
   constexpr int SLABS = BN <= 128 ? 4 : 2;
-  constexpr int SMEM_GEMM = STAGES * kStageBytes + (2 * STAGES + 2 * SLABS + 1) * 8 + 16 + 4 * BN * 4 + 1024 + 64;
+  constexpr bool WG2 = BN >= 64;
+  constexpr int SMEM_GEMM = STAGES * kStageBytes + (2 * STAGES + 2 * SLABS + 1) * 8 + 16 + (WG2 ? 8 : 4) * BN * 4 + 1024 + 64;
   constexpr int SMEM_COMM = tp::kAgRingBytes + 64 + 128;
   constexpr int SMEM = SMEM_GEMM > SMEM_COMM ? SMEM_GEMM : SMEM_COMM;
   const void* p_ptr = SWAP ? wq : xq_all;
@@ -462,14 +472,14 @@ int launch_fp8_ag(const void* xq_all, const float* xs_all, const void* wq, const
   int n_gemm = kNumSMs - ag.n_comm;
   if (total < n_gemm) n_gemm = total;
   fz.n_gemm = n_gemm;
-  auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP, kModeAg>;
+  auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP, kModeAg, WG2>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
     attr_set = true;
   }
   static const tp::RsSched no_sched{};
-  kern<<<n_gemm + ag.n_comm, kThreads, SMEM, stream>>>(tmp, tmq, prm, no_sched, fz, status);
+  kern<<<n_gemm + ag.n_comm, WG2 ? kThreads + 128 : kThreads, SMEM, stream>>>(tmp, tmq, prm, no_sched, fz, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
 }
 
