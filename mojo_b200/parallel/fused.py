@@ -176,6 +176,11 @@ class FusedTPComm:
         if self.world_size == 1:
             y = ops.linear_fp8((xq, xs), w_q, w_scale)
             return y if residual is None else y + residual
+        if (residual is None and self.ar_mode != "fused" and (M * N) % (8 * self.world_size) == 0 and M * N * 2 <= self._coll_bytes):
+            # two launches: the fp8 GEMM writes straight into the input buffer of the symmetric-memory all-reduce kernel
+            coll = self._collectives()
+            ops.linear_fp8((xq, xs), w_q, w_scale, out=coll.staging_view((M, N)))
+            return coll.all_reduce_staged((M, N))
         slot = self._rs_calls & 1
         self._rs_calls += 1
         self.C.tp_gemm_rs_fp8(xq, xs, w_q, w_scale, self.rank, self.peers, self.layout, None, residual, 1, slot, self.timeout_ns, self.status)
