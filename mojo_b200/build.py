@@ -137,13 +137,34 @@ def build(verbose: bool = False, assert_mode: int = 2, ptxas_info: bool = False,
         print(f"[mojo_b200.build] {len(tasks)} kernel/runtime objects, {len(b_tasks)} binding objects rebuilt in {time.time() - t0:.1f}s")
 
 
+def build_selftest(sanitizer: str = "address", out_dir: Path | None = None, verbose: bool = False) -> Path:
+    """Compile the host runtime with its self-test driver (`csrc/tests/runtime_selftest.cpp`) into one executable
+    under a host sanitizer: "address" (AddressSanitizer + UBSan), "thread" (ThreadSanitizer) or "" (none).
+    The device code cannot run under a sanitizer on every machine, so the CPU-only job runs the host side that
+    computes block tables, slots and schedules under one. Returns the path of the executable."""
+    out_dir = Path(out_dir) if out_dir is not None else OBJ
+    out_dir.mkdir(parents=True, exist_ok=True)
+    exe = out_dir / f"runtime_selftest_{sanitizer or 'plain'}"
+    flags = {"address": ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined", "-fno-omit-frame-pointer"],
+             "thread": ["-fsanitize=thread"], "": []}[sanitizer]
+    srcs = [CSRC / "tests" / "runtime_selftest.cpp", CSRC / "runtime" / "kv_manager.cpp", CSRC / "runtime" / "scheduler.cpp",
+            CSRC / "runtime" / "symm_sim.cpp"]
+    _run(["g++", "-std=c++17", "-O1", "-g", *flags, f"-I{CSRC / 'include'}", *[str(x) for x in srcs], "-o", str(exe), "-pthread"], verbose)
+    return exe
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("-v", "--verbose", action="store_true")
     ap.add_argument("--assert-mode", type=int, default=2, help="0 none, 1 warn, 2 safe, 3 all")
     ap.add_argument("--ptxas-info", action="store_true", help="print registers / spills / smem per kernel")
     ap.add_argument("--clean", action="store_true")
+    ap.add_argument("--selftest", choices=["address", "thread", "plain"], default=None,
+                    help="build the host runtime self-test under this sanitizer, run it and exit with its code")
     a = ap.parse_args()
+    if a.selftest is not None:
+        exe = build_selftest("" if a.selftest == "plain" else a.selftest, verbose=a.verbose)
+        sys.exit(subprocess.run([str(exe)]).returncode)
     if a.clean and OBJ.exists():
         shutil.rmtree(OBJ)
     build(verbose=a.verbose, assert_mode=a.assert_mode, ptxas_info=a.ptxas_info)

@@ -116,8 +116,10 @@ class DeepseekV2Model:
 
     # ------------------------------------------------------------------------------------------------
     def allocate_kv_cache(self, num_pages: int, page_size: int):
-        return [torch.zeros(num_pages, page_size, self.lora + self.rope, dtype=self.dtype, device=self.device)
-                for _ in range(self.cfg.num_layers)]
+        from ..utils import guard
+
+        return [guard.zeros((num_pages, page_size, self.lora + self.rope), self.dtype, self.device, f"latent cache, layer {i}")
+                for i in range(self.cfg.num_layers)]
 
     def kv_bytes_per_page(self, page_size: int) -> int:
         return self.cfg.num_layers * page_size * (self.lora + self.rope) * torch.empty((), dtype=self.dtype).element_size()

@@ -206,9 +206,11 @@ class LlamaModel:
     # KV cache
     # ------------------------------------------------------------------------------------------------
     def allocate_kv_cache(self, num_pages: int, page_size: int):
+        from ..utils import guard
+
         shape = (num_pages, self.n_kv, page_size, self.head_dim)
-        return [(torch.zeros(shape, dtype=self.dtype, device=self.device), torch.zeros(shape, dtype=self.dtype, device=self.device))
-                for _ in range(self.cfg.num_layers)]
+        return [(guard.zeros(shape, self.dtype, self.device, f"K cache, layer {i}"), guard.zeros(shape, self.dtype, self.device, f"V cache, layer {i}"))
+                for i in range(self.cfg.num_layers)]
 
     def kv_bytes_per_page(self, page_size: int) -> int:
         esz = torch.empty((), dtype=self.dtype).element_size()

@@ -20,7 +20,12 @@ def _align(n: int, a: int = 1024) -> int:
 
 class SymmRegion:
     """`nbytes` of zero-initialised symmetric memory. `ptrs[r]` is the address of rank r's copy as seen from
-    this process; `local` is a uint8 tensor over this rank's copy."""
+    this process; `local` is a uint8 tensor over this rank's copy. A band of `GUARD_BYTES` of a known pattern
+    follows the region in the same allocation: a local or peer write past `nbytes` lands there and
+    `check_guard()` counts it."""
+
+    GUARD_BYTES = 4096
+    GUARD_PATTERN = 0xA5
 
     def __init__(self, nbytes: int, info: DistInfo):
         self.info = info
@@ -30,22 +35,30 @@ class SymmRegion:
         if info.device.type != "cuda":
             raise RuntimeError("SymmRegion needs CUDA; use CpuSymmRegion for host-side protocol tests")
         if info.world_size == 1:
-            self.local = torch.zeros(self.nbytes, dtype=torch.uint8, device=info.device)
+            self._raw = torch.zeros(self.nbytes + self.GUARD_BYTES, dtype=torch.uint8, device=info.device)
+            self._raw[self.nbytes:].fill_(self.GUARD_PATTERN)
+            self.local = self._raw[: self.nbytes]
             self.ptrs = [self.local.data_ptr()]
             return
         import torch.distributed._symmetric_memory as symm_mem
 
         group = info.group
-        self.local = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=info.device)
-        self._hdl = symm_mem.rendezvous(self.local, group=group.group_name)
+        self._raw = symm_mem.empty(self.nbytes + self.GUARD_BYTES, dtype=torch.uint8, device=info.device)
+        self._hdl = symm_mem.rendezvous(self._raw, group=group.group_name)
+        self.local = self._raw[: self.nbytes]
         self.ptrs = [int(p) for p in self._hdl.buffer_ptrs]
         try:
             self.mc_ptr = int(self._hdl.multicast_ptr or 0)
         except Exception:  # noqa: BLE001
             self.mc_ptr = 0
         self.local.zero_()
+        self._raw[self.nbytes:].fill_(self.GUARD_PATTERN)
         torch.cuda.synchronize(info.device)
         dist.barrier(group=group)
+
+    def check_guard(self) -> int:
+        """Number of bytes of the band after the region that no longer hold the pattern (0 = nothing wrote past the end)."""
+        return int((self._raw[self.nbytes:] != self.GUARD_PATTERN).sum().item())
 
     def view(self, offset: int, shape, dtype: torch.dtype) -> torch.Tensor:
         n = int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()

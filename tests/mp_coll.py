@@ -132,6 +132,10 @@ def main():
     close(b, want_b, "graph chained all_reduce")
     ops.check_status(dev)
 
+    # nothing, local or from a peer, may have written past the end of the symmetric region
+    torch.cuda.synchronize()
+    dist.barrier()
+    assert coll.region.check_guard() == 0, f"rank {rank}: {coll.region.check_guard()} byte(s) of the guard band after the symmetric region were overwritten"
     dist.barrier()
     if rank == 0:
         print(f"COLL_OK {tp}", flush=True)

@@ -39,6 +39,10 @@ def main():
             want = ref.moe_forward(x, torch.cat([wg, wu], dim=1), wd, w_ref, id_ref) + shared.float()
             err = (got.float().cpu() - want).abs().max().item()
             assert err <= 0.03 * want.abs().max().item() + 0.03, f"rank {rank} iter {it}: err {err}"
+    # nothing, local or from a peer, may have written past the end of the symmetric region
+    torch.cuda.synchronize()
+    dist.barrier()
+    assert ep.region.check_guard() == 0, f"rank {rank}: {ep.region.check_guard()} byte(s) of the guard band after the symmetric region were overwritten"
     dist.barrier()
     if rank == 0:
         print(f"EP_OK {world}", flush=True)

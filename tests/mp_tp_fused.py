@@ -190,6 +190,12 @@ def main():
     close(y, want, "all-reduce after a timeout")
     ops.check_status(dev)
     progress("timeout path")
+    # nothing, local or from a peer, may have written past the end of the symmetric region
+    torch.cuda.synchronize()
+    dist.barrier()
+    assert comm.region.check_guard() == 0, f"rank {rank}: {comm.region.check_guard()} byte(s) of the guard band after the symmetric region were overwritten"
+    if comm._coll is not None:
+        assert comm._coll.region.check_guard() == 0, f"rank {rank}: collective staging region overran"
     dist.barrier()
     if rank == 0:
         print(f"TP_FUSED_OK {tp}", flush=True)

@@ -1,6 +1,7 @@
 """Config 1: tiny Llama in fp32 on CPU through the real engine (paged KV, page 16, continuous batching).
 Greedy tokens must equal a straightforward dense forward pass that knows nothing about pages or chunks."""
 import numpy as np
+import pytest
 import torch
 
 from mojo_b200.engine import EngineConfig, LLMEngine, SamplingParams
@@ -150,3 +151,43 @@ def test_trace_spans_and_request_timeline(monkeypatch):
     tl = trace.timeline(eng)
     assert len(tl) == 2 and all(len(r["token_times_s"]) == 5 and r["ttft_s"] is not None and r["ttft_s"] >= 0 for r in tl)
     trace.reset()
+
+
+def test_guard_bands_report_writes_outside_the_buffer():
+    from mojo_b200.utils import guard
+
+    t = guard.guarded_zeros((3, 5), torch.float32, "cpu", "scratch")
+    assert t.shape == (3, 5) and t.abs().sum() == 0
+    t.fill_(1.0)
+    n = guard.check_all()
+    assert n >= 1
+    buf = t._b2_guard
+    assert buf.corrupted() == (0, 0)
+    buf.raw[buf.guard - 1] = 0            # one byte before the payload
+    buf.raw[buf.guard + buf.nbytes + 7] = 1
+    assert buf.corrupted() == (1, 1)
+    with pytest.raises(guard.GuardError, match="scratch: 1 before / 1 after"):
+        guard.check_all()
+    with pytest.raises(guard.GuardError):
+        buf.check()
+    buf.raw[buf.guard - 1] = guard.PATTERN
+    buf.raw[buf.guard + buf.nbytes + 7] = guard.PATTERN
+    guard.check_all()
+    del t, buf
+    import gc
+
+    gc.collect()
+    assert all(b.name != "scratch" for b in guard.live())
+
+
+def test_kv_caches_are_guarded_when_the_switch_is_set(monkeypatch):
+    from mojo_b200.utils import guard
+
+    monkeypatch.setenv("B2_GUARD", "1")
+    model = build_model(tiny_llama(), "cpu", torch.float32).init_random(0)
+    caches = model.allocate_kv_cache(4, 16)
+    assert all(hasattr(k, "_b2_guard") and hasattr(v, "_b2_guard") for k, v in caches)
+    assert guard.check_all() >= 2 * len(caches)
+    monkeypatch.setenv("B2_GUARD", "0")
+    plain = model.allocate_kv_cache(4, 16)
+    assert not hasattr(plain[0][0], "_b2_guard")

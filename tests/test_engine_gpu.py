@@ -115,3 +115,25 @@ def test_deepseek_mla_moe_gpu_matches_cpu_logits():
     for a, b in ((a1, b1), (a2, b2)):
         assert (a - b).abs().max().item() < 0.08 * a.abs().max().item() + 0.05
         assert (a.argmax(-1) == b.argmax(-1)).float().mean() >= 0.8
+
+
+def test_engine_replay_is_bitwise_identical_and_leaves_guard_bands_intact(monkeypatch):
+    """Two fresh engines on the same seed, prompts and schedule must produce the same tokens (deterministic
+    replay), and with guard bands around every layer's KV pool no kernel of the run (KV scatter by slot, paged
+    attention by block table, chunked prefill) may have written outside its pool."""
+    from mojo_b200.utils import guard
+
+    monkeypatch.setenv("B2_GUARD", "1")
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in (100, 16, 257, 33)]
+    sp = SamplingParams(max_tokens=20)
+    runs = []
+    for _ in range(2):
+        eng = _engine("cuda", torch.bfloat16, False, budget=128)
+        assert hasattr(eng.kv_caches[0][0], "_b2_guard")
+        runs.append(eng.generate(prompts, sp))
+        torch.cuda.synchronize()
+        ops.check_status()
+        assert guard.check_all() >= 2 * _cfg().num_layers
+        del eng
+    assert runs[0] == runs[1]

@@ -414,3 +414,72 @@ def test_attention_prefill_tcgen05():
         _attn_case([5, 127, 300], [5, 127, 300], 8, 2, 128, 128)
     finally:
         ops.prefill_tensor_core = True
+
+
+def test_kernels_run_twice_bitwise_identical():
+    """Replay check for races: every kernel whose result is combined across CTAs (split-K and stream-K partial
+    sums, split-KV decode attention, the tcgen05 prefill's two-thread rows, the MoE dispatch / combine) must give
+    the same bits when the same launch runs again. A different answer on the second run means an unordered
+    reduction or a read that raced a write."""
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(96, 4096, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(3072, 4096, generator=g) * 0.05).bfloat16().to(DEV)
+    xl = torch.randn(1100, 1024, generator=g).bfloat16().to(DEV)
+    wl = (torch.randn(4096, 1024, generator=g) * 0.05).bfloat16().to(DEV)
+    for a, b, cfg in [(x, w, ops.gemm_config(True, 128, 4)), (x, w, ops.gemm_config(True, 128, stream_k=True)),
+                      (xl, wl, ops.gemm_config(False, 256, stream_k=True)), (xl, wl, ops.PAIR_CONFIG | 256), (x, w, 0)]:
+        y1 = ops.linear(a, b, config=cfg).clone()
+        y2 = ops.linear(a, b, config=cfg).clone()
+        assert torch.equal(y1, y2), f"GEMM config {cfg:#x} is not run-to-run deterministic"
+
+    n_q, n_kv, D, page = 32, 8, 128, 128
+    for q_lens, ctx in [([1] * 6, [127, 128, 129, 1000, 2500, 3]), ([300, 77], [300, 1000])]:
+        B = len(q_lens)
+        pages_per = [(c + page - 1) // page for c in ctx]
+        bt = torch.zeros(B, max(pages_per), dtype=torch.int32)
+        o = 0
+        for i, n in enumerate(pages_per):
+            bt[i, :n] = torch.arange(o, o + n, dtype=torch.int32)
+            o += n
+        kc = torch.randn(o, n_kv, page, D, generator=g).bfloat16().to(DEV)
+        vc = torch.randn(o, n_kv, page, D, generator=g).bfloat16().to(DEV)
+        T = sum(q_lens)
+        q = torch.randn(T, n_q * D, generator=g).bfloat16().to(DEV)
+        cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+        nd = B if q_lens[0] == 1 else 0
+        meta = ops.AttnMeta(cu.to(DEV), torch.tensor(ctx, dtype=torch.int32).to(DEV), bt.to(DEV), nd, max(q_lens), max(ctx))
+        o1 = ops.paged_attention(q, kc, vc, meta, 1.0 / math.sqrt(D), D).clone()
+        o2 = ops.paged_attention(q, kc, vc, meta, 1.0 / math.sqrt(D), D).clone()
+        assert torch.equal(o1, o2), f"attention q_lens={q_lens} is not run-to-run deterministic"
+    ops.check_status()
+
+
+def test_guard_bands_catch_a_write_past_the_buffer_and_stay_clean_under_kernels():
+    """Guard bands around a KV-style pool: kernels that scatter by slot (RoPE + KV write) and gather by block table
+    (decode attention) leave them intact; a deliberate host-side write one element past the end is reported."""
+    from mojo_b200.utils import guard
+
+    n_kv, D, page, pages = 2, 128, 16, 9
+    kc = guard.guarded_zeros((pages, n_kv, page, D), torch.bfloat16, DEV, "K pool")
+    vc = guard.guarded_zeros((pages, n_kv, page, D), torch.bfloat16, DEV, "V pool")
+    T = pages * page                      # fill every slot, the last page's last token included
+    g = torch.Generator().manual_seed(3)
+    qkv = torch.randn(T, (8 + 2 * n_kv) * D, generator=g).bfloat16().to(DEV)
+    pos = torch.arange(T, dtype=torch.int32, device=DEV)
+    slots = torch.randperm(T, generator=g).to(DEV)
+    qd, kd, vd = qkv.split([8 * D, n_kv * D, n_kv * D], dim=1)
+    ops.rope_kvwrite(qd, kd, vd, ref.rope_table(T, D, 500000.0).to(DEV), pos, slots, kc, vc, D)
+    bt = torch.arange(pages, dtype=torch.int32).unsqueeze(0).to(DEV)
+    meta = ops.AttnMeta(torch.tensor([0, 1], dtype=torch.int32, device=DEV), torch.tensor([T], dtype=torch.int32, device=DEV), bt, 1, 1, T)
+    ops.paged_attention(qkv[:1, : 8 * D].contiguous(), kc, vc, meta, 0.1, D)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert guard.check_all() >= 2
+    assert kc.abs().sum().item() > 0      # the pool was really written
+    # one element past the end, written from the host side through the raw allocation
+    buf = kc._b2_guard
+    buf.raw[buf.guard + buf.nbytes] = 0
+    with pytest.raises(guard.GuardError, match="K pool"):
+        guard.check_all()
+    buf.raw[buf.guard + buf.nbytes] = guard.PATTERN
+    assert guard.check_all() >= 2

@@ -167,3 +167,19 @@ def test_dtype_helpers_match_torch_bit_for_bit():
         a, w = C.e5m2_bits_to_f32(b), t.view(torch.float8_e5m2).float().item()
         assert (a != a and w != w) or a == w
     assert C.bf16_bits_to_f32(0x3F80) == 1.0
+
+
+@pytest.mark.parametrize("sanitizer", ["address", "thread"])
+def test_host_runtime_selftest_under_sanitizer(sanitizer, tmp_path):
+    """The KV manager, the scheduler and the threaded collective simulator, driven by random traffic in a plain
+    executable built with AddressSanitizer+UBSan and with ThreadSanitizer: any report makes the run exit non-zero."""
+    import subprocess
+
+    from mojo_b200 import build
+
+    exe = build.build_selftest(sanitizer, out_dir=tmp_path)
+    env = {"ASAN_OPTIONS": "detect_leaks=1:abort_on_error=0", "UBSAN_OPTIONS": "halt_on_error=1", "TSAN_OPTIONS": "halt_on_error=1",
+           "PATH": "/usr/bin:/bin"}
+    p = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300, env=env)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-4000:]
+    assert "runtime self-test: ok" in p.stdout
