@@ -46,6 +46,7 @@ class EngineConfig:
     eos_token_id: int | None = None
     seed: int = 0
     use_cuda_graphs: bool = True
+    capture_graphs_at_start: bool = True  # capture every decode bucket before serving instead of at first use
     tp_size: int = 1
     ep_size: int = 1
     lockstep: bool = False                # data-parallel attention + expert parallelism: a rank without work still joins every MoE layer
@@ -107,6 +108,8 @@ class LLMEngine:
         self.runner = ModelRunner(self.model, self.kv_caches, cfg)
         if cfg.autotune:
             self.runner.autotune()
+        if cfg.use_cuda_graphs and cfg.capture_graphs_at_start:
+            self.runner.capture_graphs()   # after tuning: the captured launches carry the tuned configurations
 
     def _auto_num_pages(self) -> int:
         cfg = self.cfg

@@ -79,6 +79,23 @@ class ModelRunner:
             self.buckets.append(b)
             b = b * 2 if b < 16 else b + max(16, b // 4) // 16 * 16
         self.buckets.append(cfg.max_num_seqs)
+        self.graph_pool = None           # memory pool shared by the decode graphs (they never replay concurrently)
+
+    def capture_graphs(self, buckets=None) -> int:
+        """Capture the decode graph of every batch-size bucket now, largest first so that the smaller ones reuse its
+        memory pool. Without this a bucket is captured the first time a decode-only step needs it, which puts a
+        capture (an eager pass plus the captured pass) into some request's inter-token latency. Returns the number
+        of graphs captured. Tensor-parallel ranks must all call it (the passes contain collectives)."""
+        if not self.use_graphs:
+            return 0
+        n = 0
+        for bb in sorted(set(buckets if buckets is not None else self.buckets), reverse=True):
+            if bb not in self.graphs:
+                self.graphs[bb] = _DecodeGraph(self, bb)
+                n += 1
+        torch.cuda.synchronize(self.device)
+        ops.check_status(self.device)
+        return n
 
     def autotune(self, verbose: bool = False) -> dict:
         """Measure the GEMM configurations of this model's weight shapes at the token counts the engine produces
@@ -254,8 +271,10 @@ class _DecodeGraph:
         torch.cuda.synchronize(dev)
         before = ops.launch_count
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        with torch.cuda.graph(self.graph, pool=runner.graph_pool):
             self.ids = run()
+        if runner.graph_pool is None:
+            runner.graph_pool = self.graph.pool()
         self.kernel_launches = ops.launch_count - before
         ops.launch_count = before
 
