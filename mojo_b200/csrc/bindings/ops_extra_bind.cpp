@@ -136,7 +136,7 @@ void bind_ops_extra(py::module_& m) {
 
   m.def("gemm_fp8",
         [](const at::Tensor& xq, const at::Tensor& xs, const at::Tensor& wq, const at::Tensor& ws, at::Tensor& y, int config,
-           c10::optional<at::Tensor> status) {
+           c10::optional<at::Tensor> status, c10::optional<at::Tensor> workspace) {
           need(xq.is_cuda() && xq.element_size() == 1 && wq.element_size() == 1 && xq.dim() == 2 && wq.dim() == 2 && xq.is_contiguous() && wq.is_contiguous(),
                "gemm_fp8: xq [M, K], wq [N, K] contiguous 8-bit");
           const int M = static_cast<int>(xq.size(0)), K = static_cast<int>(xq.size(1)), N = static_cast<int>(wq.size(0));
@@ -145,11 +145,14 @@ void bind_ops_extra(py::module_& m) {
           need(ws.scalar_type() == at::kFloat && ws.is_contiguous() && ws.numel() == static_cast<int64_t>((N + 127) / 128) * (K / 128), "gemm_fp8: ws f32 [ceil(N/128), K/128]");
           need(is_bf16_2d(y) && y.size(0) == M && y.size(1) == N, "gemm_fp8: y bf16 [M, N]");
           c10::cuda::CUDAGuard g(xq.device());
-          check(b2_gemm_fp8_block(xq.data_ptr(), xs.data_ptr<float>(), wq.data_ptr(), ws.data_ptr<float>(), y.data_ptr(), M, N, K,
-                                  y.stride(0), config, status_ptr(status), cur_stream()),
+          check(b2_gemm_fp8_block_ws(xq.data_ptr(), xs.data_ptr<float>(), wq.data_ptr(), ws.data_ptr<float>(), y.data_ptr(), M, N, K,
+                                     y.stride(0), config, workspace.has_value() ? workspace->data_ptr() : nullptr,
+                                     workspace.has_value() ? workspace->numel() * workspace->element_size() : 0, status_ptr(status),
+                                     cur_stream()),
                 "gemm_fp8");
         },
-        py::arg("xq"), py::arg("xs"), py::arg("wq"), py::arg("ws"), py::arg("y"), py::arg("config") = 0, py::arg("status") = py::none());
+        py::arg("xq"), py::arg("xs"), py::arg("wq"), py::arg("ws"), py::arg("y"), py::arg("config") = 0, py::arg("status") = py::none(),
+        py::arg("workspace") = py::none());
 
   m.def("mla_decode",
         [](const at::Tensor& q_lat, const at::Tensor& q_rope, const at::Tensor& kv_cache, at::Tensor& out_lat, const at::Tensor& ctx_lens,
@@ -173,6 +176,49 @@ void bind_ops_extra(py::module_& m) {
                                    status_ptr(status), cur_stream()),
                 "mla_decode");
         });
+
+  m.def("mla_attend",
+        [](const at::Tensor& q_lat, const at::Tensor& q_rope, const at::Tensor& kv_cache, at::Tensor& out_lat, const at::Tensor& row_ctx,
+           const at::Tensor& block_tables, c10::optional<at::Tensor> row_seq, c10::optional<at::Tensor> workspace, int num_splits,
+           double scale, c10::optional<at::Tensor> status) {
+          need(q_lat.is_cuda() && q_lat.scalar_type() == at::kBFloat16 && q_lat.dim() == 3 && q_lat.size(2) == 512 && q_lat.stride(2) == 1 && q_lat.stride(1) == 512,
+               "mla_attend: q_lat bf16 [R, H, 512] (rows may be strided)");
+          need(q_rope.is_cuda() && q_rope.scalar_type() == at::kBFloat16 && q_rope.dim() == 3 && q_rope.size(2) == 64 && q_rope.stride(2) == 1 && q_rope.stride(1) == 64 &&
+                   q_rope.size(0) == q_lat.size(0) && q_rope.size(1) == q_lat.size(1),
+               "mla_attend: q_rope bf16 [R, H, 64] (rows may be strided)");
+          need(kv_cache.is_contiguous() && kv_cache.scalar_type() == at::kBFloat16 && kv_cache.dim() == 3 && kv_cache.size(2) == 576, "mla_attend: cache bf16 [pages, page, 576]");
+          need(out_lat.is_contiguous() && out_lat.sizes() == q_lat.sizes() && out_lat.scalar_type() == at::kBFloat16, "mla_attend: out bf16 [R, H, 512] contiguous");
+          const int R = static_cast<int>(q_lat.size(0)), H = static_cast<int>(q_lat.size(1));
+          need(row_ctx.scalar_type() == at::kInt && row_ctx.is_contiguous() && row_ctx.numel() >= R, "mla_attend: row_ctx int32 [R]");
+          need(block_tables.scalar_type() == at::kInt && block_tables.dim() == 2 && block_tables.is_contiguous(), "mla_attend: block_tables int32 [S, max_blocks]");
+          if (row_seq.has_value()) need(row_seq->scalar_type() == at::kInt && row_seq->is_contiguous() && row_seq->numel() >= R, "mla_attend: row_seq int32 [R]");
+          else need(block_tables.size(0) >= R, "mla_attend: one block table per row when row_seq is not given");
+          float* ws = nullptr;
+          if (num_splits > 1) {
+            need(workspace.has_value() && workspace->numel() * 4 >= b2_mla_decode_workspace(R, H, num_splits), "mla_attend: workspace too small");
+            ws = workspace->data_ptr<float>();
+          }
+          c10::cuda::CUDAGuard g(q_lat.device());
+          check(b2_mla_attend_bf16(q_lat.data_ptr(), q_rope.data_ptr(), kv_cache.data_ptr(), out_lat.data_ptr(), row_ctx.data_ptr<int32_t>(),
+                                   block_tables.data_ptr<int32_t>(), row_seq.has_value() ? row_seq->data_ptr<int32_t>() : nullptr, ws, R,
+                                   static_cast<int>(block_tables.size(1)), H, static_cast<int>(kv_cache.size(1)), num_splits,
+                                   static_cast<float>(scale), kv_cache.size(0), q_lat.stride(0), q_rope.stride(0), status_ptr(status), cur_stream()),
+                "mla_attend");
+        },
+        py::arg("q_lat"), py::arg("q_rope"), py::arg("kv_cache"), py::arg("out_lat"), py::arg("row_ctx"), py::arg("block_tables"),
+        py::arg("row_seq") = py::none(), py::arg("workspace") = py::none(), py::arg("num_splits") = 1, py::arg("scale") = 1.0,
+        py::arg("status") = py::none());
+
+  m.def("mla_rows_meta", [](const at::Tensor& cu_q, const at::Tensor& ctx_lens, at::Tensor& row_ctx, at::Tensor& row_seq) {
+    need(cu_q.is_cuda() && cu_q.scalar_type() == at::kInt && ctx_lens.scalar_type() == at::kInt && cu_q.is_contiguous() && ctx_lens.is_contiguous() &&
+             cu_q.numel() == ctx_lens.numel() + 1,
+         "mla_rows_meta: cu_q int32 [S + 1], ctx_lens int32 [S]");
+    need(row_ctx.scalar_type() == at::kInt && row_seq.scalar_type() == at::kInt && row_ctx.is_contiguous() && row_seq.is_contiguous(), "mla_rows_meta: int32 outputs");
+    c10::cuda::CUDAGuard g(cu_q.device());
+    check(b2_mla_rows_meta(cu_q.data_ptr<int32_t>(), ctx_lens.data_ptr<int32_t>(), static_cast<int>(ctx_lens.numel()), row_ctx.data_ptr<int32_t>(),
+                           row_seq.data_ptr<int32_t>(), cur_stream()),
+          "mla_rows_meta");
+  });
 
   py::class_<B2EpLayout>(m, "EpLayout")
       .def(py::init([]() { return B2EpLayout{}; }))

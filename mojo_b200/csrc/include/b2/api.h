@@ -85,6 +85,17 @@ int b2_mla_decode_bf16(const void* q_lat, const void* q_rope, const void* kv_cac
                        int max_blocks, int n_heads, int page_size, int num_splits, float scale, int64_t num_pages,
                        b2::Status* status, cudaStream_t stream);
 int64_t b2_mla_decode_workspace(int batch, int n_heads, int num_splits);
+// The same kernel over arbitrary query rows (decode tokens and the tokens of prefill chunks in one launch): row r
+// reads q_lat + r * q_lat_stride and q_rope + r * q_rope_stride (element strides, multiples of 8), sees the first
+// row_ctx[r] cache positions of sequence row_seq[r] (row r itself when row_seq is null) and writes out_lat [rows, H, 512].
+int b2_mla_attend_bf16(const void* q_lat, const void* q_rope, const void* kv_cache, void* out_lat, const int32_t* row_ctx,
+                       const int32_t* block_tables, const int32_t* row_seq, float* workspace, int rows, int max_blocks,
+                       int n_heads, int page_size, int num_splits, float scale, int64_t num_pages, int64_t q_lat_stride,
+                       int64_t q_rope_stride, b2::Status* status, cudaStream_t stream);
+// row_ctx[t] / row_seq[t] for every token t of a batch described by cu_q [num_seqs + 1] and ctx_lens [num_seqs]:
+// token i of a sequence's chunk sees ctx - q_len + i + 1 positions (causal mask of chunked prefill; decode rows: ctx).
+int b2_mla_rows_meta(const int32_t* cu_q, const int32_t* ctx_lens, int num_seqs, int32_t* row_ctx, int32_t* row_seq,
+                     cudaStream_t stream);
 
 // ---- GEMM (tcgen05 / TMEM / TMA) ---------------------------------------------------------------
 // Epilogue selector for the tcgen05 GEMMs.
@@ -99,6 +110,12 @@ int64_t b2_gemm_workspace_bytes(int M, int N, int K);
 // fp8 block-scaled: X e4m3 [M, K] with f32 scales [M, K/128]; W e4m3 [N, K] with f32 scales [N/128, K/128].
 int b2_gemm_fp8_block(const void* xq, const float* xs, const void* wq, const float* ws, void* y, int M, int N, int K,
                       int64_t ldy, int config, b2::Status* status, cudaStream_t stream);
+// The same with a split-K workspace (layout and size rule of the bf16 GEMM's: 256 KiB of zeroed per-tile semaphores,
+// then f32 partial tiles). config bits 16..23 = split count; config 0 splits K when the tiles alone would leave
+// half of the SMs idle (decode-sized M against a narrow tensor-parallel weight shard).
+int b2_gemm_fp8_block_ws(const void* xq, const float* xs, const void* wq, const float* ws, void* y, int M, int N, int K,
+                         int64_t ldy, int config, void* workspace, int64_t workspace_bytes, b2::Status* status,
+                         cudaStream_t stream);
 // GGUF: W stored as Q4_K (type 12) or Q6_K (type 14) super-blocks, row-major [N, K/256 blocks].
 int b2_gemm_gguf(const void* x, const void* wq, int ggml_type, void* y, int M, int N, int K, b2::Status* status,
                  cudaStream_t stream);

@@ -35,6 +35,12 @@ struct Fp8Params {
   const float* sw;  // [ceil(N / 128), KB]
   int M, N, KB;
   int p_blocks, q_blocks;
+  // split-K (plain mode only): work item w = tile * splits + split covers k-blocks [split * KB / splits,
+  // (split + 1) * KB / splits); partial tiles go to `partials` as f32 [tile][split][BN][128] and the CTA that
+  // arrives last at the tile's counter adds them up in split order and stores the result
+  int splits;
+  float* partials;
+  uint32_t* counters;   // [tiles], zero on entry and on exit
 };
 
 // What the tensor-parallel variants add to the plain kernel (see tp_fused.cu for the protocols).
@@ -93,8 +99,18 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
       pb = u.pb;
       qb = u.qb;
     } else {
-      pb = w / prm.q_blocks;
-      qb = w % prm.q_blocks;
+      const int t = w / prm.splits;
+      pb = t / prm.q_blocks;
+      qb = t % prm.q_blocks;
+    }
+  };
+  auto kb_range = [&](int w, int& kb0, int& kb1) {
+    kb0 = 0;
+    kb1 = prm.KB;
+    if (MODE == kModePlain && prm.splits > 1) {
+      const int sp = w % prm.splits;
+      kb0 = sp * prm.KB / prm.splits;
+      kb1 = (sp + 1) * prm.KB / prm.splits;
     }
   };
   if (!RS || my_cta < n_gemm) {
@@ -138,7 +154,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *holder_ptr;
-  const int total = prm.p_blocks * prm.q_blocks;
+  const int total = prm.p_blocks * prm.q_blocks * (MODE == kModePlain ? prm.splits : 1);
   const int KB = prm.KB;
 
   if (warp == 0) {
@@ -156,7 +172,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
           u.qb = qb;
           if (!tp::AgGate{ag, SWAP, BN}(u, status)) { ok = false; break; }
         }
-        for (int kb = 0; kb < KB; ++kb) {
+        int kb0, kb1;
+        kb_range(w, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u)) {
             status_record(status, kTimeout, kSiteGemmEmpty, w, kb);
             ok = false;
@@ -187,7 +205,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
       uint32_t phase = 0, slab_phase = 0;
       bool ok = true;
       for (int w = my_cta; ok && w < total; w += n_ctas) {
-        for (int kb = 0; kb < KB; ++kb) {
+        int kb0, kb1;
+        kb_range(w, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!ptx::mbar_wait(slab_empty(slab), slab_phase ^ 1u)) {
             status_record(status, kTimeout, kSiteGemmTmemEmpty, w, kb);
             ok = false;
@@ -232,7 +252,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
 #pragma unroll
       for (int j = 0; j < COLS; ++j) acc[j] = 0.0f;
       const int row = pb * 128 + p_local;  // m (normal) or n (swapped)
-      for (int kb = 0; kb < KB; ++kb) {
+      int kb0, kb1;
+      kb_range(w, kb0, kb1);
+      for (int kb = kb0; kb < kb1; ++kb) {
         // scale(s) for this k-block. With the fused all-gather the token scales of a tile arrive from peers and
         // are only known to be in place once the tile's first slab is full (the producer passed the chunk gate
         // before it loaded the operands), so they are read after the wait, past L1.
@@ -288,7 +310,39 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
       }
       // the fused epilogue below synchronises the four warps, so they must agree on whether it runs
       if constexpr (RS) ok = ptx::named_barrier_and(3, 128, ok);
+      if constexpr (MODE == kModePlain) {
+        if (prm.splits > 1) ok = ptx::named_barrier_and(2, NW * 32, ok);   // the hand-over below synchronises all promotion warps
+      }
       if (!ok) break;
+      if constexpr (MODE == kModePlain) {
+        if (prm.splits > 1) {
+          const int tile = w / prm.splits, sp = w % prm.splits;
+          float* ws_tile = prm.partials + static_cast<size_t>(tile) * prm.splits * BN * 128;
+          float* mine = ws_tile + static_cast<size_t>(sp) * BN * 128 + p_local;
+#pragma unroll
+          for (int j = 0; j < COLS; ++j) __stcg(mine + (col_base + j) * 128, acc[j]);
+          __threadfence();
+          ptx::named_barrier_sync(2, NW * 32);
+          if (threadIdx.x == 64) {  // first promotion thread
+            const uint32_t old = atomicAdd(prm.counters + tile, 1u);
+            const bool last = old == static_cast<uint32_t>(prm.splits - 1);
+            if (last) prm.counters[tile] = 0;  // ready for the next launch
+            __threadfence();
+            holder_ptr[2] = last ? 1u : 0u;
+          }
+          ptx::named_barrier_sync(2, NW * 32);
+          const bool last = holder_ptr[2] != 0;
+          ptx::named_barrier_sync(2, NW * 32);  // the flag word is rewritten by the next work item
+          if (!last) continue;
+#pragma unroll
+          for (int j = 0; j < COLS; ++j) acc[j] = 0.0f;
+          for (int sidx = 0; sidx < prm.splits; ++sidx) {
+            const float* src = ws_tile + static_cast<size_t>(sidx) * BN * 128 + p_local;
+#pragma unroll
+            for (int j = 0; j < COLS; ++j) acc[j] += __ldcg(src + (col_base + j) * 128);
+          }
+        }
+      }
       // ---- store ----
       if constexpr (RS) {
         extern __shared__ uint8_t smem_dyn[];
@@ -344,7 +398,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constan
 
 template <int BN, bool SWAP>
 int launch_fp8(const void* xq, const float* xs, const void* wq, const float* ws, void* y, int M, int N, int K, int64_t ldy,
-               Status* status, cudaStream_t stream) {
+               int splits, void* workspace, int64_t workspace_bytes, Status* status, cudaStream_t stream) {
   constexpr int kStageBytes = 128 * 128 + BN * 128;
   constexpr int STAGES = (190 * 1024 / kStageBytes) > 8 ? 8 : (190 * 1024 / kStageBytes);
   constexpr int SLABS = BN <= 128 ? 4 : 2;
@@ -367,13 +421,35 @@ int launch_fp8(const void* xq, const float* xs, const void* wq, const float* ws,
   prm.KB = K / 128;
   prm.p_blocks = (rows_p + 127) / 128;
   prm.q_blocks = (rows_q + BN - 1) / BN;
+  prm.splits = 1;
+  {
+    const int64_t tiles = static_cast<int64_t>(prm.p_blocks) * prm.q_blocks;
+    const int64_t counters_bytes = 65536 * 4;   // same workspace convention as the bf16 GEMM: semaphores, then partial tiles
+    if (splits == 0) {
+      // automatic: split only when the tiles leave at least half of the SMs idle, at least four k-blocks per split
+      splits = 1;
+      if (workspace != nullptr && tiles * 2 <= kNumSMs && prm.KB >= 8) {
+        splits = static_cast<int>(kNumSMs / tiles);
+        if (splits > prm.KB / 4) splits = prm.KB / 4;
+        if (splits > 8) splits = 8;
+      }
+    }
+    if (splits > prm.KB) splits = prm.KB;
+    if (splits > 1) {
+      const int64_t need = counters_bytes + tiles * splits * BN * 128 * 4;
+      if (workspace == nullptr || workspace_bytes < need || tiles > 65536) return -kTooLarge;
+      prm.splits = splits;
+      prm.counters = static_cast<uint32_t*>(workspace);
+      prm.partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + counters_bytes);
+    }
+  }
   auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP, kModePlain, WG2>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
     attr_set = true;
   }
-  const int total = prm.p_blocks * prm.q_blocks;
+  const int total = prm.p_blocks * prm.q_blocks * prm.splits;
   static const tp::RsSched no_sched{};
   static const Fp8Fused no_fused{};
   kern<<<total < kNumSMs ? total : kNumSMs, WG2 ? kThreads + 128 : kThreads, SMEM, stream>>>(tp, tq, prm, no_sched, no_fused, status);
@@ -488,31 +564,43 @@ int launch_fp8_ag(const void* xq_all, const float* xs_all, const void* wq, const
 
 using namespace b2;
 
-extern "C" int b2_gemm_fp8_block(const void* xq, const float* xs, const void* wq, const float* ws, void* y, int M, int N,
-                                 int K, int64_t ldy, int config, Status* status, cudaStream_t stream) {
+extern "C" int b2_gemm_fp8_block_ws(const void* xq, const float* xs, const void* wq, const float* ws, void* y, int M, int N,
+                                    int K, int64_t ldy, int config, void* workspace, int64_t workspace_bytes, Status* status,
+                                    cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 128 != 0 || N % 8 != 0) return -kBadArgument;
   bool swap = M <= 64;
   int bn = swap ? (M <= 16 ? 16 : M <= 32 ? 32 : 64) : 128;
+  int splits = 0;   // automatic
   if (config != 0) {
     swap = (config >> 30) & 1;
     bn = config & 0xffff;
+    splits = (config >> 16) & 0xff;
+    if (splits == 0) splits = 1;
   }
   if (!swap && ldy % 8 != 0) return -kBadArgument;
+#define B2_FP8(BN_, SWAP_) return launch_fp8<BN_, SWAP_>(xq, xs, wq, ws, y, M, N, K, ldy, splits, workspace, workspace_bytes, status, stream)
   if (swap) {
     switch (bn) {
-      case 16: return launch_fp8<16, true>(xq, xs, wq, ws, y, M, N, K, ldy, status, stream);
-      case 32: return launch_fp8<32, true>(xq, xs, wq, ws, y, M, N, K, ldy, status, stream);
-      case 64: return launch_fp8<64, true>(xq, xs, wq, ws, y, M, N, K, ldy, status, stream);
-      case 128: return launch_fp8<128, true>(xq, xs, wq, ws, y, M, N, K, ldy, status, stream);
+      case 16: B2_FP8(16, true);
+      case 32: B2_FP8(32, true);
+      case 64: B2_FP8(64, true);
+      case 128: B2_FP8(128, true);
       default: return -kBadArgument;
     }
   }
   switch (bn) {
-    case 64: return launch_fp8<64, false>(xq, xs, wq, ws, y, M, N, K, ldy, status, stream);
-    case 128: return launch_fp8<128, false>(xq, xs, wq, ws, y, M, N, K, ldy, status, stream);
+    case 64: B2_FP8(64, false);
+    case 128: B2_FP8(128, false);
     default: return -kBadArgument;
   }
+#undef B2_FP8
+}
+
+extern "C" int b2_gemm_fp8_block(const void* xq, const float* xs, const void* wq, const float* ws, void* y, int M, int N,
+                                 int K, int64_t ldy, int config, Status* status, cudaStream_t stream) {
+  // without a workspace: explicit split-K configurations are refused, the automatic rule does not split
+  return b2_gemm_fp8_block_ws(xq, xs, wq, ws, y, M, N, K, ldy, config, nullptr, 0, status, stream);
 }
 
 extern "C" int b2_tp_gemm_rs_fp8(const void* xq, const float* xs, const void* wq, const float* ws, const B2TpRegion* reg,

@@ -1,4 +1,4 @@
-// Multi-head latent attention decode with absorbed projections.
+// Multi-head latent attention with absorbed projections: decode, and prefill chunks as one row group per query token.
 //
 // Per token the cache stores one row [c (512 latent dims) | k_rope (64 dims)] shared by all heads. With W_UK
 // folded into the query and W_UV applied after the kernel, attention for 16 heads is
@@ -10,6 +10,12 @@
 // TMA boxes through a 3-stage mbarrier ring. The 576-wide dot product is split four ways across the warps and
 // summed through shared memory (one __syncthreads per tile, parity double-buffered); each warp then owns 128
 // of the 512 output columns, so the f32 accumulator is 64 registers per thread.
+//
+// A "row group" (grid z) is one query token: its 16 heads, the context length it may see and the block table of
+// its sequence. In decode there is one row group per sequence. A prefill chunk contributes one row group per
+// token, with context = cached prefix + position in the chunk + 1 (that is the causal mask) and `row_seq` naming
+// the sequence whose block table it reads; the chunk's latents are in the cache before the kernel runs, and the
+// tiles shared by the tokens of a sequence are served by L2.
 #include <cstdint>
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -45,8 +51,9 @@ __device__ __forceinline__ uint32_t kv_addr(uint32_t base, int row, int chunk) {
 __global__ void __launch_bounds__(128) mla_decode_kernel(
     const __grid_constant__ CUtensorMap tmap_kv, const __nv_bfloat16* __restrict__ q_lat,
     const __nv_bfloat16* __restrict__ q_rope, __nv_bfloat16* __restrict__ out_lat, const int32_t* __restrict__ ctx_lens,
-    const int32_t* __restrict__ block_tables, float* __restrict__ workspace, int max_blocks, int n_heads, int page_size,
-    int num_splits, float scale_log2, int64_t num_pages, Status* status) {
+    const int32_t* __restrict__ block_tables, const int32_t* __restrict__ row_seq, float* __restrict__ workspace,
+    int max_blocks, int n_heads, int page_size, int num_splits, float scale_log2, int64_t num_pages, int64_t q_lat_stride,
+    int64_t q_rope_stride, Status* status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ int sh_fail;  // set by any thread whose wait ran out; read after the per-tile barrier so all agree
   const uint32_t sbase = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -60,7 +67,7 @@ __global__ void __launch_bounds__(128) mla_decode_kernel(
   const int split = blockIdx.x, hg = blockIdx.y, seq = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ctx = ctx_lens[seq];
-  const int32_t* table = block_tables + static_cast<int64_t>(seq) * max_blocks;
+  const int32_t* table = block_tables + static_cast<int64_t>(row_seq != nullptr ? row_seq[seq] : seq) * max_blocks;
   const int head0 = hg * 16;
   const int rows = min(16, n_heads - head0);
 
@@ -93,9 +100,9 @@ __global__ void __launch_bounds__(128) mla_decode_kernel(
     const int r = i / (kRow / 8), c = i % (kRow / 8);
     uint4 v = make_uint4(0, 0, 0, 0);
     if (r < rows) {
-      const int64_t h = static_cast<int64_t>(seq) * n_heads + head0 + r;
-      v = c < kLat / 8 ? reinterpret_cast<const uint4*>(q_lat + h * kLat)[c]
-                       : reinterpret_cast<const uint4*>(q_rope + h * kRope)[c - kLat / 8];
+      // row strides in elements: the two query parts may be column slices of one wider projection output
+      v = c < kLat / 8 ? reinterpret_cast<const uint4*>(q_lat + seq * q_lat_stride + static_cast<int64_t>(head0 + r) * kLat)[c]
+                       : reinterpret_cast<const uint4*>(q_rope + seq * q_rope_stride + static_cast<int64_t>(head0 + r) * kRope)[c - kLat / 8];
     }
     // plain row-major with an XOR on the low 3 chunk bits to spread ldmatrix rows over banks
     reinterpret_cast<uint4*>(q_gen)[r * (kRow / 8) + ((c & ~7) | ((c & 7) ^ (r & 7)))] = v;
@@ -284,6 +291,18 @@ __global__ void mla_reduce_kernel(const float* __restrict__ workspace, __nv_bflo
   for (int c = 0; c < kLat / 32; ++c) out[static_cast<int64_t>(idx) * kLat + c * 32 + lane] = __float2bfloat16(acc[c] * inv);
 }
 
+// One thread block per sequence: expand (cu_q, ctx_lens) into per-token rows for the attention kernel.
+// Token i of a sequence with q_len new tokens and `ctx` tokens in total sees ctx - q_len + i + 1 positions.
+__global__ void mla_rows_meta_kernel(const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_lens,
+                                     int32_t* __restrict__ row_ctx, int32_t* __restrict__ row_seq) {
+  const int b = blockIdx.x;
+  const int t0 = cu_q[b], q_len = cu_q[b + 1] - t0, ctx = ctx_lens[b];
+  for (int i = threadIdx.x; i < q_len; i += blockDim.x) {
+    row_ctx[t0 + i] = max(0, ctx - q_len + i + 1);
+    row_seq[t0 + i] = b;
+  }
+}
+
 }  // namespace
 }  // namespace b2
 
@@ -293,15 +312,27 @@ extern "C" int64_t b2_mla_decode_workspace(int batch, int n_heads, int num_split
   return static_cast<int64_t>(batch) * n_heads * num_splits * (kLat + 2) * 4;
 }
 
-extern "C" int b2_mla_decode_bf16(const void* q_lat, const void* q_rope, const void* kv_cache, void* out_lat,
-                                  const int32_t* ctx_lens, const int32_t* block_tables, float* workspace, int batch,
-                                  int max_blocks, int n_heads, int page_size, int num_splits, float scale,
-                                  int64_t num_pages, Status* status, cudaStream_t stream) {
-  if (batch <= 0) return 0;
+extern "C" int b2_mla_rows_meta(const int32_t* cu_q, const int32_t* ctx_lens, int num_seqs, int32_t* row_ctx, int32_t* row_seq,
+                                cudaStream_t stream) {
+  if (num_seqs <= 0) return 0;
+  mla_rows_meta_kernel<<<num_seqs, 128, 0, stream>>>(cu_q, ctx_lens, row_ctx, row_seq);
+  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+}
+
+extern "C" int b2_mla_attend_bf16(const void* q_lat, const void* q_rope, const void* kv_cache, void* out_lat,
+                                  const int32_t* row_ctx, const int32_t* block_tables, const int32_t* row_seq, float* workspace,
+                                  int rows, int max_blocks, int n_heads, int page_size, int num_splits, float scale,
+                                  int64_t num_pages, int64_t q_lat_stride, int64_t q_rope_stride, Status* status,
+                                  cudaStream_t stream) {
+  if (rows <= 0) return 0;
   if (n_heads <= 0 || page_size % BN != 0 || num_splits < 1 || (num_splits > 1 && workspace == nullptr)) return -kBadArgument;
+  // 16-byte vector loads of the query rows
+  if (q_lat_stride % 8 != 0 || q_rope_stride % 8 != 0 || (reinterpret_cast<uintptr_t>(q_lat) & 15) != 0 ||
+      (reinterpret_cast<uintptr_t>(q_rope) & 15) != 0)
+    return -kBadArgument;
   CUtensorMap tk;
-  const uint64_t rows = static_cast<uint64_t>(num_pages) * page_size;
-  if (!make_tmap_2d(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, kv_cache, rows, kRow, kRow * 2, BN, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+  const uint64_t cache_rows = static_cast<uint64_t>(num_pages) * page_size;
+  if (!make_tmap_2d(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, kv_cache, cache_rows, kRow, kRow * 2, BN, 64, CU_TENSOR_MAP_SWIZZLE_128B))
     return -kBadArgument;
   constexpr int SMEM = STAGES * kTileBytes + 16 * kRow * 2 + 2 * 4 * 16 * 32 * 4 + 64 + 1024;
   static bool set = false;
@@ -309,13 +340,31 @@ extern "C" int b2_mla_decode_bf16(const void* q_lat, const void* q_rope, const v
     if (cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
     set = true;
   }
-  dim3 grid(num_splits, (n_heads + 15) / 16, batch);
-  mla_decode_kernel<<<grid, 128, SMEM, stream>>>(tk, static_cast<const __nv_bfloat16*>(q_lat), static_cast<const __nv_bfloat16*>(q_rope),
-                                                 static_cast<__nv_bfloat16*>(out_lat), ctx_lens, block_tables, workspace, max_blocks,
-                                                 n_heads, page_size, num_splits, scale * ptx::kLog2e, num_pages, status);
-  if (num_splits > 1) {
-    const int total = batch * n_heads;
-    mla_reduce_kernel<<<(total + 3) / 4, 128, 0, stream>>>(workspace, static_cast<__nv_bfloat16*>(out_lat), num_splits, total);
+  // grid z is limited to 65535: larger row counts go out in slices
+  constexpr int kMaxZ = 65535;
+  for (int r0 = 0; r0 < rows; r0 += kMaxZ) {
+    const int n = rows - r0 < kMaxZ ? rows - r0 : kMaxZ;
+    dim3 grid(num_splits, (n_heads + 15) / 16, n);
+    float* ws = workspace == nullptr ? nullptr : workspace + static_cast<int64_t>(r0) * n_heads * num_splits * (kLat + 2);
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(out_lat) + static_cast<int64_t>(r0) * n_heads * kLat;
+    mla_decode_kernel<<<grid, 128, SMEM, stream>>>(
+        tk, static_cast<const __nv_bfloat16*>(q_lat) + r0 * q_lat_stride, static_cast<const __nv_bfloat16*>(q_rope) + r0 * q_rope_stride,
+        out, row_ctx + r0, row_seq == nullptr ? block_tables + static_cast<int64_t>(r0) * max_blocks : block_tables,
+        row_seq == nullptr ? nullptr : row_seq + r0, ws, max_blocks, n_heads, page_size,
+        num_splits, scale * ptx::kLog2e, num_pages, q_lat_stride, q_rope_stride, status);
+    if (num_splits > 1) {
+      const int total = n * n_heads;
+      mla_reduce_kernel<<<(total + 3) / 4, 128, 0, stream>>>(ws, out, num_splits, total);
+    }
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+}
+
+extern "C" int b2_mla_decode_bf16(const void* q_lat, const void* q_rope, const void* kv_cache, void* out_lat,
+                                  const int32_t* ctx_lens, const int32_t* block_tables, float* workspace, int batch,
+                                  int max_blocks, int n_heads, int page_size, int num_splits, float scale,
+                                  int64_t num_pages, Status* status, cudaStream_t stream) {
+  return b2_mla_attend_bf16(q_lat, q_rope, kv_cache, out_lat, ctx_lens, block_tables, nullptr, workspace, batch, max_blocks,
+                            n_heads, page_size, num_splits, scale, num_pages, static_cast<int64_t>(n_heads) * kLat,
+                            static_cast<int64_t>(n_heads) * kRope, status, stream);
 }

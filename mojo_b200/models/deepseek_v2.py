@@ -1,9 +1,16 @@
 """DeepSeek-V2(-Lite) decoder: multi-head latent attention (MLA) + mixture of experts with shared experts.
 
 Cache: one row per token per layer, [c_kv (kv_lora_rank) | k_rope (qk_rope_head_dim)], shared by all heads.
-Decode uses the absorbed form (W_UK folded into the query, W_UV applied to the latent-space output) and the MLA
-decode kernel; prefill expands the latents of the sequence into per-head K/V and runs the causal prefill kernel
-with a 192-wide key (128 nope + 64 rope) and V zero-padded to the same width.
+
+On CUDA attention runs entirely in the absorbed form, for decode tokens and prefill chunks alike. The per-head
+up-projections are folded into the neighbouring projection weights once, when the model first runs:
+    W_qa[h] = W_UK[h]^T W_q,nope[h]   (query straight into latent space, [H * 512, hidden])
+    W_oa[:, h] = W_o[:, h] W_UV[h]     (latent-space output straight to hidden, [hidden, H * 512])
+so a layer's attention is one GEMM producing [q_lat | q_rope | c_kv | k_rope], RMSNorm + RoPE + the cache scatter,
+one launch of the latent attention kernel over every token of the batch (`ops.mla_attend`), and one GEMM back to
+hidden. That costs about 1 % more GEMM FLOPs per token than the factored form and removes every per-head small
+matrix product, every K/V expansion and every per-sequence loop. The CPU path keeps the factored weights and the
+textbook formulation (per-head K/V expansion for prefill): it is the oracle.
 
 MoE: softmax router over all routed experts, top-k, optional renormalisation; routed experts run through the
 expert-parallel path (`parallel.ep`: dispatch, grouped GEMM, combine) and the shared experts as one fused MLP.
@@ -41,6 +48,9 @@ class DsLayer:
     w_exp_gu: torch.Tensor | None = None  # [E_local, 2F_moe, hidden] (gate rows then up rows per expert)
     w_exp_down: torch.Tensor | None = None  # [E_local, hidden, F_moe]
     w_exp_gu_il: torch.Tensor | None = None  # [E_local, 2F_moe, hidden] gate/up interleaved in blocks of 16 (EP kernels)
+    # absorbed attention weights (CUDA path, built by `DeepseekV2Model._absorb`)
+    w_qa: torch.Tensor | None = None      # [H * kv_lora + H * rope + kv_lora + rope, hidden]: q_lat | q_rope | c_kv | k_rope
+    w_oa: torch.Tensor | None = None      # [hidden, H * kv_lora]
 
 
 class DeepseekV2Model:
@@ -104,6 +114,14 @@ class DeepseekV2Model:
             self.layers.append(lw)
         self.final_norm = self._put(torch.ones(h))
         self.lm_head = self._put(rnd(cfg.vocab_size, h))
+        return self.finalize()
+
+    def finalize(self) -> "DeepseekV2Model":
+        """Call once after the weights are in place: on CUDA, folds the MLA up-projections into their neighbours."""
+        if self.device.type == "cuda" and self.lora == 512 and self.rope == 64:
+            for lw in self.layers:
+                if lw.w_qa is None:
+                    self._absorb(lw)
         return self
 
     def weight_bytes(self) -> int:
@@ -125,6 +143,35 @@ class DeepseekV2Model:
         return self.cfg.num_layers * page_size * (self.lora + self.rope) * torch.empty((), dtype=self.dtype).element_size()
 
     # ------------------------------------------------------------------------------------------------
+    def _absorb(self, lw: DsLayer) -> None:
+        """Fold W_UK into the query projection and W_UV into the output projection (fp32 products, rounded once)."""
+        H, hid = self.H, self.cfg.hidden_size
+        wq = lw.wq.float().view(H, self.nope + self.rope, hid)
+        w_q_lat = torch.einsum("hdc,hdk->hck", lw.w_uk.float(), wq[:, :self.nope]).reshape(H * self.lora, hid)
+        w_q_rope = wq[:, self.nope:].reshape(H * self.rope, hid)
+        lw.w_qa = torch.cat([w_q_lat, w_q_rope, lw.w_kv_a.float()], dim=0).to(self.dtype).contiguous()
+        wo = lw.wo.float().view(hid, H, self.vdim)
+        lw.w_oa = torch.einsum("ohv,hvc->ohc", wo, lw.w_uv.float()).reshape(hid, H * self.lora).to(self.dtype).contiguous()
+        # the factored weights are not used again on this device
+        lw.wq = lw.w_uk = lw.w_uv = lw.wo = lw.w_kv_a = None
+
+    def _attention_absorbed(self, lw: DsLayer, x: torch.Tensor, positions, slots, meta: ops.AttnMeta, cache: torch.Tensor) -> torch.Tensor:
+        """CUDA path: returns the attention block's output in hidden space (output projection included)."""
+        if lw.w_qa is None:
+            self._absorb(lw)
+        T, H = x.shape[0], self.H
+        n_lat, n_rope = H * self.lora, H * self.rope
+        qa = ops.linear(x, lw.w_qa)                                   # [T, q_lat | q_rope | c_kv | k_rope]
+        q_rope = qa[:, n_lat:n_lat + n_rope]
+        kv_a = qa[:, n_lat + n_rope:]
+        c_kv, _ = ops.rms_norm(kv_a[:, :self.lora].contiguous(), lw.kv_a_norm, self.cfg.rms_norm_eps)
+        k_rope = kv_a[:, self.lora:].contiguous()
+        ops.rope_kvwrite(q_rope, k_rope, None, self.cos_sin, positions, None, None, None, self.rope, interleaved=self.cfg.rope_interleaved)
+        # latent cache row = [c_kv | k_rope]; slots < 0 (graph padding) are skipped by the scatter
+        ops.scatter_rows(torch.cat([c_kv, k_rope], dim=1), slots, cache.view(-1, cache.shape[2]))
+        o_lat = ops.mla_attend(qa[:, :n_lat].unflatten(1, (H, self.lora)), q_rope.unflatten(1, (H, self.rope)), cache, meta, self.scale)
+        return ops.linear(o_lat.view(T, n_lat), lw.w_oa)
+
     def _attention(self, lw: DsLayer, x: torch.Tensor, positions, slots, meta: ops.AttnMeta, cache: torch.Tensor) -> torch.Tensor:
         T, H = x.shape[0], self.H
         q = ops.linear(x, lw.wq).view(T, H, self.nope + self.rope)
@@ -211,8 +258,10 @@ class DeepseekV2Model:
         residual = None
         for li, lw in enumerate(self.layers):
             x, residual = ops.rms_norm(h, lw.attn_norm, cfg.rms_norm_eps, residual)
-            attn = self._attention(lw, x, positions, slots, meta, kv_caches[li])
-            h = ops.linear(attn, lw.wo)
+            if x.is_cuda and self.lora == 512 and self.rope == 64:
+                h = self._attention_absorbed(lw, x, positions, slots, meta, kv_caches[li])
+            else:
+                h = ops.linear(self._attention(lw, x, positions, slots, meta, kv_caches[li]), lw.wo)
             x, residual = ops.rms_norm(h, lw.mlp_norm, cfg.rms_norm_eps, residual)
             if lw.w_gu is not None:
                 h = ops.linear(ops.linear_swiglu(x, lw.w_gu), lw.w_down)

@@ -338,6 +338,36 @@ def mla_decode(q_lat: torch.Tensor, q_rope: torch.Tensor, kv_cache: torch.Tensor
     return out
 
 
+def mla_attend(q_lat: torch.Tensor, q_rope: torch.Tensor, kv_cache: torch.Tensor, meta: "AttnMeta", scale: float) -> torch.Tensor:
+    """Absorbed multi-head latent attention over a whole engine batch in one launch: decode tokens and the tokens of
+    prefill chunks alike (the chunk's latents must already be in the cache). q_lat [T, H, 512] and q_rope [T, H, 64]
+    may be column slices of one projection output (strided rows). Returns [T, H, 512] in latent space."""
+    if not q_lat.is_cuda:
+        return reference.mla_attend(q_lat, q_rope, kv_cache, meta.cu_q, meta.ctx_lens, meta.block_tables, scale).to(q_lat.dtype)
+    C = _ext.require()
+    st = _state.get(q_lat.device)
+    T, H = q_lat.shape[0], q_lat.shape[1]
+    out = torch.empty(T, H, 512, dtype=q_lat.dtype, device=q_lat.device)
+    if T == 0:
+        return out
+    decode_only = meta.num_decode == meta.num_seqs
+    if decode_only:
+        row_ctx, row_seq = meta.ctx_lens, None      # one row per sequence, in order
+        n_meta = 0
+    else:
+        row_ctx = torch.empty(T, dtype=torch.int32, device=q_lat.device)
+        row_seq = torch.empty(T, dtype=torch.int32, device=q_lat.device)
+        C.mla_rows_meta(meta.cu_q, meta.ctx_lens, row_ctx, row_seq)
+        n_meta = 1
+    ctas = T * ((H + 15) // 16)
+    splits = 1
+    if ctas < 148 and meta.max_ctx > 256:
+        splits = max(1, min((148 + ctas - 1) // ctas, meta.max_ctx // 128, 16))
+    C.mla_attend(q_lat, q_rope, kv_cache, out, row_ctx, meta.block_tables, row_seq, st.attn_ws, splits, scale, st.status)
+    _count(n_meta + (2 if splits > 1 else 1))
+    return out
+
+
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     if not logits.is_cuda:
         return torch.argmax(logits.float(), dim=-1)

@@ -293,6 +293,30 @@ def mla_decode(q_lat: torch.Tensor, q_rope: torch.Tensor, kv_cache: torch.Tensor
     return out
 
 
+def mla_attend(q_lat: torch.Tensor, q_rope: torch.Tensor, kv_cache: torch.Tensor, cu_q: torch.Tensor, ctx_lens: torch.Tensor,
+               block_tables: torch.Tensor, scale: float) -> torch.Tensor:
+    """Absorbed latent attention for a mixed batch: q_lat [T, H, R], q_rope [T, H, P] hold the query tokens of every
+    sequence back to back (`cu_q` offsets); token i of a chunk of q_len tokens sees the first ctx - q_len + i + 1 cache
+    positions of its sequence. Returns [T, H, R] in latent space."""
+    T, H, R = q_lat.shape
+    page_size = kv_cache.shape[1]
+    out = torch.zeros(T, H, R, dtype=torch.float32, device=q_lat.device)
+    cu = [int(v) for v in cu_q]
+    for b in range(len(cu) - 1):
+        s0, e0, ctx = cu[b], cu[b + 1], int(ctx_lens[b])
+        if e0 == s0 or ctx == 0:
+            continue
+        n_pages = (ctx + page_size - 1) // page_size
+        kv = kv_cache[block_tables[b, :n_pages].long()].reshape(n_pages * page_size, -1)[:ctx].float()
+        lat, rope = kv[:, :R], kv[:, R:]
+        s = (torch.einsum("qhr,kr->hqk", q_lat[s0:e0].float(), lat) + torch.einsum("qhp,kp->hqk", q_rope[s0:e0].float(), rope)) * scale
+        qpos = torch.arange(ctx - (e0 - s0), ctx, device=s.device).unsqueeze(1)
+        kpos = torch.arange(ctx, device=s.device).unsqueeze(0)
+        s = s.masked_fill(~(kpos <= qpos).unsqueeze(0), float("-inf"))
+        out[s0:e0] = torch.einsum("hqk,kr->qhr", torch.softmax(s, dim=-1), lat)
+    return out
+
+
 # ------------------------------------------------------------------------------------------------------
 # MoE
 # ------------------------------------------------------------------------------------------------------

@@ -53,3 +53,43 @@ def test_tiny_deepseek_engine_matches_dense_forward():
             assert nxt == o[t], f"token {t}: engine {o[t]} vs dense {nxt}"
             ids.append(nxt)
     assert eng.kv.check_invariants() == ""
+
+
+def test_absorbed_attention_path_matches_factored_path():
+    """The CUDA formulation (up-projections folded into the query and output weights, one latent-attention call over
+    decode rows and prefill chunks) run through the CPU fallbacks of the same ops must equal the factored formulation."""
+    import copy
+
+    from mojo_b200 import ops
+    from mojo_b200.models import build_model
+
+    cfg = tiny_deepseek()
+    model = build_model(cfg, "cpu", torch.float32).init_random(0, std=0.05)
+    page, g = 16, torch.Generator().manual_seed(4)
+    q_lens, ctxs = [1, 1, 20, 7], [30, 1, 20, 25]      # two decode rows, a fresh prompt, a chunk after an 18-token prefix
+    T = sum(q_lens)
+    n_pages = [(c + page - 1) // page for c in ctxs]
+    bt = torch.zeros(len(q_lens), max(n_pages), dtype=torch.int32)
+    o = 1
+    for b, n in enumerate(n_pages):
+        bt[b, :n] = torch.arange(o, o + n, dtype=torch.int32)
+        o += n
+    cache = torch.randn(o + 1, page, cfg.kv_lora_rank + cfg.qk_rope_head_dim, generator=g) * 0.3   # cached prefixes: random latents
+    positions, slots = [], []
+    for b, (ql, c) in enumerate(zip(q_lens, ctxs)):
+        for i in range(c - ql, c):
+            positions.append(i)
+            slots.append(int(bt[b, i // page]) * page + i % page)
+    positions = torch.tensor(positions, dtype=torch.int32)
+    slots = torch.tensor(slots, dtype=torch.int64)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    meta = ops.AttnMeta(cu, torch.tensor(ctxs, dtype=torch.int32), bt, 2, max(q_lens), max(ctxs))
+    x = torch.randn(T, cfg.hidden_size, generator=g)
+    lw = model.layers[1]
+    cache_a, cache_b = cache.clone(), cache.clone()
+    want = ops.linear(model._attention(lw, x, positions, slots, meta, cache_a), lw.wo)
+    lw2 = copy.deepcopy(lw)
+    got = model._attention_absorbed(lw2, x, positions, slots, meta, cache_b)
+    assert lw2.wq is None and lw2.w_qa.shape == (cfg.num_heads * 576 + 576, cfg.hidden_size)
+    assert torch.equal(cache_a, cache_b)               # both wrote the same latents
+    assert torch.allclose(got, want, atol=2e-5, rtol=1e-4), (got - want).abs().max()

@@ -483,3 +483,39 @@ def test_guard_bands_catch_a_write_past_the_buffer_and_stay_clean_under_kernels(
         guard.check_all()
     buf.raw[buf.guard + buf.nbytes] = guard.PATTERN
     assert guard.check_all() >= 2
+
+
+@pytest.mark.parametrize("page", [32, 128])
+@pytest.mark.parametrize("q_lens,ctxs,strided", [([1, 1, 40, 9], [500, 33, 40, 100], True), ([130], [130], False), ([1, 1, 1], [1, 64, 700], True),
+                                                ([64, 1, 200], [64, 300, 456], False)])
+def test_mla_attend_mixed_decode_and_prefill_rows(page, q_lens, ctxs, strided):
+    """The latent attention kernel over a whole engine batch: decode rows plus the tokens of prefill chunks (with
+    and without a cached prefix), query parts taken as column slices of one wider projection output."""
+    g = torch.Generator().manual_seed(13)
+    H, B = 16, len(q_lens)
+    order = sorted(range(B), key=lambda i: q_lens[i] != 1)       # decode sequences first, as the scheduler emits them
+    q_lens, ctxs = [q_lens[i] for i in order], [ctxs[i] for i in order]
+    pages_per = [(c + page - 1) // page for c in ctxs]
+    total = sum(pages_per) + 2
+    perm = torch.randperm(total, generator=g)
+    bt = torch.zeros(B, max(pages_per), dtype=torch.int32)
+    o = 0
+    for b, n in enumerate(pages_per):
+        bt[b, :n] = perm[o:o + n].int()
+        o += n
+    cache = (torch.randn(total, page, 576, generator=g) * 0.5).bfloat16()
+    T = sum(q_lens)
+    width = H * 512 + H * 64 + 576 if strided else H * 512 + H * 64
+    qa = (torch.randn(T, width, generator=g) * 0.3).bfloat16()
+    q_lat, q_rope = qa[:, :H * 512].unflatten(1, (H, 512)), qa[:, H * 512:H * 576].unflatten(1, (H, 64))
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    cl = torch.tensor(ctxs, dtype=torch.int32)
+    scale = 1.0 / math.sqrt(192)
+    want = ref.mla_attend(q_lat, q_rope, cache, cu, cl, bt, scale)
+    nd = sum(1 for n in q_lens if n == 1)
+    qa_d = qa.to(DEV)
+    meta = ops.AttnMeta(cu.to(DEV), cl.to(DEV), bt.to(DEV), nd, max(q_lens), max(ctxs))
+    got = ops.mla_attend(qa_d[:, :H * 512].unflatten(1, (H, 512)), qa_d[:, H * 512:H * 576].unflatten(1, (H, 64)), cache.to(DEV), meta, scale)
+    torch.cuda.synchronize()
+    ops.check_status()
+    _close(got, want, 2e-2, 2e-2)
