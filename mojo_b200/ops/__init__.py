@@ -219,7 +219,8 @@ def linear_fp8(x, w_q: torch.Tensor, w_scale: torch.Tensor, out: torch.Tensor | 
     C = _ext.require()
     if out is None:
         out = torch.empty(xq.shape[0], w_q.shape[0], dtype=torch.bfloat16, device=xq.device)
-    C.gemm_fp8(xq, xs, w_q, w_scale, out, config, _state.get(xq.device).status)
+    st = _state.get(xq.device)
+    C.gemm_fp8(xq, xs, w_q, w_scale, out, config, st.status, st.gemm_ws)   # the workspace enables split-K for under-filled grids
     _count()
     return out
 

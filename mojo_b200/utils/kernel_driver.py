@@ -3,6 +3,7 @@
 Small, self-terminating workloads (inputs larger than the 126 MB L2, a few GB at most) meant to be wrapped by a
 profiler capture of one kernel; with `--time` the case is timed with CUDA events instead and one JSON line is printed.
 Cases: gemm_large, gemm_pair (the same product on CTA pairs), gemm_prefill, gemm_decode, gemm_swiglu, gemm_fp8,
+gemm_fp8_decode, gemm_fp8_decode_nosplit (a narrow tensor-parallel shard at 256 tokens, with and without split-K),
 attn_decode, attn_prefill, mla_decode, rmsnorm, sampling.
 """
 from __future__ import annotations
@@ -42,6 +43,25 @@ def _case(name: str):
         wq, ws = wq.to(DEV), ws.to(DEV)
         y = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
         return (lambda: ops.linear_fp8((xq, xs), wq, ws, out=y)), 2.0 * M * N * K, M * K + N * K + M * N * 2
+    if name in ("gemm_fp8_decode", "gemm_fp8_decode_nosplit"):
+        # one rank's QKV projection of a 70B model at TP = 8 with 256 decode tokens: 20 output tiles for 148 SMs unless K
+        # is split. Sixteen weight copies (168 MB) rotate so that every launch streams its weights from HBM.
+        M, N, K = 256, 1280, 8192
+        xq, xs = ops.quant_e4m3(rnd(M, K))
+        copies = []
+        for _ in range(16):
+            wq, ws = ref.quant_e4m3_128x128(rnd(N, K, scale=0.02).float().cpu())
+            copies.append((wq.to(DEV), ws.to(DEV)))
+        y = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+        cfg = ops.gemm_config(False, 128, 1) if name.endswith("nosplit") else 0
+        turn = [0]
+
+        def run():
+            wq, ws = copies[turn[0] % len(copies)]
+            turn[0] += 1
+            ops.linear_fp8((xq, xs), wq, ws, out=y, config=cfg)
+
+        return run, 2.0 * M * N * K, M * K + N * K + M * N * 2
     if name in ("attn_decode", "attn_prefill"):
         n_q, n_kv, D, page = 32, 8, 128, 128
         if name == "attn_decode":

@@ -162,7 +162,11 @@ def test_gemm_swiglu(M, config):
 
 @pytest.mark.parametrize("M,N,K,config", [(128, 256, 512, 0), (300, 1280, 1024, 0), (1000, 512, 2048, ops.gemm_config(False, 64)),
                                           (7, 384, 512, 0), (33, 1024, 4096, 0), (64, 640, 1024, 0), (100, 256, 512, ops.gemm_config(True, 128)),
-                                          (48, 8192, 1024, ops.gemm_config(True, 16))])
+                                          (48, 8192, 1024, ops.gemm_config(True, 16)),
+                                          # split-K: explicit factors in both layouts, a ragged K split (20 blocks by 3), and the
+                                          # automatic rule on a narrow shard at decode size (20 tiles -> 7 splits)
+                                          (256, 256, 2048, ops.gemm_config(False, 128, 4)), (200, 384, 2560, ops.gemm_config(False, 64, 3)),
+                                          (40, 640, 4096, ops.gemm_config(True, 64, 8)), (256, 1280, 8192, 0), (64, 1280, 8192, 0)])
 def test_gemm_fp8_block_scaled(M, N, K, config):
     g = torch.Generator().manual_seed(6)
     x = (torch.randn(M, K, generator=g) * torch.rand(M, 1, generator=g) * 4).bfloat16()
@@ -172,6 +176,9 @@ def test_gemm_fp8_block_scaled(M, N, K, config):
     want = ref.linear_fp8_block(xq, xs, wq, ws)             # oracle: dequantise both operands, fp32 matmul
     y = ops.linear_fp8((xq.to(DEV), xs.to(DEV)), wq.to(DEV), ws.to(DEV), config=config)
     _close(y, want, 0.02 * want.abs().max().item() + 1e-2, 1.5e-2)
+    # again: split-K semaphores must be back at zero, and the result must not depend on which CTA arrived last
+    y_again = ops.linear_fp8((xq.to(DEV), xs.to(DEV)), wq.to(DEV), ws.to(DEV), config=config)
+    assert torch.equal(y, y_again)
     # end to end with the device quantiser: compare against the unquantised product with fp8-sized tolerance
     y2 = ops.linear_fp8(x.to(DEV), wq.to(DEV), ws.to(DEV), config=config)
     full = x.float() @ ref.dequant_e4m3_128x128(wq, ws).t()
