@@ -157,6 +157,8 @@ def main() -> None:
         n = 0
         while True:
             i = state["next"] + n
+            if fixed is not None and i >= len(trace):
+                break           # fixed-batch configurations are one batch, present at t = 0: nothing arrives later
             req = trace[i % len(trace)]
             arrival = req.arrival + (i // len(trace)) * (trace[-1].arrival + 1.0 / max(args.rate, 1e-9))
             if arrival > now:

@@ -228,11 +228,31 @@ class LLMEngine:
         if params is None or isinstance(params, SamplingParams):
             params = [params] * len(prompts)
         rids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
-        while self.has_unfinished():
-            self.step()
+        if self.cfg.lockstep and self._lockstep_group() is not None:
+            # ranks serve different requests but must take the same number of steps: go on (idle steps join the MoE
+            # layers) until no rank has work left
+            while self._any_rank_busy():
+                self.step()
+        else:
+            while self.has_unfinished():
+                self.step()
         if self.device.type == "cuda":
             ops.check_status(self.device)
         return [list(self.requests[r].output_ids) for r in rids]
+
+    def _lockstep_group(self):
+        ep = getattr(self.model, "ep", None)
+        info = getattr(ep, "info", None)
+        if info is None or info.world_size == 1:
+            return None
+        return getattr(info, "host_group", None)
+
+    def _any_rank_busy(self) -> bool:
+        import torch.distributed as dist
+
+        flag = torch.tensor([1 if self.has_unfinished() else 0], dtype=torch.int64)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self._lockstep_group())
+        return bool(flag[0])
 
     # ------------------------------------------------------------------------------------------------
     def metrics(self) -> dict:

@@ -80,6 +80,10 @@ class ModelRunner:
             b = b * 2 if b < 16 else b + max(16, b // 4) // 16 * 16
         self.buckets.append(cfg.max_num_seqs)
         self.graph_pool = None           # memory pool shared by the decode graphs (they never replay concurrently)
+        # Expert parallelism: every rank must run the same number of MoE layer calls per step, so a decode graph can
+        # only be captured when all ranks capture together (at start-up); a bucket that is missing runs eagerly.
+        ep = getattr(model, "ep", None)
+        self.ep = ep if ep is not None and getattr(ep, "world_size", 1) > 1 else None
 
     def capture_graphs(self, buckets=None) -> int:
         """Capture the decode graph of every batch-size bucket now, largest first so that the smaller ones reuse its
@@ -124,7 +128,9 @@ class ModelRunner:
         self.last_num_tokens = int(batch.num_tokens)
         if (self.use_graphs and batch.num_prefill == 0 and batch.num_decode > 0
                 and all(s.params.temperature <= 0.0 for s in states)):
-            return self._execute_decode_graph(batch)
+            g = self.graphs.get(self._bucket(int(batch.num_seqs)))
+            if self.ep is None or (g is not None and g.usable()):
+                return self._execute_decode_graph(batch)
         st = self.staging
         st.begin()
         T, B = int(batch.num_tokens), int(batch.num_seqs)
@@ -213,6 +219,8 @@ class ModelRunner:
             self.step_events[1].record()
         self.graph_launches += 1
         self.graph_kernel_launches += g.kernel_launches
+        if self.ep is not None:
+            self.ep._calls += g.ep_calls     # the replay ran that many MoE layers: keep the buffer-bank parity in step
         self.ids_host[:B].copy_(g.ids[:B], non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
         self.d2h_bytes = B * 8
@@ -253,6 +261,8 @@ class _DecodeGraph:
         model, caches = runner.model, runner.kv_caches
 
         comm = getattr(model, "comm", None)
+        ep = runner.ep
+        calls0 = ep._calls if ep is not None else 0
 
         def run():
             if comm is not None and hasattr(comm, "begin_graph"):
@@ -269,6 +279,9 @@ class _DecodeGraph:
             run()
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
+        # the eager pass ran its MoE layers on the device; the captured pass below only records them
+        self.ep_calls = (ep._calls - calls0) if ep is not None else 0
+        self.ep_parity = (ep._calls & 1) if ep is not None else 0
         before = ops.launch_count
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph, pool=runner.graph_pool):
@@ -277,6 +290,14 @@ class _DecodeGraph:
             runner.graph_pool = self.graph.pool()
         self.kernel_launches = ops.launch_count - before
         ops.launch_count = before
+        if ep is not None:
+            ep._calls -= self.ep_calls
+
+    def usable(self) -> bool:
+        """Under expert parallelism the graph holds the receive-buffer bank (call parity) of each MoE layer as it was at
+        capture: it may replay only from the same parity, which an even number of MoE layers per step guarantees."""
+        ep = self.runner.ep
+        return ep is None or (self.ep_calls % 2 == 0 and (ep._calls & 1) == self.ep_parity)
 
     def stage(self, batch, B: int) -> int:
         bb = self.bb

@@ -57,3 +57,9 @@ def test_tensor_parallel_llama_matches_single_process_model():
     n = 2
     p = _run("mp_tp_engine.py", n, 29617)
     assert f"TP_ENGINE_OK {n}" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_engine_eager_and_graph_decode_agree():
+    p = _run("mp_ep_engine.py", 2, 29618, extra_env={"NCCL_NVLS_ENABLE": "0"})
+    assert "EP_ENGINE_OK 2" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
