@@ -54,9 +54,12 @@ class _Reader:
 
 
 def load_safetensors_into(model, path: str | Path) -> None:
-    """Fill a `LlamaModel` from a Hugging Face Llama-family checkpoint directory."""
+    """Fill a model from a Hugging Face checkpoint directory: Llama family, or DeepSeek-V2(-Lite) (MLA + MoE)."""
     rd = _Reader(read_safetensors_index(path))
     cfg = model.cfg
+    if getattr(cfg, "architecture", "llama") == "deepseek_v2":
+        _load_deepseek_v2(model, rd)
+        return
     model.layers.clear()
     model.load_tensor("embed", rd.get("model.embed_tokens.weight"))
     for i in range(cfg.num_layers):
@@ -78,6 +81,87 @@ def load_safetensors_into(model, path: str | Path) -> None:
     model.load_tensor("final_norm", rd.get("model.norm.weight"))
     head = "lm_head.weight" if rd.has("lm_head.weight") else "model.embed_tokens.weight"
     model.load_tensor("lm_head", rd.get(head))
+
+
+def _load_deepseek_v2(model, rd: _Reader) -> None:
+    """HF `DeepseekV2ForCausalLM` names -> `DeepseekV2Model` layers. Each rank reads only its slice of the routed
+    experts (expert parallelism shards at load); `kv_b_proj` [H * (nope + v), kv_lora] is split into the per-head
+    up-projections W_UK and W_UV that the model folds into its query / output weights on CUDA."""
+    from ..models.deepseek_v2 import DsLayer
+    from ..ops import reference
+
+    cfg = model.cfg
+    if rd.has("model.layers.0.self_attn.q_a_proj.weight"):
+        raise NotImplementedError("DeepSeek-V2 checkpoints with a low-rank query projection (q_lora_rank) are not supported; V2-Lite is")
+    put = model._put
+    H, nope, vdim = model.H, model.nope, model.vdim
+    model.layers.clear()
+    model.embed = put(rd.get("model.embed_tokens.weight"))
+    e0 = model.ep_rank * model.e_local
+    for i in range(cfg.num_layers):
+        p = f"model.layers.{i}."
+        kv_b = rd.get(p + "self_attn.kv_b_proj.weight").view(H, nope + vdim, model.lora)
+        lw = DsLayer(
+            attn_norm=put(rd.get(p + "input_layernorm.weight")), wq=put(rd.get(p + "self_attn.q_proj.weight")),
+            w_kv_a=put(rd.get(p + "self_attn.kv_a_proj_with_mqa.weight")), kv_a_norm=put(rd.get(p + "self_attn.kv_a_layernorm.weight")),
+            w_uk=put(kv_b[:, :nope]), w_uv=put(kv_b[:, nope:]), wo=put(rd.get(p + "self_attn.o_proj.weight")),
+            mlp_norm=put(rd.get(p + "post_attention_layernorm.weight")))
+        if rd.has(p + "mlp.gate_proj.weight"):
+            lw.w_gu = put(reference.interleave_gate_up(rd.get(p + "mlp.gate_proj.weight"), rd.get(p + "mlp.up_proj.weight")))
+            lw.w_down = put(rd.get(p + "mlp.down_proj.weight"))
+        else:
+            lw.w_router = put(rd.get(p + "mlp.gate.weight"))
+            if rd.has(p + "mlp.shared_experts.gate_proj.weight"):
+                lw.w_shared_gu = put(reference.interleave_gate_up(rd.get(p + "mlp.shared_experts.gate_proj.weight"),
+                                                                  rd.get(p + "mlp.shared_experts.up_proj.weight")))
+                lw.w_shared_down = put(rd.get(p + "mlp.shared_experts.down_proj.weight"))
+            gates, ups, downs = [], [], []
+            for e in range(e0, e0 + model.e_local):
+                q = f"{p}mlp.experts.{e}."
+                gates.append(rd.get(q + "gate_proj.weight"))
+                ups.append(rd.get(q + "up_proj.weight"))
+                downs.append(rd.get(q + "down_proj.weight"))
+            lw.w_exp_down = put(torch.stack(downs))
+            if model.ep is not None:
+                lw.w_exp_gu_il = put(torch.stack([reference.interleave_gate_up(g, u) for g, u in zip(gates, ups)]))
+            else:
+                lw.w_exp_gu = put(torch.stack([torch.cat([g, u], dim=0) for g, u in zip(gates, ups)]))
+        model.layers.append(lw)
+    model.final_norm = put(rd.get("model.norm.weight"))
+    model.lm_head = put(rd.get("lm_head.weight" if rd.has("lm_head.weight") else "model.embed_tokens.weight"))
+    model.finalize()
+
+
+def deepseek_v2_state_dict(model) -> dict:
+    """HF-named tensors of a `DeepseekV2Model` that still holds its factored weights (a CPU model, all experts local):
+    the inverse of the loader, used to write test checkpoints."""
+    from ..ops import reference
+
+    out = {"model.embed_tokens.weight": model.embed, "model.norm.weight": model.final_norm, "lm_head.weight": model.lm_head}
+    for i, lw in enumerate(model.layers):
+        p = f"model.layers.{i}."
+        out[p + "input_layernorm.weight"] = lw.attn_norm
+        out[p + "post_attention_layernorm.weight"] = lw.mlp_norm
+        out[p + "self_attn.q_proj.weight"] = lw.wq
+        out[p + "self_attn.kv_a_proj_with_mqa.weight"] = lw.w_kv_a
+        out[p + "self_attn.kv_a_layernorm.weight"] = lw.kv_a_norm
+        out[p + "self_attn.kv_b_proj.weight"] = torch.cat([lw.w_uk, lw.w_uv], dim=1).reshape(-1, lw.w_uk.shape[2])
+        out[p + "self_attn.o_proj.weight"] = lw.wo
+        if lw.w_gu is not None:
+            g, u = reference.deinterleave_gate_up(lw.w_gu)
+            out[p + "mlp.gate_proj.weight"], out[p + "mlp.up_proj.weight"], out[p + "mlp.down_proj.weight"] = g, u, lw.w_down
+        else:
+            out[p + "mlp.gate.weight"] = lw.w_router
+            if lw.w_shared_gu is not None:
+                g, u = reference.deinterleave_gate_up(lw.w_shared_gu)
+                out[p + "mlp.shared_experts.gate_proj.weight"], out[p + "mlp.shared_experts.up_proj.weight"] = g, u
+                out[p + "mlp.shared_experts.down_proj.weight"] = lw.w_shared_down
+            f = lw.w_exp_gu.shape[1] // 2
+            for e in range(lw.w_exp_gu.shape[0]):
+                q = f"{p}mlp.experts.{e}."
+                out[q + "gate_proj.weight"], out[q + "up_proj.weight"] = lw.w_exp_gu[e, :f], lw.w_exp_gu[e, f:]
+                out[q + "down_proj.weight"] = lw.w_exp_down[e]
+    return out
 
 
 def save_llama_safetensors(model_full: dict, path: str | Path, config: dict) -> None:

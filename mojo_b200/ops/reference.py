@@ -168,6 +168,13 @@ def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor, block: int = 16
     return torch.stack([g, u], dim=1).reshape(2 * f, k).contiguous()
 
 
+def deinterleave_gate_up(w_gu: torch.Tensor, block: int = 16):
+    """Inverse of `interleave_gate_up`: (w_gate [F, K], w_up [F, K])."""
+    two_f, k = w_gu.shape
+    v = w_gu.reshape(two_f // (2 * block), 2, block, k)
+    return v[:, 0].reshape(two_f // 2, k).contiguous(), v[:, 1].reshape(two_f // 2, k).contiguous()
+
+
 def linear_swiglu_interleaved(x: torch.Tensor, w_gu: torch.Tensor, block: int = 16) -> torch.Tensor:
     """silu(x @ Wg.T) * (x @ Wu.T) for a weight stored by `interleave_gate_up`."""
     y = x.float() @ w_gu.float().t()  # [M, 2F] interleaved

@@ -93,3 +93,62 @@ def test_absorbed_attention_path_matches_factored_path():
     assert lw2.wq is None and lw2.w_qa.shape == (cfg.num_heads * 576 + 576, cfg.hidden_size)
     assert torch.equal(cache_a, cache_b)               # both wrote the same latents
     assert torch.allclose(got, want, atol=2e-5, rtol=1e-4), (got - want).abs().max()
+
+
+def _write_tiny_deepseek_checkpoint(tmp_path, model):
+    from mojo_b200.loaders.safetensors_loader import deepseek_v2_state_dict, save_llama_safetensors
+
+    cfg = model.cfg
+    hf_cfg = {"architectures": ["DeepseekV2ForCausalLM"], "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers,
+              "num_attention_heads": cfg.num_heads, "num_key_value_heads": cfg.num_heads, "intermediate_size": cfg.intermediate_size,
+              "vocab_size": cfg.vocab_size, "rms_norm_eps": cfg.rms_norm_eps, "rope_theta": cfg.rope_theta,
+              "max_position_embeddings": cfg.max_position_embeddings, "kv_lora_rank": cfg.kv_lora_rank, "q_lora_rank": None,
+              "qk_rope_head_dim": cfg.qk_rope_head_dim, "qk_nope_head_dim": cfg.qk_nope_head_dim, "v_head_dim": cfg.v_head_dim,
+              "n_routed_experts": cfg.n_routed_experts, "n_shared_experts": cfg.n_shared_experts,
+              "num_experts_per_tok": cfg.num_experts_per_tok, "moe_intermediate_size": cfg.moe_intermediate_size,
+              "first_k_dense_replace": cfg.first_k_dense_replace, "routed_scaling_factor": cfg.routed_scaling_factor,
+              "norm_topk_prob": cfg.norm_topk_prob}
+    save_llama_safetensors(deepseek_v2_state_dict(model), tmp_path, hf_cfg)
+
+
+def test_deepseek_hf_checkpoint_roundtrip_and_expert_slicing(tmp_path):
+    """A checkpoint in the Hugging Face DeepseekV2ForCausalLM layout (kv_b_proj fused, one tensor per expert
+    projection) loads into the same model; an expert-parallel rank reads only its own experts."""
+    from mojo_b200.loaders import load_safetensors_into
+    from mojo_b200.models import build_model
+    from mojo_b200.pipelines import LLM, PipelineConfig
+
+    src = build_model(tiny_deepseek(), "cpu", torch.float32).init_random(3, std=0.05)
+    _write_tiny_deepseek_checkpoint(tmp_path, src)
+    llm = LLM(PipelineConfig(model=str(tmp_path), device="cpu", dtype="float32", page_size=16, num_pages=32, max_num_seqs=4,
+                             max_num_batched_tokens=64, max_model_len=128))
+    got = llm.engine.model
+    assert got.cfg.architecture == "deepseek_v2" and len(got.layers) == len(src.layers)
+    for a, b in zip(src.layers, got.layers):
+        for name in ("wq", "w_kv_a", "kv_a_norm", "w_uk", "w_uv", "wo", "w_gu", "w_down", "w_router", "w_shared_gu", "w_shared_down",
+                     "w_exp_gu", "w_exp_down"):
+            x, y = getattr(a, name), getattr(b, name)
+            assert (x is None) == (y is None), name
+            if x is not None:
+                assert torch.equal(x, y), name
+    prompt = torch.randint(0, 1024, (12,), generator=torch.Generator().manual_seed(5)).tolist()
+    out = llm.generate([prompt], SamplingParams(max_tokens=5))[0]
+    ids = list(prompt)
+    for t in range(5):
+        nxt = int(torch.argmax(dense_logits(src, ids)))
+        assert nxt == out.token_ids[t]
+        ids.append(nxt)
+
+    class _Ep:          # stands in for the expert-parallel communicator: only its geometry matters at load time
+        world_size, rank = 2, 1
+
+    part = build_model(tiny_deepseek(), "cpu", torch.float32, ep=_Ep())
+    load_safetensors_into(part, tmp_path)
+    moe = [lw for lw in part.layers if lw.w_router is not None]
+    ref_moe = [lw for lw in src.layers if lw.w_router is not None]
+    half = tiny_deepseek().n_routed_experts // 2
+    for a, b in zip(ref_moe, moe):
+        assert b.w_exp_gu is None and b.w_exp_gu_il.shape[0] == half
+        assert torch.equal(b.w_exp_down, a.w_exp_down[half:])
+        f = a.w_exp_gu.shape[1] // 2
+        assert torch.equal(b.w_exp_gu_il[0], ref.interleave_gate_up(a.w_exp_gu[half, :f], a.w_exp_gu[half, f:]))
