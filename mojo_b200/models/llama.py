@@ -67,7 +67,11 @@ class LlamaModel:
         self.dtype = dtype
         self.comm = comm or NoComm()
         self.tp = self.comm.world_size
-        assert cfg.num_heads % self.tp == 0, "query heads must divide by tp"
+        if cfg.num_heads % self.tp != 0:
+            raise ValueError(f"{cfg.num_heads} query heads do not divide by tensor-parallel degree {self.tp}")
+        if cfg.intermediate_size % (16 * self.tp) != 0:
+            # the SwiGLU GEMM epilogue pairs gate and up rows in blocks of 16 within each rank's shard
+            raise ValueError(f"FFN width {cfg.intermediate_size} must be a multiple of 16 x tensor-parallel degree {self.tp}")
         self.n_q = cfg.num_heads // self.tp
         # kv heads are replicated when tp exceeds their number
         self.n_kv = max(1, cfg.num_kv_heads // self.tp)

@@ -52,7 +52,14 @@ class _Tokenizer:
 
 
 class LLM:
-    def __init__(self, config: PipelineConfig, comm=None):
+    """`LLM(config).generate(...)`. With `tensor_parallel` or `expert_parallel` above 1 the process must be one of
+    that many ranks started by `python -m torch.distributed.run --nproc-per-node N ...` (one rank per GPU): the
+    constructor joins the process group and builds the communicator itself (fused GEMM+collective kernels over
+    symmetric memory on CUDA, `torch.distributed` collectives on CPU); every rank then makes the same `generate`
+    calls (tensor parallelism) or serves its own prompts in lock-step (expert parallelism with data-parallel
+    attention). A ready-made communicator can be passed instead (`comm` for tensor, `ep` for expert parallelism)."""
+
+    def __init__(self, config: PipelineConfig, comm=None, ep=None):
         self.config = config
         device = config.device or ("cuda" if torch.cuda.is_available() else "cpu")
         dtype = getattr(torch, config.dtype) if device.startswith("cuda") else torch.float32
@@ -75,7 +82,10 @@ class LLM:
         if config.quantization:
             mcfg.quantization = config.quantization
         self.model_config = mcfg
-        model = build_model(mcfg, device, dtype, comm=comm)
+        degree = max(config.tensor_parallel, config.expert_parallel)
+        if degree > 1 and comm is None and ep is None:
+            comm, ep, device = self._join_ranks(mcfg, device, degree)
+        model = build_model(mcfg, device, dtype, comm=comm, ep=ep)
         if config.random_init or (not is_gguf and not (Path(src) / "config.json").exists()):
             model.init_random(config.seed)
         elif is_gguf:
@@ -95,9 +105,41 @@ class LLM:
                             max_num_batched_tokens=config.max_num_batched_tokens, max_model_len=config.max_model_len,
                             enable_prefix_cache=config.enable_prefix_cache, enable_chunked_prefill=config.enable_chunked_prefill,
                             eos_token_id=config.eos_token_id, seed=config.seed, use_cuda_graphs=config.use_cuda_graphs,
-                            tp_size=config.tensor_parallel, ep_size=config.expert_parallel)
+                            tp_size=config.tensor_parallel, ep_size=config.expert_parallel,
+                            lockstep=ep is not None and getattr(ep, "world_size", 1) > 1)
         self.engine = LLMEngine(ecfg, model=model, comm=comm)
+        self.comm, self.ep = comm, ep
         self.tokenizer = _Tokenizer(config.tokenizer)
+
+    def _join_ranks(self, mcfg, device: str, degree: int):
+        """Join the process group of a `torch.distributed.run` launch and build this rank's communicator."""
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        if world != degree:
+            raise RuntimeError(f"parallel degree {degree} needs {degree} ranks (WORLD_SIZE={world}): start the program with "
+                               f"`python -m torch.distributed.run --nproc-per-node {degree} --master-addr 127.0.0.1 ...`")
+        from ..parallel import init_distributed
+
+        info = init_distributed("cuda" if device.startswith("cuda") else "cpu")
+        cfg = self.config
+        if cfg.expert_parallel > 1:
+            if mcfg.architecture != "deepseek_v2":
+                raise ValueError("expert_parallel applies to mixture-of-experts models")
+            if info.device.type != "cuda":
+                raise RuntimeError("expert parallelism runs on CUDA devices")
+            from ..parallel.ep import EPComm
+
+            ep = EPComm(info, mcfg.n_routed_experts, mcfg.hidden_size, mcfg.moe_intermediate_size, mcfg.num_experts_per_tok,
+                        max_tokens=cfg.max_num_batched_tokens)
+            return None, ep, str(info.device)
+        if info.device.type == "cuda":
+            from ..parallel.fused import FusedTPComm
+
+            comm = FusedTPComm(info, max_tokens=cfg.max_num_batched_tokens, hidden=mcfg.hidden_size, max_k=mcfg.hidden_size)
+        else:
+            from ..parallel.tp import NcclTPComm
+
+            comm = NcclTPComm(info)
+        return comm, None, str(info.device)
 
     def generate(self, prompts, sampling_params: SamplingParams | list | None = None) -> list[GenerationOutput]:
         ids = [self.tokenizer.encode(p) for p in prompts]

@@ -94,3 +94,41 @@ def test_openai_server_endpoints():
         assert c.post("/v1/completions", json={"max_tokens": 3}).status_code == 400
         assert "b2_output_tokens" in c.get("/metrics").text
     app.state.engine.shutdown()
+
+
+def test_llm_tensor_parallel_joins_ranks_itself_on_cpu(tmp_path):
+    """`LLM(PipelineConfig(tensor_parallel=2))` under a two-process gloo launch: each rank loads its shard of a
+    safetensors checkpoint and produces the same tokens as one process."""
+    import os
+    import subprocess
+    import sys
+
+    from mojo_b200.loaders.safetensors_loader import save_llama_safetensors
+
+    hid, heads, kv, d, ffn, vocab, layers = 256, 4, 2, 64, 704, 1000, 2
+    g = torch.Generator().manual_seed(1)
+    full = {"model.embed_tokens.weight": torch.randn(vocab, hid, generator=g) * 0.05, "model.norm.weight": torch.ones(hid),
+            "lm_head.weight": torch.randn(vocab, hid, generator=g) * 0.05}
+    for i in range(layers):
+        p = f"model.layers.{i}."
+        full[p + "input_layernorm.weight"] = torch.ones(hid)
+        full[p + "post_attention_layernorm.weight"] = torch.ones(hid)
+        for name, shape in (("self_attn.q_proj", (heads * d, hid)), ("self_attn.k_proj", (kv * d, hid)), ("self_attn.v_proj", (kv * d, hid)),
+                            ("self_attn.o_proj", (hid, heads * d)), ("mlp.gate_proj", (ffn, hid)), ("mlp.up_proj", (ffn, hid)),
+                            ("mlp.down_proj", (hid, ffn))):
+            full[p + name + ".weight"] = torch.randn(*shape, generator=g) * 0.05
+    save_llama_safetensors(full, tmp_path, {"architectures": ["LlamaForCausalLM"], "hidden_size": hid, "num_hidden_layers": layers,
+                                            "num_attention_heads": heads, "num_key_value_heads": kv, "intermediate_size": ffn,
+                                            "vocab_size": vocab, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+                                            "max_position_embeddings": 256, "tie_word_embeddings": False})
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29641", os.path.join(root, "tests", "mp_pipeline_cpu.py")]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", B2_TEST_CHECKPOINT=str(tmp_path))
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=root)
+    assert "PIPELINE_TP_OK 2" in p.stdout, p.stdout[-2000:] + p.stderr[-3000:]
+
+
+def test_llm_parallel_degree_without_ranks_is_refused():
+    with pytest.raises(RuntimeError, match="torch.distributed.run"):
+        LLM(PipelineConfig(model="tiny-llama", random_init=True, device="cpu", tensor_parallel=2))
