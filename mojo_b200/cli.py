@@ -48,6 +48,12 @@ def _cmd_bench(a) -> None:
     llm = LLM(cfg)
     eng = llm.engine
     vocab = llm.model_config.vocab_size
+    # keep prompt + output inside the engine's context limit (it is capped by the model's position range)
+    room = eng.cfg.max_model_len - 1
+    a.output_max = max(1, min(a.output_max, room // 2))
+    a.output_min = min(a.output_min, a.output_max)
+    a.prompt_max = max(1, min(a.prompt_max, room - a.output_max))
+    a.prompt_min = min(a.prompt_min, a.prompt_max)
     if a.trace == "poisson":
         trace = poisson_trace(a.requests, a.rate, (a.prompt_min, a.prompt_max), (a.output_min, a.output_max), vocab, seed=a.seed)
     else:

@@ -82,6 +82,10 @@ class LLMEngine:
         self.device = torch.device(cfg.device)
         self.model = model if model is not None else build_model(cfg.model, self.device, cfg.dtype, comm=comm).init_random(cfg.seed)
         self.comm = comm
+        # positions beyond the model's rotary table do not exist: the context limit cannot exceed it
+        max_pos = int(getattr(self.model.cfg, "max_position_embeddings", 0) or 0)
+        if max_pos and cfg.max_model_len > max_pos:
+            cfg.max_model_len = max_pos
         num_pages = cfg.num_pages or self._auto_num_pages()
         self.kv_caches = self.model.allocate_kv_cache(num_pages, cfg.page_size)
         self.kv = self.C.KVCacheManager(num_pages, cfg.page_size, cfg.enable_prefix_cache)
@@ -130,12 +134,20 @@ class LLMEngine:
         rid = self._next_id if request_id is None else request_id
         self._next_id = max(self._next_id, rid) + 1
         prompt = np.asarray(prompt_ids, dtype=np.int32)
+        self.check_prompt_len(len(prompt))
         max_new = max(1, min(params.max_tokens, self.cfg.max_model_len - len(prompt)))
         now = time.perf_counter() if arrival is None else arrival
         self.scheduler.add_request(rid, prompt, max_new, now)
         self.requests[rid] = RequestState(rid, len(prompt), params, now)
         self._prompts[rid] = prompt
         return rid
+
+    def check_prompt_len(self, n: int) -> None:
+        """A request needs at least one prompt token and room for at least one generated token."""
+        if n < 1:
+            raise ValueError("empty prompt")
+        if n >= self.cfg.max_model_len:
+            raise ValueError(f"prompt of {n} tokens does not fit the context limit of {self.cfg.max_model_len} tokens")
 
     def prompt_of(self, rid: int) -> np.ndarray:
         return self._prompts[rid]

@@ -75,6 +75,7 @@ class AsyncEngine:
     _ids_lock = threading.Lock()
 
     def submit(self, ids, sp: SamplingParams) -> tuple[int, asyncio.Queue]:
+        self.engine.check_prompt_len(len(ids))      # ValueError -> 400 at the endpoint, before anything is queued
         with AsyncEngine._ids_lock:
             AsyncEngine._ids += 1
             rid = AsyncEngine._ids
@@ -171,7 +172,10 @@ def build_app(llm, model_name: str = "mojo_b200"):
         except ValueError as e:
             raise HTTPException(status_code=400, detail=str(e))
         sp = _sampling_from(body)
-        rid, q = aeng.submit(ids, sp)
+        try:
+            rid, q = aeng.submit(ids, sp)
+        except ValueError as e:
+            raise HTTPException(status_code=400, detail=str(e))
         cid = "cmpl-" + uuid.uuid4().hex[:24]
         created = int(time.time())
         if body.get("stream"):
@@ -191,7 +195,10 @@ def build_app(llm, model_name: str = "mojo_b200"):
             raise HTTPException(status_code=400, detail="messages is required")
         ids = tok.apply_chat_template(messages)
         sp = _sampling_from(body, default_max=256)
-        rid, q = aeng.submit(ids, sp)
+        try:
+            rid, q = aeng.submit(ids, sp)
+        except ValueError as e:
+            raise HTTPException(status_code=400, detail=str(e))
         cid = "chatcmpl-" + uuid.uuid4().hex[:24]
         created = int(time.time())
         if body.get("stream"):

@@ -92,6 +92,10 @@ def test_openai_server_endpoints():
         r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3}).json()
         assert r["object"] == "chat.completion" and r["usage"]["completion_tokens"] == 3
         assert c.post("/v1/completions", json={"max_tokens": 3}).status_code == 400
+        # a prompt that leaves no room in the context is refused before it reaches the engine thread
+        too_long = c.post("/v1/completions", json={"prompt": [7] * llm.engine.cfg.max_model_len, "max_tokens": 3})
+        assert too_long.status_code == 400 and "context limit" in too_long.json()["detail"]
+        assert c.post("/v1/completions", json={"prompt": [], "max_tokens": 3}).status_code == 400
         assert "b2_output_tokens" in c.get("/metrics").text
     app.state.engine.shutdown()
 

@@ -191,3 +191,15 @@ def test_kv_caches_are_guarded_when_the_switch_is_set(monkeypatch):
     monkeypatch.setenv("B2_GUARD", "0")
     plain = model.allocate_kv_cache(4, 16)
     assert not hasattr(plain[0][0], "_b2_guard")
+
+
+def test_context_limit_is_capped_by_the_position_table_and_enforced_at_admission():
+    cfg = tiny_llama()
+    ecfg = EngineConfig(model=cfg, device="cpu", dtype=torch.float32, page_size=16, num_pages=32, max_num_seqs=2,
+                        max_num_batched_tokens=64, max_model_len=1 << 20)
+    eng = LLMEngine(ecfg)
+    assert eng.cfg.max_model_len == cfg.max_position_embeddings
+    with pytest.raises(ValueError, match="context limit"):
+        eng.add_request(list(range(cfg.max_position_embeddings)))
+    with pytest.raises(ValueError, match="empty prompt"):
+        eng.add_request([])
