@@ -4,7 +4,7 @@ Small, self-terminating workloads (inputs larger than the 126 MB L2, a few GB at
 profiler capture of one kernel; with `--time` the case is timed with CUDA events instead and one JSON line is printed.
 Cases: gemm_large, gemm_pair (the same product on CTA pairs), gemm_prefill, gemm_decode, gemm_swiglu, gemm_fp8,
 gemm_fp8_decode, gemm_fp8_decode_nosplit (a narrow tensor-parallel shard at 256 tokens, with and without split-K),
-attn_decode, attn_prefill, mla_decode, rmsnorm, sampling.
+attn_decode, attn_prefill, mla_decode, mla_prefill, rmsnorm, sampling.
 """
 from __future__ import annotations
 
@@ -92,6 +92,19 @@ def _case(name: str):
         ql, qr = rnd(B, H, 512, scale=0.3), rnd(B, H, 64, scale=0.3)
         cl = torch.full((B,), ctx, dtype=torch.int32, device=DEV)
         return (lambda: ops.mla_decode(ql, qr, cache, cl, bt, 1 / math.sqrt(192), ctx)), 2.0 * B * H * ctx * (576 + 512), B * ctx * 576 * 2
+    if name == "mla_prefill":
+        # one engine step of DeepSeek-V2-Lite prefill: eight 512-token prompts, every token a row group of the latent
+        # attention kernel; the query parts are column slices of the fused projection output, as in the model
+        S, L, H, page = 8, 512, 16, 128
+        pages = L // page
+        bt = torch.arange(S * pages, dtype=torch.int32).view(S, pages).to(DEV)
+        cache = rnd(S * pages + 1, page, 576, scale=0.5)
+        qa = rnd(S * L, H * 576 + 576, scale=0.3)
+        ql, qr = qa[:, :H * 512].unflatten(1, (H, 512)), qa[:, H * 512:H * 576].unflatten(1, (H, 64))
+        cu = torch.arange(0, (S + 1) * L, L, dtype=torch.int32, device=DEV)
+        meta = ops.AttnMeta(cu, torch.full((S,), L, dtype=torch.int32, device=DEV), bt, 0, L, L)
+        flops = 2.0 * S * H * (576 + 512) * L * (L + 1) / 2
+        return (lambda: ops.mla_attend(ql, qr, cache, meta, 1 / math.sqrt(192))), flops, S * L * 576 * 2 + 2 * S * L * H * 576 * 2
     if name == "rmsnorm":
         rows, h = 65536, 4096
         x, r, w = rnd(rows, h), rnd(rows, h), torch.ones(h, device=DEV, dtype=torch.bfloat16)
