@@ -129,9 +129,18 @@ def main(argv=None) -> None:
     b.set_defaults(fn=_cmd_bench)
     o = sub.add_parser("bench-ops", help="run as: python -m torch.distributed.run ... -m mojo_b200.bench_ops")
     o.set_defaults(fn=lambda a: print("launch with: python -m torch.distributed.run --nproc-per-node N -m mojo_b200.bench_ops"))
+    sub.add_parser("bench-kernels", help="micro-benchmarks of kernels and host runtime; options as in python -m mojo_b200.bench_kernels --help")
     d = sub.add_parser("deviceinfo")
     d.set_defaults(fn=_cmd_deviceinfo)
-    a = ap.parse_args(argv)
+    import sys
+
+    args = list(sys.argv[1:] if argv is None else argv)
+    if args and args[0] == "bench-kernels":      # its own option parser takes the rest of the line
+        from . import bench_kernels
+
+        bench_kernels.main(args[1:])
+        return
+    a = ap.parse_args(args)
     a.fn(a)
 
 

@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "b2/engine.h"
+#include "b2/shape.h"
 #include "b2/symm_sim.h"
 
 namespace {
@@ -209,6 +210,23 @@ void collective_sim() {
   CHECK(!parse_fault("drop_signal:rank=x", &f));
 }
 
+// Shapes and strides as the kernels use them: the paged KV cache [pages, kv heads, page size, head dim].
+void shape_arithmetic() {
+  const auto cache = b2::make_shape(9, 2, 16, 128);
+  CHECK(cache.rank() == 4 && cache.numel() == 9 * 2 * 16 * 128);
+  const auto st = b2::row_major(cache);
+  CHECK(st[3] == 1 && st[2] == 128 && st[1] == 16 * 128 && st[0] == 2 * 16 * 128);
+  const b2::Coord<4> c = b2::make_shape(7, 1, 15, 127);
+  CHECK(st.offset(c) == ((7 * 2 + 1) * 16 + 15) * 128 + 127);
+  CHECK(b2::in_bounds(c, cache));
+  CHECK(!b2::in_bounds(b2::make_shape(9, 0, 0, 0), cache) && !b2::in_bounds(b2::make_shape(0, 0, -1, 0), cache));
+  for (int64_t i : {int64_t{0}, int64_t{1}, int64_t{4095}, int64_t{4096}, cache.numel() - 1}) {
+    const auto back = b2::delinearize(i, cache);
+    CHECK(b2::in_bounds(back, cache) && st.offset(back) == i);
+  }
+  CHECK(b2::make_shape(3, 4) == b2::make_shape(3, 4) && !(b2::make_shape(3, 4) == b2::make_shape(4, 3)));
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
@@ -219,6 +237,7 @@ int main(int argc, char** argv) {
   }
   if (only.empty() || only == "sched") scheduler_stress();
   if (only.empty() || only == "sim") collective_sim();
+  if (only.empty() || only == "shape") shape_arithmetic();
   if (g_failed != 0) {
     std::fprintf(stderr, "runtime self-test: %d check(s) failed\n", g_failed);
     return 1;

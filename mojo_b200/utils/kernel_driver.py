@@ -115,6 +115,10 @@ def _case(name: str):
     raise SystemExit(f"unknown case {name!r}")
 
 
+CASES = ("gemm_large", "gemm_pair", "gemm_prefill", "gemm_decode", "gemm_swiglu", "gemm_fp8", "gemm_fp8_decode", "gemm_fp8_decode_nosplit",
+         "attn_decode", "attn_prefill", "mla_decode", "mla_prefill", "rmsnorm", "sampling")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("case")
