@@ -148,7 +148,7 @@ def build_selftest(sanitizer: str = "address", out_dir: Path | None = None, verb
     flags = {"address": ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined", "-fno-omit-frame-pointer"],
              "thread": ["-fsanitize=thread"], "": []}[sanitizer]
     srcs = [CSRC / "tests" / "runtime_selftest.cpp", CSRC / "runtime" / "kv_manager.cpp", CSRC / "runtime" / "scheduler.cpp",
-            CSRC / "runtime" / "symm_sim.cpp"]
+            CSRC / "runtime" / "symm_sim.cpp", CSRC / "runtime" / "context.cpp", CSRC / "runtime" / "io.cpp"]
     _run(["g++", "-std=c++17", "-O1", "-g", *flags, f"-I{CSRC / 'include'}", *[str(x) for x in srcs], "-o", str(exe), "-pthread"], verbose)
     return exe
 

@@ -277,6 +277,7 @@ py::dict device_caps(int device) {
 
 void bind_ops_extra(py::module_& m);
 void bind_coll(py::module_& m);
+void bind_io(py::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "mojo_b200 native extension: sm_100a kernels + engine runtime";
@@ -312,4 +313,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("device_caps", &device_caps, py::arg("device") = 0);
   bind_ops_extra(m);
   bind_coll(m);
+  bind_io(m);
 }

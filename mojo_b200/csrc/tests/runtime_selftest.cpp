@@ -6,13 +6,19 @@
 //
 // Exit code 0 = every check passed. Each failed check prints one line and the process exits 1.
 #include <cstdio>
+#include <atomic>
 #include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <stdexcept>
 #include <random>
 #include <set>
 #include <string>
 #include <vector>
 
 #include "b2/engine.h"
+#include "b2/io.h"
+#include "b2/runtime.h"
 #include "b2/shape.h"
 #include "b2/symm_sim.h"
 
@@ -227,6 +233,93 @@ void shape_arithmetic() {
   CHECK(b2::make_shape(3, 4) == b2::make_shape(3, 4) && !(b2::make_shape(3, 4) == b2::make_shape(4, 3)));
 }
 
+// Worker pool: every index of a parallel loop runs exactly once, submitted tasks finish before wait_idle returns, a
+// throwing task is counted and does not take a worker down, nested use from the caller's thread makes progress.
+void worker_pool() {
+  b2::rt::WorkerPool pool(4);
+  std::vector<std::atomic<int>> hits(1000);
+  for (auto& h : hits) h.store(0);
+  pool.parallel_for(1000, [&](int64_t i) { hits[static_cast<size_t>(i)].fetch_add(1); });
+  for (auto& h : hits) CHECK(h.load() == 1);
+  std::atomic<int64_t> sum{0};
+  for (int i = 1; i <= 100; ++i) pool.submit([&sum, i] { sum.fetch_add(i); });
+  pool.submit([] { throw std::runtime_error("task failure"); });
+  pool.wait_idle();
+  CHECK(sum.load() == 5050);
+  CHECK(pool.failed_tasks() == 1);
+  pool.parallel_for(1, [&](int64_t) { sum.fetch_add(1); });
+  CHECK(sum.load() == 5051);
+  bool threw = false;
+  try {
+    pool.parallel_for(64, [](int64_t i) { if (i == 5) throw std::runtime_error("loop body failure"); });
+  } catch (const std::runtime_error&) {
+    threw = true;
+  }
+  (void)threw;   // the body that throws may run on a helper (swallowed) or on this thread (rethrown); both leave the pool usable
+  pool.parallel_for(8, [&](int64_t) { sum.fetch_add(1); });
+  CHECK(sum.load() == 5059);
+
+  auto& ctx = b2::rt::Context::instance();
+  static int inits = 0;
+  void* a = ctx.global("selftest.block", 64, [](void* p) { ++inits; static_cast<char*>(p)[0] = 7; });
+  void* b = ctx.global("selftest.block", 64, [](void* p) { ++inits; static_cast<char*>(p)[0] = 9; });
+  CHECK(a != nullptr && a == b && inits == 1 && static_cast<char*>(a)[0] == 7 && static_cast<char*>(a)[1] == 0);
+  CHECK(ctx.global("selftest.block", 128) == nullptr);            // same name, other size
+  CHECK(ctx.global_or_null("selftest.block") == a && ctx.global_or_null("selftest.none") == nullptr);
+  CHECK(ctx.pool().size() >= 1);
+}
+
+// A safetensors file written byte by byte here: header parsing (escapes, metadata, unknown keys), offsets, the copy
+// paths, and the errors a damaged file must raise instead of reading out of bounds.
+void safetensors_io(const std::string& dir) {
+  using b2::io::SafetensorsFile;
+  auto write = [&](const std::string& name, const std::string& header, const std::string& data, uint64_t claimed_len = UINT64_MAX) {
+    const std::string path = dir + "/" + name;
+    std::ofstream f(path, std::ios::binary);
+    uint64_t n = claimed_len == UINT64_MAX ? header.size() : claimed_len;
+    for (int i = 0; i < 8; ++i) f.put(static_cast<char>((n >> (8 * i)) & 0xff));
+    f << header << data;
+    return path;
+  };
+  const size_t big = 9u << 20;
+  std::string data(16 + 24 + big, '\0');
+  for (size_t i = 0; i < data.size(); ++i) data[i] = static_cast<char>((i * 131 + 7) & 0xff);
+  const std::string header =
+      std::string(R"({"__metadata__":{"format":"pt","note":"a\u00e9\n \ud83d\ude00"}, "w\"q":{"dtype":"F32","shape":[2,2],"data_offsets":[0,16],"extra":[1,{"x":null}]},)") +
+      R"("big":{"dtype":"U8","shape":[)" + std::to_string(big) + R"(],"data_offsets":[40,)" + std::to_string(40 + big) + R"(]},)" +
+      R"("b":{"dtype":"BF16","shape":[3,4],"data_offsets":[16,40]}}   )";
+  const std::string path = write("ok.safetensors", header, data);
+  {
+    SafetensorsFile f(path);
+    CHECK(f.names().size() == 3 && f.names()[0] == "w\"q" && f.names()[1] == "b" && f.names()[2] == "big");   // data order
+    CHECK(f.metadata().at("format") == "pt" && f.metadata().at("note") == "a\xc3\xa9\n \xf0\x9f\x98\x80");
+    CHECK(f.info("b").dtype == "BF16" && f.info("b").shape == std::vector<int64_t>({3, 4}) && f.info("b").nbytes() == 24);
+    CHECK(std::memcmp(f.tensor_data("b"), data.data() + 16, 24) == 0);
+    std::vector<char> out(big);
+    b2::io::parallel_copy(out.data(), f.tensor_data("big"), out.size());
+    CHECK(std::memcmp(out.data(), data.data() + 40, out.size()) == 0);
+    std::fill(out.begin(), out.end(), 0);
+    b2::io::parallel_copy(out.data(), f.tensor_data("big"), out.size(), 1);
+    CHECK(std::memcmp(out.data(), data.data() + 40, out.size()) == 0);
+    CHECK(!f.has("nope"));
+    bool threw = false;
+    try { f.info("nope"); } catch (const std::out_of_range&) { threw = true; }
+    CHECK(threw);
+  }
+  auto must_fail = [&](const std::string& p) {
+    bool threw = false;
+    try { SafetensorsFile f(p); } catch (const std::runtime_error&) { threw = true; }
+    CHECK(threw);
+  };
+  must_fail(dir + "/missing.safetensors");
+  must_fail(write("short_header.safetensors", "{}", "", 1000));                                                   // header length past the end
+  must_fail(write("range.safetensors", R"({"a":{"dtype":"F32","shape":[4],"data_offsets":[0,16]}})", "12345678"));     // data past the end
+  must_fail(write("mismatch.safetensors", R"({"a":{"dtype":"F32","shape":[3],"data_offsets":[0,16]}})", std::string(16, 'x')));
+  must_fail(write("garbage.safetensors", R"({"a":{"dtype":"F32","shape":[4 "data_offsets":[0,16]}})", std::string(16, 'x')));
+  must_fail(write("nofields.safetensors", R"({"a":{"dtype":"F32"}})", ""));
+  { SafetensorsFile empty(write("empty.safetensors", "{}", "")); CHECK(empty.names().empty()); }
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
@@ -238,6 +331,11 @@ int main(int argc, char** argv) {
   if (only.empty() || only == "sched") scheduler_stress();
   if (only.empty() || only == "sim") collective_sim();
   if (only.empty() || only == "shape") shape_arithmetic();
+  if (only.empty() || only == "pool") worker_pool();
+  if (only.empty() || only == "io") {
+    const char* tmp = std::getenv("B2_SELFTEST_DIR");
+    safetensors_io(tmp != nullptr ? tmp : "/tmp");
+  }
   if (g_failed != 0) {
     std::fprintf(stderr, "runtime self-test: %d check(s) failed\n", g_failed);
     return 1;

@@ -1,8 +1,10 @@
 """Hugging Face safetensors checkpoints -> model shards.
 
-Files are memory-mapped (`safetensors.safe_open`), tensors are read one layer at a time, sliced for this rank's
-tensor-parallel shard and copied to the device; nothing bigger than one layer is ever held on the host. This is the
-product's counterpart of the reference's buffered file layer (stdlib/src/builtin/file.mojo:71-498).
+Files are memory-mapped by the C++ runtime (`SafetensorsFile`: header parser, read-only mapping, tensors handed out
+as views of the mapping with no copy; whole-tensor reads go through the worker pool, to device memory through
+pinned staging buffers). Tensors are read one layer at a time, sliced for this rank's tensor-parallel shard and
+copied to the device; nothing bigger than one layer is ever held on the host. This is the product's counterpart of
+the reference's buffered file layer (stdlib/src/builtin/file.mojo:71-498).
 
 fp8 checkpoints in the 128x128 block-scaled format carry `<name>.weight` as float8_e4m3fn and
 `<name>.weight_scale_inv` as fp32 [ceil(N/128), ceil(K/128)]; both are kept as they are for the fp8 GEMM.
@@ -22,13 +24,13 @@ def read_safetensors_index(path: str | Path) -> dict[str, Path]:
     if idx.exists():
         wm = json.loads(idx.read_text())["weight_map"]
         return {k: path / v for k, v in wm.items()}
-    from safetensors import safe_open
+    from .. import _ext
 
+    C = _ext.require()
     out = {}
     for f in sorted(path.glob("*.safetensors")):
-        with safe_open(str(f), framework="pt") as sf:
-            for k in sf.keys():
-                out[k] = f
+        for k in C.SafetensorsFile(str(f)).keys():
+            out[k] = f
     if not out:
         raise FileNotFoundError(f"no safetensors files under {path}")
     return out
@@ -39,15 +41,23 @@ class _Reader:
         self.index = index
         self._open: dict[Path, object] = {}
 
-    def get(self, name: str) -> torch.Tensor:
-        from safetensors import safe_open
+    def _file(self, name: str):
+        from .. import _ext
 
         f = self.index[name]
         h = self._open.get(f)
         if h is None:
-            h = safe_open(str(f), framework="pt")
+            h = _ext.require().SafetensorsFile(str(f))
             self._open[f] = h
-        return h.get_tensor(name)
+        return h
+
+    def get(self, name: str) -> torch.Tensor:
+        """The tensor as a read-only view of the file mapping (no copy): slice it, then move the slice."""
+        return self._file(name).get(name)
+
+    def read_into(self, name: str, dst: torch.Tensor) -> None:
+        """Whole tensor straight into `dst` (host: parallel copy; device: through pinned staging)."""
+        self._file(name).read_into(name, dst)
 
     def has(self, name: str) -> bool:
         return name in self.index

@@ -183,3 +183,63 @@ def test_host_runtime_selftest_under_sanitizer(sanitizer, tmp_path):
     p = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300, env=env)
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-4000:]
     assert "runtime self-test: ok" in p.stdout
+
+
+def test_safetensors_reader_matches_the_reference_writer(tmp_path):
+    """Files written by the `safetensors` package read back bit for bit through the C++ reader: every dtype the
+    loaders use, zero-copy views, whole-tensor reads through the worker pool, metadata, and clean errors."""
+    from safetensors.torch import save_file
+
+    g = torch.Generator().manual_seed(0)
+    tensors = {
+        "a.bf16": torch.randn(33, 64, generator=g).bfloat16(), "b.f32": torch.randn(7, generator=g), "c.f16": torch.randn(3, 5, 2, generator=g).half(),
+        "d.i64": torch.arange(10), "e.u8": torch.randint(0, 255, (9 << 20,), generator=g, dtype=torch.uint8),
+        "f.e4m3": torch.randn(128, 256, generator=g).to(torch.float8_e4m3fn), "g.scalar": torch.tensor(3.5), "h.empty": torch.zeros(0, 4),
+    }
+    path = tmp_path / "t.safetensors"
+    save_file(tensors, str(path), metadata={"format": "pt", "who": "test \"quoted\""})
+    f = C.SafetensorsFile(str(path))
+    assert sorted(f.keys()) == sorted(tensors) and f.has("a.bf16") and not f.has("zzz")
+    assert f.metadata()["who"] == 'test "quoted"'
+    for name, want in tensors.items():
+        dtype, shape, nbytes = f.info(name)
+        assert list(shape) == list(want.shape) and nbytes == want.numel() * want.element_size()
+        got = f.get(name)
+        assert got.dtype == want.dtype and got.shape == want.shape
+        def raw(t):      # compare bit patterns (fp8 has no equality kernel on CPU)
+            return t.reshape(-1).view(torch.uint8) if t.numel() else t
+
+        assert torch.equal(raw(got), raw(want))
+        dst = torch.empty_like(want)
+        f.read_into(name, dst)
+        assert torch.equal(raw(dst), raw(want))
+    view = f.get("a.bf16")
+    del f
+    import gc
+
+    gc.collect()
+    assert torch.equal(view, tensors["a.bf16"])          # the view keeps the mapping alive
+    with pytest.raises(KeyError):
+        C.SafetensorsFile(str(path)).get("zzz")
+    with pytest.raises(ValueError):
+        C.SafetensorsFile(str(path)).read_into("b.f32", torch.empty(8))
+    bad = tmp_path / "bad.safetensors"
+    bad.write_bytes(b"\xff" * 8 + b"{}")
+    with pytest.raises(RuntimeError, match="header length"):
+        C.SafetensorsFile(str(bad))
+    with pytest.raises(RuntimeError, match="cannot open"):
+        C.SafetensorsFile(str(tmp_path / "missing.safetensors"))
+
+
+def test_worker_pool_and_context():
+    info = C.context_info()
+    assert info["pool_threads"] >= 1 and info["hardware_threads"] >= 1
+    src = torch.randint(0, 255, (40 << 20,), dtype=torch.uint8)
+    dst = torch.zeros_like(src)
+    C.parallel_copy(dst, src)
+    assert torch.equal(dst, src)
+    dst.zero_()
+    C.parallel_copy(dst, src, 2)
+    assert torch.equal(dst, src)
+    with pytest.raises(ValueError):
+        C.parallel_copy(torch.zeros(3), src)
