@@ -137,3 +137,25 @@ def test_engine_replay_is_bitwise_identical_and_leaves_guard_bands_intact(monkey
         assert guard.check_all() >= 2 * _cfg().num_layers
         del eng
     assert runs[0] == runs[1]
+
+
+def test_safetensors_read_into_device_memory_through_pinned_staging(tmp_path):
+    """Whole tensors from a memory-mapped checkpoint into CUDA tensors: larger than the two 32 MB staging buffers
+    (several turns of the ring), smaller than one, and an fp8 tensor."""
+    from safetensors.torch import save_file
+
+    from mojo_b200 import _ext
+
+    g = torch.Generator().manual_seed(1)
+    tensors = {"big": torch.randn(5000, 4100, generator=g).bfloat16(),            # 41 MB
+               "huge": torch.randint(0, 255, (150 << 20,), generator=g, dtype=torch.uint8),
+               "small": torch.randn(17, generator=g), "q": torch.randn(256, 384, generator=g).to(torch.float8_e4m3fn)}
+    path = tmp_path / "w.safetensors"
+    save_file(tensors, str(path))
+    f = _ext.require().SafetensorsFile(str(path))
+    for name, want in tensors.items():
+        dst = torch.empty_like(want, device="cuda")
+        f.read_into(name, dst)
+        torch.cuda.synchronize()
+        assert torch.equal(dst.cpu().reshape(-1).view(torch.uint8), want.reshape(-1).view(torch.uint8)), name
+    ops.check_status()
