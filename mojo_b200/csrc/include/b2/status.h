@@ -66,6 +66,20 @@ __device__ __forceinline__ void status_record(Status* s, int32_t code, int32_t s
   }
 }
 
+#else
+// Host restatement of the device recorder (first failure wins): host-side validation uses the same macro, and the
+// assertion modes can be exercised without a device.
+inline void status_record(Status* s, int32_t code, int32_t site, int64_t a = 0, int64_t b = 0) {
+  if (s == nullptr || s->code != 0) return;
+  s->code = code;
+  s->site = site;
+  s->block = -1;
+  s->thread = -1;
+  s->a = a;
+  s->b = b;
+}
+#endif  // __CUDACC__
+
 // B2_ASSERT(status, cond, site, a, b): evaluates to `cond`; when false it records and the caller
 // is expected to skip the access (`if (!B2_ASSERT(...)) continue;`).
 #if B2_ASSERT_MODE == 0
@@ -79,7 +93,7 @@ __device__ __forceinline__ void status_record(Status* s, int32_t code, int32_t s
 #else
 #define B2_ASSERT_ALL(status, cond, site, a, b) (true)
 #endif
-#endif  // __CUDACC__
+
 
 inline const char* status_code_name(int32_t c) {
   switch (c) {

@@ -243,3 +243,27 @@ def test_worker_pool_and_context():
     assert torch.equal(dst, src)
     with pytest.raises(ValueError):
         C.parallel_copy(torch.zeros(3), src)
+
+
+@pytest.mark.parametrize("mode,ran_cheap,cheap,ran_costly,costly", [(0, 1, "TIMEOUT", 1, "OK"), (1, 1, "ASSERT", 1, "OK"), (2, 0, "ASSERT", 1, "OK"),
+                                                                 (3, 0, "ASSERT", 0, "ASSERT")])
+def test_assertion_modes_config_matrix(mode, ran_cheap, cheap, ran_costly, costly, tmp_path):
+    """The same source under the four assertion modes (none / warn / safe / all): what gets recorded and whether the
+    guarded access still runs. In mode none the failed check leaves the word empty, so the program's later explicit
+    TIMEOUT record is the first one and is what shows."""
+    import subprocess
+    from pathlib import Path
+
+    import mojo_b200
+
+    csrc = Path(mojo_b200.__file__).parent / "csrc"
+    exe = tmp_path / f"assert_modes_{mode}"
+    subprocess.run(["g++", "-std=c++17", f"-DB2_ASSERT_MODE={mode}", f"-I{csrc / 'include'}", str(csrc / "tests" / "assert_modes.cpp"), "-o", str(exe)],
+                   check=True, capture_output=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    got = dict(kv.split("=") for kv in out)
+    assert got["mode"] == str(mode)
+    assert (int(got["ran_cheap"]), got["cheap"], int(got["ran_costly"]), got["costly"]) == (ran_cheap, cheap, ran_costly, costly)
+    assert got["ran_passing"] == "1" and got["passing"] == "OK"
+    if cheap == "ASSERT":      # the first record is kept: site kSiteTest with the offending index and its limit
+        assert (got["site"], got["a"], got["b"]) == ("15", "41", "8")
