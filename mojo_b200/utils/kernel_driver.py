@@ -105,6 +105,48 @@ def _case(name: str):
         meta = ops.AttnMeta(cu, torch.full((S,), L, dtype=torch.int32, device=DEV), bt, 0, L, L)
         flops = 2.0 * S * H * (576 + 512) * L * (L + 1) / 2
         return (lambda: ops.mla_attend(ql, qr, cache, meta, 1 / math.sqrt(192))), flops, S * L * 576 * 2 + 2 * S * L * H * 576 * 2
+    if name in ("tp_gemm_rs_single", "tp_ag_gemm_single"):
+        # The fused tensor-parallel kernels on ONE rank (a world of one: the only peer is this GPU's own region), so that
+        # their tensor-core / epilogue / staging behaviour can be captured under a profiler, which never runs on a
+        # multi-rank job. Shapes: one rank's share of the 8-GPU op sweep (K or N = 28672 / 8) at 4096 tokens.
+        from ..parallel.dist import DistInfo
+        from ..parallel.fused import FusedTPComm
+
+        info = DistInfo(0, 1, 0, torch.device(DEV), None, None)
+        M, big, shard = 4096, 8192, 3584
+        comm = FusedTPComm(info, max_tokens=M, hidden=big, max_k=big, timeout_s=2.0)
+        C, turn = comm.C, [0]
+        if name == "tp_gemm_rs_single":
+            x, w = rnd(M, shard), rnd(big, shard, scale=0.02)
+            out = torch.empty(M, big, device=DEV, dtype=torch.bfloat16)
+
+            def run():
+                C.tp_gemm_rs(x, w, 0, comm.peers, comm.layout, out, None, 0, turn[0] & 1, comm.timeout_ns, 0, comm.status)
+                turn[0] += 1
+
+            want = ops.linear(x, w)
+            flops, nbytes = 2.0 * M * big * shard, (M * shard + big * shard + 2 * M * big) * 2
+        else:
+            w = rnd(shard, big, scale=0.02)
+            out = torch.empty(M, shard, device=DEV, dtype=torch.bfloat16)
+            x = rnd(M, big)
+
+            def run():
+                slot = turn[0] & 1
+                full = comm.region.view(comm.layout.off_xall + slot * comm.layout.xall_half_bytes, (M, big), torch.bfloat16)
+                full.copy_(x)
+                C.tp_ag_gemm(w, 0, comm.peers, comm.layout, out, M, slot, comm.timeout_ns, 0, 0, comm.status)
+                turn[0] += 1
+
+            want = ops.linear(x, w)
+            flops, nbytes = 2.0 * M * big * shard, (M * big + big * shard + M * shard) * 2
+        run()
+        torch.cuda.synchronize()
+        ops.check_status()
+        err = (out.float() - want.float()).abs().max().item()
+        if not err <= 0.05 * want.float().abs().max().item() + 0.05:
+            raise SystemExit(f"{name}: single-rank result differs from the plain GEMM by {err}")
+        return run, flops, nbytes
     if name == "rmsnorm":
         rows, h = 65536, 4096
         x, r, w = rnd(rows, h), rnd(rows, h), torch.ones(h, device=DEV, dtype=torch.bfloat16)
@@ -117,6 +159,7 @@ def _case(name: str):
 
 CASES = ("gemm_large", "gemm_pair", "gemm_prefill", "gemm_decode", "gemm_swiglu", "gemm_fp8", "gemm_fp8_decode", "gemm_fp8_decode_nosplit",
          "attn_decode", "attn_prefill", "mla_decode", "mla_prefill", "rmsnorm", "sampling")
+# single-rank forms of the fused tensor-parallel kernels (profiling only): tp_gemm_rs_single, tp_ag_gemm_single
 
 
 def main() -> None:
