@@ -169,13 +169,15 @@ struct RsEpilogue {
         }
       }
     }
-    // publish: data first (system scope), then one flag per owner this tile touched
-    __threadfence_system();
+    // publish: the barrier orders every epilogue thread's stores before the signalling threads (CTA scope); each of
+    // those then fences at system scope and releases one flag per owner this tile touched. One fence per flag
+    // instead of one per thread: the per-thread form showed up as the top stall of this epilogue.
     ptx::named_barrier_sync(1, gemm::kEpiThreads);
     const int m_lo = SWAP ? u.qb * BN : u.pb * 128;
     const int m_hi = min(p.M, m_lo + (SWAP ? BN : 128)) - 1;
     const int o_lo = m_lo / p.R, o_hi = m_hi / p.R;
     if (t <= o_hi - o_lo) {
+      __threadfence_system();
       const int owner = o_lo + t;
       const int unit = unit_index<SWAP, BN>(p, owner, u.pb, u.qb);
       uint32_t* f = reinterpret_cast<uint32_t*>(p.peer[owner] + p.off_flags) + static_cast<int64_t>(unit) * p.tp + p.rank;
