@@ -21,6 +21,24 @@ def _cmd_serve(a) -> None:
     from .serve import build_app
 
     llm = LLM(PipelineConfig.from_args(a))
+    comm = getattr(llm, "comm", None)
+    if comm is not None and getattr(comm, "world_size", 1) > 1:
+        # tensor parallelism: rank 0 serves HTTP and broadcasts its commands, the other ranks follow
+        from .serve.api_server import RankSync, follower_loop
+
+        sync = RankSync(comm.info)
+        if not sync.leader:
+            follower_loop(llm, sync)
+            return
+        app = build_app(llm, model_name=a.model, sync=sync)
+        try:
+            uvicorn.run(app, host=a.host, port=a.port, log_level="info")
+        finally:
+            app.state.engine.shutdown()
+        return
+    if getattr(llm, "ep", None) is not None and llm.ep.world_size > 1:
+        raise SystemExit("serve: expert-parallel (data-parallel attention) serving needs a request router in front of the ranks; "
+                         "use the LLM API under torch.distributed.run, or tensor parallelism")
     uvicorn.run(build_app(llm, model_name=a.model), host=a.host, port=a.port, log_level="info")
 
 

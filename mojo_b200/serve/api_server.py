@@ -5,6 +5,11 @@ through per-request asyncio queues, the engine thread drains the inbox between s
 the reference's coroutine plumbing (stdlib/src/builtin/coroutine.mojo:83-249): asyncio on the serving side, a plain
 loop on the device side. A watchdog records the time of the last completed step; `/health` turns unhealthy when the
 loop stops making progress while requests are pending, or when a kernel reported an error status.
+
+Tensor-parallel serving: only rank 0 runs the HTTP application. Before every engine iteration it broadcasts the
+requests it admits and aborts (`RankSync`, host-side gloo group); every rank applies the same commands in the same
+order and then takes the same step, so the engines, whose kernels meet in collectives, never diverge. The other
+ranks run `follower_loop` instead of a server.
 """
 from __future__ import annotations
 
@@ -18,10 +23,58 @@ import uuid
 from ..engine import SamplingParams
 
 
+class RankSync:
+    """Command broadcast from rank 0 to the other ranks of a tensor-parallel group, once per engine iteration."""
+
+    def __init__(self, info):
+        self.info = info
+
+    @property
+    def leader(self) -> bool:
+        return self.info.rank == 0
+
+    def exchange(self, cmds):
+        """Rank 0 passes its command list, the others pass None; everyone gets rank 0's list."""
+        from ..parallel import host_broadcast_object
+
+        return host_broadcast_object(cmds, self.info)
+
+
+def _apply(eng, cmds, on_error=None) -> bool:
+    """Apply broadcast commands to an engine; returns False when a stop command was among them."""
+    go = True
+    for c in cmds:
+        if c[0] == "add":
+            _, rid, ids, sp = c
+            try:
+                eng.add_request(ids, SamplingParams(**sp), request_id=rid)
+            except Exception as e:  # noqa: BLE001  (bad request: every rank refuses it alike)
+                if on_error is not None:
+                    on_error(rid, str(e))
+        elif c[0] == "abort":
+            eng.abort_request(c[1])
+        elif c[0] == "stop":
+            go = False
+    return go
+
+
+def follower_loop(llm, sync: RankSync, idle_sleep: float = 0.0) -> None:
+    """Ranks other than 0 of a tensor-parallel server: apply rank 0's commands, step when there is work."""
+    eng = llm.engine
+    while True:
+        if not _apply(eng, sync.exchange(None)):
+            return
+        if eng.has_unfinished():
+            eng.step()
+        elif idle_sleep:
+            time.sleep(idle_sleep)
+
+
 class AsyncEngine:
-    def __init__(self, llm):
+    def __init__(self, llm, sync: RankSync | None = None):
         self.llm = llm
         self.engine = llm.engine
+        self.sync = sync
         self.inbox: queue.Queue = queue.Queue()
         self.streams: dict[int, tuple[asyncio.AbstractEventLoop, asyncio.Queue]] = {}
         self.last_step = time.time()
@@ -31,26 +84,37 @@ class AsyncEngine:
         self.thread.start()
 
     def _loop(self) -> None:
+        from dataclasses import asdict
+
         eng = self.engine
-        while not self._stop.is_set():
+        while True:
+            stopping = self._stop.is_set()
+            cmds = [("stop",)] if stopping else []
             try:
-                while True:
+                while not stopping:
                     kind, payload = self.inbox.get_nowait()
                     if kind == "add":
                         rid, ids, sp, loop, q = payload
-                        try:
-                            eng.add_request(ids, sp, request_id=rid)
-                            self.streams[rid] = (loop, q)
-                        except Exception as e:  # noqa: BLE001  (bad request: tell the client, keep serving)
-                            loop.call_soon_threadsafe(q.put_nowait, ("error", str(e)))
+                        self.streams[rid] = (loop, q)
+                        cmds.append(("add", rid, list(ids), asdict(sp)))
                     elif kind == "abort":
-                        eng.abort_request(payload)
                         self.streams.pop(payload, None)
+                        cmds.append(("abort", payload))
             except queue.Empty:
                 pass
+            if self.sync is not None:
+                cmds = self.sync.exchange(cmds)      # followers now hold the same list
+
+            def refuse(rid, msg):
+                s = self.streams.pop(rid, None)
+                if s is not None:
+                    s[0].call_soon_threadsafe(s[1].put_nowait, ("error", msg))
+
+            if not _apply(eng, cmds, refuse):
+                return
             if not eng.has_unfinished():
                 self.last_step = time.time()
-                time.sleep(0.001)
+                time.sleep(0.001 if self.sync is None else 0.003)
                 continue
             try:
                 outs = eng.step()
@@ -91,7 +155,9 @@ class AsyncEngine:
         return self.thread.is_alive() and not stalled
 
     def shutdown(self) -> None:
+        """Stop the engine thread; with followers, the stop command reaches them through the next broadcast."""
         self._stop.set()
+        self.thread.join(timeout=10.0)
 
 
 def _sampling_from(body: dict, default_max: int = 16) -> SamplingParams:
@@ -101,12 +167,12 @@ def _sampling_from(body: dict, default_max: int = 16) -> SamplingParams:
                           stop_token_ids=stop_ids, ignore_eos=bool(body.get("ignore_eos", False)), seed=body.get("seed"))
 
 
-def build_app(llm, model_name: str = "mojo_b200"):
+def build_app(llm, model_name: str = "mojo_b200", sync: RankSync | None = None):
     from fastapi import FastAPI, HTTPException
     from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
     app = FastAPI(title="mojo_b200")
-    aeng = AsyncEngine(llm)
+    aeng = AsyncEngine(llm, sync)
     app.state.engine = aeng
     tok = llm.tokenizer
 

@@ -100,13 +100,8 @@ def test_openai_server_endpoints():
     app.state.engine.shutdown()
 
 
-def test_llm_tensor_parallel_joins_ranks_itself_on_cpu(tmp_path):
-    """`LLM(PipelineConfig(tensor_parallel=2))` under a two-process gloo launch: each rank loads its shard of a
-    safetensors checkpoint and produces the same tokens as one process."""
-    import os
-    import subprocess
-    import sys
-
+def _write_tp_checkpoint(tmp_path):
+    """A small Llama checkpoint whose FFN width divides by 16 x 2 ranks."""
     from mojo_b200.loaders.safetensors_loader import save_llama_safetensors
 
     hid, heads, kv, d, ffn, vocab, layers = 256, 4, 2, 64, 704, 1000, 2
@@ -125,6 +120,16 @@ def test_llm_tensor_parallel_joins_ranks_itself_on_cpu(tmp_path):
                                             "num_attention_heads": heads, "num_key_value_heads": kv, "intermediate_size": ffn,
                                             "vocab_size": vocab, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
                                             "max_position_embeddings": 256, "tie_word_embeddings": False})
+
+
+def test_llm_tensor_parallel_joins_ranks_itself_on_cpu(tmp_path):
+    """`LLM(PipelineConfig(tensor_parallel=2))` under a two-process gloo launch: each rank loads its shard of a
+    safetensors checkpoint and produces the same tokens as one process."""
+    import os
+    import subprocess
+    import sys
+
+    _write_tp_checkpoint(tmp_path)
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
            "--master-port", "29641", os.path.join(root, "tests", "mp_pipeline_cpu.py")]
@@ -136,3 +141,18 @@ def test_llm_tensor_parallel_joins_ranks_itself_on_cpu(tmp_path):
 def test_llm_parallel_degree_without_ranks_is_refused():
     with pytest.raises(RuntimeError, match="torch.distributed.run"):
         LLM(PipelineConfig(model="tiny-llama", random_init=True, device="cpu", tensor_parallel=2))
+
+
+def test_openai_server_over_two_tensor_parallel_ranks_on_cpu(tmp_path):
+    """Rank 0 serves HTTP and broadcasts its commands, rank 1 follows: same completions as one process."""
+    import os
+    import subprocess
+    import sys
+
+    _write_tp_checkpoint(tmp_path)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29643", os.path.join(root, "tests", "mp_serve_cpu.py")]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", B2_TEST_CHECKPOINT=str(tmp_path))
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=root)
+    assert "SERVE_TP_OK 2" in p.stdout, p.stdout[-2000:] + p.stderr[-3000:]
