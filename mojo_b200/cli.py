@@ -21,12 +21,17 @@ def _cmd_serve(a) -> None:
     from .serve import build_app
 
     llm = LLM(PipelineConfig.from_args(a))
-    comm = getattr(llm, "comm", None)
+    comm, ep = getattr(llm, "comm", None), getattr(llm, "ep", None)
+    info = None
     if comm is not None and getattr(comm, "world_size", 1) > 1:
-        # tensor parallelism: rank 0 serves HTTP and broadcasts its commands, the other ranks follow
+        info, data_parallel = comm.info, False      # tensor parallelism: every rank admits every request
+    elif ep is not None and getattr(ep, "world_size", 1) > 1:
+        info, data_parallel = ep.info, True         # data-parallel attention + expert parallelism: requests are routed to an owner rank
+    if info is not None:
+        # rank 0 serves HTTP and broadcasts its commands once per engine iteration, the other ranks follow
         from .serve.api_server import RankSync, follower_loop
 
-        sync = RankSync(comm.info)
+        sync = RankSync(info, data_parallel=data_parallel)
         if not sync.leader:
             follower_loop(llm, sync)
             return
@@ -36,9 +41,6 @@ def _cmd_serve(a) -> None:
         finally:
             app.state.engine.shutdown()
         return
-    if getattr(llm, "ep", None) is not None and llm.ep.world_size > 1:
-        raise SystemExit("serve: expert-parallel (data-parallel attention) serving needs a request router in front of the ranks; "
-                         "use the LLM API under torch.distributed.run, or tensor parallelism")
     uvicorn.run(build_app(llm, model_name=a.model), host=a.host, port=a.port, log_level="info")
 
 

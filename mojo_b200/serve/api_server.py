@@ -10,6 +10,12 @@ Tensor-parallel serving: only rank 0 runs the HTTP application. Before every eng
 requests it admits and aborts (`RankSync`, host-side gloo group); every rank applies the same commands in the same
 order and then takes the same step, so the engines, whose kernels meet in collectives, never diverge. The other
 ranks run `follower_loop` instead of a server.
+
+Data-parallel serving (`RankSync(info, data_parallel=True)`: independent replicas, or data-parallel attention with
+expert-parallel MoE) uses the same broadcast, but a request is admitted only by the rank that owns it
+(request id modulo the number of ranks), every rank steps whenever any rank has work (an expert-parallel rank
+without requests still joins the MoE layers), and the outputs of each iteration are gathered to rank 0, which
+feeds the HTTP streams.
 """
 from __future__ import annotations
 
@@ -24,10 +30,23 @@ from ..engine import SamplingParams
 
 
 class RankSync:
-    """Command broadcast from rank 0 to the other ranks of a tensor-parallel group, once per engine iteration."""
+    """Command broadcast from rank 0 to the other ranks of a group, once per engine iteration; with `data_parallel`
+    also the routing of requests to their owner rank and the gather of each iteration's outputs to rank 0."""
 
-    def __init__(self, info):
+    def __init__(self, info, data_parallel: bool = False):
         self.info = info
+        self.data_parallel = data_parallel
+
+    def owns(self, rid: int) -> bool:
+        return not self.data_parallel or rid % self.info.world_size == self.info.rank
+
+    def gather(self, item):
+        """Every rank contributes one object; rank 0 gets the list (by rank), the others None."""
+        import torch.distributed as dist
+
+        box = [None] * self.info.world_size if self.leader else None
+        dist.gather_object(item, box, dst=0, group=self.info.host_group)
+        return box
 
     @property
     def leader(self) -> bool:
@@ -40,10 +59,13 @@ class RankSync:
         return host_broadcast_object(cmds, self.info)
 
 
-def _apply(eng, cmds, on_error=None) -> bool:
-    """Apply broadcast commands to an engine; returns False when a stop command was among them."""
+def _apply(eng, cmds, on_error=None, sync: "RankSync | None" = None) -> bool:
+    """Apply broadcast commands to an engine; returns False when a stop command was among them. Under data
+    parallelism only the owner of a request admits or aborts it."""
     go = True
     for c in cmds:
+        if c[0] in ("add", "abort") and sync is not None and not sync.owns(c[1]):
+            continue
         if c[0] == "add":
             _, rid, ids, sp = c
             try:
@@ -59,12 +81,18 @@ def _apply(eng, cmds, on_error=None) -> bool:
 
 
 def follower_loop(llm, sync: RankSync, idle_sleep: float = 0.0) -> None:
-    """Ranks other than 0 of a tensor-parallel server: apply rank 0's commands, step when there is work."""
+    """Ranks other than 0 of a multi-rank server: apply rank 0's commands, step when there is work."""
     eng = llm.engine
+    refused: list = []
     while True:
-        if not _apply(eng, sync.exchange(None)):
+        msg = sync.exchange(None)
+        if not _apply(eng, msg["cmds"], lambda rid, err: refused.append((rid, err)), sync):
             return
-        if eng.has_unfinished():
+        if sync.data_parallel:
+            outs = eng.step() if msg["any_busy"] else []
+            sync.gather({"outs": outs, "busy": eng.has_unfinished(), "refused": refused})
+            refused = []
+        elif eng.has_unfinished():
             eng.step()
         elif idle_sleep:
             time.sleep(idle_sleep)
@@ -75,6 +103,7 @@ class AsyncEngine:
         self.llm = llm
         self.engine = llm.engine
         self.sync = sync
+        self._any_busy = False     # data parallelism: whether any rank had unfinished requests after the last iteration
         self.inbox: queue.Queue = queue.Queue()
         self.streams: dict[int, tuple[asyncio.AbstractEventLoop, asyncio.Queue]] = {}
         self.last_step = time.time()
@@ -102,29 +131,49 @@ class AsyncEngine:
                         cmds.append(("abort", payload))
             except queue.Empty:
                 pass
+            step_now = False
             if self.sync is not None:
-                cmds = self.sync.exchange(cmds)      # followers now hold the same list
+                # data parallelism: every rank steps in an iteration or none does (expert-parallel ranks meet in the MoE
+                # layers), so the decision is rank 0's: some rank had work after the last iteration, or work arrives now
+                step_now = self._any_busy or any(c[0] == "add" for c in cmds)
+                msg = self.sync.exchange({"cmds": cmds, "any_busy": step_now})      # followers now hold the same list
+                cmds = msg["cmds"]
 
             def refuse(rid, msg):
                 s = self.streams.pop(rid, None)
                 if s is not None:
                     s[0].call_soon_threadsafe(s[1].put_nowait, ("error", msg))
 
-            if not _apply(eng, cmds, refuse):
+            if not _apply(eng, cmds, refuse, self.sync):
                 return
-            if not eng.has_unfinished():
+            dp = self.sync is not None and self.sync.data_parallel
+            if not dp and not eng.has_unfinished():
                 self.last_step = time.time()
                 time.sleep(0.001 if self.sync is None else 0.003)
                 continue
             try:
-                outs = eng.step()
+                outs = eng.step() if (not dp or step_now) else []
             except Exception as e:  # noqa: BLE001  (kernel status error etc.): fail in-flight requests, stay alive
                 self.error = repr(e)
                 for rid, (loop, q) in list(self.streams.items()):
                     loop.call_soon_threadsafe(q.put_nowait, ("error", self.error))
                     eng.abort_request(rid)
                 self.streams.clear()
-                continue
+                outs = []
+                if not dp:
+                    continue
+            if dp:
+                # one gather per iteration: every rank's new tokens, whether it still has work, what it refused
+                parts = self.sync.gather({"outs": outs, "busy": eng.has_unfinished(), "refused": []})
+                outs = [o for part in parts for o in part["outs"]]
+                self._any_busy = any(part["busy"] for part in parts)
+                for part in parts:
+                    for rid, err in part["refused"]:
+                        refuse(rid, err)
+                if not self._any_busy and not outs:
+                    self.last_step = time.time()
+                    time.sleep(0.003)
+                    continue
             self.last_step = time.time()
             for o in outs:
                 s = self.streams.get(o.request_id)

@@ -156,3 +156,16 @@ def test_openai_server_over_two_tensor_parallel_ranks_on_cpu(tmp_path):
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", B2_TEST_CHECKPOINT=str(tmp_path))
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=root)
     assert "SERVE_TP_OK 2" in p.stdout, p.stdout[-2000:] + p.stderr[-3000:]
+
+
+def test_openai_server_over_two_data_parallel_ranks_on_cpu():
+    """Rank 0 serves HTTP, routes requests to their owner rank and gathers the tokens of every iteration."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29644", os.path.join(root, "tests", "mp_serve_dp_cpu.py")]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), cwd=root)
+    assert "SERVE_DP_OK 2" in p.stdout, p.stdout[-2000:] + p.stderr[-3000:]
