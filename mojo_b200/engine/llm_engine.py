@@ -97,6 +97,14 @@ class LLMEngine:
         self.scheduler = self.C.Scheduler(sc, self.kv)
         self.requests: dict[int, RequestState] = {}
         self._prompts: dict[int, np.ndarray] = {}
+        # running latency histograms (Prometheus-style cumulative buckets are derived on read); they survive `forget`
+        self.ttft_bounds_ms = np.array([10, 25, 50, 100, 250, 500, 1000, 2500, 5000, 10000, 30000], dtype=np.float64)
+        self.itl_bounds_ms = np.array([1, 2, 5, 10, 20, 50, 100, 250, 1000], dtype=np.float64)
+        self._ttft_hist = np.zeros(len(self.ttft_bounds_ms) + 1, dtype=np.int64)
+        self._itl_hist = np.zeros(len(self.itl_bounds_ms) + 1, dtype=np.int64)
+        self._ttft_sum_ms = self._itl_sum_ms = 0.0
+        self.finished_requests = 0
+        self.generated_tokens = 0
         self._next_id = 0
         self.step_count = 0
         # failure detection (all optional, all on the host): see engine/watchdog.py and utils/fault.py
@@ -214,13 +222,17 @@ class LLMEngine:
         self.step_count += 1
         now = time.perf_counter()
         outs = []
+        ttfts, itls = [], []
         for rid, tok, st in zip(sample_ids, tokens, states):
             rid, tok = int(rid), int(tok)
             hit_max = self.scheduler.append_token(rid, tok)
             st.output_ids.append(tok)
-            st.token_times.append(now)
             if st.first_token_time is None:
                 st.first_token_time = now
+                ttfts.append(now - st.arrival)
+            else:
+                itls.append(now - st.token_times[-1])
+            st.token_times.append(now)
             reason = None
             eos = self.cfg.eos_token_id
             if not st.params.ignore_eos and eos is not None and tok == eos:
@@ -232,8 +244,31 @@ class LLMEngine:
             if reason is not None:
                 st.finished, st.finish_reason = True, reason
                 self.scheduler.finish(rid)
+                self.finished_requests += 1
             outs.append(RequestOutput(rid, [tok], st.output_ids, st.finished, reason))
+        self.generated_tokens += len(outs)
+        if ttfts:
+            v = np.asarray(ttfts) * 1e3
+            np.add.at(self._ttft_hist, np.searchsorted(self.ttft_bounds_ms, v, side="left"), 1)
+            self._ttft_sum_ms += float(v.sum())
+        if itls:
+            v = np.asarray(itls) * 1e3
+            np.add.at(self._itl_hist, np.searchsorted(self.itl_bounds_ms, v, side="left"), 1)
+            self._itl_sum_ms += float(v.sum())
         return outs
+
+    def forget(self, rid: int) -> None:
+        """Drop the bookkeeping of a finished (or aborted) request. A long-running server calls this when a stream
+        ends; the latency histograms and counters keep what they recorded."""
+        st = self.requests.get(rid)
+        if st is not None and st.finished:
+            del self.requests[rid]
+            self._prompts.pop(rid, None)
+
+    def histograms(self) -> dict:
+        """{"ttft_ms" | "itl_ms": {"bounds": [...], "counts": per-bucket counts (last = above the top bound), "sum": ms}}"""
+        return {"ttft_ms": {"bounds": self.ttft_bounds_ms.tolist(), "counts": self._ttft_hist.tolist(), "sum": self._ttft_sum_ms},
+                "itl_ms": {"bounds": self.itl_bounds_ms.tolist(), "counts": self._itl_hist.tolist(), "sum": self._itl_sum_ms}}
 
     def generate(self, prompts, params: SamplingParams | list | None = None) -> list[list[int]]:
         """Blocking convenience: run a list of token-id prompts to completion, return generated ids in order."""

@@ -88,14 +88,18 @@ def follower_loop(llm, sync: RankSync, idle_sleep: float = 0.0) -> None:
         msg = sync.exchange(None)
         if not _apply(eng, msg["cmds"], lambda rid, err: refused.append((rid, err)), sync):
             return
+        outs = []
         if sync.data_parallel:
             outs = eng.step() if msg["any_busy"] else []
             sync.gather({"outs": outs, "busy": eng.has_unfinished(), "refused": refused})
             refused = []
         elif eng.has_unfinished():
-            eng.step()
+            outs = eng.step()
         elif idle_sleep:
             time.sleep(idle_sleep)
+        for o in outs:
+            if o.finished:
+                eng.forget(o.request_id)
 
 
 class AsyncEngine:
@@ -183,6 +187,9 @@ class AsyncEngine:
                 loop.call_soon_threadsafe(q.put_nowait, ("token", (o.new_token_ids, o.finished, o.finish_reason)))
                 if o.finished:
                     self.streams.pop(o.request_id, None)
+            for o in outs:
+                if o.finished:
+                    eng.forget(o.request_id)     # a server runs for days: finished requests leave no state behind
 
     _ids = 0
     _ids_lock = threading.Lock()
@@ -273,8 +280,26 @@ def build_app(llm, model_name: str = "mojo_b200", sync: RankSync | None = None):
         for k, v in m.items():
             if isinstance(v, (int, float)) and v is not None:
                 lines.append(f"# TYPE b2_{k} gauge\nb2_{k} {v}")
-        lines.append(f"# TYPE b2_waiting gauge\nb2_waiting {aeng.engine.scheduler.num_waiting()}")
-        lines.append(f"# TYPE b2_running gauge\nb2_running {aeng.engine.scheduler.num_running()}")
+        eng = aeng.engine
+        lines.append(f"# TYPE b2_waiting gauge\nb2_waiting {eng.scheduler.num_waiting()}")
+        lines.append(f"# TYPE b2_running gauge\nb2_running {eng.scheduler.num_running()}")
+        st = eng.kv.stats()
+        used = st.num_pages - st.free_pages - st.cached_pages
+        lines.append(f"# TYPE b2_kv_utilisation gauge\nb2_kv_utilisation {used / max(st.num_pages, 1):.6f}")
+        lines.append(f"# TYPE b2_kv_cached_pages gauge\nb2_kv_cached_pages {st.cached_pages}")
+        lines.append(f"# TYPE b2_requests_finished_total counter\nb2_requests_finished_total {eng.finished_requests}")
+        lines.append(f"# TYPE b2_generated_tokens_total counter\nb2_generated_tokens_total {eng.generated_tokens}")
+        for name, h in eng.histograms().items():
+            metric = "b2_" + name.replace("_ms", "_milliseconds")
+            lines.append(f"# TYPE {metric} histogram")
+            running = 0
+            for bound, n in zip(h["bounds"], h["counts"]):
+                running += n
+                lines.append(f'{metric}_bucket{{le="{bound:g}"}} {running}')
+            running += h["counts"][-1]
+            lines.append(f'{metric}_bucket{{le="+Inf"}} {running}')
+            lines.append(f"{metric}_sum {h['sum']:.3f}")
+            lines.append(f"{metric}_count {running}")
         return PlainTextResponse("\n".join(lines) + "\n")
 
     @app.post("/v1/completions")

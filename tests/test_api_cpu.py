@@ -96,7 +96,12 @@ def test_openai_server_endpoints():
         too_long = c.post("/v1/completions", json={"prompt": [7] * llm.engine.cfg.max_model_len, "max_tokens": 3})
         assert too_long.status_code == 400 and "context limit" in too_long.json()["detail"]
         assert c.post("/v1/completions", json={"prompt": [], "max_tokens": 3}).status_code == 400
-        assert "b2_output_tokens" in c.get("/metrics").text
+        text = c.get("/metrics").text
+        assert "b2_output_tokens" in text or "b2_generated_tokens_total" in text
+        assert 'b2_ttft_milliseconds_bucket{le="+Inf"} 3' in text          # three requests were served
+        assert "b2_itl_milliseconds_count 10" in text                       # 5 + 5 + 3 tokens -> 4 + 4 + 2 gaps
+        assert "b2_kv_utilisation" in text and "b2_requests_finished_total 3" in text and "b2_generated_tokens_total 13" in text
+        assert llm.engine.requests == {}                                     # finished streams leave no per-request state
     app.state.engine.shutdown()
 
 
