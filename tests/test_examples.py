@@ -40,3 +40,23 @@ def test_example_kernels_match_cpu_restatements():
     bg = raytrace.background()
     img = raytrace.render_gpu(torch.from_numpy(bg).cuda()).cpu().numpy()
     assert (np.abs(img - raytrace.render_cpu(bg)).max(-1) > 2e-2).mean() < 2e-3
+
+
+def test_example_runner_runs_host_examples_and_reports_the_rest(capsys):
+    from mojo_b200.examples.__main__ import main
+
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("covered by the gpu run of the same runner")
+    assert main([]) == 0
+    out = capsys.readouterr().out
+    assert "== nbody" in out and "skipped (needs a CUDA device)" in out
+    assert main(["nosuch"]) == 2
+
+
+@pytest.mark.gpu
+def test_example_runner_runs_everything_on_a_gpu():
+    from mojo_b200.examples.__main__ import main
+
+    assert main(["deviceinfo", "mandelbrot", "nbody", "life"]) == 0
