@@ -147,6 +147,21 @@ def _case(name: str):
         if not err <= 0.05 * want.float().abs().max().item() + 0.05:
             raise SystemExit(f"{name}: single-rank result differs from the plain GEMM by {err}")
         return run, flops, nbytes
+    if name == "moe_ep_single":
+        # One DeepSeek-V2-Lite MoE layer on a world of one (all 64 experts local): router + dispatch, the two grouped
+        # tcgen05 GEMMs, combine. The expert-parallel kernels as they run on every rank, without link traffic.
+        from ..parallel.dist import DistInfo
+        from ..parallel.ep import EPComm
+
+        T, E, k, H, F = 4096, 64, 6, 2048, 1408
+        ep = EPComm(DistInfo(0, 1, 0, torch.device(DEV), None, None), E, H, F, k, max_tokens=T, timeout_s=2.0)
+        x = rnd(T, H)
+        logits = rnd(T, E, scale=1.0)
+        w_gu = rnd(E, 2 * F, H, scale=0.02)
+        w_down = rnd(E, H, F, scale=0.02)
+        flops = 2.0 * T * k * (2 * F * H + H * F)
+        nbytes = (w_gu.numel() + w_down.numel()) * 2 + 4 * T * k * H * 2
+        return (lambda: ep.moe(x, logits, w_gu, w_down)), flops, nbytes
     if name == "rmsnorm":
         rows, h = 65536, 4096
         x, r, w = rnd(rows, h), rnd(rows, h), torch.ones(h, device=DEV, dtype=torch.bfloat16)
@@ -159,7 +174,8 @@ def _case(name: str):
 
 CASES = ("gemm_large", "gemm_pair", "gemm_prefill", "gemm_decode", "gemm_swiglu", "gemm_fp8", "gemm_fp8_decode", "gemm_fp8_decode_nosplit",
          "attn_decode", "attn_prefill", "mla_decode", "mla_prefill", "rmsnorm", "sampling")
-# single-rank forms of the fused tensor-parallel kernels (profiling only): tp_gemm_rs_single, tp_ag_gemm_single
+# single-rank forms of the fused tensor-parallel and expert-parallel kernels (profiling only): tp_gemm_rs_single,
+# tp_ag_gemm_single, moe_ep_single
 
 
 def main() -> None:
