@@ -223,6 +223,42 @@ def _sampling_from(body: dict, default_max: int = 16) -> SamplingParams:
                           stop_token_ids=stop_ids, ignore_eos=bool(body.get("ignore_eos", False)), seed=body.get("seed"))
 
 
+def _stops_from(body: dict) -> list[str]:
+    stop = body.get("stop")
+    if stop is None:
+        return []
+    if isinstance(stop, str):
+        stop = [stop]
+    if not isinstance(stop, list) or not all(isinstance(x, str) and x for x in stop):
+        raise ValueError("stop must be a non-empty string or a list of non-empty strings")
+    return stop
+
+
+class _TextStream:
+    """Turns the token stream of one request into text deltas and watches for stop strings. Text that could still
+    turn out to be the beginning of a stop string is held back until the next token settles it; at a stop the text
+    is cut before the stop string (which is not returned) and the request is to be aborted."""
+
+    def __init__(self, decode, stops: list[str]):
+        self.decode, self.stops = decode, stops
+        self.hold = max((len(x) for x in stops), default=1) - 1
+        self.ids: list[int] = []
+        self.sent = 0
+
+    def push(self, new, finished: bool) -> tuple[str, bool]:
+        """(text to emit now, whether a stop string was reached)."""
+        self.ids.extend(new)
+        text = self.decode(self.ids)
+        hits = [i for i in (text.find(x) for x in self.stops) if i >= 0]
+        if hits:
+            cut = max(min(hits), self.sent)
+            delta, self.sent = text[self.sent:cut], cut
+            return delta, True
+        end = len(text) if finished else max(self.sent, len(text) - self.hold)
+        delta, self.sent = text[self.sent:end], end
+        return delta, False
+
+
 def build_app(llm, model_name: str = "mojo_b200", sync: RankSync | None = None):
     from fastapi import FastAPI, HTTPException
     from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
@@ -236,18 +272,25 @@ def build_app(llm, model_name: str = "mojo_b200", sync: RankSync | None = None):
         t = tok.decode(ids)
         return t if t is not None else " ".join(str(i) for i in ids)
 
-    async def collect(q):
-        out, reason = [], None
+    async def collect(q, rid, stops):
+        """(token ids, text, finish reason) of a whole request."""
+        ts = _TextStream(text_of, stops)
+        parts = []
         while True:
             kind, payload = await q.get()
             if kind == "error":
                 raise HTTPException(status_code=500, detail=payload)
             new, finished, reason = payload
-            out.extend(new)
+            delta, stopped = ts.push(new, finished)
+            parts.append(delta)
+            if stopped:
+                aeng.abort(rid)
+                return ts.ids, "".join(parts), "stop"
             if finished:
-                return out, reason
+                return ts.ids, "".join(parts), reason
 
-    async def sse(q, rid, make_chunk, final_chunk):
+    async def sse(q, rid, make_chunk, final_chunk, stops=()):
+        ts = _TextStream(text_of, list(stops))
         try:
             while True:
                 kind, payload = await q.get()
@@ -255,7 +298,10 @@ def build_app(llm, model_name: str = "mojo_b200", sync: RankSync | None = None):
                     yield f"data: {json.dumps({'error': payload})}\n\n"
                     break
                 new, finished, reason = payload
-                yield f"data: {json.dumps(make_chunk(new, reason if finished else None))}\n\n"
+                delta, stopped = ts.push(new, finished)
+                if stopped:
+                    finished, reason = True, "stop"
+                yield f"data: {json.dumps(make_chunk(new, delta, reason if finished else None))}\n\n"
                 if finished:
                     if final_chunk is not None:
                         yield f"data: {json.dumps(final_chunk(reason))}\n\n"
@@ -313,19 +359,20 @@ def build_app(llm, model_name: str = "mojo_b200", sync: RankSync | None = None):
             raise HTTPException(status_code=400, detail=str(e))
         sp = _sampling_from(body)
         try:
+            stops = _stops_from(body)
             rid, q = aeng.submit(ids, sp)
         except ValueError as e:
             raise HTTPException(status_code=400, detail=str(e))
         cid = "cmpl-" + uuid.uuid4().hex[:24]
         created = int(time.time())
         if body.get("stream"):
-            def chunk(new, reason):
+            def chunk(new, text, reason):
                 return {"id": cid, "object": "text_completion", "created": created, "model": model_name,
-                        "choices": [{"index": 0, "text": text_of(new), "token_ids": new, "finish_reason": reason}]}
-            return StreamingResponse(sse(q, rid, chunk, None), media_type="text/event-stream")
-        out, reason = await collect(q)
+                        "choices": [{"index": 0, "text": text, "token_ids": new, "finish_reason": reason}]}
+            return StreamingResponse(sse(q, rid, chunk, None, stops), media_type="text/event-stream")
+        out, text, reason = await collect(q, rid, stops)
         return {"id": cid, "object": "text_completion", "created": created, "model": model_name,
-                "choices": [{"index": 0, "text": text_of(out), "token_ids": out, "finish_reason": reason}],
+                "choices": [{"index": 0, "text": text, "token_ids": out, "finish_reason": reason}],
                 "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out), "total_tokens": len(ids) + len(out)}}
 
     @app.post("/v1/chat/completions")
@@ -336,6 +383,7 @@ def build_app(llm, model_name: str = "mojo_b200", sync: RankSync | None = None):
         ids = tok.apply_chat_template(messages)
         sp = _sampling_from(body, default_max=256)
         try:
+            stops = _stops_from(body)
             rid, q = aeng.submit(ids, sp)
         except ValueError as e:
             raise HTTPException(status_code=400, detail=str(e))
@@ -344,17 +392,17 @@ def build_app(llm, model_name: str = "mojo_b200", sync: RankSync | None = None):
         if body.get("stream"):
             first = {"sent": False}
 
-            def chunk(new, reason):
-                delta = {"content": text_of(new)}
+            def chunk(new, text, reason):
+                delta = {"content": text}
                 if not first["sent"]:
                     delta["role"] = "assistant"
                     first["sent"] = True
                 return {"id": cid, "object": "chat.completion.chunk", "created": created, "model": model_name,
                         "choices": [{"index": 0, "delta": delta, "finish_reason": reason}]}
-            return StreamingResponse(sse(q, rid, chunk, None), media_type="text/event-stream")
-        out, reason = await collect(q)
+            return StreamingResponse(sse(q, rid, chunk, None, stops), media_type="text/event-stream")
+        out, text, reason = await collect(q, rid, stops)
         return {"id": cid, "object": "chat.completion", "created": created, "model": model_name,
-                "choices": [{"index": 0, "message": {"role": "assistant", "content": text_of(out)}, "finish_reason": reason}],
+                "choices": [{"index": 0, "message": {"role": "assistant", "content": text}, "finish_reason": reason}],
                 "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out), "total_tokens": len(ids) + len(out)}}
 
     return app

@@ -174,3 +174,57 @@ def test_openai_server_over_two_data_parallel_ranks_on_cpu():
            "--master-port", "29644", os.path.join(root, "tests", "mp_serve_dp_cpu.py")]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), cwd=root)
     assert "SERVE_DP_OK 2" in p.stdout, p.stdout[-2000:] + p.stderr[-3000:]
+
+
+def test_text_stream_holds_back_possible_stop_prefixes_and_cuts_at_the_stop():
+    from mojo_b200.serve.api_server import _TextStream
+
+    table = {1: "Hel", 2: "lo", 3: " wor", 4: "ld", 5: "!<", 6: "end", 7: ">"}
+    ts = _TextStream(lambda ids: "".join(table[i] for i in ids), ["<end>", "ZZ"])
+    out = []
+    for i, t in enumerate([1, 2, 3, 4, 5]):
+        d, stop = ts.push([t], False)
+        assert not stop
+        out.append(d)
+    assert "".join(out) == "Hello wor"                 # len("<end>") - 1 = 4 characters are held back: "ld!<" is not out yet
+    d, stop = ts.push([6], False)
+    assert not stop and "".join(out + [d]) == "Hello world!"          # "<end" could still become the stop string
+    d2, stop = ts.push([7], False)
+    assert stop and d2 == ""                           # the stop string itself is never emitted
+    # without a stop the tail is flushed when the request finishes
+    ts = _TextStream(lambda ids: "".join(table[i] for i in ids), ["<end>"])
+    assert ts.push([1, 2], False) == ("H", False)
+    assert ts.push([3], True) == ("ello wor", False)
+    # no stop strings: nothing is held back
+    ts = _TextStream(lambda ids: "".join(table[i] for i in ids), [])
+    assert ts.push([1], False) == ("Hel", False)
+
+
+def test_openai_server_stop_strings():
+    from fastapi.testclient import TestClient
+
+    from mojo_b200.serve import build_app
+
+    llm = tiny_llm()
+    prompt = [5, 900, 77, 3021, 15000]
+    want = tiny_llm().generate([prompt], SamplingParams(max_tokens=8))[0].token_ids
+    k = next(i for i, t in enumerate(want) if t != want[0])          # the first token that differs from the repeated one
+    stop = f" {want[k]}"                                             # without a tokenizer the text is the ids joined by spaces
+    cut_text = " ".join(str(t) for t in want[:k])
+    app = build_app(llm, "tiny-llama")
+    with TestClient(app) as c:
+        r = c.post("/v1/completions", json={"prompt": prompt, "max_tokens": 8, "stop": stop}).json()
+        ch = r["choices"][0]
+        assert ch["finish_reason"] == "stop" and ch["text"] == cut_text
+        assert ch["token_ids"] == want[:k + 1]                        # the token that completed the stop string was generated, not shown
+        with c.stream("POST", "/v1/completions", json={"prompt": prompt, "max_tokens": 8, "stream": True, "stop": [stop, "nope"]}) as s:
+            lines = [json.loads(l[6:]) for l in s.iter_lines() if l.startswith("data: ") and l != "data: [DONE]"]
+        assert "".join(l["choices"][0]["text"] for l in lines) == cut_text
+        assert lines[-1]["choices"][0]["finish_reason"] == "stop"
+        r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "stop": "never-there"}).json()
+        assert r["choices"][0]["finish_reason"] == "length"
+        assert c.post("/v1/completions", json={"prompt": [1, 2], "stop": 5}).status_code == 400
+        # the engine thread is still healthy and serves the next request after the aborts
+        r = c.post("/v1/completions", json={"prompt": prompt, "max_tokens": 8}).json()
+        assert r["choices"][0]["token_ids"] == want
+    app.state.engine.shutdown()
