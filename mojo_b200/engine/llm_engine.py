@@ -186,6 +186,14 @@ class LLMEngine:
             self.requests[rid].finished = True
             self.requests[rid].finish_reason = "abort"
 
+    def abort_all(self) -> list[int]:
+        """Abort every request that has not finished (after a failed step the batch's state is unknown: the KV written
+        by the step may be partial). Returns their ids."""
+        rids = [rid for rid, st in self.requests.items() if not st.finished]
+        for rid in rids:
+            self.abort_request(rid)
+        return rids
+
     def has_unfinished(self) -> bool:
         return self.scheduler.has_unfinished()
 
@@ -215,6 +223,7 @@ class LLMEngine:
             self.watchdog.begin_step()
         with trace.span("engine.execute"):
             tokens = self.runner.execute(batch, states, self.step_count)
+        self.fault.after_execute(self.step_count)
         if self.watchdog is not None:
             self.watchdog.end_step(self.step_count)
         if self.heartbeat is not None:

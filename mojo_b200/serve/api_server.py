@@ -40,6 +40,16 @@ class RankSync:
     def owns(self, rid: int) -> bool:
         return not self.data_parallel or rid % self.info.world_size == self.info.rank
 
+    def any_failed(self, failed: bool) -> bool:
+        """Whether the step that just ran failed on any rank (one small host all-reduce). Ranks that share collectives
+        must take the same decision after a failure, or their next steps would not match."""
+        import torch
+        import torch.distributed as dist
+
+        flag = torch.tensor([1 if failed else 0], dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.info.host_group)
+        return bool(flag[0])
+
     def gather(self, item):
         """Every rank contributes one object; rank 0 gets the list (by rank), the others None."""
         import torch.distributed as dist
@@ -75,6 +85,7 @@ def _apply(eng, cmds, on_error=None, sync: "RankSync | None" = None) -> bool:
                     on_error(rid, str(e))
         elif c[0] == "abort":
             eng.abort_request(c[1])
+            eng.forget(c[1])
         elif c[0] == "stop":
             go = False
     return go
@@ -89,14 +100,22 @@ def follower_loop(llm, sync: RankSync, idle_sleep: float = 0.0) -> None:
         if not _apply(eng, msg["cmds"], lambda rid, err: refused.append((rid, err)), sync):
             return
         outs = []
-        if sync.data_parallel:
-            outs = eng.step() if msg["any_busy"] else []
-            sync.gather({"outs": outs, "busy": eng.has_unfinished(), "refused": refused})
-            refused = []
-        elif eng.has_unfinished():
-            outs = eng.step()
+        stepping = msg["any_busy"] if sync.data_parallel else eng.has_unfinished()
+        if stepping:
+            failed = False
+            try:
+                outs = eng.step()
+            except Exception:  # noqa: BLE001  (reported to rank 0 through the flag below; this rank stays in the group)
+                failed = True
+            if sync.any_failed(failed):
+                for rid in eng.abort_all():
+                    eng.forget(rid)
+                outs = []
         elif idle_sleep:
             time.sleep(idle_sleep)
+        if sync.data_parallel:
+            sync.gather({"outs": outs, "busy": eng.has_unfinished(), "refused": refused})
+            refused = []
         for o in outs:
             if o.finished:
                 eng.forget(o.request_id)
@@ -155,15 +174,22 @@ class AsyncEngine:
                 self.last_step = time.time()
                 time.sleep(0.001 if self.sync is None else 0.003)
                 continue
+            stepping = (not dp) or step_now
+            failed, err = False, None
             try:
-                outs = eng.step() if (not dp or step_now) else []
+                outs = eng.step() if stepping else []
             except Exception as e:  # noqa: BLE001  (kernel status error etc.): fail in-flight requests, stay alive
-                self.error = repr(e)
+                failed, err, outs = True, repr(e), []
+            if stepping and self.sync is not None and self.sync.any_failed(failed) and not failed:
+                failed, err = True, "a step failed on another rank"
+            if failed:
+                # the batch's state is unknown on at least one rank: every rank drops every in-flight request
+                self.error = err
                 for rid, (loop, q) in list(self.streams.items()):
-                    loop.call_soon_threadsafe(q.put_nowait, ("error", self.error))
-                    eng.abort_request(rid)
+                    loop.call_soon_threadsafe(q.put_nowait, ("error", err))
                 self.streams.clear()
-                outs = []
+                for rid in eng.abort_all():
+                    eng.forget(rid)
                 if not dp:
                     continue
             if dp:

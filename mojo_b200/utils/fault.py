@@ -4,12 +4,14 @@ sleeps, skips a launch or leaves between steps; a dropped signal in the CPU-rank
 The spec is a colon-separated string, usually from the `B2_FAULT` environment variable:
 
     raise:rank=1:step=3           rank 1 raises InjectedFault at the start of step 3
+    raise_after:rank=1:step=3     rank 1 raises InjectedFault at the end of step 3, after its launches and collectives
+                                  have completed (what a kernel status error looks like to the host)
     delay:rank=0:step=2:ms=500    rank 0 sleeps 500 ms before step 2
     skip_launch:rank=2:step=5     rank 2 does not launch step 5 (the engine runs the scheduler but not the model)
     leave:rank=3:step=4           rank 3 announces that it is leaving and exits its loop before step 4
     drop_signal:rank=1:step=7     only meaningful to the CPU-rank simulator (`symm_sim_run`)
 
-`FaultInjector.before_step(step)` is the single hook the engine loop calls.
+`FaultInjector.before_step(step)` and `after_execute(step)` are the hooks the engine loop calls.
 """
 from __future__ import annotations
 
@@ -17,7 +19,7 @@ import os
 import time
 from dataclasses import dataclass
 
-KINDS = ("raise", "delay", "skip_launch", "leave", "drop_signal")
+KINDS = ("raise", "raise_after", "delay", "skip_launch", "leave", "drop_signal")
 
 
 class InjectedFault(RuntimeError):
@@ -71,9 +73,15 @@ class FaultInjector:
         s = self.spec
         return s is not None and not self.fired and s.rank == self.rank and s.step == step
 
+    def after_execute(self, step: int) -> None:
+        """Called when the step's device work has been issued and its results read back."""
+        if self.spec is not None and self.spec.kind == "raise_after" and self._mine(step):
+            self.fired = True
+            raise InjectedFault(f"injected fault on rank {self.rank} after step {step}")
+
     def before_step(self, step: int) -> bool:
         """Returns True when this step's launch must be skipped. May sleep or raise, according to the spec."""
-        if not self._mine(step):
+        if not self._mine(step) or self.spec.kind == "raise_after":
             return False
         self.fired = True
         kind = self.spec.kind

@@ -40,6 +40,13 @@ def main():
         toks = [t for l in lines[:-1] for t in json.loads(l[6:])["choices"][0]["token_ids"]]
         assert lines[-1] == "data: [DONE]" and toks == want2, (toks, want2)
         assert c.get("/health").json()["status"] == "ok"
+        if os.environ.get("B2_FAULT"):
+            # A step fails on rank 1 only (host-side injection). Both ranks must agree to drop the in-flight request:
+            # the client gets an error, and the next request is served by engines that are still in step.
+            bad = c.post("/v1/completions", json={"prompt": p1, "max_tokens": 6})
+            assert bad.status_code == 500 and "another rank" in bad.json()["detail"], bad.text
+            r = c.post("/v1/completions", json={"prompt": p1, "max_tokens": 6}).json()
+            assert r["choices"][0]["token_ids"] == want1, (r, want1)
     app.state.engine.shutdown()          # the stop command reaches the follower through the next broadcast
     print(f"SERVE_TP_OK {world}", flush=True)
     dist.destroy_process_group()

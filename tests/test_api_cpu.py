@@ -148,8 +148,11 @@ def test_llm_parallel_degree_without_ranks_is_refused():
         LLM(PipelineConfig(model="tiny-llama", random_init=True, device="cpu", tensor_parallel=2))
 
 
-def test_openai_server_over_two_tensor_parallel_ranks_on_cpu(tmp_path):
-    """Rank 0 serves HTTP and broadcasts its commands, rank 1 follows: same completions as one process."""
+@pytest.mark.parametrize("fault", ["", "raise_after:rank=1:step=17"])
+def test_openai_server_over_two_tensor_parallel_ranks_on_cpu(tmp_path, fault):
+    """Rank 0 serves HTTP and broadcasts its commands, rank 1 follows: same completions as one process. With a fault
+    injected on rank 1 alone (host side, at the end of the third step of a later request, as a kernel status error would surface) both ranks must drop that request,
+    report the error to the client and serve the next request correctly."""
     import os
     import subprocess
     import sys
@@ -157,8 +160,8 @@ def test_openai_server_over_two_tensor_parallel_ranks_on_cpu(tmp_path):
     _write_tp_checkpoint(tmp_path)
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29643", os.path.join(root, "tests", "mp_serve_cpu.py")]
-    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", B2_TEST_CHECKPOINT=str(tmp_path))
+           "--master-port", "29643" if not fault else "29645", os.path.join(root, "tests", "mp_serve_cpu.py")]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", B2_TEST_CHECKPOINT=str(tmp_path), B2_FAULT=fault)
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=root)
     assert "SERVE_TP_OK 2" in p.stdout, p.stdout[-2000:] + p.stderr[-3000:]
 
