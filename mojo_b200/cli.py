@@ -27,6 +27,8 @@ def _cmd_serve(a) -> None:
         info, data_parallel = comm.info, False      # tensor parallelism: every rank admits every request
     elif ep is not None and getattr(ep, "world_size", 1) > 1:
         info, data_parallel = ep.info, True         # data-parallel attention + expert parallelism: requests are routed to an owner rank
+    elif getattr(llm, "dist_info", None) is not None and llm.dist_info.world_size > 1:
+        info, data_parallel = llm.dist_info, True   # whole-model replicas behind one endpoint
     if info is not None:
         # rank 0 serves HTTP and broadcasts its commands once per engine iteration, the other ranks follow
         from .serve.api_server import RankSync, follower_loop

@@ -16,6 +16,7 @@ class PipelineConfig:
     device: str | None = None             # default: cuda if available
     tensor_parallel: int = 1
     expert_parallel: int = 1
+    data_parallel: int = 1                # independent replicas, one per rank, behind one endpoint (`cli serve`)
     page_size: int = 128
     max_num_seqs: int = 256
     max_num_batched_tokens: int = 4096
@@ -42,7 +43,7 @@ class PipelineConfig:
             name = "--" + f.name.replace("_", "-")
             if f.type in ("bool", bool):
                 ap.add_argument(name, action="store_true" if not f.default else "store_false", dest=f.name, default=f.default)
-            elif f.name in ("tensor_parallel", "expert_parallel", "page_size", "max_num_seqs", "max_num_batched_tokens", "max_model_len", "seed"):
+            elif f.name in ("tensor_parallel", "expert_parallel", "data_parallel", "page_size", "max_num_seqs", "max_num_batched_tokens", "max_model_len", "seed"):
                 ap.add_argument(name, type=int, default=f.default, dest=f.name)
             elif f.name in ("num_pages", "eos_token_id"):
                 ap.add_argument(name, type=int, default=None, dest=f.name)

@@ -83,6 +83,12 @@ class LLM:
             mcfg.quantization = config.quantization
         self.model_config = mcfg
         degree = max(config.tensor_parallel, config.expert_parallel)
+        self.dist_info = None
+        if config.data_parallel > 1:
+            if degree > 1:
+                raise ValueError("data_parallel replicas are whole models: combine it with neither tensor_parallel nor expert_parallel")
+            self.dist_info = self._join_replicas(device, config.data_parallel)
+            device = str(self.dist_info.device)
         if degree > 1 and comm is None and ep is None:
             comm, ep, device = self._join_ranks(mcfg, device, degree)
         model = build_model(mcfg, device, dtype, comm=comm, ep=ep)
@@ -110,6 +116,18 @@ class LLM:
         self.engine = LLMEngine(ecfg, model=model, comm=comm)
         self.comm, self.ep = comm, ep
         self.tokenizer = _Tokenizer(config.tokenizer)
+
+    @staticmethod
+    def _join_replicas(device: str, degree: int):
+        """Data parallelism: every rank holds the whole model on its own device; the process group only carries the
+        serving front end's control messages."""
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        if world != degree:
+            raise RuntimeError(f"data_parallel={degree} needs {degree} ranks (WORLD_SIZE={world}): start the program with "
+                               f"`python -m torch.distributed.run --nproc-per-node {degree} --master-addr 127.0.0.1 ...`")
+        from ..parallel import init_distributed
+
+        return init_distributed("cuda" if device.startswith("cuda") else "cpu")
 
     def _join_ranks(self, mcfg, device: str, degree: int):
         """Join the process group of a `torch.distributed.run` launch and build this rank's communicator."""

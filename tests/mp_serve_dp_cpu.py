@@ -9,15 +9,16 @@ import threading
 import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-from mojo_b200.parallel import init_distributed  # noqa: E402
 from mojo_b200.pipelines import LLM, PipelineConfig, SamplingParams  # noqa: E402
 from mojo_b200.serve.api_server import RankSync, build_app, follower_loop  # noqa: E402
 
 
 def main():
-    info = init_distributed("cpu")
+    world = int(os.environ["WORLD_SIZE"])
     llm = LLM(PipelineConfig(model="tiny-llama", random_init=True, device="cpu", page_size=16, num_pages=64, max_num_seqs=4,
-                             max_num_batched_tokens=48, max_model_len=128, seed=0))
+                             max_num_batched_tokens=48, max_model_len=128, seed=0, data_parallel=world))   # joins the ranks itself
+    info = llm.dist_info
+    assert info is not None and info.world_size == world
     sync = RankSync(info, data_parallel=True)
     if not sync.leader:
         follower_loop(llm, sync)
