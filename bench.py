@@ -76,7 +76,6 @@ def main() -> None:
         reference_arm(args)
         return
 
-    import numpy as np
     import torch
 
     from mojo_b200 import ops
