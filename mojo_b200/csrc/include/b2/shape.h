@@ -9,8 +9,10 @@
 
 #if defined(__CUDACC__)
 #define B2_HD __host__ __device__ __forceinline__
+#define B2_UNROLL _Pragma("unroll")
 #else
 #define B2_HD inline
+#define B2_UNROLL
 #endif
 
 namespace b2 {
@@ -26,13 +28,13 @@ struct Shape {
   // number of elements (the product of the extents; 1 for an empty product is never needed: N >= 1)
   B2_HD int64_t numel() const {
     int64_t n = 1;
-#pragma unroll
+B2_UNROLL
     for (int i = 0; i < N; ++i) n *= d[i];
     return n;
   }
   B2_HD bool operator==(const Shape& o) const {
     bool eq = true;
-#pragma unroll
+B2_UNROLL
     for (int i = 0; i < N; ++i) eq = eq && d[i] == o.d[i];
     return eq;
   }
@@ -51,7 +53,7 @@ struct Stride {
   // element offset of a coordinate
   B2_HD int64_t offset(const Coord<N>& c) const {
     int64_t o = 0;
-#pragma unroll
+B2_UNROLL
     for (int i = 0; i < N; ++i) o += c.d[i] * s[i];
     return o;
   }
@@ -62,7 +64,7 @@ template <int N>
 B2_HD Stride<N> row_major(const Shape<N>& shape) {
   Stride<N> st{};
   int64_t run = 1;
-#pragma unroll
+B2_UNROLL
   for (int i = N - 1; i >= 0; --i) {
     st.s[i] = run;
     run *= shape.d[i];
@@ -74,7 +76,7 @@ B2_HD Stride<N> row_major(const Shape<N>& shape) {
 template <int N>
 B2_HD Coord<N> delinearize(int64_t i, const Shape<N>& shape) {
   Coord<N> c{};
-#pragma unroll
+B2_UNROLL
   for (int k = N - 1; k >= 0; --k) {
     c.d[k] = i % shape.d[k];
     i /= shape.d[k];
@@ -86,7 +88,7 @@ B2_HD Coord<N> delinearize(int64_t i, const Shape<N>& shape) {
 template <int N>
 B2_HD bool in_bounds(const Coord<N>& c, const Shape<N>& shape) {
   bool ok = true;
-#pragma unroll
+B2_UNROLL
   for (int i = 0; i < N; ++i) ok = ok && c.d[i] >= 0 && c.d[i] < shape.d[i];
   return ok;
 }
