@@ -128,10 +128,14 @@ sys.path.insert(0, {root!r})
 from mojo_b200.engine.watchdog import Heartbeat, WorkerLost
 rank, world, path, mode = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
 store = dist.FileStore(path, world)
-hb = Heartbeat(store, rank, world, limit_s=1.0)
-store.add("ready", 1)
-while int(store.add("ready", 0)) < world:
-    time.sleep(0.01)
+hb = Heartbeat(store, rank, world, limit_s=2.0)
+# processes start seconds apart on a busy machine: meet, beat afresh, meet again, so that no first check sees a
+# heartbeat that is stale only because its owner was still importing
+for gate in ("ready", "go"):
+    store.add(gate, 1)
+    while int(store.add(gate, 0)) < world:
+        time.sleep(0.01)
+    hb.beat(-1)
 for step in range(200):
     try:
         hb.check()
