@@ -28,6 +28,7 @@ class SamplingParams:
     stop_token_ids: tuple = ()
     ignore_eos: bool = False
     seed: int | None = None
+    logprobs: int | None = None       # None: off; k >= 0: log-probability of each sampled token plus the k most likely ones
 
 
 @dataclass
@@ -64,6 +65,7 @@ class RequestState:
     first_token_time: float | None = None
     finished: bool = False
     finish_reason: str | None = None
+    logprobs: list = field(default_factory=list)   # per generated token: (logprob, [(token id, logprob), ...]) when requested
 
 
 @dataclass
@@ -73,6 +75,7 @@ class RequestOutput:
     output_ids: list
     finished: bool
     finish_reason: str | None
+    logprobs: list | None = None      # for the new tokens, when the request asked for them
 
 
 class LLMEngine:
@@ -232,10 +235,16 @@ class LLMEngine:
         now = time.perf_counter()
         outs = []
         ttfts, itls = [], []
-        for rid, tok, st in zip(sample_ids, tokens, states):
+        step_lp = self.runner.last_logprobs     # None unless a request of this batch asked for log-probabilities
+        for row, (rid, tok, st) in enumerate(zip(sample_ids, tokens, states)):
             rid, tok = int(rid), int(tok)
             hit_max = self.scheduler.append_token(rid, tok)
             st.output_ids.append(tok)
+            new_lp = None
+            if step_lp is not None and st.params.logprobs is not None:
+                lp, top = step_lp[row]
+                new_lp = [(lp, top[: st.params.logprobs])]
+                st.logprobs.extend(new_lp)
             if st.first_token_time is None:
                 st.first_token_time = now
                 ttfts.append(now - st.arrival)
@@ -254,7 +263,7 @@ class LLMEngine:
                 st.finished, st.finish_reason = True, reason
                 self.scheduler.finish(rid)
                 self.finished_requests += 1
-            outs.append(RequestOutput(rid, [tok], st.output_ids, st.finished, reason))
+            outs.append(RequestOutput(rid, [tok], st.output_ids, st.finished, reason, new_lp))
         self.generated_tokens += len(outs)
         if ttfts:
             v = np.asarray(ttfts) * 1e3
@@ -284,17 +293,21 @@ class LLMEngine:
         if params is None or isinstance(params, SamplingParams):
             params = [params] * len(prompts)
         rids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        self.run_until_done()
+        if self.device.type == "cuda":
+            ops.check_status(self.device)
+        return [list(self.requests[r].output_ids) for r in rids]
+
+    def run_until_done(self) -> None:
+        """Step until every admitted request has finished. In lock-step mode (data-parallel attention with
+        expert-parallel MoE) ranks serve different requests but must take the same number of steps: go on, with idle
+        steps that only join the MoE layers, until no rank has work left."""
         if self.cfg.lockstep and self._lockstep_group() is not None:
-            # ranks serve different requests but must take the same number of steps: go on (idle steps join the MoE
-            # layers) until no rank has work left
             while self._any_rank_busy():
                 self.step()
         else:
             while self.has_unfinished():
                 self.step()
-        if self.device.type == "cuda":
-            ops.check_status(self.device)
-        return [list(self.requests[r].output_ids) for r in rids]
 
     def _lockstep_group(self):
         ep = getattr(self.model, "ep", None)

@@ -74,6 +74,7 @@ class ModelRunner:
         self.graph_kernel_launches = 0   # kernels executed inside replayed graphs
         self.step_events = None          # optional (start, end) CUDA events recorded around the device work
         self.last_num_tokens = 0
+        self.last_logprobs = None        # per sampled row (logprob of the chosen token, [(id, logprob)] top-k) of the last step, on request
         b, self.buckets = 1, []
         while b < cfg.max_num_seqs:
             self.buckets.append(b)
@@ -126,7 +127,9 @@ class ModelRunner:
     # ------------------------------------------------------------------------------------------------
     def execute(self, batch, states, step: int) -> list[int]:
         self.last_num_tokens = int(batch.num_tokens)
-        if (self.use_graphs and batch.num_prefill == 0 and batch.num_decode > 0
+        self.last_logprobs = None
+        top_lp = max((s.params.logprobs for s in states if s.params.logprobs is not None), default=None)
+        if (top_lp is None and self.use_graphs and batch.num_prefill == 0 and batch.num_decode > 0
                 and all(s.params.temperature <= 0.0 for s in states)):
             g = self.graphs.get(self._bucket(int(batch.num_seqs)))
             if self.ep is None or (g is not None and g.usable()):
@@ -171,7 +174,8 @@ class ModelRunner:
                 self.step_events[1].record()
             self.d2h_bytes = 0
             return []
-        fused_greedy = greedy and getattr(self.model, "greedy_in_forward", False)
+        # log-probabilities need the logits themselves: no arg-max inside the forward pass for such a step
+        fused_greedy = greedy and top_lp is None and getattr(self.model, "greedy_in_forward", False)
         if fused_greedy:
             ids = self.model.forward(token_ids, positions, slots, meta, self.kv_caches, rows, greedy=True)
         else:
@@ -184,6 +188,16 @@ class ModelRunner:
             seed = self.cfg.seed if states[0].params.seed is None else states[0].params.seed
             ids = ops.sample(logits.float() if not self.cuda else logits, st.view(seg_temp, torch.float32),
                              st.view(seg_topk, torch.int32), st.view(seg_topp, torch.float32), seed, step)
+        if top_lp is not None:
+            # optional diagnostic output, off the measured path: plain tensor ops on the step's logits
+            lp = torch.log_softmax(logits.float(), dim=-1)
+            chosen = lp.gather(1, ids.view(-1, 1).long()).view(-1).tolist()
+            if top_lp > 0:
+                tv, ti = lp.topk(min(top_lp, lp.shape[1]), dim=-1)
+                tv, ti = tv.tolist(), ti.tolist()
+                self.last_logprobs = [(chosen[r], list(zip(ti[r], tv[r]))) for r in range(S)]
+            else:
+                self.last_logprobs = [(chosen[r], []) for r in range(S)]
         if self.step_events is not None:
             self.step_events[1].record()
         if self.cuda:

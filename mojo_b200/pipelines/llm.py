@@ -20,6 +20,7 @@ class GenerationOutput:
     token_ids: list
     text: str | None
     finish_reason: str | None
+    logprobs: list | None = None      # per token (logprob, [(token id, logprob), ...]) when SamplingParams.logprobs was set
 
 
 class _Tokenizer:
@@ -164,12 +165,13 @@ class LLM:
         if sampling_params is None or isinstance(sampling_params, SamplingParams):
             sampling_params = [sampling_params or SamplingParams()] * len(ids)
         rids = [self.engine.add_request(p, sp) for p, sp in zip(ids, sampling_params)]
-        while self.engine.has_unfinished():
-            self.engine.step()
+        self.engine.run_until_done()
         outs = []
         for rid, p in zip(rids, ids):
             st = self.engine.requests[rid]
-            outs.append(GenerationOutput(rid, p, list(st.output_ids), self.tokenizer.decode(st.output_ids), st.finish_reason))
+            outs.append(GenerationOutput(rid, p, list(st.output_ids), self.tokenizer.decode(st.output_ids), st.finish_reason,
+                                         list(st.logprobs) if st.params.logprobs is not None else None))
+            self.engine.forget(rid)
         return outs
 
     def stream(self, prompt, sampling_params: SamplingParams | None = None) -> Iterator[int]:

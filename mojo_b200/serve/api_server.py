@@ -210,7 +210,7 @@ class AsyncEngine:
                 if s is None:
                     continue
                 loop, q = s
-                loop.call_soon_threadsafe(q.put_nowait, ("token", (o.new_token_ids, o.finished, o.finish_reason)))
+                loop.call_soon_threadsafe(q.put_nowait, ("token", (o.new_token_ids, o.finished, o.finish_reason, o.logprobs)))
                 if o.finished:
                     self.streams.pop(o.request_id, None)
             for o in outs:
@@ -242,9 +242,24 @@ class AsyncEngine:
         self.thread.join(timeout=10.0)
 
 
-def _sampling_from(body: dict, default_max: int = 16) -> SamplingParams:
+def _logprobs_from(body: dict, chat: bool) -> int | None:
+    """Completions: `logprobs: k`. Chat: `logprobs: true` with optional `top_logprobs: k`. At most 20 alternatives."""
+    if chat:
+        if not body.get("logprobs"):
+            return None
+        k = int(body.get("top_logprobs") or 0)
+    else:
+        if body.get("logprobs") is None or body.get("logprobs") is False:
+            return None
+        k = int(body.get("logprobs"))
+    if k < 0 or k > 20:
+        raise ValueError("logprobs / top_logprobs must be between 0 and 20")
+    return k
+
+
+def _sampling_from(body: dict, default_max: int = 16, chat: bool = False) -> SamplingParams:
     stop_ids = tuple(body.get("stop_token_ids") or ())
-    return SamplingParams(temperature=float(body.get("temperature", 0.0) or 0.0), top_k=int(body.get("top_k", 0) or 0),
+    return SamplingParams(logprobs=_logprobs_from(body, chat), temperature=float(body.get("temperature", 0.0) or 0.0), top_k=int(body.get("top_k", 0) or 0),
                           top_p=float(body.get("top_p", 1.0) or 1.0), max_tokens=int(body.get("max_tokens") or default_max),
                           stop_token_ids=stop_ids, ignore_eos=bool(body.get("ignore_eos", False)), seed=body.get("seed"))
 
@@ -298,22 +313,28 @@ def build_app(llm, model_name: str = "mojo_b200", sync: RankSync | None = None):
         t = tok.decode(ids)
         return t if t is not None else " ".join(str(i) for i in ids)
 
+    def lp_json(ids, lps):
+        """OpenAI completions layout: tokens, their log-probabilities, and per position a map of the alternatives."""
+        return {"tokens": [text_of([t]) for t in ids], "token_ids": list(ids), "token_logprobs": [lp for lp, _ in lps],
+                "top_logprobs": [{text_of([t]): v for t, v in top} for _, top in lps]}
+
     async def collect(q, rid, stops):
         """(token ids, text, finish reason) of a whole request."""
         ts = _TextStream(text_of, stops)
-        parts = []
+        parts, lps = [], []
         while True:
             kind, payload = await q.get()
             if kind == "error":
                 raise HTTPException(status_code=500, detail=payload)
-            new, finished, reason = payload
+            new, finished, reason, lp = payload
             delta, stopped = ts.push(new, finished)
             parts.append(delta)
+            lps.extend(lp or [])
             if stopped:
                 aeng.abort(rid)
-                return ts.ids, "".join(parts), "stop"
+                return ts.ids, "".join(parts), "stop", lps
             if finished:
-                return ts.ids, "".join(parts), reason
+                return ts.ids, "".join(parts), reason, lps
 
     async def sse(q, rid, make_chunk, final_chunk, stops=()):
         ts = _TextStream(text_of, list(stops))
@@ -323,11 +344,14 @@ def build_app(llm, model_name: str = "mojo_b200", sync: RankSync | None = None):
                 if kind == "error":
                     yield f"data: {json.dumps({'error': payload})}\n\n"
                     break
-                new, finished, reason = payload
+                new, finished, reason, lp = payload
                 delta, stopped = ts.push(new, finished)
                 if stopped:
                     finished, reason = True, "stop"
-                yield f"data: {json.dumps(make_chunk(new, delta, reason if finished else None))}\n\n"
+                chunk = make_chunk(new, delta, reason if finished else None)
+                if lp:
+                    chunk["choices"][0]["logprobs"] = lp_json(new, lp)
+                yield f"data: {json.dumps(chunk)}\n\n"
                 if finished:
                     if final_chunk is not None:
                         yield f"data: {json.dumps(final_chunk(reason))}\n\n"
@@ -383,8 +407,8 @@ def build_app(llm, model_name: str = "mojo_b200", sync: RankSync | None = None):
             ids = tok.encode(prompt)
         except ValueError as e:
             raise HTTPException(status_code=400, detail=str(e))
-        sp = _sampling_from(body)
         try:
+            sp = _sampling_from(body)
             stops = _stops_from(body)
             rid, q = aeng.submit(ids, sp)
         except ValueError as e:
@@ -396,9 +420,10 @@ def build_app(llm, model_name: str = "mojo_b200", sync: RankSync | None = None):
                 return {"id": cid, "object": "text_completion", "created": created, "model": model_name,
                         "choices": [{"index": 0, "text": text, "token_ids": new, "finish_reason": reason}]}
             return StreamingResponse(sse(q, rid, chunk, None, stops), media_type="text/event-stream")
-        out, text, reason = await collect(q, rid, stops)
+        out, text, reason, lps = await collect(q, rid, stops)
         return {"id": cid, "object": "text_completion", "created": created, "model": model_name,
-                "choices": [{"index": 0, "text": text, "token_ids": out, "finish_reason": reason}],
+                "choices": [{"index": 0, "text": text, "token_ids": out, "finish_reason": reason,
+                             "logprobs": lp_json(out, lps) if sp.logprobs is not None else None}],
                 "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out), "total_tokens": len(ids) + len(out)}}
 
     @app.post("/v1/chat/completions")
@@ -407,8 +432,8 @@ def build_app(llm, model_name: str = "mojo_b200", sync: RankSync | None = None):
         if not messages:
             raise HTTPException(status_code=400, detail="messages is required")
         ids = tok.apply_chat_template(messages)
-        sp = _sampling_from(body, default_max=256)
         try:
+            sp = _sampling_from(body, default_max=256, chat=True)
             stops = _stops_from(body)
             rid, q = aeng.submit(ids, sp)
         except ValueError as e:
@@ -426,9 +451,13 @@ def build_app(llm, model_name: str = "mojo_b200", sync: RankSync | None = None):
                 return {"id": cid, "object": "chat.completion.chunk", "created": created, "model": model_name,
                         "choices": [{"index": 0, "delta": delta, "finish_reason": reason}]}
             return StreamingResponse(sse(q, rid, chunk, None, stops), media_type="text/event-stream")
-        out, text, reason = await collect(q, rid, stops)
+        out, text, reason, lps = await collect(q, rid, stops)
+        chat_lp = None
+        if sp.logprobs is not None:
+            chat_lp = {"content": [{"token": text_of([t]), "logprob": lp, "top_logprobs": [{"token": text_of([a]), "logprob": v} for a, v in top]}
+                                   for t, (lp, top) in zip(out, lps)]}
         return {"id": cid, "object": "chat.completion", "created": created, "model": model_name,
-                "choices": [{"index": 0, "message": {"role": "assistant", "content": text}, "finish_reason": reason}],
+                "choices": [{"index": 0, "message": {"role": "assistant", "content": text}, "finish_reason": reason, "logprobs": chat_lp}],
                 "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out), "total_tokens": len(ids) + len(out)}}
 
     return app

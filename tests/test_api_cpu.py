@@ -231,3 +231,30 @@ def test_openai_server_stop_strings():
         r = c.post("/v1/completions", json={"prompt": prompt, "max_tokens": 8}).json()
         assert r["choices"][0]["token_ids"] == want
     app.state.engine.shutdown()
+
+
+def test_openai_server_logprobs():
+    from fastapi.testclient import TestClient
+
+    from mojo_b200.serve import build_app
+
+    llm = tiny_llm()
+    prompt = [5, 900, 77, 3021, 15000]
+    ref = tiny_llm().generate([prompt], SamplingParams(max_tokens=4, logprobs=2))[0]
+    assert len(ref.logprobs) == 4 and all(len(top) == 2 for _, top in ref.logprobs)
+    app = build_app(llm, "tiny-llama")
+    with TestClient(app) as c:
+        r = c.post("/v1/completions", json={"prompt": prompt, "max_tokens": 4, "logprobs": 2}).json()["choices"][0]
+        assert r["token_ids"] == ref.token_ids
+        assert r["logprobs"]["token_logprobs"] == pytest.approx([lp for lp, _ in ref.logprobs], abs=1e-5)
+        assert [len(m) for m in r["logprobs"]["top_logprobs"]] == [2, 2, 2, 2] and all(v <= 0 for m in r["logprobs"]["top_logprobs"] for v in m.values())
+        assert c.post("/v1/completions", json={"prompt": prompt, "max_tokens": 2}).json()["choices"][0]["logprobs"] is None
+        r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3, "logprobs": True,
+                                                 "top_logprobs": 1}).json()["choices"][0]
+        assert len(r["logprobs"]["content"]) == 3 and len(r["logprobs"]["content"][0]["top_logprobs"]) == 1
+        with c.stream("POST", "/v1/completions", json={"prompt": prompt, "max_tokens": 4, "stream": True, "logprobs": 0}) as s:
+            lines = [json.loads(l[6:]) for l in s.iter_lines() if l.startswith("data: ") and l != "data: [DONE]"]
+        got = [v for l in lines for v in l["choices"][0]["logprobs"]["token_logprobs"]]
+        assert got == pytest.approx([lp for lp, _ in ref.logprobs], abs=1e-5)
+        assert c.post("/v1/completions", json={"prompt": prompt, "logprobs": 99}).status_code == 400
+    app.state.engine.shutdown()

@@ -203,3 +203,36 @@ def test_context_limit_is_capped_by_the_position_table_and_enforced_at_admission
         eng.add_request(list(range(cfg.max_position_embeddings)))
     with pytest.raises(ValueError, match="empty prompt"):
         eng.add_request([])
+
+
+def test_logprobs_match_the_models_own_distribution():
+    """SamplingParams.logprobs: the log-probability of each generated token and the k most likely alternatives, equal
+    to log_softmax of the logits the model produces for the same prefix; requests without the option are unaffected."""
+    from mojo_b200 import ops
+
+    cfg = tiny_llama()
+    ecfg = EngineConfig(model=cfg, device="cpu", dtype=torch.float32, page_size=16, num_pages=64, max_num_seqs=4,
+                        max_num_batched_tokens=64, max_model_len=256)
+    eng = LLMEngine(ecfg)
+    prompt = torch.randint(0, cfg.vocab_size, (21,), generator=torch.Generator().manual_seed(9)).tolist()
+    plain = eng.generate([prompt], SamplingParams(max_tokens=5))[0]
+    r_lp = eng.add_request(prompt, SamplingParams(max_tokens=5, logprobs=3))
+    r_no = eng.add_request(prompt[:7], SamplingParams(max_tokens=5))
+    eng.run_until_done()
+    st = eng.requests[r_lp]
+    assert st.output_ids == plain and len(st.logprobs) == 5
+    assert eng.requests[r_no].logprobs == []
+    ids = list(prompt)
+    for tok, (lp, top) in zip(st.output_ids, st.logprobs):
+        T = len(ids)
+        caches = eng.model.allocate_kv_cache((T + 15) // 16 + 1, 16)
+        bt = torch.arange((T + 15) // 16, dtype=torch.int32).unsqueeze(0)
+        meta = ops.AttnMeta(torch.tensor([0, T], dtype=torch.int32), torch.tensor([T], dtype=torch.int32), bt, 0, T, T)
+        logits = eng.model.forward(torch.tensor(ids), torch.arange(T, dtype=torch.int32), torch.arange(T, dtype=torch.int64), meta, caches,
+                                   torch.tensor([T - 1]))[0].float()
+        want = torch.log_softmax(logits, -1)
+        assert abs(lp - want[tok].item()) < 1e-4
+        assert len(top) == 3 and top[0][0] == tok                       # greedy: the chosen token is the most likely one
+        assert [t for t, _ in top] == want.topk(3).indices.tolist()
+        assert all(abs(v - want[t].item()) < 1e-4 for t, v in top)
+        ids.append(tok)
