@@ -81,6 +81,7 @@ class ModelRunner:
             b = b * 2 if b < 16 else b + max(16, b // 4) // 16 * 16
         self.buckets.append(cfg.max_num_seqs)
         self.graph_pool = None           # memory pool shared by the decode graphs (they never replay concurrently)
+        self.failed_buckets: dict[int, str] = {}   # buckets whose capture failed: their steps run eagerly
         # Expert parallelism: every rank must run the same number of MoE layer calls per step, so a decode graph can
         # only be captured when all ranks capture together (at start-up); a bucket that is missing runs eagerly.
         ep = getattr(model, "ep", None)
@@ -95,12 +96,29 @@ class ModelRunner:
             return 0
         n = 0
         for bb in sorted(set(buckets if buckets is not None else self.buckets), reverse=True):
-            if bb not in self.graphs:
-                self.graphs[bb] = _DecodeGraph(self, bb)
+            if bb not in self.graphs and bb not in self.failed_buckets and self._capture(bb) is not None:
                 n += 1
-        torch.cuda.synchronize(self.device)
-        ops.check_status(self.device)
+        if self.cuda:
+            torch.cuda.synchronize(self.device)
+            ops.check_status(self.device)
         return n
+
+    def _capture(self, bb: int):
+        """Capture one bucket. A capture that fails (an operation that a capturing stream does not allow) is not fatal:
+        the bucket is remembered as failed and its steps run eagerly. The failure is the same on every rank of a
+        tensor-parallel group (same shapes, same code), so the ranks keep taking the same path."""
+        try:
+            g = _DecodeGraph(self, bb)
+        except Exception as e:  # noqa: BLE001
+            import warnings
+
+            self.failed_buckets[bb] = repr(e)
+            if self.cuda:
+                torch.cuda.synchronize(self.device)
+            warnings.warn(f"mojo_b200: CUDA-graph capture of the {bb}-sequence decode step failed ({e!r}); such steps run eagerly", stacklevel=2)
+            return None
+        self.graphs[bb] = g
+        return g
 
     def autotune(self, verbose: bool = False) -> dict:
         """Measure the GEMM configurations of this model's weight shapes at the token counts the engine produces
@@ -131,8 +149,11 @@ class ModelRunner:
         top_lp = max((s.params.logprobs for s in states if s.params.logprobs is not None), default=None)
         if (top_lp is None and self.use_graphs and batch.num_prefill == 0 and batch.num_decode > 0
                 and all(s.params.temperature <= 0.0 for s in states)):
-            g = self.graphs.get(self._bucket(int(batch.num_seqs)))
-            if self.ep is None or (g is not None and g.usable()):
+            bb = self._bucket(int(batch.num_seqs))
+            g = self.graphs.get(bb)
+            if g is None and self.ep is None and bb not in self.failed_buckets:
+                g = self._capture(bb)          # first use of a bucket that was not captured at start-up
+            if g is not None and g.usable():
                 return self._execute_decode_graph(batch)
         st = self.staging
         st.begin()
@@ -221,10 +242,7 @@ class ModelRunner:
     def _execute_decode_graph(self, batch) -> list[int]:
         B = int(batch.num_seqs)
         bb = self._bucket(B)
-        g = self.graphs.get(bb)
-        if g is None:
-            g = _DecodeGraph(self, bb)
-            self.graphs[bb] = g
+        g = self.graphs[bb]
         self.h2d_bytes = g.stage(batch, B)
         if self.step_events is not None:
             self.step_events[0].record()

@@ -236,3 +236,50 @@ def test_logprobs_match_the_models_own_distribution():
         assert [t for t, _ in top] == want.topk(3).indices.tolist()
         assert all(abs(v - want[t].item()) < 1e-4 for t, v in top)
         ids.append(tok)
+
+
+def test_decode_graph_dispatch_and_fallback_when_a_capture_fails(monkeypatch):
+    """The runner's choice between graph replay and eager execution, exercised on CPU with stand-ins for the graph
+    objects: a bucket is captured at first use, a capture that raises is remembered and its steps run eagerly (with
+    the same tokens), and other buckets keep replaying."""
+    import warnings
+
+    from mojo_b200.engine import model_runner as mr
+
+    ecfg = EngineConfig(model=tiny_llama(), device="cpu", dtype=torch.float32, page_size=16, num_pages=64, max_num_seqs=4,
+                        max_num_batched_tokens=64, max_model_len=128)
+    eng = LLMEngine(ecfg)
+    runner = eng.runner
+    prompts = [[3, 4, 5, 6], [9, 8, 7]]
+    want = LLMEngine(ecfg).generate(prompts, SamplingParams(max_tokens=6))
+    captured, replayed = [], []
+
+    class FakeGraph:
+        def __init__(self, r, bb):
+            if bb == 2:
+                raise RuntimeError("operation not permitted when stream is capturing")
+            captured.append(bb)
+            self.ep_calls = 0
+
+        def usable(self):
+            return True
+
+    def fake_replay(batch):
+        replayed.append(int(batch.num_seqs))
+        runner.use_graphs = False                      # compute the step's tokens through the eager path
+        try:
+            return runner.execute(batch, [eng.requests[int(r)] for r in batch.sample_seq_ids], 0)
+        finally:
+            runner.use_graphs = True
+
+    monkeypatch.setattr(mr, "_DecodeGraph", FakeGraph)
+    monkeypatch.setattr(runner, "_execute_decode_graph", fake_replay)
+    runner.use_graphs = True
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        got = eng.generate(prompts, SamplingParams(max_tokens=6))          # two sequences decode together: bucket 2 fails
+        one = eng.generate([prompts[0]], SamplingParams(max_tokens=6))     # one sequence: bucket 1 captures and replays
+    assert got == want and one == [want[0]]
+    assert list(runner.failed_buckets) == [2] and captured == [1] and replayed and set(replayed) == {1}
+    assert sum("capture" in str(x.message) for x in w) == 1                # warned once, not once per step
+    assert runner.capture_graphs() == 1 and sorted(captured) == [1, 4]     # the remaining bucket; the failed one is not retried
