@@ -152,7 +152,6 @@ def main() -> None:
     ap.add_argument("--inner-ag", type=int, default=8192, help="K of the all-gather GEMM (activation width)")
     ap.add_argument("--cols-ag", type=int, default=28672, help="N of the all-gather GEMM before sharding")
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--rs-bn", type=int, default=0, help="force the UMMA N of the fused reduce-scatter GEMM (0 = automatic)")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"],
                     help="fp8: e4m3 operands with 1x128 activation and 128x128 weight scales (block-scaled), bf16 out")
     ap.add_argument("--out", default=None)
@@ -187,9 +186,8 @@ def main() -> None:
 
         t_base_rs = timed(base_rs, a.iters, 3, info)
         t_base_ar = timed(base_ar, a.iters, 3, info)
-        rs_cfg = ops.gemm_config(M <= 128, a.rs_bn) if a.rs_bn else 0
-        t_rs = timed(lambda: comm.linear_reduce_scatter(x, w, config=rs_cfg), a.iters, 3, info)
-        t_ar = timed(lambda: comm.linear_all_reduce(x, w, config=rs_cfg), a.iters, 3, info)
+        t_rs = timed(lambda: comm.linear_reduce_scatter(x, w), a.iters, 3, info)
+        t_ar = timed(lambda: comm.linear_all_reduce(x, w), a.iters, 3, info)
         t_gemm = timed(lambda: ops.linear(x, w, out=y_full), a.iters, 3, info)
         flops = 2.0 * Mp * a.cols * k_local
         t_compute = flops / (peak * 1e6)

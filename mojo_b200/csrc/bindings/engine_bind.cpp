@@ -143,6 +143,7 @@ void bind_engine(py::module_& m) {
       .def("append_token", &Scheduler::append_token)
       .def("finish", &Scheduler::finish)
       .def("abort", &Scheduler::abort)
+      .def("commit_step", &Scheduler::commit_step)
       .def("has_unfinished", &Scheduler::has_unfinished)
       .def("num_waiting", &Scheduler::num_waiting)
       .def("num_running", &Scheduler::num_running)

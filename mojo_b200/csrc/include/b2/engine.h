@@ -12,6 +12,7 @@
 #include <list>
 #include <string>
 #include <unordered_map>
+#include <utility>
 #include <vector>
 
 namespace b2 {
@@ -139,6 +140,10 @@ class Scheduler {
   bool append_token(int64_t id, int32_t token);
   void finish(int64_t id);
   void abort(int64_t id) { finish(id); }
+  // Register the full pages written by the last batch in the prefix cache. The engine calls it when the step has
+  // completed; `step()` calls it for the previous batch as well. A sequence that is finished, aborted or preempted
+  // before that keeps no entry for the unconfirmed step, so a failed step cannot leave half-written pages shared.
+  void commit_step();
 
   bool has_unfinished() const { return !waiting_.empty() || !running_.empty(); }
   int64_t num_waiting() const { return static_cast<int64_t>(waiting_.size()); }
@@ -149,6 +154,7 @@ class Scheduler {
  private:
   bool preempt_one(int64_t keep_id, Batch* b);
   void emit(Request& r, int64_t n_tokens, Batch* b);
+  void drop_pending_commit(int64_t id);
 
   SchedulerConfig cfg_;
   KVCacheManager* kv_;
@@ -156,6 +162,7 @@ class Scheduler {
   std::deque<int64_t> waiting_;
   std::vector<int64_t> running_;  // admission order
   int64_t total_preemptions_ = 0;
+  std::vector<std::pair<int64_t, int64_t>> pending_commits_;  // (sequence, tokens computed) of the batch in flight
 };
 
 }  // namespace engine

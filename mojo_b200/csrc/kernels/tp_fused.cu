@@ -349,12 +349,14 @@ extern "C" int b2_tp_gemm_rs_bf16(const void* x, const void* w, const B2TpRegion
   prm.timeout_ns = timeout_ns;
   prm.region_bytes = lay->total_bytes;
   bool swap = M <= 128;
-  // 256-wide tiles faulted here with a residual at M = 2048 (cause not found by reading): they stay off until it is.
   int bn = swap ? pick_bn_swap(M) : 128;
   if (config != 0) {
     swap = (config >> 30) & 1;
     bn = config & 0xffff;
   }
+  // 256-wide tiles are not built for this kernel: that instantiation raised an illegal memory access twice and the
+  // cause was not found by reading, so no configuration word reaches it.
+  if (bn > 128) return -kBadArgument;
   // flag capacity: units of the busiest owner
   const int tm = swap ? bn : 128;
   const int64_t units = static_cast<int64_t>((R + tm - 1) / tm + 1) * (swap ? (N + 127) / 128 : (N + bn - 1) / bn);
@@ -366,14 +368,12 @@ extern "C" int b2_tp_gemm_rs_bf16(const void* x, const void* w, const B2TpRegion
       case 32: B2_RS(32, true);
       case 64: B2_RS(64, true);
       case 128: B2_RS(128, true);
-      case 256: B2_RS(256, true);
       default: return -kBadArgument;
     }
   }
   switch (bn) {
     case 64: B2_RS(64, false);
     case 128: B2_RS(128, false);
-    case 256: B2_RS(256, false);
     default: return -kBadArgument;
   }
 #undef B2_RS

@@ -21,6 +21,9 @@ void Scheduler::add_request(int64_t id, const int32_t* prompt, int64_t prompt_le
   if (reqs_.count(id)) throw std::invalid_argument("Scheduler: duplicate request id");
   if (prompt_len <= 0) throw std::invalid_argument("Scheduler: empty prompt");
   if (prompt_len + 1 > cfg_.max_model_len) throw std::invalid_argument("Scheduler: prompt longer than max_model_len");
+  // Without chunked prefill a prompt must fit one step's token budget, or it would sit at the head of the queue forever.
+  if (!cfg_.enable_chunked_prefill && prompt_len > cfg_.max_num_batched_tokens)
+    throw std::invalid_argument("Scheduler: prompt longer than max_num_batched_tokens and chunked prefill is off");
   const int64_t max_pages = (std::min<int64_t>(prompt_len + max_new_tokens, cfg_.max_model_len) + kv_->page_size() - 1) / kv_->page_size();
   if (max_pages > kv_->num_pages()) throw std::invalid_argument("Scheduler: request can never fit in the KV cache");
   Request r;
@@ -43,6 +46,7 @@ bool Scheduler::preempt_one(int64_t keep_id, Batch* b) {
   const int64_t victim = running_.back();
   running_.pop_back();
   Request& r = reqs_.at(victim);
+  drop_pending_commit(victim);
   kv_->free_sequence(victim);
   r.computed = 0;
   r.status = SeqStatus::kWaiting;
@@ -76,11 +80,29 @@ void Scheduler::emit(Request& r, int64_t n, Batch* b) {
     b->sample_seq_ids.push_back(r.id);
   }
   r.computed = start + n;
-  kv_->commit(r.id, r.tokens.data(), r.computed);
+  // The pages become prefix-cache entries only once the step that writes their KV has completed (commit_step).
+  pending_commits_.push_back({r.id, r.computed});
   b->max_q_len = std::max<int>(b->max_q_len, static_cast<int>(n));
 }
 
+void Scheduler::commit_step() {
+  for (const auto& pc : pending_commits_) {
+    auto it = reqs_.find(pc.first);
+    if (it == reqs_.end()) continue;
+    kv_->commit(pc.first, it->second.tokens.data(), std::min<int64_t>(pc.second, static_cast<int64_t>(it->second.tokens.size())));
+  }
+  pending_commits_.clear();
+}
+
+void Scheduler::drop_pending_commit(int64_t id) {
+  pending_commits_.erase(std::remove_if(pending_commits_.begin(), pending_commits_.end(),
+                                        [id](const std::pair<int64_t, int64_t>& pc) { return pc.first == id; }),
+                         pending_commits_.end());
+}
+
 Batch Scheduler::step() {
+  // Asking for the next batch says that the previous one ran to completion: its pages may now be shared.
+  commit_step();
   Batch b;
   int64_t budget = cfg_.max_num_batched_tokens;
   std::vector<Entry> entries;
@@ -92,7 +114,9 @@ Batch Scheduler::step() {
     Request& r = reqs_.at(id);
     const int64_t pending = static_cast<int64_t>(r.tokens.size()) - r.computed;
     int64_t n = pending == 1 ? 1 : std::min(pending, budget);
-    if (pending > 1 && !cfg_.enable_chunked_prefill && n < pending) n = 0;
+    // chunked prefill off: wait for a step with room for the whole run, unless no step ever has it (a preempted
+    // sequence recomputes prompt + generated tokens, which may exceed the budget): that run is chunked after all
+    if (pending > 1 && !cfg_.enable_chunked_prefill && n < pending && pending <= cfg_.max_num_batched_tokens) n = 0;
     if (n <= 0 || budget <= 0) { ++i; continue; }
     bool self_preempted = false;
     while (!kv_->reserve(id, r.computed + n)) {
@@ -113,7 +137,7 @@ Batch Scheduler::step() {
     if (!kv_->has_sequence(id)) r.computed = kv_->add_sequence(id, r.tokens.data(), static_cast<int64_t>(r.tokens.size()));
     const int64_t pending = static_cast<int64_t>(r.tokens.size()) - r.computed;
     int64_t n = std::min(pending, budget);
-    if (!cfg_.enable_chunked_prefill && n < pending) break;
+    if (!cfg_.enable_chunked_prefill && n < pending && pending <= cfg_.max_num_batched_tokens) break;
     // Admission needs the pages of the whole known sequence, not just this chunk: a request that can
     // start but not finish its prompt would only be preempted again.
     const int64_t need_all = kv_->pages_needed(id, static_cast<int64_t>(r.tokens.size()) + 1);
@@ -156,6 +180,7 @@ bool Scheduler::append_token(int64_t id, int32_t token) {
 void Scheduler::finish(int64_t id) {
   auto it = reqs_.find(id);
   if (it == reqs_.end()) return;
+  drop_pending_commit(id);   // a step that was not confirmed leaves no prefix-cache entry behind
   kv_->free_sequence(id);
   running_.erase(std::remove(running_.begin(), running_.end(), id), running_.end());
   waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), id), waiting_.end());

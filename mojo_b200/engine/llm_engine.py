@@ -159,6 +159,8 @@ class LLMEngine:
             raise ValueError("empty prompt")
         if n >= self.cfg.max_model_len:
             raise ValueError(f"prompt of {n} tokens does not fit the context limit of {self.cfg.max_model_len} tokens")
+        if not self.cfg.enable_chunked_prefill and n > self.cfg.max_num_batched_tokens:
+            raise ValueError(f"prompt of {n} tokens exceeds the per-step token budget of {self.cfg.max_num_batched_tokens} and chunked prefill is off")
 
     def prompt_of(self, rid: int) -> np.ndarray:
         return self._prompts[rid]
@@ -227,6 +229,9 @@ class LLMEngine:
         with trace.span("engine.execute"):
             tokens = self.runner.execute(batch, states, self.step_count)
         self.fault.after_execute(self.step_count)
+        # the step ran: its full pages may enter the prefix cache (a step that raised never gets here, and the abort
+        # that follows it drops the pages it may have half written)
+        self.scheduler.commit_step()
         if self.watchdog is not None:
             self.watchdog.end_step(self.step_count)
         if self.heartbeat is not None:

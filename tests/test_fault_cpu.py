@@ -168,3 +168,51 @@ def test_ranks_learn_on_the_host_that_a_peer_is_gone(tmp_path, mode):
         assert "1" in lost and (why.startswith("left") if mode == "leave" else why.startswith("sent"))
         assert int(step) >= 5
     assert outs[1] == ""
+
+
+def test_a_failed_step_leaves_no_prefix_cache_entry_and_recovery_matches_the_clean_run():
+    """With the prefix cache on, a step that fails before its KV is written must not leave its pages shareable:
+    recovery re-queues the same prompts, and a cache hit on a half-written page would feed garbage to attention."""
+    def engine():
+        cfg = EngineConfig(model=tiny_llama(), device="cpu", dtype=torch.float32, page_size=16, num_pages=64, max_num_seqs=8,
+                           max_num_batched_tokens=64, max_model_len=256, enable_prefix_cache=True)
+        return LLMEngine(cfg)
+
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, 32000, (n,), generator=g).tolist() for n in (50, 37, 20)]
+    sp = SamplingParams(max_tokens=6)
+    want = engine().generate(prompts, sp)
+
+    eng = engine()
+    real = eng.runner.execute
+    calls = {"n": 0}
+
+    def failing_execute(batch, states, step):
+        calls["n"] += 1
+        if calls["n"] == 1:
+            raise fault.InjectedFault("the launch failed: nothing was written")   # scheduled, never computed
+        return real(batch, states, step)
+
+    eng.runner.execute = failing_execute
+    rids = [eng.add_request(p, sp) for p in prompts]
+    with pytest.raises(fault.InjectedFault):
+        eng.step()
+    assert recover(eng)
+    assert eng.kv.stats().cached_pages == 0        # the failed step's full pages did not enter the cache
+    eng.run_until_done()
+    assert [eng.requests[r].output_ids for r in rids] == want
+    assert eng.kv.check_invariants() == ""
+    # pages of completed steps are shared as before: the same prompts again hit the cache
+    hits0 = eng.kv.stats().prefix_hits
+    assert eng.generate(prompts, sp) == want and eng.kv.stats().prefix_hits > hits0
+
+
+def test_prompts_beyond_the_token_budget_are_refused_when_chunked_prefill_is_off():
+    cfg = EngineConfig(model=tiny_llama(), device="cpu", dtype=torch.float32, page_size=16, num_pages=64, max_num_seqs=4,
+                       max_num_batched_tokens=32, max_model_len=256, enable_chunked_prefill=False)
+    eng = LLMEngine(cfg)
+    with pytest.raises(ValueError):
+        eng.add_request(list(range(40)), SamplingParams(max_tokens=4))
+    # a prompt that fits runs, and nothing is left waiting behind a request that can never be scheduled
+    assert len(eng.generate([list(range(30))], SamplingParams(max_tokens=4))[0]) == 4
+    assert not eng.has_unfinished()
