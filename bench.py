@@ -49,6 +49,7 @@ def parse_args():
     ap.add_argument("--page-size", type=int, default=128)
     ap.add_argument("--max-ramp-steps", type=int, default=400)
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--no-mixed-graphs", action="store_true", help="CUDA graphs for decode-only steps only; steps with prefill chunks launch eagerly")
     ap.add_argument("--no-autotune", action="store_true", help="skip the start-up measurement of GEMM configurations")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--ar-mode", default="auto", choices=["auto", "fused", "split"],
@@ -134,6 +135,7 @@ def main() -> None:
                         max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_batched_tokens,
                         max_model_len=max_model_len, seed=0, use_cuda_graphs=not args.no_graphs, tp_size=1 if ep_mode else world,
                         ep_size=world if ep_mode else 1, lockstep=ep_mode and world > 1,
+                        mixed_step_graphs=not args.no_mixed_graphs, capture_mixed_graphs_at_start=True,
                         autotune=(args.impl == "mojo_b200" and not args.no_autotune and device.type == "cuda"))
     model = build_model(mcfg, device, torch.bfloat16, comm=comm, ep=ep).init_random(0)
     if args.sp and world > 1 and args.comm == "fused":
@@ -246,6 +248,7 @@ def main() -> None:
     # ---- timed region: exactly K engine steps ----
     ops.reset_launch_count()
     engine.runner.graph_launches = 0
+    engine.runner.graph_kernel_launches = 0
     tokens = 0
     h2d = d2h = 0
     prefill_tokens = 0
@@ -296,7 +299,7 @@ def main() -> None:
                 "parallelism": (f"dp{world}-attention + ep{world}-experts" if ep_mode else f"tp{world}"), "requests": args.requests, "poisson_rate_per_s": args.rate,
                 "max_num_batched_tokens": args.max_batched_tokens, "page_size": args.page_size, "ramp_steps": ramp,
                 "l2": "inputs larger than L2: every step streams this rank's full weight set (GBs) through the 126 MB L2",
-                "cuda_graphs": not args.no_graphs, "gemm_autotune": bool(ecfg.autotune), "comm": args.comm if world > 1 else "none", "all_reduce_form": (args.ar_mode if world > 1 and args.comm == "fused" and not ep_mode else None), "sequence_parallel": bool(getattr(model, "sequence_parallel", False)),
+                "cuda_graphs": not args.no_graphs, "mixed_step_graphs": bool(engine.runner.use_mixed_graphs), "graph_replays": engine.runner.graph_launches, "gemm_autotune": bool(ecfg.autotune), "comm": args.comm if world > 1 else "none", "all_reduce_form": (args.ar_mode if world > 1 and args.comm == "fused" and not ep_mode else None), "sequence_parallel": bool(getattr(model, "sequence_parallel", False)),
                 "prefill_tokens_in_timed_region": prefill_tokens, "output_tokens_in_timed_region": tokens,
             },
             "clocks": {k: clocks.summary().get(k) for k in ("sm_mhz", "sm_max_mhz", "reasons", "power_w_max")},

@@ -3,13 +3,21 @@
 #include <c10/cuda/CUDAStream.h>
 #include <c10/cuda/CUDAGuard.h>
 #include "b2/api.h"
+#include "b2/launch.h"
 #include "b2/coll.h"
 namespace py = pybind11;
 
 namespace {
 cudaStream_t cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
 void check(int rc, const char* what) {
-  if (rc != 0) throw std::runtime_error(std::string("mojo_b200: ") + what + " rejected its arguments: " + b2::status_code_name(-rc));
+  if (rc == 0) return;
+  if (b2::is_cuda_rc(rc)) {
+    // the CUDA runtime refused the launch or its set-up: say which error, not a generic "bad argument"
+    const cudaError_t e = b2::cuda_error_of(rc);
+    throw std::runtime_error(std::string("mojo_b200: ") + what + " failed: CUDA error " + std::to_string(static_cast<int>(e)) + " (" +
+                             cudaGetErrorName(e) + ": " + cudaGetErrorString(e) + ")");
+  }
+  throw std::runtime_error(std::string("mojo_b200: ") + what + " rejected its arguments: " + b2::status_code_name(-rc));
 }
 void need(bool cond, const char* msg) {
   if (!cond) throw std::invalid_argument(std::string("mojo_b200: ") + msg);

@@ -4,6 +4,7 @@
 #include <c10/cuda/CUDAStream.h>
 #include <c10/cuda/CUDAGuard.h>
 #include "b2/api.h"
+#include "b2/launch.h"
 
 namespace py = pybind11;
 void bind_engine(py::module_& m);
@@ -13,7 +14,14 @@ namespace {
 cudaStream_t cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
 
 void check(int rc, const char* what) {
-  if (rc != 0) throw std::runtime_error(std::string("mojo_b200: ") + what + " rejected its arguments: " + b2::status_code_name(-rc));
+  if (rc == 0) return;
+  if (b2::is_cuda_rc(rc)) {
+    // the CUDA runtime refused the launch or its set-up: say which error, not a generic "bad argument"
+    const cudaError_t e = b2::cuda_error_of(rc);
+    throw std::runtime_error(std::string("mojo_b200: ") + what + " failed: CUDA error " + std::to_string(static_cast<int>(e)) + " (" +
+                             cudaGetErrorName(e) + ": " + cudaGetErrorString(e) + ")");
+  }
+  throw std::runtime_error(std::string("mojo_b200: ") + what + " rejected its arguments: " + b2::status_code_name(-rc));
 }
 void need(bool cond, const char* msg) {
   if (!cond) throw std::invalid_argument(std::string("mojo_b200: ") + msg);
@@ -196,8 +204,13 @@ void gemm_bf16_pair(const at::Tensor& x, const at::Tensor& w, at::Tensor& y, int
 
 void attn_prefill_tc(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache, at::Tensor& out,
                      const at::Tensor& cu_q, const at::Tensor& ctx_lens, const at::Tensor& block_tables, int64_t max_q_len,
-                     double scale, int64_t variant, c10::optional<at::Tensor> status) {
+                     double scale, int64_t variant, c10::optional<at::Tensor> status, c10::optional<at::Tensor> work,
+                     c10::optional<at::Tensor> n_work, int64_t work_items) {
   check_cache(q, k_cache, v_cache, 128);
+  if (work.has_value()) {
+    need(work->is_cuda() && work->scalar_type() == at::kInt && work->is_contiguous() && work->numel() >= 2 * work_items, "attn_prefill_tc: work must be CUDA int32 [items, 2]");
+    if (n_work.has_value()) need(n_work->is_cuda() && n_work->scalar_type() == at::kInt && n_work->numel() >= 1, "attn_prefill_tc: n_work must be a CUDA int32 scalar");
+  }
   need(k_cache.size(2) == 128 && k_cache.size(3) == 128, "attn_prefill_tc: head_dim 128 and page_size 128 only");
   need(out.dim() == 2 && out.stride(1) == 1 && is_bf16(out) && out.size(0) == q.size(0), "attention: bad out");
   need(cu_q.scalar_type() == at::kInt && ctx_lens.scalar_type() == at::kInt && block_tables.scalar_type() == at::kInt, "attention: metadata must be int32");
@@ -209,7 +222,10 @@ void attn_prefill_tc(const at::Tensor& q, const at::Tensor& k_cache, const at::T
                                 ctx_lens.data_ptr<int32_t>(), block_tables.data_ptr<int32_t>(), batch,
                                 static_cast<int>(block_tables.size(1)), static_cast<int>(q.size(1) / 128),
                                 static_cast<int>(k_cache.size(1)), static_cast<int>(max_q_len), static_cast<float>(scale), q.size(0),
-                                q.stride(0), out.stride(0), k_cache.size(0), static_cast<int>(variant), status_ptr(status), cur_stream()),
+                                q.stride(0), out.stride(0), k_cache.size(0), static_cast<int>(variant),
+                                work.has_value() ? work->data_ptr<int32_t>() : nullptr,
+                                work.has_value() && n_work.has_value() ? n_work->data_ptr<int32_t>() : nullptr,
+                                static_cast<int>(work_items), status_ptr(status), cur_stream()),
         "attn_prefill_tc");
 }
 
@@ -302,7 +318,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_bf16_pair", &gemm_bf16_pair, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("epilogue") = 0, py::arg("bn") = 256, py::arg("status") = py::none());
   m.def("attn_prefill_tc", &attn_prefill_tc, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("out"), py::arg("cu_q"),
         py::arg("ctx_lens"), py::arg("block_tables"), py::arg("max_q_len"), py::arg("scale"), py::arg("variant") = 0,
-        py::arg("status") = py::none());
+        py::arg("status") = py::none(), py::arg("work") = py::none(), py::arg("n_work") = py::none(), py::arg("work_items") = 0);
   m.def("attn_decode", &attn_decode, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("out"), py::arg("ctx_lens"),
         py::arg("block_tables"), py::arg("workspace"), py::arg("head_dim"), py::arg("num_splits"), py::arg("scale"),
         py::arg("status") = py::none());

@@ -71,7 +71,8 @@ int b2_gemm_bf16_pair(const void* x, const void* w, void* y, int M, int N, int K
 int b2_attn_prefill_tc_bf16(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* cu_q,
                             const int32_t* ctx_lens, const int32_t* block_tables, int batch, int max_blocks, int n_q,
                             int n_kv, int max_q_len, float scale, int64_t q_rows, int64_t q_stride, int64_t out_stride,
-                            int64_t num_pages, int variant, b2::Status* status, cudaStream_t stream);
+                            int64_t num_pages, int variant, const int32_t* work, const int32_t* n_work, int work_items,
+                            b2::Status* status, cudaStream_t stream);
 // One query token per sequence, split over the KV length. workspace: f32, size from b2_attn_decode_workspace.
 int b2_attn_decode_bf16(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* ctx_lens,
                         const int32_t* block_tables, float* workspace, int batch, int max_blocks, int n_q, int n_kv,

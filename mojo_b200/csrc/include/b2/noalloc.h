@@ -14,11 +14,18 @@
 //     -b2::kTooLarge before anything is launched; nothing is ever allocated as a fallback.
 //   * The first call on each device looks up the array's device address (cudaGetSymbolAddress) and clears its
 //     semaphore words. Make that first call outside any stream capture; later calls only launch the kernel.
+//     That first call may come from several host threads at once (the set-up is serialised by a mutex).
 //   * All calls on a device share the one array. Calls that may overlap on the GPU (different streams without an
 //     ordering between them) race on it; keep them on one stream or order them with events.
 //   * The semaphore words are returned to zero by every launch, and partial sums are fully rewritten before they
 //     are read, so stale contents from the previous call are harmless.
-// Returns 0, or a negative b2::StatusCode (kBadArgument, kTooLarge).
+//   * The call returns as soon as the kernel is queued, so it cannot tell whether a bounded wait inside the kernel
+//     ran out. `b2_gemm_bf16_noalloc_status(stream)` can: it waits for `stream`, returns 0 or the negative
+//     b2::StatusCode a kernel of this entry point recorded on the current device since the last query (-kTimeout),
+//     and after such a failure puts the semaphore words back to zero so later calls count correctly. It copies
+//     32 bytes to the host and allocates nothing.
+// Returns 0, a negative b2::StatusCode (kBadArgument, kTooLarge), or -(1000 + cudaError_t) if the CUDA runtime
+// refused the launch or the one-time set-up (b2/launch.h).
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
@@ -31,6 +38,7 @@ extern "C" {
 
 int b2_gemm_bf16_noalloc(const void* x, const void* w, void* y, int M, int N, int K, int64_t ldx, int64_t ldw,
                          int64_t ldy, cudaStream_t stream);
+int b2_gemm_bf16_noalloc_status(cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -12,6 +12,7 @@
 #include <cstdint>
 #include <cuda_bf16.h>
 #include "b2/api.h"
+#include "b2/launch.h"
 #include "b2/ptx.cuh"
 #include "b2/tma.h"
 #include "b2/vec.cuh"
@@ -596,26 +597,20 @@ extern "C" int b2_attn_prefill_bf16(const void* q, const void* k_cache, const vo
   auto op = static_cast<__nv_bfloat16*>(out);
   if (head_dim == 128) {
     constexpr int SMEM = 4 * 16 * 128 * 2 + 4 * 64 * 128 * 2;
-    static bool set = false;
-    if (!set) {
-      cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-      set = true;
-    }
+    static DeviceOnce attr_once;
+    if (const int rc = attr_once.run([&] { return cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); })) return rc;
     attn_prefill_kernel<128><<<grid, 128, SMEM, stream>>>(qp, kp, vp, op, cu_q, ctx_lens, block_tables, max_blocks, n_q,
                                                           n_kv, page_size, scale_log2, q_stride, out_stride, num_pages,
                                                           status);
   } else {
     constexpr int SMEM = 4 * 16 * 64 * 2 + 4 * 64 * 64 * 2;
-    static bool set = false;
-    if (!set) {
-      cudaFuncSetAttribute(attn_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-      set = true;
-    }
+    static DeviceOnce attr_once;
+    if (const int rc = attr_once.run([&] { return cudaFuncSetAttribute(attn_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); })) return rc;
     attn_prefill_kernel<64><<<grid, 128, SMEM, stream>>>(qp, kp, vp, op, cu_q, ctx_lens, block_tables, max_blocks, n_q,
                                                          n_kv, page_size, scale_log2, q_stride, out_stride, num_pages,
                                                          status);
   }
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 
 extern "C" int64_t b2_attn_decode_workspace(int batch, int n_q, int head_dim, int num_splits) {
@@ -648,11 +643,8 @@ extern "C" int b2_attn_decode_bf16(const void* q, const void* k_cache, const voi
     constexpr int STAGES = 3;
     if (head_dim == 128) {
       constexpr int SMEM = STAGES * 2 * 32 * 128 * 2 + 16 * 128 * 2 + 64 + 1024;
-      static bool set = false;
-      if (!set) {
-        cudaFuncSetAttribute(attn_decode_tma_kernel<128, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        set = true;
-      }
+      static DeviceOnce attr_once;
+    if (const int rc = attr_once.run([&] { return cudaFuncSetAttribute(attn_decode_tma_kernel<128, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); })) return rc;
       attn_decode_tma_kernel<128, STAGES><<<grid, 32, SMEM, stream>>>(tk, tv, qp, op, ctx_lens, block_tables, workspace, max_blocks,
                                                                     n_q, n_kv, page_size, num_splits, scale_log2, q_stride,
                                                                     out_stride, num_pages, status);
@@ -660,26 +652,20 @@ extern "C" int b2_attn_decode_bf16(const void* q, const void* k_cache, const voi
         attn_decode_reduce_kernel<128><<<(total + 3) / 4, 128, 0, stream>>>(workspace, op, n_q, num_splits, out_stride, total);
     } else {
       constexpr int SMEM = STAGES * 2 * 32 * 64 * 2 + 16 * 64 * 2 + 64 + 1024;
-      static bool set = false;
-      if (!set) {
-        cudaFuncSetAttribute(attn_decode_tma_kernel<64, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        set = true;
-      }
+      static DeviceOnce attr_once;
+    if (const int rc = attr_once.run([&] { return cudaFuncSetAttribute(attn_decode_tma_kernel<64, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); })) return rc;
       attn_decode_tma_kernel<64, STAGES><<<grid, 32, SMEM, stream>>>(tk, tv, qp, op, ctx_lens, block_tables, workspace, max_blocks,
                                                                    n_q, n_kv, page_size, num_splits, scale_log2, q_stride,
                                                                    out_stride, num_pages, status);
       if (num_splits > 1)
         attn_decode_reduce_kernel<64><<<(total + 3) / 4, 128, 0, stream>>>(workspace, op, n_q, num_splits, out_stride, total);
     }
-    return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+    return last_launch_rc();
   }
   if (head_dim == 128) {
     constexpr int SMEM = 4 * (16 * 128 * 2 + 4 * 32 * 128 * 2);
-    static bool set = false;
-    if (!set) {
-      cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-      set = true;
-    }
+    static DeviceOnce attr_once;
+    if (const int rc = attr_once.run([&] { return cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); })) return rc;
     attn_decode_kernel<128><<<grid, 128, SMEM, stream>>>(qp, kp, vp, op, ctx_lens, block_tables, workspace, max_blocks,
                                                          n_q, n_kv, page_size, num_splits, scale_log2, q_stride,
                                                          out_stride, num_pages, status);
@@ -687,16 +673,13 @@ extern "C" int b2_attn_decode_bf16(const void* q, const void* k_cache, const voi
       attn_decode_reduce_kernel<128><<<(total + 3) / 4, 128, 0, stream>>>(workspace, op, n_q, num_splits, out_stride, total);
   } else {
     constexpr int SMEM = 4 * (16 * 64 * 2 + 4 * 32 * 64 * 2);
-    static bool set = false;
-    if (!set) {
-      cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-      set = true;
-    }
+    static DeviceOnce attr_once;
+    if (const int rc = attr_once.run([&] { return cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); })) return rc;
     attn_decode_kernel<64><<<grid, 128, SMEM, stream>>>(qp, kp, vp, op, ctx_lens, block_tables, workspace, max_blocks,
                                                         n_q, n_kv, page_size, num_splits, scale_log2, q_stride,
                                                         out_stride, num_pages, status);
     if (num_splits > 1)
       attn_decode_reduce_kernel<64><<<(total + 3) / 4, 128, 0, stream>>>(workspace, op, n_q, num_splits, out_stride, total);
   }
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }

@@ -24,6 +24,7 @@
 #include <cuda_runtime.h>
 
 #include "b2/api.h"
+#include "b2/launch.h"
 #include "b2/config.h"
 #include "b2/gemm_tc.cuh"
 #include "b2/ptx.cuh"
@@ -62,6 +63,11 @@ struct AttnTcParams {
   float scale_log2;   // softmax scale * log2(e)
   // descriptor of the MN-major V operand (bytes): stride between 64-column groups, stride between 8-row groups
   uint32_t v_lbo, v_sbo;
+  // Optional work list: item i = (sequence, query tile) as two ints, for grids of (items, heads). `n_work` (device
+  // memory) is the number of valid items, so that a captured launch with a fixed grid serves any batch; null means
+  // every CTA of the grid has an item. Without a list the grid is (query tiles, heads, sequences).
+  const int* work;
+  const int* n_work;
 };
 
 // Shared-memory descriptor with explicit leading / stride byte offsets, 128-byte swizzle.
@@ -78,7 +84,13 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
 __global__ void __launch_bounds__(kThreadsAttn, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_v, AttnTcParams prm, Status* status) {
-  const int seq = blockIdx.z, head = blockIdx.y, qt = blockIdx.x;
+  int seq = blockIdx.z, qt = blockIdx.x;
+  const int head = blockIdx.y;
+  if (prm.work != nullptr) {
+    if (prm.n_work != nullptr && static_cast<int>(blockIdx.x) >= *prm.n_work) return;
+    seq = prm.work[2 * blockIdx.x];
+    qt = prm.work[2 * blockIdx.x + 1];
+  }
   const int q_begin = prm.cu_q[seq], q_len = prm.cu_q[seq + 1] - q_begin;
   if (qt * kTile >= q_len) return;                       // uniform per CTA: before any barrier or allocation
   const int ctx = prm.ctx_lens[seq];
@@ -375,12 +387,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 using namespace b2;
 
 // Same contract as b2_attn_prefill_bf16 with head_dim = 128 and page_size = 128 fixed; out rows 16-byte aligned.
-// `variant` is reserved (0).
+// `variant` is reserved (0). With `work` (device memory, `work_items` pairs of (sequence, query tile)) the grid is one
+// CTA per item and head; `n_work` (device memory, may be null) bounds the valid items, for launches whose grid is
+// fixed ahead of the batch (CUDA graphs). The caller orders the items, longest context first for an even finish.
 extern "C" int b2_attn_prefill_tc_bf16(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* cu_q,
                                        const int32_t* ctx_lens, const int32_t* block_tables, int batch, int max_blocks, int n_q,
                                        int n_kv, int max_q_len, float scale, int64_t q_rows, int64_t q_stride, int64_t out_stride,
-                                       int64_t num_pages, int variant, Status* status, cudaStream_t stream) {
+                                       int64_t num_pages, int variant, const int32_t* work, const int32_t* n_work, int work_items,
+                                       Status* status, cudaStream_t stream) {
   if (batch <= 0 || max_q_len <= 0) return 0;
+  if (work != nullptr && work_items <= 0) return 0;
   if (n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0 || q_stride % 8 != 0 || out_stride % 8 != 0 ||
       (reinterpret_cast<uintptr_t>(q) & 15) != 0 || (reinterpret_cast<uintptr_t>(out) & 15) != 0)
     return -kBadArgument;
@@ -404,14 +420,17 @@ extern "C" int b2_attn_prefill_tc_bf16(const void* q, const void* k_cache, const
   prm.scale_log2 = scale * 1.4426950408889634f;
   prm.v_lbo = kHalfBytes;   // the second 64 columns of the head dimension are the second TMA box
   prm.v_sbo = 1024;         // 8 KV rows of 128 bytes
+  prm.work = work;
+  prm.n_work = work != nullptr ? n_work : nullptr;
   (void)variant;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttn) != cudaSuccess)
-      return -kBadArgument;
-    attr_set = true;
-  }
+  static DeviceOnce attr_once;
+  if (const int rc = attr_once.run([&] {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttn);
+        return e;
+      }))
+    return rc;
   dim3 grid((max_q_len + kTile - 1) / kTile, n_q, batch);
+  if (work != nullptr) grid = dim3(work_items, n_q, 1);
   attn_prefill_tc_kernel<<<grid, kThreadsAttn, kSmemAttn, stream>>>(tq, tk, tv, prm, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }

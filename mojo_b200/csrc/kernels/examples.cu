@@ -6,6 +6,7 @@
 #include <cstdint>
 #include <cuda_runtime.h>
 #include "b2/api.h"
+#include "b2/launch.h"
 #include "b2/examples.h"
 #include "b2/vec.cuh"
 
@@ -156,12 +157,12 @@ extern "C" int b2_ex_matmul(const float* a, const float* b, float* c, int M, int
   } else {
     matmul_tiled_kernel<<<dim3((N + kTile - 1) / kTile, (M + kTile - 1) / kTile), dim3(kTile, kTile), 0, stream>>>(a, b, c, M, N, K);
   }
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 extern "C" int b2_ex_mandelbrot(int32_t* out, int rows, int cols, int max_iters, float min_x, float max_x, float min_y, float max_y,
                                 cudaStream_t stream) {
   mandelbrot_kernel<<<dim3((cols + 31) / 32, (rows + 7) / 8), dim3(32, 8), 0, stream>>>(out, rows, cols, max_iters, min_x, max_x, min_y, max_y);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 extern "C" int b2_ex_reduce_sum(const float* x, int64_t n, double* out, cudaStream_t stream) {
   if (cudaMemsetAsync(out, 0, sizeof(double), stream) != cudaSuccess) return -kBadArgument;
@@ -169,15 +170,15 @@ extern "C" int b2_ex_reduce_sum(const float* x, int64_t n, double* out, cudaStre
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (blocks < 1) blocks = 1;
   reduce_sum_kernel<<<blocks, 256, 0, stream>>>(x, n, out);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 extern "C" int b2_ex_life(const uint8_t* cur, uint8_t* nxt, int rows, int cols, cudaStream_t stream) {
   life_kernel<<<dim3((cols + 31) / 32, (rows + 7) / 8), dim3(32, 8), 0, stream>>>(cur, nxt, rows, cols);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 extern "C" int b2_ex_raytrace(float* img, const float* bg, int H, int W, int bg_h, int bg_w, const B2Scene* scene, cudaStream_t stream) {
   if (scene == nullptr || scene->n_spheres > 8 || scene->n_lights > 4) return -kBadArgument;
   if (cudaMemcpyToSymbolAsync(c_scene, scene, sizeof(B2Scene), 0, cudaMemcpyHostToDevice, stream) != cudaSuccess) return -kBadArgument;
   raytrace_kernel<<<dim3((W + 15) / 16, (H + 15) / 16), dim3(16, 16), 0, stream>>>(img, bg, H, W, bg_h, bg_w);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }

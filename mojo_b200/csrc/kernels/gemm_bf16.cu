@@ -12,6 +12,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include "b2/api.h"
+#include "b2/launch.h"
 #include "b2/gemm_tc.cuh"
 #include "b2/ptx.cuh"
 #include "b2/tma.h"
@@ -334,12 +335,12 @@ int launch(const void* x, const void* w, int M, int N, int K, int64_t ldx, int64
     }
   }
   auto kern = gemm_bf16_kernel<BN, STAGES, SWAP>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes) != cudaSuccess)
-      return -kBadArgument;
-    attr_set = true;
-  }
+  static DeviceOnce attr_once;
+  if (const int rc = attr_once.run([&] {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes);
+        return e;
+      }))
+    return rc;
   const int total = sched.p_blocks * sched.q_blocks * splits;
   const int grid = (total < kNumSMs && sched.sk_tiles == 0) ? total : kNumSMs;
   // Weights are read once per step: stream them; activations are re-read by every weight tile: keep them.
@@ -347,7 +348,7 @@ int launch(const void* x, const void* w, int M, int N, int K, int64_t ldx, int64
   const uint64_t pol_p = SWAP ? pol_w : (M <= 1024 ? pol_x : ptx::kEvictNormal);
   const uint64_t pol_q = SWAP ? pol_x : (M <= 1024 ? pol_w : ptx::kEvictNormal);
   kern<<<grid, gemm::kThreads, L::kTotalBytes, stream>>>(tp, tq, sched, ep, pol_p, pol_q, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 
 }  // namespace
@@ -453,28 +454,47 @@ extern "C" int b2_gemm_bf16(const void* x, const void* w, void* y, const void* r
 #include "b2/noalloc.h"
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[B2_NOALLOC_SCRATCH_BYTES];
+// Where a kernel launched through this entry point records a wait that ran out (it has no caller-supplied status).
+static __device__ b2::Status g_noalloc_status;
+
+#include <mutex>
 
 namespace {
 constexpr int kNoallocMaxDevices = 64;
-void* g_noalloc_ptr[kNoallocMaxDevices] = {};
+constexpr int64_t kNoallocCounterBytes = 65536 * 4;
+struct NoallocDevice {
+  std::atomic<void*> scratch{nullptr};
+  b2::Status* status = nullptr;
+};
+NoallocDevice g_noalloc_dev[kNoallocMaxDevices];
+std::mutex g_noalloc_mutex;   // first use per device may come from several host threads at once
 
-// Device address of the scratch for the current device; first use clears the semaphore words.
-int noalloc_scratch(void** out, cudaStream_t stream) {
+// Device addresses of the scratch and the status word for the current device. The first use on a device looks
+// them up (the names above are host-side handles, not addresses a kernel could use) and clears the semaphore words
+// and the status word.
+int noalloc_device(NoallocDevice** out, cudaStream_t stream) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoallocMaxDevices) return -b2::kBadArgument;
-  if (g_noalloc_ptr[dev] == nullptr) {
-    void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) {
-      cudaGetLastError();
-      return -b2::kBadArgument;
+  NoallocDevice& d = g_noalloc_dev[dev];
+  if (d.scratch.load(std::memory_order_acquire) == nullptr) {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (d.scratch.load(std::memory_order_relaxed) == nullptr) {
+      void* p = nullptr;
+      void* st = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+      if (e == cudaSuccess) e = cudaGetSymbolAddress(&st, g_noalloc_status);
+      if (e == cudaSuccess && (p == nullptr || st == nullptr)) e = cudaErrorInvalidSymbol;
+      if (e == cudaSuccess) e = cudaMemsetAsync(p, 0, kNoallocCounterBytes, stream);
+      if (e == cudaSuccess) e = cudaMemsetAsync(st, 0, sizeof(b2::Status), stream);
+      if (e != cudaSuccess) {
+        cudaGetLastError();
+        return b2::cuda_rc(e);
+      }
+      d.status = static_cast<b2::Status*>(st);
+      d.scratch.store(p, std::memory_order_release);
     }
-    if (cudaMemsetAsync(p, 0, 65536 * 4, stream) != cudaSuccess) {
-      cudaGetLastError();
-      return -b2::kBadArgument;
-    }
-    g_noalloc_ptr[dev] = p;
   }
-  *out = g_noalloc_ptr[dev];
+  *out = &d;
   return 0;
 }
 }  // namespace
@@ -483,22 +503,23 @@ extern "C" int b2_gemm_bf16_noalloc(const void* x, const void* w, void* y, int M
                                     int64_t ldw, int64_t ldy, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (x == nullptr || w == nullptr || y == nullptr || K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return -kBadArgument;
-  // Same configuration rule as the allocating entry point, then checked against the fixed capacity.
+  // Same configuration rule and the same clamps as the allocating entry point, then checked against the fixed capacity.
   Config c = choose_config(M, N, K, B2_EPI_NONE);
   const int num_kb = (K + 63) / 64;
   if (c.splits > num_kb) c.splits = num_kb;
+  if (c.splits > 16) c.splits = 16;
   while (c.splits > 1 && ((num_kb + c.splits - 1) / c.splits) * (c.splits - 1) >= num_kb) --c.splits;
   if (!c.swap && (N % 8 != 0 || ldy % 8 != 0)) return -kBadArgument;
   const int rows_p = c.swap ? N : M, rows_q = c.swap ? M : N;
   const int64_t tiles = static_cast<int64_t>((rows_p + 127) / 128) * ((rows_q + c.bn - 1) / c.bn);
-  const int64_t counters_bytes = 65536 * 4;
   if (c.splits > 1) {
-    const int64_t need = counters_bytes + tiles * c.splits * c.bn * 128 * 4;
+    const int64_t need = kNoallocCounterBytes + tiles * c.splits * c.bn * 128 * 4;
     if (need > B2_NOALLOC_SCRATCH_BYTES || tiles > 65536) return -kTooLarge;
   }
-  void* scratch = nullptr;
-  const int rc = noalloc_scratch(&scratch, stream);
+  NoallocDevice* d = nullptr;
+  const int rc = noalloc_device(&d, stream);
   if (rc != 0) return rc;
+  void* scratch = d->scratch.load(std::memory_order_acquire);
   EpiParams ep{};
   ep.y = static_cast<__nv_bfloat16*>(y);
   ep.ldy = ldy;
@@ -507,8 +528,8 @@ extern "C" int b2_gemm_bf16_noalloc(const void* x, const void* w, void* y, int M
   ep.N = N;
   ep.mode = B2_EPI_NONE;
   ep.counters = static_cast<uint32_t*>(scratch);
-  ep.workspace = reinterpret_cast<float*>(static_cast<char*>(scratch) + counters_bytes);
-#define B2_LAUNCH_NA(BN_, SWAP_) return launch<BN_, SWAP_>(x, w, M, N, K, ldx, ldw, c.splits, false, ep, nullptr, stream)
+  ep.workspace = reinterpret_cast<float*>(static_cast<char*>(scratch) + kNoallocCounterBytes);
+#define B2_LAUNCH_NA(BN_, SWAP_) return launch<BN_, SWAP_>(x, w, M, N, K, ldx, ldw, c.splits, false, ep, d->status, stream)
   if (c.swap) {
     switch (c.bn) {
       case 16: B2_LAUNCH_NA(16, true);
@@ -530,6 +551,29 @@ extern "C" int b2_gemm_bf16_noalloc(const void* x, const void* w, void* y, int M
     default: return -kBadArgument;
   }
 #undef B2_LAUNCH_NA
+}
+
+extern "C" int b2_gemm_bf16_noalloc_status(cudaStream_t stream) {
+  NoallocDevice* d = nullptr;
+  const int rc = noalloc_device(&d, stream);
+  if (rc != 0) return rc;
+  b2::Status host{};
+  cudaError_t e = cudaMemcpyAsync(&host, d->status, sizeof(host), cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return b2::cuda_rc(e);
+  }
+  if (host.code == kOk) return 0;
+  // A kernel that gave up may have left semaphores mid-count: put both the semaphores and the record back to zero,
+  // so the calls that follow count from a clean state.
+  e = cudaMemsetAsync(d->scratch.load(std::memory_order_acquire), 0, kNoallocCounterBytes, stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(d->status, 0, sizeof(b2::Status), stream);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return b2::cuda_rc(e);
+  }
+  return -host.code;
 }
 
 // The configuration the automatic rule picks for a shape, encoded like the `config` argument

@@ -19,6 +19,7 @@
 #include <cuda_runtime.h>
 
 #include "b2/api.h"
+#include "b2/launch.h"
 #include "b2/config.h"
 #include "b2/ptx.cuh"
 #include "b2/status.h"
@@ -269,16 +270,16 @@ int launch_pair(const void* x, const void* w, void* y, int M, int N, int K, int6
   p.m_tiles = (M + 255) / 256;
   p.n_tiles = (N + BN - 1) / BN;
   p.swiglu = epilogue == B2_EPI_SWIGLU ? 1 : 0;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_bf16_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem) != cudaSuccess)
-      return -kBadArgument;
-    attr_set = true;
-  }
+  static DeviceOnce attr_once;
+  if (const int rc = attr_once.run([&] {
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
+        return e;
+      }))
+    return rc;
   const int total = p.m_tiles * p.n_tiles;
   const int pairs = total < kNumSMs / 2 ? total : kNumSMs / 2;
   gemm_bf16_pair_kernel<BN><<<2 * pairs, kPairThreads, Cfg::kSmem, stream>>>(tx, tw, p, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 
 }  // namespace

@@ -16,6 +16,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include "b2/api.h"
+#include "b2/launch.h"
 #include "b2/gemm_tc.cuh"
 #include "b2/ptx.cuh"
 #include "b2/tma.h"
@@ -444,16 +445,17 @@ int launch_fp8(const void* xq, const float* xs, const void* wq, const float* ws,
     }
   }
   auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP, kModePlain, WG2>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
-    attr_set = true;
-  }
+  static DeviceOnce attr_once;
+  if (const int rc = attr_once.run([&] {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        return e;
+      }))
+    return rc;
   const int total = prm.p_blocks * prm.q_blocks * prm.splits;
   static const tp::RsSched no_sched{};
   static const Fp8Fused no_fused{};
   kern<<<total < kNumSMs ? total : kNumSMs, WG2 ? kThreads + 128 : kThreads, SMEM, stream>>>(tp, tq, prm, no_sched, no_fused, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 
 template <int BN, bool SWAP>
@@ -490,11 +492,12 @@ int launch_fp8_rs(const void* xq, const float* xs, const void* wq, const float* 
   rs.p_blocks = prm.p_blocks;
   rs.q_blocks = prm.q_blocks;
   auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP, kModeRs, false>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
-    attr_set = true;
-  }
+  static DeviceOnce attr_once;
+  if (const int rc = attr_once.run([&] {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        return e;
+      }))
+    return rc;
   const int total = prm.p_blocks * prm.q_blocks;
   int n_gemm = kNumSMs - (rs.tp > 1 ? (M >= 2048 ? 4 : 12) : 0);
   if (total < n_gemm) n_gemm = total;
@@ -503,7 +506,7 @@ int launch_fp8_rs(const void* xq, const float* xs, const void* wq, const float* 
   fz.ectl = ectl;
   fz.n_gemm = n_gemm;
   kern<<<kNumSMs, kThreads, SMEM, stream>>>(tmp, tmq, prm, sched, fz, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 
 template <int BN, bool SWAP>
@@ -549,14 +552,15 @@ int launch_fp8_ag(const void* xq_all, const float* xs_all, const void* wq, const
   if (total < n_gemm) n_gemm = total;
   fz.n_gemm = n_gemm;
   auto kern = gemm_fp8_kernel<BN, STAGES, SLABS, SWAP, kModeAg, WG2>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
-    attr_set = true;
-  }
+  static DeviceOnce attr_once;
+  if (const int rc = attr_once.run([&] {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        return e;
+      }))
+    return rc;
   static const tp::RsSched no_sched{};
   kern<<<n_gemm + ag.n_comm, WG2 ? kThreads + 128 : kThreads, SMEM, stream>>>(tmp, tmq, prm, no_sched, fz, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 
 }  // namespace

@@ -8,6 +8,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include "b2/api.h"
+#include "b2/launch.h"
 #include "b2/gemm_tc.cuh"
 #include "b2/gguf.cuh"
 #include "b2/ptx.cuh"
@@ -127,14 +128,15 @@ int launch_gguf(const void* x, const void* wq, int ggml_type, void* y, int M, in
   GgufFill fill{static_cast<const uint8_t*>(wq), ggml_type, N, K / gguf::kQK};
   GgufEpiParams ep{static_cast<__nv_bfloat16*>(y), N, M, N};
   auto kern = gemm_gguf_kernel<BN, STAGES>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes) != cudaSuccess) return -kBadArgument;
-    attr_set = true;
-  }
+  static DeviceOnce attr_once;
+  if (const int rc = attr_once.run([&] {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes);
+        return e;
+      }))
+    return rc;
   const int total = sched.p_blocks * sched.q_blocks;
   kern<<<total < kNumSMs ? total : kNumSMs, gemm::kThreadsWithFill, L::kTotalBytes, stream>>>(tx, sched, fill, ep, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 
 }  // namespace
@@ -148,7 +150,7 @@ extern "C" int b2_dequant_gguf(const void* wq, int ggml_type, void* out_bf16, in
   const int64_t groups = n_elems / 32;
   dequant_kernel<<<static_cast<unsigned>((groups + 127) / 128), 128, 0, stream>>>(static_cast<const uint8_t*>(wq), ggml_type,
                                                                                   static_cast<__nv_bfloat16*>(out_bf16), groups);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 
 extern "C" int b2_gemm_gguf(const void* x, const void* wq, int ggml_type, void* y, int M, int N, int K, b2::Status* status,

@@ -21,6 +21,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include "b2/api.h"
+#include "b2/launch.h"
 #include "b2/ptx.cuh"
 #include "b2/tma.h"
 
@@ -321,7 +322,7 @@ extern "C" int b2_mla_rows_meta(const int32_t* cu_q, const int32_t* ctx_lens, in
                                 cudaStream_t stream) {
   if (num_seqs <= 0) return 0;
   mla_rows_meta_kernel<<<num_seqs, 128, 0, stream>>>(cu_q, ctx_lens, row_ctx, row_seq);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 
 extern "C" int b2_mla_attend_bf16(const void* q_lat, const void* q_rope, const void* kv_cache, void* out_lat,
@@ -347,11 +348,8 @@ extern "C" int b2_mla_attend_bf16(const void* q_lat, const void* q_rope, const v
   const int stages = forced == 3 ? 3 : 2;
   const int SMEM = stages * kTileBytes + 16 * kRow * 2 + 2 * 4 * 16 * 32 * 4 + 64 + 1024;
   auto kern = stages == 2 ? mla_decode_kernel<2> : mla_decode_kernel<3>;
-  static bool set[2] = {false, false};
-  if (!set[stages - 2]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -kBadArgument;
-    set[stages - 2] = true;
-  }
+  static DeviceOnce attr_once[2];
+  if (const int rc = attr_once[stages - 2].max_smem(kern, SMEM)) return rc;
   // grid z is limited to 65535: larger row counts go out in slices
   constexpr int kMaxZ = 65535;
   for (int r0 = 0; r0 < rows; r0 += kMaxZ) {
@@ -369,7 +367,7 @@ extern "C" int b2_mla_attend_bf16(const void* q_lat, const void* q_rope, const v
       mla_reduce_kernel<<<(total + 3) / 4, 128, 0, stream>>>(ws, out, num_splits, total);
     }
   }
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 
 extern "C" int b2_mla_decode_bf16(const void* q_lat, const void* q_rope, const void* kv_cache, void* out_lat,

@@ -17,6 +17,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include "b2/api.h"
+#include "b2/launch.h"
 #include "b2/ep.h"
 #include "b2/gemm_tc.cuh"
 #include "b2/ptx.cuh"
@@ -267,13 +268,14 @@ int launch_grouped(const void* x, const void* w, const uint32_t* counts, void* y
   sched.p_blocks = (N + 127) / 128;
   GroupedEpiParams ep{static_cast<__nv_bfloat16*>(y), ldy, counts, cap, N, swiglu};
   auto kern = moe_grouped_kernel<BN, STAGES>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes) != cudaSuccess) return -kBadArgument;
-    attr_set = true;
-  }
+  static DeviceOnce attr_once;
+  if (const int rc = attr_once.run([&] {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes);
+        return e;
+      }))
+    return rc;
   kern<<<kNumSMs, gemm::kThreads, L::kTotalBytes, stream>>>(tw, tx, sched, ep, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -373,7 +375,7 @@ extern "C" int b2_ep_dispatch(const void* x, const void* logits, float* weights_
   if (blocks > 2 * kNumSMs) blocks = 2 * kNumSMs;
   ep_dispatch_kernel<<<blocks, 256, 0, stream>>>(d, static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(logits),
                                                  weights_out, ids_out, T, E, top_k, norm_topk, route_scale, slot & 1, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 
 extern "C" int b2_moe_grouped_gemm(const void* x, const void* w, const uint32_t* counts, void* y, int e_local, int cap, int N,
@@ -397,5 +399,5 @@ extern "C" int b2_ep_combine(const void* y_local, const float* weights, const vo
   ep_combine_kernel<<<kNumSMs, 256, 0, stream>>>(d, static_cast<const __nv_bfloat16*>(y_local), weights,
                                                  static_cast<const __nv_bfloat16*>(shared), static_cast<__nv_bfloat16*>(out), T, top_k,
                                                  slot & 1, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }

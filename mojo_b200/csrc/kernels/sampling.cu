@@ -9,6 +9,7 @@
 #include <cstdint>
 #include <cuda_bf16.h>
 #include "b2/api.h"
+#include "b2/launch.h"
 #include "b2/ptx.cuh"
 #include "b2/vec.cuh"
 
@@ -239,7 +240,7 @@ extern "C" int b2_argmax(const void* logits, int is_bf16, int64_t* ids, float* m
   if (vocab <= 0) return -kBadArgument;
   if (is_bf16) argmax_kernel<true><<<rows, kThreads, 0, stream>>>(logits, ids, max_out, vocab, row_stride);
   else argmax_kernel<false><<<rows, kThreads, 0, stream>>>(logits, ids, max_out, vocab, row_stride);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 
 extern "C" int b2_sample(const void* logits, int is_bf16, int64_t* ids, const float* temperature, const int32_t* top_k,
@@ -253,5 +254,5 @@ extern "C" int b2_sample(const void* logits, int is_bf16, int64_t* ids, const fl
   else
     sample_kernel<false><<<rows, kThreads, 0, stream>>>(logits, ids, temperature, top_k, top_p, uniforms, seed, step,
                                                         vocab, row_stride);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }

@@ -14,6 +14,7 @@
 #include <cuda_runtime.h>
 
 #include "b2/coll.h"
+#include "b2/launch.h"
 #include "b2/config.h"
 #include "b2/ptx.cuh"
 #include "b2/status.h"
@@ -285,7 +286,7 @@ int grid_for(int64_t n_vec) {
   return static_cast<int>(g > kNumSMs ? kNumSMs : g);
 }
 
-int launched() { return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument; }
+int launched() { return last_launch_rc(); }
 
 }  // namespace
 }  // namespace b2

@@ -23,6 +23,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include "b2/api.h"
+#include "b2/launch.h"
 #include "b2/gemm_tc.cuh"
 #include "b2/ptx.cuh"
 #include "b2/tma.h"
@@ -118,13 +119,13 @@ int launch_rs(const void* x, const void* w, int M, int N, int K, int64_t ldx, in
     const char* e = std::getenv("B2_RS_SIDE");
     return e != nullptr && e[0] == '1';
   }();
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_rs_kernel<BN, STAGES, SWAP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
-        cudaFuncSetAttribute(gemm_rs_kernel<BN, STAGES, SWAP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
-      return -kBadArgument;
-    attr_set = true;
-  }
+  static DeviceOnce attr_once;
+  if (const int rc = attr_once.run([&] {
+        cudaError_t e = cudaFuncSetAttribute(gemm_rs_kernel<BN, STAGES, SWAP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_rs_kernel<BN, STAGES, SWAP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        return e;
+      }))
+    return rc;
   const int total = sched.p_blocks * sched.q_blocks;
   if (side) {
     // Full persistent grid: every CTA that has tiles runs the GEMM with its reduction side warps; CTAs beyond the
@@ -139,7 +140,7 @@ int launch_rs(const void* x, const void* w, int M, int N, int K, int64_t ldx, in
     if (total < n_gemm) n_gemm = total;
     gemm_rs_kernel<BN, STAGES, SWAP, false><<<kNumSMs, gemm::kThreads, SMEM, stream>>>(tp, tq, sched, prm, ectl, n_gemm, status);
   }
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -271,13 +272,13 @@ int launch_ag(const void* xall_local, const void* w, void* y, int M, int N, int 
     const char* e = std::getenv("B2_AG_SIDE");
     return e != nullptr && e[0] == '1';
   }();
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(ag_gemm_kernel<BN, STAGES, SWAP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes) != cudaSuccess ||
-        cudaFuncSetAttribute(ag_gemm_kernel<BN, STAGES, SWAP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes) != cudaSuccess)
-      return -kBadArgument;
-    attr_set = true;
-  }
+  static DeviceOnce attr_once;
+  if (const int rc = attr_once.run([&] {
+        cudaError_t e = cudaFuncSetAttribute(ag_gemm_kernel<BN, STAGES, SWAP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(ag_gemm_kernel<BN, STAGES, SWAP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes);
+        return e;
+      }))
+    return rc;
   const int total = sched.p_blocks * sched.q_blocks;
   if (side) {
     const int grid = total < kNumSMs ? total : kNumSMs;
@@ -287,7 +288,7 @@ int launch_ag(const void* xall_local, const void* w, void* y, int M, int N, int 
     if (total < n_gemm) n_gemm = total;
     ag_gemm_kernel<BN, STAGES, SWAP, false><<<n_gemm + prm.n_comm, gemm::kThreads, L::kTotalBytes, stream>>>(tp, tq, sched, prm, ep, ectl, status);
   }
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 
 // Cross-GPU barrier: every rank raises its slot on every peer, then waits for all slots.
@@ -460,13 +461,14 @@ extern "C" int b2_tp_all_gather(const B2TpRegion* reg, const B2TpLayout* lay, in
   prm.n_comm = prm.chunks_per_rank < 32 ? prm.chunks_per_rank : 32;
   prm.timeout_ns = timeout_ns;
   constexpr int kPushSmem = kAgRingBytes + 64 + 128;
-  static bool push_attr = false;
-  if (!push_attr) {
-    if (cudaFuncSetAttribute(ag_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPushSmem) != cudaSuccess) return -kBadArgument;
-    push_attr = true;
-  }
+  static DeviceOnce attr_once;
+  if (const int rc = attr_once.run([&] {
+        cudaError_t e = cudaFuncSetAttribute(ag_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPushSmem);
+        return e;
+      }))
+    return rc;
   ag_push_kernel<<<prm.n_comm, 256, kPushSmem, stream>>>(prm, ectl, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 
 extern "C" int b2_symm_barrier(const B2TpRegion* reg, const B2TpLayout* lay, uint64_t timeout_ns, b2::Status* status,
@@ -475,11 +477,11 @@ extern "C" int b2_symm_barrier(const B2TpRegion* reg, const B2TpLayout* lay, uin
   uint8_t* self = static_cast<uint8_t*>(reg->peer[reg->rank]);
   EpochCtl ectl{reinterpret_cast<uint32_t*>(self + lay->off_epoch_bar), reinterpret_cast<uint32_t*>(self + lay->off_epoch_bar + 4)};
   symm_barrier_kernel<<<1, 32, 0, stream>>>(*reg, lay->off_barrier, ectl, timeout_ns, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }
 
 extern "C" int b2_wait_flag(const uint32_t* flag, uint32_t want, uint64_t timeout_ns, b2::Status* status,
                             cudaStream_t stream) {
   wait_flag_kernel<<<1, 32, 0, stream>>>(flag, want, timeout_ns, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -kBadArgument;
+  return last_launch_rc();
 }

@@ -48,6 +48,8 @@ class EngineConfig:
     seed: int = 0
     use_cuda_graphs: bool = True
     capture_graphs_at_start: bool = True  # capture every decode bucket before serving instead of at first use
+    mixed_step_graphs: bool = True        # steps that carry prefill chunks replay CUDA graphs too (captured at first use of a shape)
+    capture_mixed_graphs_at_start: bool = False   # capture every mixed-step shape before serving (a few seconds for an 8B model)
     tp_size: int = 1
     ep_size: int = 1
     lockstep: bool = False                # data-parallel attention + expert parallelism: a rank without work still joins every MoE layer
@@ -124,7 +126,8 @@ class LLMEngine:
         if cfg.autotune:
             self.runner.autotune()
         if cfg.use_cuda_graphs and cfg.capture_graphs_at_start:
-            self.runner.capture_graphs()   # after tuning: the captured launches carry the tuned configurations
+            # after tuning: the captured launches carry the tuned configurations
+            self.runner.capture_graphs(mixed=cfg.capture_mixed_graphs_at_start)
 
     def _auto_num_pages(self) -> int:
         cfg = self.cfg

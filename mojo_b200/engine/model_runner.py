@@ -2,8 +2,17 @@
 
 All integer metadata of a step (token ids, positions, KV slots, sequence offsets, block tables, rows to sample,
 sampling parameters) is packed into one pinned host buffer and moved with a single host->device copy; the only
-device->host traffic is the vector of sampled token ids. Decode-only steps replay a CUDA graph captured per
-batch-size bucket, so their ~10 launches per layer cost one `cudaGraphLaunch`.
+device->host traffic is the vector of sampled token ids.
+
+Greedy steps replay CUDA graphs, so the ten-odd launches per layer cost one `cudaGraphLaunch`:
+  * decode-only steps: one graph per batch-size bucket (`_DecodeGraph`);
+  * steps that also carry prefill chunks, which under continuous batching is nearly every step: one graph per
+    (token-count bucket, decode-row bucket, prefill-sequence bucket) (`_MixedGraph`). Tokens are padded to the bucket
+    (slot -1: nothing is written for a padding row); the decode-attention launch covers a fixed number of rows and
+    reads a context length of 0 for the rows that are not decode sequences; the prefill-attention launch covers a
+    fixed number of (sequence, query tile) work items of which the device-side count says how many are real.
+Everything else (sampling with temperature, log-probabilities, models without the static attention form) runs the
+launch sequence eagerly.
 """
 from __future__ import annotations
 
@@ -18,20 +27,31 @@ def _align(n: int, a: int = 16) -> int:
 
 
 class _Staging:
-    """Pinned host buffer + same-sized device buffer, carved into typed segments per step."""
+    """Pinned host buffers + one device buffer of the same size, carved into typed segments per step.
+
+    The host->device copy of a step is asynchronous, and a step with nothing to sample never waits for the device, so
+    the copy of step k may still be queued when step k + 1 is staged: the host side alternates between two pinned
+    buffers, and a buffer is refilled only after the copy that last read it has completed (an event recorded right
+    behind that copy)."""
 
     def __init__(self, nbytes: int, device: torch.device):
         self.device = device
         self.cuda = device.type == "cuda"
-        self.host = torch.empty(nbytes, dtype=torch.uint8, pin_memory=self.cuda)
-        self.host_np = self.host.numpy()
+        n_host = 2 if self.cuda else 1
+        self.hosts = [torch.empty(nbytes, dtype=torch.uint8, pin_memory=self.cuda) for _ in range(n_host)]
+        self.hosts_np = [h.numpy() for h in self.hosts]
+        self.copied = [torch.cuda.Event() if self.cuda else None for _ in range(n_host)]
+        self.turn = 0
+        self.host, self.host_np = self.hosts[0], self.hosts_np[0]
         self.dev = torch.empty(nbytes, dtype=torch.uint8, device=device) if self.cuda else self.host
         self.off = 0
-        self.segments = []
 
     def begin(self):
         self.off = 0
-        self.segments = []
+        if self.cuda:
+            self.turn ^= 1
+            self.copied[self.turn].synchronize()    # no-op unless the copy two steps back is still in flight
+            self.host, self.host_np = self.hosts[self.turn], self.hosts_np[self.turn]
 
     def put(self, arr: np.ndarray, dtype) -> tuple[int, int, torch.dtype, tuple]:
         arr = np.ascontiguousarray(arr, dtype=dtype)
@@ -47,6 +67,7 @@ class _Staging:
         """Issue the single host->device copy of everything staged; returns bytes copied."""
         if self.cuda and self.off:
             self.dev[:self.off].copy_(self.host[:self.off], non_blocking=True)
+            self.copied[self.turn].record()
         return self.off
 
     def view(self, seg, dtype: torch.dtype) -> torch.Tensor:
@@ -80,21 +101,44 @@ class ModelRunner:
             self.buckets.append(b)
             b = b * 2 if b < 16 else b + max(16, b // 4) // 16 * 16
         self.buckets.append(cfg.max_num_seqs)
-        self.graph_pool = None           # memory pool shared by the decode graphs (they never replay concurrently)
-        self.failed_buckets: dict[int, str] = {}   # buckets whose capture failed: their steps run eagerly
+        self.graph_pool = None           # memory pool shared by all graphs (they never replay concurrently)
+        self.failed_buckets: dict = {}   # buckets / mixed-step keys whose capture failed: their steps run eagerly
+        # mixed steps (decode rows + prefill chunks) as graphs: token-count buckets are the counts the GEMM tables are
+        # measured at; decode rows and prefill sequences come in two sizes each
+        self.mixed_graphs: dict[tuple, "_MixedGraph"] = {}
+        self.mixed_launches = 0
+        self.use_mixed_graphs = bool(self.use_graphs and getattr(cfg, "mixed_step_graphs", True)
+                                     and getattr(model, "supports_static_attention", lambda *_: False)(cfg.page_size))
+        tb = [t for t in (16, 32, 64, 128, 192, 256) if t < cfg.max_num_batched_tokens]
+        t = 384
+        while t < cfg.max_num_batched_tokens:
+            tb.append(t)
+            t += 128
+        tb.append(cfg.max_num_batched_tokens)
+        self.token_buckets = tb
+        self.prefill_seq_buckets = (4, 32)
+        self.decode_row_buckets = (min(32, cfg.max_num_seqs), cfg.max_num_seqs)
         # Expert parallelism: every rank must run the same number of MoE layer calls per step, so a decode graph can
         # only be captured when all ranks capture together (at start-up); a bucket that is missing runs eagerly.
         ep = getattr(model, "ep", None)
         self.ep = ep if ep is not None and getattr(ep, "world_size", 1) > 1 else None
 
-    def capture_graphs(self, buckets=None) -> int:
+    def capture_graphs(self, buckets=None, mixed: bool = False) -> int:
         """Capture the decode graph of every batch-size bucket now, largest first so that the smaller ones reuse its
         memory pool. Without this a bucket is captured the first time a decode-only step needs it, which puts a
-        capture (an eager pass plus the captured pass) into some request's inter-token latency. Returns the number
-        of graphs captured. Tensor-parallel ranks must all call it (the passes contain collectives)."""
+        capture (an eager pass plus the captured pass) into some request's inter-token latency. With `mixed` the
+        graphs of steps that carry prefill chunks are captured too (every token-count bucket times two decode-row and
+        two prefill-sequence sizes). Returns the number of graphs captured. Tensor-parallel ranks must all call it
+        (the passes contain collectives)."""
         if not self.use_graphs:
             return 0
         n = 0
+        if mixed and self.use_mixed_graphs:
+            # the shapes of a loaded server (decode rows at the large bucket); the cold-start shapes are captured at first use
+            steady = [k for k in self.mixed_keys() if k[1] == min(self.decode_row_buckets[-1], k[0])]
+            for key in sorted(steady, reverse=True):
+                if key not in self.mixed_graphs and key not in self.failed_buckets and self._capture_mixed(key) is not None:
+                    n += 1
         for bb in sorted(set(buckets if buckets is not None else self.buckets), reverse=True):
             if bb not in self.graphs and bb not in self.failed_buckets and self._capture(bb) is not None:
                 n += 1
@@ -102,6 +146,38 @@ class ModelRunner:
             torch.cuda.synchronize(self.device)
             ops.check_status(self.device)
         return n
+
+    def mixed_keys(self) -> list[tuple]:
+        """Every (token bucket, decode rows, prefill-sequence bucket) a mixed step can map to."""
+        keys = set()
+        for tb in self.token_buckets:
+            for db in (0,) + tuple(self.decode_row_buckets):
+                for pb in self.prefill_seq_buckets:
+                    keys.add((tb, min(db, tb), min(pb, tb)))
+        return sorted(keys)
+
+    def mixed_key(self, T: int, nd: int, P: int):
+        """Bucket of a step with T tokens, nd decode sequences and P prefill chunks; None if no graph shape covers it."""
+        if P < 1 or P > self.prefill_seq_buckets[-1] or T > self.token_buckets[-1]:
+            return None
+        tb = next(t for t in self.token_buckets if t >= T)
+        pb = min(next(p for p in self.prefill_seq_buckets if p >= P), tb)
+        db = 0 if nd == 0 else min(next(d for d in self.decode_row_buckets if d >= nd), tb)
+        return (tb, db, pb)
+
+    def _capture_mixed(self, key):
+        try:
+            g = _MixedGraph(self, *key)
+        except Exception as e:  # noqa: BLE001
+            import warnings
+
+            self.failed_buckets[key] = repr(e)
+            if self.cuda:
+                torch.cuda.synchronize(self.device)
+            warnings.warn(f"mojo_b200: CUDA-graph capture of the mixed step {key} failed ({e!r}); such steps run eagerly", stacklevel=2)
+            return None
+        self.mixed_graphs[key] = g
+        return g
 
     def _capture(self, bb: int):
         """Capture one bucket. A capture that fails (an operation that a capturing stream does not allow) is not fatal:
@@ -155,6 +231,15 @@ class ModelRunner:
                 g = self._capture(bb)          # first use of a bucket that was not captured at start-up
             if g is not None and g.usable():
                 return self._execute_decode_graph(batch)
+        if (top_lp is None and self.use_mixed_graphs and batch.num_prefill > 0
+                and all(s.params.temperature <= 0.0 for s in states)):
+            key = self.mixed_key(int(batch.num_tokens), int(batch.num_decode), int(batch.num_prefill))
+            if key is not None:
+                g = self.mixed_graphs.get(key)
+                if g is None and key not in self.failed_buckets:
+                    g = self._capture_mixed(key)      # first use of a shape that was not captured at start-up
+                if g is not None:
+                    return self._execute_mixed_graph(g, batch)
         st = self.staging
         st.begin()
         T, B = int(batch.num_tokens), int(batch.num_seqs)
@@ -167,6 +252,13 @@ class ModelRunner:
         sample_rows = batch.sample_rows
         S = len(sample_rows)
         seg_rows = st.put(sample_rows.astype(np.int64), np.int64)
+        seg_work, n_items = None, 0
+        if self.cuda and batch.num_prefill > 0 and getattr(self.model, "supports_static_attention", lambda *_: False)(self.cfg.page_size):
+            # one CTA per (sequence, query tile) of the chunks, longest context first, instead of a padded grid
+            work = ops.prefill_work_items(batch.cu_q, batch.ctx_lens, int(batch.num_decode))
+            n_items = int(work.shape[0])
+            if n_items:
+                seg_work = st.put(work, np.int32)
         greedy = all(s.params.temperature <= 0.0 for s in states)
         if not greedy:
             seg_temp = st.put(np.array([s.params.temperature for s in states], dtype=np.float32), np.float32)
@@ -179,7 +271,8 @@ class ModelRunner:
         positions = st.view(seg_pos, torch.int32)
         ctx_np = batch.ctx_lens
         meta = ops.AttnMeta(st.view(seg_cu, torch.int32), st.view(seg_ctx, torch.int32), st.view(seg_bt, torch.int32),
-                            batch.num_decode, batch.max_q_len, int(ctx_np.max()) if B else 0)
+                            batch.num_decode, batch.max_q_len, int(ctx_np.max()) if B else 0,
+                            work=st.view(seg_work, torch.int32) if seg_work is not None else None, n_items=n_items)
         rows = st.view(seg_rows, torch.int64)
         if self.step_events is not None:
             self.step_events[0].record()
@@ -257,6 +350,25 @@ class ModelRunner:
         torch.cuda.current_stream(self.device).synchronize()
         self.d2h_bytes = B * 8
         return self.ids_host[:B].tolist()
+
+    def _execute_mixed_graph(self, g: "_MixedGraph", batch) -> list[int]:
+        S = int(len(batch.sample_rows))
+        self.h2d_bytes = g.stage(batch)
+        if self.step_events is not None:
+            self.step_events[0].record()
+        g.graph.replay()
+        if self.step_events is not None:
+            self.step_events[1].record()
+        self.graph_launches += 1
+        self.mixed_launches += 1
+        self.graph_kernel_launches += g.kernel_launches
+        if S == 0:
+            self.d2h_bytes = 0      # mid-prompt chunks only: nothing to read back, the host runs ahead
+            return []
+        self.ids_host[:S].copy_(g.ids[:S], non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        self.d2h_bytes = S * 8
+        return self.ids_host[:S].tolist()
 
 
 class _DecodeGraph:
@@ -346,3 +458,122 @@ class _DecodeGraph:
         self.h_bt[:B, :bt.shape[1]] = bt
         self.dev.copy_(self.host, non_blocking=True)
         return self.host.numel()
+
+
+class _MixedGraph:
+    """Static buffers + captured forward/argmax for steps with `tb` tokens (padded), up to `db` decode rows and up to
+    `pb` prefill chunks. One pinned block is filled on the host and moved with one copy; the graph reads everything
+    that varies (ids, positions, slots, context lengths, block tables, work items and their count, rows to sample)
+    from the device copy of that block."""
+
+    def __init__(self, runner: ModelRunner, tb: int, db: int, pb: int):
+        self.runner, self.tb, self.db, self.pb = runner, tb, db, pb
+        mb, dev = runner.max_blocks, runner.device
+        self.max_items = tb // 128 + pb
+        self.sb = max(1, min(db + pb, tb))          # rows that can be sampled in one step
+        lay, off = {}, 0
+
+        def seg(name, nbytes):
+            nonlocal off
+            lay[name] = (off, nbytes)
+            off = _align(off + nbytes)
+
+        seg("tok", 8 * tb); seg("slot", 8 * tb); seg("pos", 4 * tb)
+        seg("d_ctx", 4 * max(db, 1)); seg("d_bt", 4 * max(db, 1) * mb)
+        seg("p_cu", 4 * (pb + 1)); seg("p_ctx", 4 * pb); seg("p_bt", 4 * pb * mb)
+        seg("work", 8 * self.max_items); seg("n_work", 4); seg("rows", 8 * self.sb)
+        self.nbytes = off
+        self.host = torch.zeros(off, dtype=torch.uint8, pin_memory=True)
+        self.dev = torch.zeros(off, dtype=torch.uint8, device=dev)
+        self.copied = torch.cuda.Event()
+        hn = self.host.numpy()
+
+        def hv(name, dtype, shape=None):
+            o, n = lay[name]
+            a = hn[o:o + n].view(dtype)
+            return a.reshape(shape) if shape is not None else a
+
+        def dv(name, dtype, shape=None):
+            o, n = lay[name]
+            t = self.dev[o:o + n].view(dtype)
+            return t.view(*shape) if shape is not None else t
+
+        self.h = {"tok": hv("tok", np.int64), "slot": hv("slot", np.int64), "pos": hv("pos", np.int32),
+                  "d_ctx": hv("d_ctx", np.int32), "d_bt": hv("d_bt", np.int32, (max(db, 1), mb)),
+                  "p_cu": hv("p_cu", np.int32), "p_ctx": hv("p_ctx", np.int32), "p_bt": hv("p_bt", np.int32, (pb, mb)),
+                  "work": hv("work", np.int32, (self.max_items, 2)), "n_work": hv("n_work", np.int32), "rows": hv("rows", np.int64)}
+        self.h["slot"][:] = -1
+        self.dev.copy_(self.host)
+        self.tok, self.slot, self.pos = dv("tok", torch.int64), dv("slot", torch.int64), dv("pos", torch.int32)
+        self.rows = dv("rows", torch.int64)
+        n_kv = runner.kv_caches[0][0].shape[1]
+        static = ops.StaticAttn(db, dv("d_ctx", torch.int32), dv("d_bt", torch.int32, (max(db, 1), mb)),
+                                ops._decode_splits(db, n_kv, runner.cfg.max_model_len) if db else 1,
+                                dv("p_cu", torch.int32), dv("p_ctx", torch.int32), dv("p_bt", torch.int32, (pb, mb)),
+                                dv("work", torch.int32, (self.max_items, 2)), dv("n_work", torch.int32), self.max_items, tb)
+        self.meta = ops.AttnMeta(None, None, None, 0, tb, runner.cfg.max_model_len, static=static)
+        model, caches = runner.model, runner.kv_caches
+        comm = getattr(model, "comm", None)
+
+        def run():
+            if comm is not None and hasattr(comm, "begin_graph"):
+                comm.begin_graph()
+            if getattr(model, "greedy_in_forward", False):
+                return model.forward(self.tok, self.pos, self.slot, self.meta, caches, self.rows, greedy=True)
+            return ops.argmax(model.forward(self.tok, self.pos, self.slot, self.meta, caches, self.rows))
+
+        # one eager pass on a side stream (one-time kernel attribute set-up must not happen under capture); the block
+        # is all padding at this point: slots -1, no decode context, no work items, so the pass touches no KV page
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            run()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        before = ops.launch_count
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, pool=runner.graph_pool):
+            self.ids = run()
+        if runner.graph_pool is None:
+            runner.graph_pool = self.graph.pool()
+        self.kernel_launches = ops.launch_count - before
+        ops.launch_count = before
+
+    def stage(self, batch) -> int:
+        """Fill the pinned block from the scheduler's batch and start its copy. Returns the bytes copied."""
+        self.copied.synchronize()       # the previous copy out of this block has been consumed
+        h = self.h
+        T, B, nd = int(batch.num_tokens), int(batch.num_seqs), int(batch.num_decode)
+        P = B - nd
+        h["tok"][:T] = batch.token_ids
+        h["tok"][T:] = 0
+        h["slot"][:T] = batch.slots
+        h["slot"][T:] = -1
+        h["pos"][:T] = batch.positions
+        h["pos"][T:] = 0
+        ctx, cu, bt = batch.ctx_lens, batch.cu_q, batch.block_tables
+        w = bt.shape[1]
+        if self.db:
+            h["d_ctx"][:nd] = ctx[:nd]
+            h["d_ctx"][nd:] = 0
+            h["d_bt"][:nd, :w] = bt[:nd]
+        h["p_cu"][:P + 1] = cu[nd:]
+        h["p_cu"][P + 1:] = cu[-1]
+        h["p_ctx"][:P] = ctx[nd:]
+        h["p_ctx"][P:] = 0
+        h["p_bt"][:P, :w] = bt[nd:]
+        work = ops.prefill_work_items(cu, ctx, nd)
+        n = work.shape[0]
+        if n > self.max_items:
+            raise RuntimeError(f"mixed-step graph {self.tb, self.db, self.pb}: {n} attention work items exceed {self.max_items}")
+        h["work"][:n] = work
+        h["n_work"][0] = n
+        rows = batch.sample_rows
+        S = len(rows)
+        if S > self.sb:
+            raise RuntimeError(f"mixed-step graph {self.tb, self.db, self.pb}: {S} rows to sample exceed {self.sb}")
+        h["rows"][:S] = rows
+        h["rows"][S:] = 0
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copied.record()
+        return self.nbytes

@@ -303,6 +303,8 @@ class LlamaModel:
             gu, residual = norm_gather_linear(h, residual, lw.mlp_norm, lw.w_gu, getattr(lw, "s_gu", None))
             act = ops.swiglu(gu, interleaved=not fp8)   # bf16 gate/up weights are stacked for the SwiGLU GEMM epilogue
             h = comm.linear_fp8_reduce_scatter(act, lw.w_down, lw.s_down) if fp8 else comm.linear_reduce_scatter(act, lw.w_down)
+        if sample_rows is not None and sample_rows.numel() == 0:
+            return self._no_rows(greedy)
         # final norm on the local rows, then gather the hidden states for the LM head
         ops.rms_norm(h, self.final_norm, cfg.rms_norm_eps, residual, out=comm.gather_input(Tp, H))
         x = comm.all_gather_rows(Tp, H)[:T]
@@ -337,6 +339,8 @@ class LlamaModel:
         """Final norm (unless `normed` already holds it), row gather and the vocabulary-parallel LM head. `greedy`
         on a tensor-parallel communicator that can merge arg-maxes returns int64 token ids instead of gathered logits."""
         cfg = self.cfg
+        if sample_rows is not None and sample_rows.numel() == 0:
+            return self._no_rows(greedy)
         x = normed if normed is not None else ops.rms_norm(h, self.final_norm, cfg.rms_norm_eps, residual)[0]
         if sample_rows is not None:
             x = ops.gather_rows(x, sample_rows)
@@ -345,6 +349,19 @@ class LlamaModel:
             valid = max(1, min(self.vocab_local, cfg.vocab_size - self.vocab_start))
             return self.comm.vocab_argmax(logits[:, :valid], self.vocab_local)
         return self.comm.all_gather_vocab(logits)[:, :cfg.vocab_size]
+
+    def supports_static_attention(self, page_size: int) -> bool:
+        """Whether a whole step of this model (decode rows and prefill chunks together) can run with fixed launch
+        shapes, i.e. inside a CUDA graph: needs the prefill kernel that takes a device-side work list (head dim 128,
+        128-token pages) and the token-replicated dataflow (the sequence-parallel one pads and slices per step)."""
+        return (self.device.type == "cuda" and not self.sequence_parallel and ops.prefill_on_tensor_core(self.head_dim, page_size))
+
+    def _no_rows(self, greedy: bool) -> torch.Tensor:
+        """Result of a step that samples nothing (only chunks from the middle of prompts): the layers ran for their
+        KV writes, the LM head and its collective are skipped."""
+        if greedy and self.greedy_in_forward:
+            return torch.empty(0, dtype=torch.int64, device=self.device)
+        return torch.empty(0, self.cfg.vocab_size, dtype=self.dtype, device=self.device)
 
     @property
     def greedy_in_forward(self) -> bool:

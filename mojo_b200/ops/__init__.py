@@ -262,17 +262,64 @@ def gemm_config(swap: bool, bn: int, splits: int = 1, stream_k: bool = False) ->
 
 
 class AttnMeta:
-    """Device-side description of one ragged batch (decode sequences first, then prefill chunks)."""
+    """Device-side description of one ragged batch (decode sequences first, then prefill chunks).
 
-    __slots__ = ("cu_q", "ctx_lens", "block_tables", "num_decode", "num_seqs", "max_q_len", "num_tokens", "max_ctx")
+    Optional extras, both built on the host by the model runner:
+      work, n_items   (sequence, query tile) items of the prefill chunks, longest context first, as an int32 [n, 2] device
+                      tensor whose sequence index counts from the first prefill sequence; the tcgen05 prefill kernel then
+                      launches exactly one CTA per item and head
+      static          a `StaticAttn`: every shape and grid fixed ahead of the batch, so that the launches can sit in a
+                      CUDA graph that serves any batch of its bucket
+    """
 
-    def __init__(self, cu_q, ctx_lens, block_tables, num_decode, max_q_len, max_ctx=0):
+    __slots__ = ("cu_q", "ctx_lens", "block_tables", "num_decode", "num_seqs", "max_q_len", "num_tokens", "max_ctx", "work", "n_items", "static")
+
+    def __init__(self, cu_q, ctx_lens, block_tables, num_decode, max_q_len, max_ctx=0, work=None, n_items=0, static=None):
         self.cu_q, self.ctx_lens, self.block_tables = cu_q, ctx_lens, block_tables
         self.num_decode = int(num_decode)
-        self.num_seqs = int(ctx_lens.numel())
+        self.num_seqs = int(ctx_lens.numel()) if ctx_lens is not None else 0
         self.max_q_len = int(max_q_len)
         self.num_tokens = None
         self.max_ctx = int(max_ctx)
+        self.work, self.n_items = work, int(n_items)
+        self.static = static
+
+
+class StaticAttn:
+    """Attention metadata of a captured step. The decode launch covers the first `d_rows` token rows: row i < number of
+    decode sequences has its context length in `d_ctx[i]`, every other row has 0 there (the kernel writes zeros, which
+    the prefill launch then overwrites where the row belongs to a chunk). The prefill launch covers `max_items` work
+    items of which the first `n_work[0]` are valid; `p_cu` / `p_ctx` / `p_bt` describe the prefill sequences only
+    (`p_cu` holds absolute token rows; unused entries repeat the last offset)."""
+
+    __slots__ = ("d_rows", "d_ctx", "d_bt", "d_splits", "p_cu", "p_ctx", "p_bt", "work", "n_work", "max_items", "max_q_len")
+
+    def __init__(self, d_rows, d_ctx, d_bt, d_splits, p_cu, p_ctx, p_bt, work, n_work, max_items, max_q_len):
+        self.d_rows, self.d_ctx, self.d_bt, self.d_splits = int(d_rows), d_ctx, d_bt, int(d_splits)
+        self.p_cu, self.p_ctx, self.p_bt = p_cu, p_ctx, p_bt
+        self.work, self.n_work, self.max_items, self.max_q_len = work, n_work, int(max_items), int(max_q_len)
+
+
+def prefill_work_items(cu_q, ctx_lens, num_decode: int, tile: int = 128):
+    """Host-side work list of the prefill chunks of one batch: an int32 [n, 2] numpy array of (prefill sequence index,
+    query tile), ordered by the number of KV tiles each item visits, longest first (the CTAs that take longest start
+    first). `cu_q` [B + 1] and `ctx_lens` [B] are the batch's host arrays."""
+    import numpy as np
+
+    cu = np.asarray(cu_q[num_decode:], dtype=np.int64)
+    ctx = np.asarray(ctx_lens[num_decode:], dtype=np.int64)
+    q_len = cu[1:] - cu[:-1]
+    tiles = (q_len + tile - 1) // tile
+    n = int(tiles.sum())
+    if n == 0:
+        return np.zeros((0, 2), dtype=np.int32)
+    seq = np.repeat(np.arange(len(tiles), dtype=np.int64), tiles)
+    first = np.cumsum(tiles) - tiles
+    qt = np.arange(n, dtype=np.int64) - np.repeat(first, tiles)
+    rows = np.minimum(tile, q_len[seq] - qt * tile)
+    kv_tiles = np.minimum((ctx[seq] - q_len[seq] + qt * tile + rows + tile - 1) // tile, (ctx[seq] + tile - 1) // tile)
+    order = np.argsort(-kv_tiles, kind="stable")
+    return np.stack([seq[order], qt[order]], axis=1).astype(np.int32)
 
 
 def _decode_splits(batch: int, n_kv: int, max_ctx: int) -> int:
@@ -289,6 +336,10 @@ def _decode_splits(batch: int, n_kv: int, max_ctx: int) -> int:
 prefill_tensor_core = True
 
 
+def prefill_on_tensor_core(head_dim: int, page_size: int) -> bool:
+    return bool(prefill_tensor_core and head_dim == 128 and page_size == 128)
+
+
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, meta: AttnMeta, scale: float,
                     head_dim: int, out: torch.Tensor | None = None) -> torch.Tensor:
     """Causal GQA attention over the paged cache. q, out: [T, n_q * D]."""
@@ -301,6 +352,18 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     st = _state.get(q.device)
     if out is None:
         out = torch.empty(q.shape[0], q.shape[1], dtype=q.dtype, device=q.device)
+    sa = meta.static
+    if sa is not None:
+        # captured step: fixed grids, everything that varies is read from device memory
+        if sa.d_rows > 0:
+            C.attn_decode(q[:sa.d_rows], k_cache, v_cache, out[:sa.d_rows], sa.d_ctx, sa.d_bt, st.attn_ws, head_dim, sa.d_splits,
+                          scale, st.status)
+            _count(2 if sa.d_splits > 1 else 1)
+        if sa.max_items > 0:
+            C.attn_prefill_tc(q, k_cache, v_cache, out, sa.p_cu, sa.p_ctx, sa.p_bt, sa.max_q_len, scale, 0, st.status,
+                              sa.work, sa.n_work, sa.max_items)
+            _count()
+        return out
     nd, ns = meta.num_decode, meta.num_seqs
     if nd > 0:
         splits = _decode_splits(nd, k_cache.shape[1], meta.max_ctx)
@@ -309,10 +372,14 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _count(2 if splits > 1 else 1)
     if ns > nd:
         # cu_q offsets are absolute token rows, so q/out are passed whole
-        if prefill_tensor_core and head_dim == 128 and k_cache.shape[2] == 128:
+        if prefill_on_tensor_core(head_dim, k_cache.shape[2]):
             # tcgen05 / TMEM kernel: one KV tile = one 128-token page
-            C.attn_prefill_tc(q, k_cache, v_cache, out, meta.cu_q[nd:], meta.ctx_lens[nd:], meta.block_tables[nd:],
-                              meta.max_q_len, scale, 0, st.status)
+            if meta.work is not None and meta.n_items > 0:
+                C.attn_prefill_tc(q, k_cache, v_cache, out, meta.cu_q[nd:], meta.ctx_lens[nd:], meta.block_tables[nd:],
+                                  meta.max_q_len, scale, 0, st.status, meta.work, None, meta.n_items)
+            else:
+                C.attn_prefill_tc(q, k_cache, v_cache, out, meta.cu_q[nd:], meta.ctx_lens[nd:], meta.block_tables[nd:],
+                                  meta.max_q_len, scale, 0, st.status)
         else:
             C.attn_prefill(q, k_cache, v_cache, out, meta.cu_q[nd:], meta.ctx_lens[nd:], meta.block_tables[nd:], head_dim,
                            meta.max_q_len, scale, st.status)

@@ -68,6 +68,27 @@ def main():
         same = sum(int(a == b) for w, g in zip(want_tok, got_tok) for a, b in zip(w, g))
         first = sum(int(w[0] == g[0]) for w, g in zip(want_tok, got_tok))
         assert first >= len(prompts) - 1 and same >= 0.5 * sum(len(w) for w in want_tok), (sp, want_tok, got_tok)
+    # steps that mix decode rows and prefill chunks, as CUDA graphs under tensor parallelism (head dim 128 and
+    # 128-token pages: the tcgen05 prefill kernel with its device-side work list); against the eager launch sequence
+    cfg2 = ModelConfig(vocab_size=4096, hidden_size=512, num_layers=2, num_heads=8, num_kv_heads=8 if tp > 4 else 4,
+                       head_dim=128, intermediate_size=1024, max_position_embeddings=1024)
+    prompts2 = [[int(t) for t in torch.randint(0, cfg2.vocab_size, (n,), generator=torch.Generator().manual_seed(100 + n))] for n in (300, 40, 200, 7)]
+    fused2 = FusedTPComm(info, max_tokens=256, hidden=cfg2.hidden_size, timeout_s=10.0)
+    toks = {}
+    for graphs in (False, True):
+        model = build_model(cfg2, dev, torch.bfloat16, comm=fused2).init_random(0, std=0.06)
+        eng = LLMEngine(EngineConfig(model=cfg2, device=str(dev), dtype=torch.bfloat16, page_size=128, num_pages=32, max_num_seqs=8,
+                                     max_num_batched_tokens=256, max_model_len=512, tp_size=tp, use_cuda_graphs=graphs), model=model, comm=fused2)
+        toks[graphs] = eng.generate(prompts2, SamplingParams(max_tokens=10))
+        torch.cuda.synchronize()
+        ops.check_status(dev)
+        if graphs:
+            assert eng.runner.mixed_launches > 0 and not eng.runner.failed_buckets, eng.runner.failed_buckets
+        box = [None] * tp
+        dist.all_gather_object(box, toks[graphs])
+        assert all(b == box[0] for b in box), "ranks disagree on the generated tokens"
+    same = sum(int(a == b) for w, g in zip(toks[False], toks[True]) for a, b in zip(w, g))
+    assert [w[0] for w in toks[False]] == [g[0] for g in toks[True]] and same >= 0.7 * sum(len(w) for w in toks[False]), toks
     dist.barrier()
     if rank == 0:
         print(f"TP_ENGINE_OK {tp}", flush=True)

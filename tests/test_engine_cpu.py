@@ -283,3 +283,35 @@ def test_decode_graph_dispatch_and_fallback_when_a_capture_fails(monkeypatch):
     assert list(runner.failed_buckets) == [2] and captured == [1] and replayed and set(replayed) == {1}
     assert sum("capture" in str(x.message) for x in w) == 1                # warned once, not once per step
     assert runner.capture_graphs() == 1 and sorted(captured) == [1, 4]     # the remaining bucket; the failed one is not retried
+
+
+def test_prefill_work_items_cover_every_query_tile_once_longest_first():
+    import numpy as np
+
+    from mojo_b200 import ops
+
+    rng = np.random.default_rng(0)
+    for _ in range(20):
+        nd, P = int(rng.integers(0, 5)), int(rng.integers(1, 6))
+        q = np.concatenate([np.ones(nd, dtype=np.int64), rng.integers(1, 700, P)])
+        ctx = q + np.concatenate([rng.integers(0, 900, nd), rng.integers(0, 3, P) * 128])   # chunks start at page boundaries or 0
+        cu = np.concatenate([[0], np.cumsum(q)])
+        w = ops.prefill_work_items(cu, ctx, nd)
+        want = {(s, t) for s in range(P) for t in range((q[nd + s] + 127) // 128)}
+        assert len(w) == len(want) and {(int(a), int(b)) for a, b in w} == want
+        cost = [min((ctx[nd + s] - q[nd + s] + t * 128 + min(128, q[nd + s] - t * 128) + 127) // 128, (ctx[nd + s] + 127) // 128) for s, t in w]
+        assert cost == sorted(cost, reverse=True)
+        assert len(w) <= cu[-1] // 128 + P     # the bound the captured launch's grid is sized with
+
+
+def test_mixed_step_buckets_cover_every_schedulable_batch():
+    ecfg = EngineConfig(model=tiny_llama(), device="cpu", dtype=torch.float32, page_size=16, num_pages=64, max_num_seqs=48,
+                        max_num_batched_tokens=1000, max_model_len=128)
+    r = LLMEngine(ecfg).runner
+    assert r.token_buckets[-1] == 1000 and r.token_buckets == sorted(set(r.token_buckets))
+    keys = set(r.mixed_keys())
+    for T, nd, P in [(1000, 48, 1), (17, 16, 1), (5, 0, 1), (300, 33, 4), (300, 2, 30), (129, 0, 32), (16, 3, 13)]:
+        k = r.mixed_key(T, nd, P)
+        tb, db, pb = k
+        assert k in keys and tb >= T and db >= nd and pb >= P and db <= tb and pb <= tb
+    assert r.mixed_key(300, 2, 33) is None and r.mixed_key(300, 300, 0) is None     # too many chunks / no chunk: not a mixed step

@@ -59,6 +59,73 @@ def test_gpu_engine_matches_cpu_reference(graphs):
         assert eng.runner.graph_launches > 0
 
 
+def _cfg128():
+    # head dim 128 and (below) 128-token pages: the shapes of the tcgen05 prefill kernel and of the mixed-step graphs
+    return ModelConfig(hidden_size=512, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=128, intermediate_size=1408,
+                       vocab_size=4096, max_position_embeddings=2048, tie_word_embeddings=True)
+
+
+def _engine128(device, dtype, graphs, budget, page=128, mixed=True):
+    ecfg = EngineConfig(model=_cfg128(), device=device, dtype=dtype, page_size=page, num_pages=64 if page == 128 else 512, max_num_seqs=8,
+                        max_num_batched_tokens=budget, max_model_len=1024, seed=0, use_cuda_graphs=graphs, mixed_step_graphs=mixed)
+    model = build_model(_cfg128(), device, dtype).init_random(0, std=0.08)
+    return LLMEngine(ecfg, model=model)
+
+
+def _same_up_to_near_ties(cpu_model, prompts, want, got):
+    """Token lists agree; a first divergence is accepted only where the fp32 logits put the two candidates within bf16 noise."""
+    for prompt, w, o in zip(prompts, want, got):
+        assert len(o) == len(w)
+        for i, (a, b) in enumerate(zip(w, o)):
+            if a != b:
+                lg = _cpu_last_logits(cpu_model, list(prompt) + list(w[:i]))
+                margin = (lg[a] - lg[b]).item()
+                assert margin < 0.03 * lg.abs().max().item() + 0.02, f"token {i}: fp32 margin {margin} is not a near-tie"
+                break
+
+
+def test_mixed_step_graphs_give_the_eager_tokens():
+    """Steps that carry prefill chunks next to decode rows replay CUDA graphs (padded tokens, fixed attention grids,
+    device-side work list): same tokens as the eager launch sequence and as the CPU fp32 engine."""
+    g = torch.Generator().manual_seed(21)
+    prompts = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in (300, 40, 700, 129, 5, 260)]
+    sp = SamplingParams(max_tokens=20)
+    cpu_eng = _engine128("cpu", torch.float32, False, budget=256, page=16)
+    want = cpu_eng.generate(prompts, sp)
+    eager = _engine128("cuda", torch.bfloat16, False, budget=256)
+    got_eager = eager.generate(prompts, sp)
+    eng = _engine128("cuda", torch.bfloat16, True, budget=256)
+    got = eng.generate(prompts, sp)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert eng.runner.mixed_launches > 0 and not eng.runner.failed_buckets, eng.runner.failed_buckets
+    assert eng.runner.graph_launches > eng.runner.mixed_launches          # decode-only steps replay their own graphs
+    _same_up_to_near_ties(cpu_eng.model, prompts, want, got_eager)
+    _same_up_to_near_ties(cpu_eng.model, prompts, want, got)
+    assert [o[0] for o in got] == [o[0] for o in got_eager]
+    # a second batch through the same (already captured) graphs: replay is deterministic
+    assert eng.generate(prompts, sp) == got
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_long_prompt_in_many_chunks_matches_one_chunk(graphs):
+    """A prompt of five chunks: the steps in the middle of the prompt sample nothing, so the host never waits for the
+    device between them and runs several steps ahead. Every chunk must still see its own metadata."""
+    g = torch.Generator().manual_seed(22)
+    prompts = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in (620, 900)]
+    sp = SamplingParams(max_tokens=8)
+    cpu_eng = _engine128("cpu", torch.float32, False, budget=2048, page=16)
+    want = cpu_eng.generate(prompts, sp)
+    one = _engine128("cuda", torch.bfloat16, False, budget=2048).generate(prompts, sp)
+    eng = _engine128("cuda", torch.bfloat16, graphs, budget=128)
+    got = eng.generate(prompts, sp)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert [o[0] for o in got] == [o[0] for o in one] == [w[0] for w in want]
+    _same_up_to_near_ties(cpu_eng.model, prompts, want, got)
+    _same_up_to_near_ties(cpu_eng.model, prompts, want, one)
+
+
 def test_gpu_logits_close_to_cpu_reference():
     cfg = _cfg()
     cpu = build_model(cfg, "cpu", torch.float32).init_random(0, std=0.08)

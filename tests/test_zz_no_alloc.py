@@ -45,15 +45,39 @@ def test_no_alloc_gemm_matches_regular_entry_point_twice():
     ops.check_status()
 
 
+def _split_k_need(lib, M, N, K):
+    """Scratch bytes the automatic configuration of this shape needs (0 if it does not split K), from the library's own rule."""
+    cfg = lib.b2_gemm_auto_config(M, N, K, 0)
+    swap, splits, bn = (cfg >> 30) & 1, (cfg >> 16) & 0xFF, cfg & 0xFFFF
+    num_kb = (K + 63) // 64
+    splits = min(splits, num_kb, 16)
+    while splits > 1 and ((num_kb + splits - 1) // splits) * (splits - 1) >= num_kb:
+        splits -= 1
+    if splits <= 1:
+        return 0
+    rows_p, rows_q = (N, M) if swap else (M, N)
+    tiles = ((rows_p + 127) // 128) * ((rows_q + bn - 1) // bn)
+    return 65536 * 4 + tiles * splits * bn * 128 * 4
+
+
 def test_no_alloc_gemm_rejects_what_does_not_fit():
     lib = _ext.kernels_lib()
     lib.b2_gemm_bf16_noalloc.restype = ctypes.c_int
-    # 128 tokens x 4096 outputs x K = 14336 splits K with partial sums far beyond the 8 MiB array
-    x = torch.zeros(128, 14336, dtype=torch.bfloat16, device="cuda")
-    w = torch.zeros(4096, 14336, dtype=torch.bfloat16, device="cuda")
-    y = torch.zeros(128, 4096, dtype=torch.bfloat16, device="cuda")
-    rc = _call(lib, x, w, y)
+    lib.b2_gemm_auto_config.restype = ctypes.c_int
+    cap = 8 << 20
+    # a shape whose automatic configuration splits K into partial sums beyond the 8 MiB array: found with the
+    # library's own rule, so the refusal below is certain to be the capacity check and nothing else
+    shape = next(((M, N, K) for M in (128, 64, 32, 256) for N in (4096, 8192, 2048, 16384) for K in (14336, 8192, 28672, 4096)
+                  if _split_k_need(lib, M, N, K) > cap), None)
+    assert shape is not None, "no candidate shape splits K beyond the static scratch: extend the candidate list"
+    M, N, K = shape
+    x = torch.zeros(M, K, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(N, K, dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+    assert _call(lib, x, w, y) == -5          # TOO_LARGE, before anything is launched
+    bad = _call(lib, x[:, :K - 6], w, y)
+    assert bad == -4                          # K not a multiple of 8: BAD_ARGUMENT, nothing launched
     torch.cuda.synchronize()
-    assert rc in (0, -5)      # either the chosen configuration does not split, or it is refused as TOO_LARGE
-    bad = _call(lib, x[:, :14330], w, y)
-    assert bad == -4          # K not a multiple of 8: BAD_ARGUMENT, nothing launched
+    # no kernel of this entry point has recorded a failure on this device
+    lib.b2_gemm_bf16_noalloc_status.restype = ctypes.c_int
+    assert lib.b2_gemm_bf16_noalloc_status(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
