@@ -72,6 +72,28 @@ void bind_coll(py::module_& m) {
                                                 timeout_ns, status_ptr(status), cur_stream()),
                 "coll_all_reduce_rmsnorm");
         });
+  m.def("coll_all_reduce_rmsnorm_nvls",
+        [](int rank, const std::vector<int64_t>& peers, const B2CollLayout& lay, int64_t mc_base, c10::optional<at::Tensor> residual,
+           const at::Tensor& weight, int rows, double eps, int slot, uint64_t timeout_ns, c10::optional<at::Tensor> status) {
+          const B2TpRegion reg = make_region(rank, peers);
+          need(weight.is_cuda() && weight.scalar_type() == at::kBFloat16 && weight.is_contiguous(), "coll_all_reduce_rmsnorm_nvls: weight bf16 [hidden]");
+          const int hidden = static_cast<int>(weight.numel());
+          if (residual.has_value())
+            need(residual->scalar_type() == at::kBFloat16 && residual->is_contiguous() && residual->numel() == static_cast<int64_t>(rows) * hidden,
+                 "coll_all_reduce_rmsnorm_nvls: residual bf16 [rows, hidden]");
+          c10::cuda::CUDAGuard g(weight.device());
+          check(b2_coll_all_reduce_rmsnorm_nvls_bf16(&reg, &lay, reinterpret_cast<void*>(mc_base), residual.has_value() ? residual->data_ptr() : nullptr,
+                                                     weight.data_ptr(), rows, hidden, static_cast<float>(eps), slot, timeout_ns, status_ptr(status),
+                                                     cur_stream()),
+                "coll_all_reduce_rmsnorm_nvls");
+        });
+  m.def("coll_p2p_probe",
+        [](int rank, const std::vector<int64_t>& peers, const B2CollLayout& lay, int64_t bytes, int n_peers, uint32_t senders, bool pull, int ctas,
+           int slot, uint64_t timeout_ns, c10::optional<at::Tensor> status) {
+          const B2TpRegion reg = make_region(rank, peers);
+          check(b2_coll_p2p_probe(&reg, &lay, bytes, n_peers, senders, pull ? 1 : 0, ctas, slot, timeout_ns, status_ptr(status), cur_stream()),
+                "coll_p2p_probe");
+        });
   m.def("coll_reduce_scatter",
         [](int rank, const std::vector<int64_t>& peers, const B2CollLayout& lay, at::Tensor& out, int64_t n, int slot, uint64_t timeout_ns,
            c10::optional<at::Tensor> status) {

@@ -35,6 +35,13 @@ int b2_coll_all_reduce_bf16(const struct B2TpRegion* reg, const struct B2CollLay
 int b2_coll_all_reduce_rmsnorm_bf16(const struct B2TpRegion* reg, const struct B2CollLayout* lay, void* residual, const void* weight,
                                     void* out, int rows, int hidden, float eps, int slot, uint64_t timeout_ns, b2::Status* status,
                                     cudaStream_t stream);
+// The same through the NVLink switch: each rank reduces 1 / tp of the rows with multimem.ld_reduce on the multicast
+// mapping `mc_base` and multimem.st's its normalised rows and new residual rows into every rank's `out` half, which
+// then holds bf16 [rows, hidden] normalised followed by bf16 [rows, hidden] residual. `residual` (may be null) is
+// only read. 2 * rows * hidden * 2 bytes must fit in an `out` half.
+int b2_coll_all_reduce_rmsnorm_nvls_bf16(const struct B2TpRegion* reg, const struct B2CollLayout* lay, void* mc_base, const void* residual,
+                                         const void* weight, int rows, int hidden, float eps, int slot, uint64_t timeout_ns,
+                                         b2::Status* status, cudaStream_t stream);
 // out = this rank's n / tp elements of the sum.
 int b2_coll_reduce_scatter_bf16(const struct B2TpRegion* reg, const struct B2CollLayout* lay, void* out, int64_t n, int slot,
                                 uint64_t timeout_ns, b2::Status* status, cudaStream_t stream);
@@ -51,6 +58,12 @@ int b2_coll_all_to_all(const struct B2TpRegion* reg, const struct B2CollLayout* 
 int b2_coll_vocab_argmax(const struct B2TpRegion* reg, const struct B2CollLayout* lay, const void* logits, int64_t ld,
                          const int64_t* local_idx, int64_t* tokens, int S, int v_local, int v_stride, int slot,
                          uint64_t timeout_ns, b2::Status* status, cudaStream_t stream);
+
+// Link bandwidth probe built from the same peer loads / stores the collectives use: every rank whose bit is set in
+// `senders` moves `bytes` (multiple of 16, at most one `buf` half) to (push) or from (pull) each of its next `n_peers`
+// ranks, with `ctas` CTAs of 256 threads. The launch returns when every byte has been delivered on every rank.
+int b2_coll_p2p_probe(const struct B2TpRegion* reg, const struct B2CollLayout* lay, int64_t bytes, int n_peers, uint32_t senders,
+                      int pull, int ctas, int slot, uint64_t timeout_ns, b2::Status* status, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -169,6 +169,70 @@ __global__ void __launch_bounds__(kCollThreads) all_reduce_rmsnorm_kernel(CollPa
   tp::epoch_end(ectl, epoch);
 }
 
+// The same operation through the NVLink switch (NVLS), for messages where the one-shot form's traffic (every rank reads
+// every peer's partials: tp - 1 times the message in per rank) is the cost. Rank r owns rows [r * rows_per, ...):
+//   * `multimem.ld_reduce` on the multicast address returns the sum over all ranks' partials (added in f32 inside the
+//     switch, rounded to bf16), so each partial byte crosses NVLink once and only 1 / tp of the message comes in;
+//   * the owner adds the residual rows, normalises, and stores the new residual rows and the normalised rows with
+//     `multimem.st`, which the switch replicates into every rank's result half.
+// Results therefore live in the symmetric result half: [rows, hidden] normalised, then [rows, hidden] residual.
+// Every rank gets bit-identical rows (one rank computed them). Flags A before (all partials are in place), B after.
+template <int VPT>
+__global__ void __launch_bounds__(kCollThreads) all_reduce_rmsnorm_nvls_kernel(CollParams p, EpochCtl ectl, uint8_t* mc_base,
+                                                                               const uint4* __restrict__ residual, const uint4* __restrict__ weight,
+                                                                               int rows, int hidden, float eps, int64_t off_res_out, Status* status) {
+  __shared__ float scratch[33];
+  const uint32_t epoch = tp::epoch_begin(ectl);
+  const bool ok = arrive_and_wait(p, p.off_flags_a, epoch, blockIdx.x == 0, status);
+  const int nvec = hidden >> 3;
+  const int rows_per = (rows + p.tp - 1) / p.tp;
+  const int row_lo = rows_per * p.rank, row_hi = min(rows, row_lo + rows_per);
+  if (ok) {
+    for (int row = row_lo + blockIdx.x; row < row_hi; row += gridDim.x) {
+      const int64_t base = static_cast<int64_t>(row) * nvec;
+      float v[VPT][8];
+      float ss = 0.0f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * kCollThreads;
+        if (c < nvec) {
+          bf16x8_to_f32(ptx::multimem_ld_reduce_bf16x8(mc_base + p.off_buf + (base + c) * 16), v[i]);
+          if (residual != nullptr) {
+            float r[8];
+            bf16x8_to_f32(residual[base + c], r);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[i][j] += r[j];
+          }
+          const uint4 packed = f32_to_bf16x8(v[i]);
+          ptx::multimem_st_v4(mc_base + off_res_out + (base + c) * 16, packed);
+          bf16x8_to_f32(packed, v[i]);                            // the stream is stored in bf16: normalise what is stored
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
+        }
+      }
+      ss = block_sum(ss, scratch);
+      const float rstd = ptx::rsqrt(ss / static_cast<float>(hidden) + eps);
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * kCollThreads;
+        if (c < nvec) {
+          float w[8];
+          bf16x8_to_f32(weight[c], w);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] = v[i][j] * rstd * w[j];
+          ptx::multimem_st_v4(mc_base + p.off_out + (base + c) * 16, f32_to_bf16x8(v[i]));
+        }
+      }
+    }
+  }
+  publish_writes(p, epoch);
+  arrive_and_wait(p, p.off_flags_b, epoch, false, status);
+  tp::epoch_end(ectl, epoch);
+}
+
 __global__ void __launch_bounds__(kCollThreads) reduce_scatter_kernel(CollParams p, EpochCtl ectl, uint4* out, int64_t n_vec_per_rank,
                                                                       Status* status) {
   const uint32_t epoch = tp::epoch_begin(ectl);
@@ -189,6 +253,43 @@ __global__ void __launch_bounds__(kCollThreads) all_gather_kernel(CollParams p, 
     for (int64_t i = tid; i < n_vec; i += nthreads) {
       const uint4 v = in[i];
       for (int d = 0; d < p.tp; ++d) ptx::st_v4(p.peer[(p.rank + d) % p.tp] + p.off_out + (p.rank * n_vec + i) * 16, v);
+    }
+  }
+  publish_writes(p, epoch);
+  arrive_and_wait(p, p.off_flags_b, epoch, false, status);
+  tp::epoch_end(ectl, epoch);
+}
+
+// Link probe: every rank whose bit is set in `senders` moves `n_vec` 16-byte vectors to (push: plain stores into the
+// peer's result half, block [rank]) or from (pull: loads from the peer's input half into the local result half, block
+// [peer]) each of the peers rank + 1 ... rank + n_peers (mod tp), eight vectors in flight per thread. Flags A before and
+// B after, so the timed launch covers the delivery of every byte. This is how the NVLink figure used in the rooflines
+// of the fused kernels is measured: with the library's own peer loads and stores, not with a driver copy.
+__global__ void __launch_bounds__(kCollThreads) p2p_probe_kernel(CollParams p, EpochCtl ectl, int n_peers, uint32_t senders, int pull,
+                                                                 int64_t n_vec, int64_t block_vec, Status* status) {
+  const uint32_t epoch = tp::epoch_begin(ectl);
+  const bool ok = arrive_and_wait(p, p.off_flags_a, epoch, blockIdx.x == 0, status);
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  if (ok && ((senders >> p.rank) & 1u)) {
+    constexpr int U = 8;
+    for (int d = 1; d <= n_peers; ++d) {
+      const int peer = (p.rank + d) % p.tp;
+      const uint4* src = reinterpret_cast<const uint4*>((pull ? p.peer[peer] : p.peer[p.rank]) + p.off_buf);
+      uint4* dst = reinterpret_cast<uint4*>((pull ? p.peer[p.rank] : p.peer[peer]) + p.off_out) + (pull ? peer : p.rank) * block_vec;
+      for (int64_t i0 = tid; i0 < n_vec; i0 += nthreads * U) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int64_t i = i0 + u * nthreads;
+          if (i < n_vec) v[u] = pull ? ptx::ld_relaxed_sys_v4(src + i) : src[i];
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int64_t i = i0 + u * nthreads;
+          if (i < n_vec) ptx::st_v4(dst + i, v[u]);
+        }
+      }
     }
   }
   publish_writes(p, epoch);
@@ -330,6 +431,33 @@ extern "C" int b2_coll_all_reduce_rmsnorm_bf16(const B2TpRegion* reg, const B2Co
   return launched();
 }
 
+extern "C" int b2_coll_all_reduce_rmsnorm_nvls_bf16(const B2TpRegion* reg, const B2CollLayout* lay, void* mc_base, const void* residual,
+                                                    const void* weight, int rows, int hidden, float eps, int slot, uint64_t timeout_ns,
+                                                    Status* status, cudaStream_t stream) {
+  CollParams p{};
+  EpochCtl ectl{};
+  if (!fill(p, ectl, reg, lay, slot, timeout_ns) || rows <= 0 || hidden <= 0 || hidden % 8 != 0 || hidden > 8 * kCollThreads * 8 ||
+      weight == nullptr || mc_base == nullptr)
+    return -kBadArgument;
+  const int64_t bytes = static_cast<int64_t>(rows) * hidden * 2;
+  if (bytes > lay->buf_half_bytes || 2 * bytes > lay->out_half_bytes) return -kTooLarge;
+  const int nvec = hidden / 8;
+  const int vpt = (nvec + kCollThreads - 1) / kCollThreads;
+  const int rows_per = (rows + p.tp - 1) / p.tp;
+  const int grid = rows_per < 2 * kNumSMs ? rows_per : 2 * kNumSMs;
+  const uint4* res = static_cast<const uint4*>(residual);
+  const uint4* w = static_cast<const uint4*>(weight);
+  uint8_t* mc = static_cast<uint8_t*>(mc_base);
+  const int64_t off_res = p.off_out + bytes;
+#define B2_NVLS_NORM(V) all_reduce_rmsnorm_nvls_kernel<V><<<grid, kCollThreads, 0, stream>>>(p, ectl, mc, res, w, rows, hidden, eps, off_res, status)
+  if (vpt <= 1) B2_NVLS_NORM(1);
+  else if (vpt <= 2) B2_NVLS_NORM(2);
+  else if (vpt <= 4) B2_NVLS_NORM(4);
+  else B2_NVLS_NORM(8);
+#undef B2_NVLS_NORM
+  return launched();
+}
+
 extern "C" int b2_coll_reduce_scatter_bf16(const B2TpRegion* reg, const B2CollLayout* lay, void* out, int64_t n, int slot,
                                            uint64_t timeout_ns, Status* status, cudaStream_t stream) {
   CollParams p{};
@@ -384,5 +512,16 @@ extern "C" int b2_coll_vocab_argmax(const B2TpRegion* reg, const B2CollLayout* l
   if (static_cast<int64_t>(S) * p.tp * 8 > lay->out_half_bytes) return -kTooLarge;
   vocab_argmax_kernel<<<1, kCollThreads, 0, stream>>>(p, ectl, static_cast<const __nv_bfloat16*>(logits), ld, local_idx, tokens, S, v_local,
                                                       v_stride, status);
+  return launched();
+}
+
+extern "C" int b2_coll_p2p_probe(const B2TpRegion* reg, const B2CollLayout* lay, int64_t bytes, int n_peers, uint32_t senders, int pull,
+                                 int ctas, int slot, uint64_t timeout_ns, Status* status, cudaStream_t stream) {
+  CollParams p{};
+  EpochCtl ectl{};
+  if (!fill(p, ectl, reg, lay, slot, timeout_ns) || bytes <= 0 || bytes % 16 != 0 || n_peers < 1 || n_peers >= p.tp || ctas < 1 || ctas > 8 * kNumSMs)
+    return -kBadArgument;
+  if (bytes > lay->buf_half_bytes || bytes * p.tp > lay->out_half_bytes) return -kTooLarge;
+  p2p_probe_kernel<<<ctas, kCollThreads, 0, stream>>>(p, ectl, n_peers, senders, pull ? 1 : 0, bytes / 16, bytes / 16, status);
   return launched();
 }

@@ -210,8 +210,12 @@ class ModelRunner:
                 for m, (cfg, us, us_auto) in report[(N, K, epi)].items():
                     print(f"[autotune] N={N} K={K} epi={epi} M={m}: {ops.autotune.describe(cfg)} {us:.1f} us (rule: {us_auto:.1f} us)")
         comm = getattr(self.model, "comm", None)
-        if comm is not None and hasattr(comm, "tune_all_reduce") and hasattr(self.model, "row_parallel_shapes"):
-            # fused GEMM+all-reduce kernel or GEMM -> symmetric all-reduce kernel: whichever is faster per token count
+        if comm is not None and hasattr(comm, "tune_all_reduce_norm") and hasattr(self.model, "row_parallel_shapes"):
+            # row-parallel linear + all-reduce + residual + norm: one-shot kernel, in-switch kernel, all-reduce kernel + norm,
+            # or the fused GEMM+all-reduce kernel + norm: whichever measures fastest per token count
+            for N, K in self.model.row_parallel_shapes():
+                report[("all_reduce_norm", N, K)] = comm.tune_all_reduce_norm(N, K, [m for m in counts if m >= 8])
+        elif comm is not None and hasattr(comm, "tune_all_reduce") and hasattr(self.model, "row_parallel_shapes"):
             for N, K in self.model.row_parallel_shapes():
                 report[("all_reduce", N, K)] = comm.tune_all_reduce(N, K, [m for m in counts if m >= 8])
         torch.cuda.synchronize(self.device)

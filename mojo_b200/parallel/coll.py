@@ -24,6 +24,9 @@ from .symm import SymmRegion, _align
 
 class SymmCollectives:
     ONE_SHOT_MAX_BYTES = 256 << 10
+    # all-reduce + residual + RMSNorm: above this many bytes per rank the in-switch form (each rank reduces 1 / tp of the
+    # rows through the multicast mapping) replaces the one-shot form (each rank reads every peer's whole message)
+    NVLS_NORM_MIN_BYTES = 128 << 10
 
     def __init__(self, info: DistInfo, max_bytes: int = 8 << 20, timeout_s: float = 20.0, nvls: bool = False):
         self.info = info
@@ -103,16 +106,41 @@ class SymmCollectives:
             out = self.region.view(self.layout.off_out + slot * self.layout.out_half_bytes, (n,), torch.bfloat16)
         return out.view(*shape)
 
-    def all_reduce_rmsnorm_staged(self, shape, weight: torch.Tensor, eps: float, residual: torch.Tensor | None):
+    def all_reduce_rmsnorm_staged(self, shape, weight: torch.Tensor, eps: float, residual: torch.Tensor | None, form: str = "auto"):
         """One kernel for all-reduce + residual add + RMSNorm of the [rows, hidden] partials written into
-        `staging_view(shape)`: `residual` (bf16 [rows, hidden], updated in place; None = no residual) += sum;
-        returns (rmsnorm(residual) * weight, residual or the reduced rows)."""
+        `staging_view(shape)`: new stream = residual (bf16 [rows, hidden]; None = no residual) + sum; returns
+        (rmsnorm(new stream) * weight, new stream). The one-shot form updates `residual` in place and returns it; the
+        in-switch form (multicast mapping present, message large enough) leaves `residual` untouched and returns views
+        into the symmetric result half. Callers must use the returned stream. `form`: "one_shot", "nvls" or "auto"."""
         rows, hidden = int(shape[0]), int(shape[1])
         slot = self._slot()
+        nbytes = rows * hidden * 2
+        if form == "auto":
+            form = "nvls" if (self.mc_ptr and nbytes >= self.NVLS_NORM_MIN_BYTES and 2 * nbytes <= self.layout.out_half_bytes) else "one_shot"
+        if form == "nvls":
+            if not self.mc_ptr or 2 * nbytes > self.layout.out_half_bytes:
+                raise RuntimeError("in-switch all-reduce + norm needs a multicast mapping and room for two result tensors")
+            # in-switch reduction; the normalised rows and the new residual stream land in the symmetric result half of
+            # every rank (valid until the second collective after this one; `residual` itself is only read)
+            self.C.coll_all_reduce_rmsnorm_nvls(self.rank, self.peers, self.layout, self.mc_ptr, residual, weight, rows, eps, slot,
+                                                self.timeout_ns, self.status)
+            ops._count()
+            base = self.layout.off_out + slot * self.layout.out_half_bytes
+            return (self.region.view(base, (rows, hidden), torch.bfloat16), self.region.view(base + nbytes, (rows, hidden), torch.bfloat16))
         out = torch.empty(rows, hidden, dtype=torch.bfloat16, device=self.info.device)
         self.C.coll_all_reduce_rmsnorm(self.rank, self.peers, self.layout, residual, weight, out, eps, slot, self.timeout_ns, self.status)
         ops._count()
         return out, residual
+
+    def p2p_probe(self, nbytes: int, n_peers: int = 1, senders: int | None = None, pull: bool = False, ctas: int = 148) -> None:
+        """One launch of the link probe: every rank in the `senders` bit mask (default: all) moves `nbytes` to (push) or
+        from (pull) each of its next `n_peers` ranks with the library's own peer stores / loads. Time it with CUDA events."""
+        if self.world_size == 1:
+            return
+        senders = (1 << self.world_size) - 1 if senders is None else int(senders)
+        self.C.coll_p2p_probe(self.rank, self.peers, self.layout, int(nbytes), int(n_peers), senders, bool(pull), int(ctas), self._slot(),
+                              self.timeout_ns, self.status)
+        ops._count()
 
     def all_reduce(self, x: torch.Tensor, algo: str = "auto") -> torch.Tensor:
         if self.world_size == 1:

@@ -24,7 +24,14 @@ from .symm import SymmRegion, _align
 
 
 class FusedTPComm:
-    def __init__(self, info: DistInfo, max_tokens: int, hidden: int, max_k: int | None = None, timeout_s: float = 20.0):
+    def __init__(self, info: DistInfo, max_tokens: int, hidden: int, max_k: int | None = None, timeout_s: float = 20.0,
+                 nvls: bool | None = None):
+        """`nvls`: let the all-reduce kernels reduce inside the NVLink switch (multimem on the multicast mapping) where the
+        fabric offers one; None = yes unless the environment says B2_NVLS=0. Failure-detection tests pass False: a rank
+        that dies while its memory is bound to a multicast object can raise NVLink faults on its peers."""
+        import os
+
+        self.nvls = (os.environ.get("B2_NVLS", "1") != "0") if nvls is None else bool(nvls)
         self.info = info
         self.world_size, self.rank = info.world_size, info.rank
         self.group = info.group
@@ -71,6 +78,7 @@ class FusedTPComm:
         self._coll_bytes = max(16 << 20, self.max_tokens * hidden * 2)
         self.ar_mode = "auto"
         self._ar_table: dict = {}
+        self._norm_table: dict = {}
         self.status = _state.get(info.device).status
 
     # -- fused ops ---------------------------------------------------------------------------------
@@ -137,22 +145,102 @@ class FusedTPComm:
         ops._count()
         return self.region.view(self.layout.off_yall + slot * self.layout.yall_half_bytes, (M, N), torch.bfloat16)
 
-    # largest reduction (bytes per rank) that goes through the one-shot all-reduce + residual + RMSNorm kernel
+    # largest reduction (bytes per rank) that goes through the one-shot all-reduce + residual + RMSNorm kernel untuned
     FUSED_NORM_MAX_BYTES = 4 << 20
+    # forms of "row-parallel linear + all-reduce + residual add + RMSNorm", all NCCL-free:
+    #   oneshot_norm  GEMM -> one kernel: every rank reads all peers' partials, adds, normalises
+    #   nvls_norm     GEMM -> one kernel: in-switch reduction of 1 / tp of the rows per rank, results multicast to all ranks
+    #   split         GEMM -> all-reduce kernel (two-shot, in-switch where possible) -> norm kernel
+    #   fused         the fused GEMM + all-reduce kernel -> norm kernel
+    NORM_FORMS = ("oneshot_norm", "nvls_norm", "split", "fused")
+
+    def _norm_form_ok(self, form: str, M: int, N: int) -> bool:
+        nbytes = M * N * 2
+        if form == "fused":
+            return True
+        if nbytes > self._coll_bytes or (M * N) % 8 != 0:
+            return False
+        coll = self._collectives()
+        if form == "oneshot_norm":
+            return N % 8 == 0 and N <= 16384
+        if form == "nvls_norm":
+            return bool(coll.mc_ptr) and N % 8 == 0 and N <= 16384 and 2 * nbytes <= coll.layout.out_half_bytes
+        return (M * N) % (8 * self.world_size) == 0      # split
+
+    def _norm_form(self, M: int, N: int, K: int) -> str:
+        """Measured table first (`tune_all_reduce_norm`), else a rule: the in-switch kernel from four ranks up (below that a
+        rank's one-shot read of its peers moves no more than the in-switch form does), the one-shot kernel for small
+        messages, the split form above."""
+        if self.ar_mode == "fused":
+            return "fused"
+        table = self._norm_table.get((N, K))
+        if table:
+            for bound, form in table:
+                if M <= bound and self._norm_form_ok(form, M, N) and not (form == "fused" and self.ar_mode == "split"):
+                    return form
+        nbytes = M * N * 2
+        if self.world_size >= 4 and nbytes >= (128 << 10) and self._norm_form_ok("nvls_norm", M, N):
+            return "nvls_norm"
+        if nbytes <= self.FUSED_NORM_MAX_BYTES and self._norm_form_ok("oneshot_norm", M, N):
+            return "oneshot_norm"
+        return "split" if self._norm_form_ok("split", M, N) else "fused"
+
+    def tune_all_reduce_norm(self, N: int, K: int, token_counts, norm_weight: torch.Tensor | None = None, iters: int = 5) -> dict:
+        """Time every valid form of `linear_all_reduce_norm` at each token count (all ranks call this together; the slowest
+        rank decides) and remember the fastest. Returns {M: {form: microseconds}}."""
+        dev = self.info.device
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+        nw = norm_weight if norm_weight is not None else torch.ones(N, device=dev, dtype=torch.bfloat16)
+        report, table = {}, []
+        for M in sorted(set(int(m) for m in token_counts)):
+            x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+            res = torch.zeros(M, N, device=dev, dtype=torch.bfloat16)
+            times = {}
+            for form in self.NORM_FORMS:
+                if not self._norm_form_ok(form, M, N):
+                    continue
+                self.linear_all_reduce_norm(x, w, nw, 1e-5, res, form=form)
+                torch.cuda.synchronize(dev)
+                dist.barrier(group=self.group)
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                for _ in range(iters):
+                    self.linear_all_reduce_norm(x, w, nw, 1e-5, res, form=form)
+                e.record()
+                e.synchronize()
+                t = torch.tensor([s.elapsed_time(e) * 1e3 / iters], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+                times[form] = float(t)
+            report[M] = times
+            table.append((M, min(times, key=times.get)))
+        self._norm_table[(N, K)] = table
+        ops.check_status(dev)
+        return report
 
     def linear_all_reduce_norm(self, x: torch.Tensor, w: torch.Tensor, norm_weight: torch.Tensor, eps: float,
-                               residual: torch.Tensor):
+                               residual: torch.Tensor, form: str | None = None):
         """The row-parallel linear, its all-reduce, the residual add and the next RMSNorm:
-        residual += all_reduce(x @ w.T); returns (rmsnorm(residual) * norm_weight, residual). For decode-sized
-        token counts this is GEMM -> one kernel (all-reduce + add + norm); larger ones take `linear_all_reduce`
-        followed by the norm kernel."""
+        stream = residual + all_reduce(x @ w.T); returns (rmsnorm(stream) * norm_weight, stream). `residual` may or may
+        not be updated in place: use the returned stream. The form (see NORM_FORMS) is the measured-fastest one for this
+        token count, or a rule when nothing was measured."""
         M, N = x.shape[0], w.shape[0]
-        if (self.world_size > 1 and self.ar_mode != "fused" and M * N * 2 <= self.FUSED_NORM_MAX_BYTES and N % 8 == 0 and N <= 16384
-                and M * N * 2 <= self._coll_bytes):
+        if self.world_size == 1:
+            return ops.rms_norm(ops.linear(x, w), norm_weight, eps, residual)
+        form = form or self._norm_form(M, N, x.shape[1])
+        if form in ("oneshot_norm", "nvls_norm"):
             coll = self._collectives()
             ops.linear(x, w, out=coll.staging_view((M, N)))
-            return coll.all_reduce_rmsnorm_staged((M, N), norm_weight, eps, residual)
-        h = self.linear_all_reduce(x, w)
+            return coll.all_reduce_rmsnorm_staged((M, N), norm_weight, eps, residual, form="nvls" if form == "nvls_norm" else "one_shot")
+        if form == "split":
+            coll = self._collectives()
+            ops.linear(x, w, out=coll.staging_view((M, N)))
+            h = coll.all_reduce_staged((M, N))
+        else:
+            saved, self.ar_mode = self.ar_mode, "fused"
+            try:
+                h = self.linear_all_reduce(x, w)
+            finally:
+                self.ar_mode = saved
         return ops.rms_norm(h, norm_weight, eps, residual)
 
     def linear_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None, config: int = 0) -> torch.Tensor:
@@ -272,7 +360,7 @@ class FusedTPComm:
         if self._coll is None:
             from .coll import SymmCollectives
 
-            self._coll = SymmCollectives(self.info, max_bytes=self._coll_bytes, timeout_s=self.timeout_ns / 1e9)
+            self._coll = SymmCollectives(self.info, max_bytes=self._coll_bytes, timeout_s=self.timeout_ns / 1e9, nvls=self.nvls)
         return self._coll
 
     def all_gather_vocab(self, logits: torch.Tensor) -> torch.Tensor:

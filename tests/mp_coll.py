@@ -71,6 +71,12 @@ def main():
             torch.cuda.synchronize()
             close(res_out, want_res.to(dev), f"fused all-reduce+norm residual {rows}x{hidden}")
             close(x, want_x.to(dev), f"fused all-reduce+norm output {rows}x{hidden}")
+            # every rank must hold the same bits (greedy decoding takes the arg-max of what follows on every rank)
+            mine = torch.cat([x.reshape(-1), res_out.reshape(-1)]).view(torch.int16).to(torch.int32)
+            lo, hi = mine.clone(), mine.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+            assert torch.equal(lo, hi), f"fused all-reduce+norm {rows}x{hidden}: ranks hold different bits"
     ops.check_status(dev)
 
     # all-to-all with per-peer row counts (zero rows to some peers)
@@ -138,7 +144,7 @@ def main():
     assert coll.region.check_guard() == 0, f"rank {rank}: {coll.region.check_guard()} byte(s) of the guard band after the symmetric region were overwritten"
     dist.barrier()
     if rank == 0:
-        print(f"COLL_OK {tp}", flush=True)
+        print(f"COLL_OK {tp} nvls={int(bool(coll.mc_ptr))}", flush=True)
     from mojo_b200.parallel.dist import shutdown
 
     shutdown()

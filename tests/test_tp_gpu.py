@@ -43,10 +43,20 @@ def test_symmetric_collectives_two_gpus():
     assert "COLL_OK 2" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_symmetric_collectives_in_switch_reduction_two_gpus():
+    """The same collectives with the multicast mapping on: all-reduce and all-reduce + residual + RMSNorm reduce inside
+    the NVLink switch (multimem.ld_reduce / multimem.st). Not a failure test: every rank runs to the end."""
+    p = _run("mp_coll.py", 2, 29618, extra_env={"B2_TEST_NVLS": "1"})
+    assert "COLL_OK 2" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_symmetric_collectives_and_moe_all_gpus():
     n = 8 if torch.cuda.device_count() >= 8 else 4
     p = _run("mp_coll.py", n, 29615)
+    assert f"COLL_OK {n}" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+    p = _run("mp_coll.py", n, 29619, extra_env={"B2_TEST_NVLS": "1"})
     assert f"COLL_OK {n}" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
     p = _run("mp_ep.py", n, 29616)
     assert f"EP_OK {n}" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
