@@ -144,6 +144,9 @@ void bind_engine(py::module_& m) {
       .def("finish", &Scheduler::finish)
       .def("abort", &Scheduler::abort)
       .def("commit_step", &Scheduler::commit_step)
+      .def("set_auto_commit", &Scheduler::set_auto_commit)
+      .def("set_token", &Scheduler::set_token)
+      .def("num_tokens", &Scheduler::num_tokens)
       .def("has_unfinished", &Scheduler::has_unfinished)
       .def("num_waiting", &Scheduler::num_waiting)
       .def("num_running", &Scheduler::num_running)

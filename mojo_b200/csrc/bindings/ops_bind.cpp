@@ -107,6 +107,18 @@ void embedding(const at::Tensor& ids, const at::Tensor& table, at::Tensor& out, 
         "embedding");
 }
 
+void patch_tokens(at::Tensor& tok, const at::Tensor& rows, const at::Tensor& src, const at::Tensor& prev, int64_t n, c10::optional<at::Tensor> status) {
+  need(tok.is_cuda() && tok.scalar_type() == at::kLong && tok.is_contiguous() && prev.is_cuda() && prev.scalar_type() == at::kLong && prev.is_contiguous(),
+       "patch_tokens: tok and prev must be contiguous CUDA int64");
+  need(rows.is_cuda() && src.is_cuda() && rows.scalar_type() == at::kInt && src.scalar_type() == at::kInt && rows.is_contiguous() && src.is_contiguous() &&
+           rows.numel() >= n && src.numel() >= n,
+       "patch_tokens: rows and src must be contiguous CUDA int32 with at least n entries");
+  c10::cuda::CUDAGuard g(tok.device());
+  check(b2_patch_tokens(tok.data_ptr<int64_t>(), rows.data_ptr<int32_t>(), src.data_ptr<int32_t>(), prev.data_ptr<int64_t>(), static_cast<int>(n),
+                        tok.numel(), prev.numel(), status_ptr(status), cur_stream()),
+        "patch_tokens");
+}
+
 void gather_rows(const at::Tensor& src, const at::Tensor& index, at::Tensor& out, c10::optional<at::Tensor> status) {
   need(src.is_cuda() && is_bf16(src) && src.is_contiguous() && src.dim() == 2 && out.is_contiguous() && is_bf16(out), "gather_rows: bf16 contiguous 2-D required");
   need(index.scalar_type() == at::kLong && index.is_contiguous(), "gather_rows: index must be int64");
@@ -231,7 +243,8 @@ void attn_prefill_tc(const at::Tensor& q, const at::Tensor& k_cache, const at::T
 
 void attn_decode(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache, at::Tensor& out,
                  const at::Tensor& ctx_lens, const at::Tensor& block_tables, c10::optional<at::Tensor> workspace,
-                 int64_t head_dim, int64_t num_splits, double scale, c10::optional<at::Tensor> status) {
+                 int64_t head_dim, int64_t num_splits, double scale, c10::optional<at::Tensor> status,
+                 c10::optional<at::Tensor> counters) {
   check_cache(q, k_cache, v_cache, head_dim);
   need(out.dim() == 2 && out.stride(1) == 1 && is_bf16(out) && out.size(0) == q.size(0), "attention: bad out");
   need(ctx_lens.scalar_type() == at::kInt && block_tables.scalar_type() == at::kInt && block_tables.dim() == 2 && block_tables.is_contiguous(), "attention: metadata must be contiguous int32");
@@ -244,12 +257,18 @@ void attn_decode(const at::Tensor& q, const at::Tensor& k_cache, const at::Tenso
     need(workspace->numel() * 4 >= b2_attn_decode_workspace(batch, n_q, static_cast<int>(head_dim), static_cast<int>(num_splits)), "attention: workspace too small");
     ws = workspace->data_ptr<float>();
   }
+  uint32_t* cnt = nullptr;
+  if (num_splits > 1 && counters.has_value()) {
+    need(counters->is_cuda() && counters->scalar_type() == at::kInt && counters->is_contiguous(), "attention: split counters must be a contiguous CUDA int32 tensor");
+    if (counters->numel() * 4 >= b2_attn_decode_counter_bytes(batch, static_cast<int>(k_cache.size(1))))
+      cnt = reinterpret_cast<uint32_t*>(counters->data_ptr());
+  }
   c10::cuda::CUDAGuard g(q.device());
   check(b2_attn_decode_bf16(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), ctx_lens.data_ptr<int32_t>(),
                             block_tables.data_ptr<int32_t>(), ws, batch, static_cast<int>(block_tables.size(1)), n_q,
                             static_cast<int>(k_cache.size(1)), static_cast<int>(head_dim), static_cast<int>(k_cache.size(2)),
                             static_cast<int>(num_splits), static_cast<float>(scale), q.stride(0), out.stride(0),
-                            k_cache.size(0), status_ptr(status), cur_stream()),
+                            k_cache.size(0), cnt, status_ptr(status), cur_stream()),
         "attn_decode");
 }
 
@@ -306,6 +325,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("status") = py::none());
   m.def("swiglu", &swiglu, py::arg("gate_up"), py::arg("out"), py::arg("interleaved") = false);
   m.def("embedding", &embedding, py::arg("ids"), py::arg("table"), py::arg("out"), py::arg("vocab_start") = 0);
+  m.def("patch_tokens", &patch_tokens, py::arg("tok"), py::arg("rows"), py::arg("src"), py::arg("prev"), py::arg("n"), py::arg("status") = py::none());
   m.def("gather_rows", &gather_rows, py::arg("src"), py::arg("index"), py::arg("out"), py::arg("status") = py::none());
   m.def("scatter_rows", &scatter_rows, py::arg("src"), py::arg("slots"), py::arg("dst"), py::arg("status") = py::none());
   m.def("copy_pages", &copy_pages, py::arg("cache"), py::arg("src_pages"), py::arg("dst_pages"), py::arg("status") = py::none());
@@ -321,7 +341,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("status") = py::none(), py::arg("work") = py::none(), py::arg("n_work") = py::none(), py::arg("work_items") = 0);
   m.def("attn_decode", &attn_decode, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("out"), py::arg("ctx_lens"),
         py::arg("block_tables"), py::arg("workspace"), py::arg("head_dim"), py::arg("num_splits"), py::arg("scale"),
-        py::arg("status") = py::none());
+        py::arg("status") = py::none(), py::arg("counters") = py::none());
   m.def("gemm_bf16", &gemm_bf16, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("residual") = py::none(),
         py::arg("epilogue") = 0, py::arg("config") = 0, py::arg("workspace") = py::none(), py::arg("status") = py::none());
   m.def("gemm_workspace_bytes", [](int M, int N, int K) { return b2_gemm_workspace_bytes(M, N, K); });

@@ -62,10 +62,11 @@ void bind_ops_extra(py::module_& m) {
   m.def("tp_gemm_rs",
         [](const at::Tensor& x, const at::Tensor& w, int rank, const std::vector<int64_t>& peers, const B2TpLayout& lay,
            c10::optional<at::Tensor> out, c10::optional<at::Tensor> residual, int mode, int slot, uint64_t timeout_ns,
-           int config, c10::optional<at::Tensor> status) {
+           int config, c10::optional<at::Tensor> status, int64_t mc_base) {
           need(is_bf16_2d(x) && is_bf16_2d(w) && x.size(1) == w.size(1), "tp_gemm_rs: x [M, K/tp], w [N, K/tp] bf16");
           const int M = static_cast<int>(x.size(0)), K = static_cast<int>(x.size(1)), N = static_cast<int>(w.size(0));
-          const B2TpRegion reg = make_region(rank, peers);
+          B2TpRegion reg = make_region(rank, peers);
+          reg.mc_base = reinterpret_cast<void*>(mc_base);   // multicast mapping of the region: the reduction runs in the switch
           if (mode == 0) need(out.has_value() && is_bf16_2d(*out) && out->is_contiguous() && out->size(0) * reg.tp == M && out->size(1) == N, "tp_gemm_rs: out must be contiguous [M/tp, N]");
           if (residual.has_value()) need(is_bf16_2d(*residual) && residual->is_contiguous() && residual->size(1) == N, "tp_gemm_rs: residual must be contiguous [rows, N]");
           c10::cuda::CUDAGuard g(x.device());
@@ -75,7 +76,7 @@ void bind_ops_extra(py::module_& m) {
                 "tp_gemm_rs");
         },
         py::arg("x"), py::arg("w"), py::arg("rank"), py::arg("peers"), py::arg("layout"), py::arg("out"), py::arg("residual"),
-        py::arg("mode"), py::arg("slot"), py::arg("timeout_ns"), py::arg("config") = 0, py::arg("status") = py::none());
+        py::arg("mode"), py::arg("slot"), py::arg("timeout_ns"), py::arg("config") = 0, py::arg("status") = py::none(), py::arg("mc_base") = 0);
 
   m.def("tp_gemm_rs_fp8",
         [](const at::Tensor& xq, const at::Tensor& xs, const at::Tensor& wq, const at::Tensor& ws, int rank,

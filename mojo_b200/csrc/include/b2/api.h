@@ -33,6 +33,10 @@ int b2_rope_kvwrite_bf16(void* q, void* k, const void* v, const float* cos_sin, 
 // out[t, j] = silu(gate_up[t, j]) * gate_up[t, F + j]
 int b2_swiglu_bf16(const void* gate_up, void* out, int rows, int ffn, int interleaved, cudaStream_t stream);
 // out[t, :] = table[ids[t] - vocab_start, :] for ids inside [vocab_start, vocab_start + vocab_rows), else 0.
+// tok[rows[i]] = prev[src[i]], i < n (int32 row / source indices, int64 token ids): feeds the tokens sampled by the
+// previous step straight into the next step's input while the host is still one step behind.
+int b2_patch_tokens(int64_t* tok, const int32_t* rows, const int32_t* src, const int64_t* prev, int n, int64_t tok_rows,
+                    int64_t prev_rows, b2::Status* status, cudaStream_t stream);
 int b2_embedding_bf16(const int64_t* ids, const void* table, void* out, int tokens, int hidden, int64_t vocab_start,
                       int64_t vocab_rows, cudaStream_t stream);
 // out[i, :] = src[index[i], :] (row gather, 16-byte vectorised; used for last-token selection).
@@ -74,10 +78,14 @@ int b2_attn_prefill_tc_bf16(const void* q, const void* k_cache, const void* v_ca
                             int64_t num_pages, int variant, const int32_t* work, const int32_t* n_work, int work_items,
                             b2::Status* status, cudaStream_t stream);
 // One query token per sequence, split over the KV length. workspace: f32, size from b2_attn_decode_workspace.
+// `counters` (may be null): u32 [batch * n_kv], zero before the first use and left at zero by every launch; with it
+// (and page sizes that are multiples of 32) the split that finishes last merges the partials itself, otherwise a
+// second small kernel does.
 int b2_attn_decode_bf16(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* ctx_lens,
                         const int32_t* block_tables, float* workspace, int batch, int max_blocks, int n_q, int n_kv,
                         int head_dim, int page_size, int num_splits, float scale, int64_t q_stride,
-                        int64_t out_stride, int64_t num_pages, b2::Status* status, cudaStream_t stream);
+                        int64_t out_stride, int64_t num_pages, uint32_t* counters, b2::Status* status, cudaStream_t stream);
+int64_t b2_attn_decode_counter_bytes(int batch, int n_kv);
 int64_t b2_attn_decode_workspace(int batch, int n_q, int head_dim, int num_splits);
 // MLA decode with absorbed weights: q_lat [B, H, 512], q_rope [B, H, 64]; cache [num_pages, page, 576]
 // (512 latent + 64 rope); out_lat [B, H, 512].

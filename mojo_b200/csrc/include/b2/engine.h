@@ -138,12 +138,20 @@ class Scheduler {
   // Record the token sampled for a sequence after the step. Returns true when the sequence hit
   // max_new_tokens (the caller may also finish it earlier, e.g. on EOS or a stop string).
   bool append_token(int64_t id, int32_t token);
+  // Pipelined engines append a placeholder (-1) when a step is launched and fill in the sampled token one step later:
+  // `set_token` overwrites position `pos` of the sequence (false if the request is gone or `pos` is out of range);
+  // `num_tokens` is the current length (prompt + generated, placeholders included; -1 for an unknown request).
+  bool set_token(int64_t id, int64_t pos, int32_t token);
+  int64_t num_tokens(int64_t id) const;
   void finish(int64_t id);
   void abort(int64_t id) { finish(id); }
   // Register the full pages written by the last batch in the prefix cache. The engine calls it when the step has
   // completed; `step()` calls it for the previous batch as well. A sequence that is finished, aborted or preempted
   // before that keeps no entry for the unconfirmed step, so a failed step cannot leave half-written pages shared.
   void commit_step();
+  // With auto-commit off, `step()` no longer confirms earlier batches: every `commit_step()` confirms the oldest
+  // unconfirmed batch, in launch order (engines that schedule one step ahead of the device).
+  void set_auto_commit(bool on) { auto_commit_ = on; }
 
   bool has_unfinished() const { return !waiting_.empty() || !running_.empty(); }
   int64_t num_waiting() const { return static_cast<int64_t>(waiting_.size()); }
@@ -162,7 +170,8 @@ class Scheduler {
   std::deque<int64_t> waiting_;
   std::vector<int64_t> running_;  // admission order
   int64_t total_preemptions_ = 0;
-  std::vector<std::pair<int64_t, int64_t>> pending_commits_;  // (sequence, tokens computed) of the batch in flight
+  std::deque<std::vector<std::pair<int64_t, int64_t>>> pending_commits_;  // per unconfirmed batch: (sequence, tokens computed)
+  bool auto_commit_ = true;
 };
 
 }  // namespace engine

@@ -137,6 +137,9 @@ __device__ __forceinline__ void run(const CUtensorMap* tmap_p, const CUtensorMap
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder_ptr;
+  // Everything above touched only shared memory, TMEM and the kernel's own parameters: under a programmatic dependent
+  // launch it ran while the previous kernel was finishing. Operands, gates and outputs are global memory: wait here.
+  ptx::grid_dep_sync();
 
   const int total = sched.total();
 

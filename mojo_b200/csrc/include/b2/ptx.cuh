@@ -498,6 +498,18 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t a_fmt, uint32_t b_fmt
 }
 
 // ----------------------------------------------------------------------------------------------
+// Programmatic dependent launch (see b2/launch.h). `grid_dep_wait` returns once every kernel this one was launched
+// behind has completed and its memory operations are visible (a no-op under an ordinary launch);
+// `grid_dep_launch` allows the kernel launched behind this one to be scheduled.
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_sync() {
+  grid_dep_wait();
+  grid_dep_launch();
+}
+
+// ----------------------------------------------------------------------------------------------
 // multimem (NVLS): the address is a multicast mapping bound on every GPU of the group.
 // ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {

@@ -15,6 +15,7 @@ extern "C" {
 struct B2TpRegion {
   int rank, tp;
   void* peer[8];
+  void* mc_base;   // multicast (NVLS) mapping of the same region on all ranks, or null: kernels that can reduce in the switch use it
 };
 
 struct B2TpLayout {

@@ -56,6 +56,12 @@ struct RsParams {
   uint64_t timeout_ns;
   int64_t region_bytes;    // size of every rank's symmetric region: accesses into it are checked against this bound
   Status* status;          // where a failed bounds check is recorded (the access is skipped)
+  // In-switch reduction (NVLS): with a multicast mapping of the region, a rank keeps its partial tiles in its OWN staging
+  // half, laid out like the result ([M][N] bf16), and only raises the owner's flag; the owner then reads each 16-byte
+  // vector of its rows once with multimem.ld_reduce, which returns the sum over all ranks (added in f32 inside the
+  // switch). NVLink carries each partial byte once, pulled, and the owner issues one load where the peer-store form
+  // issues tp. All-reduce mode stores the result with one multimem.st instead of tp peer stores. Null: peer-store form.
+  uint8_t* mc_base;
 };
 
 // Bounds check of a 16-byte access at byte offset `off` of a symmetric region; `what` names the access in the record.
@@ -88,13 +94,16 @@ struct RsEpilogue {
   uint8_t* epi_smem;
 
   __device__ __forceinline__ __nv_bfloat16* staging_row(int m) const {
+    if (p.mc_base != nullptr)   // in-switch form: the partial stays here, at its place in the [M][N] result
+      return reinterpret_cast<__nv_bfloat16*>(p.peer[p.rank] + p.off_staging) + static_cast<int64_t>(m) * p.N;
     const int owner = m / p.R;
     return reinterpret_cast<__nv_bfloat16*>(p.peer[owner] + p.off_staging) +
            (static_cast<int64_t>(p.rank) * p.R + (m - owner * p.R)) * p.N;
   }
 
-  // byte offset inside the owner's region of column n of row m as written by this rank
+  // byte offset inside the (owner's, or with in-switch reduction this rank's) region of column n of row m as written by this rank
   __device__ __forceinline__ int64_t staging_off(int m, int n) const {
+    if (p.mc_base != nullptr) return p.off_staging + (static_cast<int64_t>(m) * p.N + n) * 2;
     const int owner = m / p.R;
     return p.off_staging + ((static_cast<int64_t>(p.rank) * p.R + (m - owner * p.R)) * p.N + n) * 2;
   }
@@ -246,6 +255,45 @@ __device__ inline bool reduce_phase(const RsParams& p, Status* status) {
     const int c_lo = tn * TN, c_hi = min(p.N, tn * TN + TN);
     const int vec_per_row = (c_hi - c_lo) >> 3;
     const int n_vec = (r_hi - r_lo) * vec_per_row;
+    if (p.mc_base != nullptr) {
+      // in-switch form: one multimem.ld_reduce per 16-byte vector returns the sum of all ranks' partials
+      constexpr int UN = 8;
+      for (int i0 = Team::tid(); i0 < n_vec; i0 += Team::size() * UN) {
+        uint4 sum[UN];
+        int64_t el[UN];   // element offset of the vector in the [M][N] result
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+          const int i = i0 + u * Team::size();
+          const int m = r_lo + (i < n_vec ? i / vec_per_row : 0);
+          const int col = c_lo + (i < n_vec ? (i % vec_per_row) * 8 : 0);
+          el[u] = static_cast<int64_t>(m) * p.N + col;
+          if (i < n_vec && rs_in_region(p, p.off_staging + el[u] * 2, 3)) sum[u] = ptx::multimem_ld_reduce_bf16x8(p.mc_base + p.off_staging + el[u] * 2);
+          else sum[u] = make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+          const int i = i0 + u * Team::size();
+          if (i >= n_vec) continue;
+          uint4 pk = sum[u];
+          const int m = static_cast<int>(el[u] / p.N);
+          const int col = static_cast<int>(el[u] - static_cast<int64_t>(m) * p.N);
+          if (p.residual != nullptr) {
+            float acc[8], v[8];
+            bf16x8_to_f32(pk, acc);
+            const int64_t rrow = p.mode == 0 ? m - row0 : m;
+            bf16x8_to_f32(ptx::ld_v4(p.residual + rrow * p.N + col), v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += v[j];
+            pk = f32_to_bf16x8(acc);
+          }
+          if (p.mode == 0) {
+            ptx::st_v4(p.out + static_cast<int64_t>(m - row0) * p.N + col, pk);
+          } else if (rs_in_region(p, p.off_yall + el[u] * 2, 4)) {
+            ptx::multimem_st_v4(p.mc_base + p.off_yall + el[u] * 2, pk);   // the switch writes every rank's copy
+          }
+        }
+      }
+    } else {
     constexpr int U = 4;  // independent 16-byte vectors per thread per pass: keeps tp * U loads in flight
     for (int i0 = Team::tid(); i0 < n_vec; i0 += Team::size() * U) {
       uint4 raw[U][kMaxTp];
@@ -299,6 +347,7 @@ __device__ inline bool reduce_phase(const RsParams& p, Status* status) {
           }
         }
       }
+    }
     }
     if (p.mode == 1) {
       __threadfence_system();

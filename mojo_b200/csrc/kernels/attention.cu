@@ -209,6 +209,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
     const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ cu_q,
     const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ block_tables, int max_blocks, int n_q, int n_kv,
     int page_size, float scale_log2, int64_t q_stride, int64_t out_stride, int64_t num_pages, Status* status) {
+  ptx::grid_dep_sync();
   constexpr int BM = 64, BN = 64;
   constexpr int TILE_BYTES = BN * D * 2;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -300,6 +301,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
     const int32_t* __restrict__ block_tables, float* __restrict__ workspace, int max_blocks, int n_q, int n_kv,
     int page_size, int num_splits, float scale_log2, int64_t q_stride, int64_t out_stride, int64_t num_pages,
     Status* status) {
+  ptx::grid_dep_sync();
   constexpr int BN = 32;
   constexpr int TILE_BYTES = BN * D * 2;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -426,7 +428,8 @@ __global__ void __launch_bounds__(32) attn_decode_tma_kernel(
     const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ ctx_lens,
     const int32_t* __restrict__ block_tables, float* __restrict__ workspace, int max_blocks, int n_q, int n_kv,
     int page_size, int num_splits, float scale_log2, int64_t q_stride, int64_t out_stride, int64_t num_pages,
-    Status* status) {
+    uint32_t* __restrict__ split_counters, Status* status) {
+  ptx::grid_dep_sync();
   constexpr int BN = 32;
   constexpr int HALVES = D / 64;
   constexpr int SUB_BYTES = BN * 128;              // one [32][64] box
@@ -544,12 +547,47 @@ __global__ void __launch_bounds__(32) attn_decode_tma_kernel(
       }
     }
   }
+  if (num_splits > 1 && split_counters != nullptr) {
+    // The split that finishes last merges the partials of its (sequence, kv head): no second launch. Its own stores
+    // and the others' are ordered by the fence on each side of the counter.
+    __threadfence();
+    __syncwarp();
+    uint32_t old = 0;
+    if (lane == 0) old = atomicAdd(split_counters + static_cast<int64_t>(seq) * n_kv + kvh, 1u);
+    old = __shfl_sync(0xffffffffu, old, 0);
+    if (old != static_cast<uint32_t>(num_splits - 1)) return;
+    if (lane == 0) split_counters[static_cast<int64_t>(seq) * n_kv + kvh] = 0;   // ready for the next launch
+    __threadfence();
+    constexpr int RS = D + 2;
+    for (int row = 0; row < group; ++row) {
+      const int head = kvh * group + row;
+      const float* base = workspace + (static_cast<int64_t>(seq) * n_q + head) * num_splits * RS;
+      float mm = -INFINITY;
+      for (int sp = 0; sp < num_splits; ++sp) mm = fmaxf(mm, __ldcg(base + sp * RS + D));
+      const float sub = mm == -INFINITY ? 0.0f : mm;
+      float ll = 0.0f;
+      float acc[D / 32];
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) acc[c] = 0.0f;
+      for (int sp = 0; sp < num_splits; ++sp) {
+        const float f = ptx::ex2(__ldcg(base + sp * RS + D) - sub);
+        ll += __ldcg(base + sp * RS + D + 1) * f;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) acc[c] += __ldcg(base + sp * RS + c * 32 + lane) * f;
+      }
+      const float inv = ll > 0.0f ? 1.0f / ll : 0.0f;
+      __nv_bfloat16* dst = out + static_cast<int64_t>(seq) * out_stride + static_cast<int64_t>(head) * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) dst[c * 32 + lane] = __float2bfloat16(acc[c] * inv);
+    }
+  }
 }
 
 // Merge split partials: one warp per (sequence, head).
 template <int D>
 __global__ void attn_decode_reduce_kernel(const float* __restrict__ workspace, __nv_bfloat16* __restrict__ out,
                                           int n_q, int num_splits, int64_t out_stride, int total) {
+  ptx::grid_dep_sync();
   constexpr int RS = D + 2;
   const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -599,14 +637,14 @@ extern "C" int b2_attn_prefill_bf16(const void* q, const void* k_cache, const vo
     constexpr int SMEM = 4 * 16 * 128 * 2 + 4 * 64 * 128 * 2;
     static DeviceOnce attr_once;
     if (const int rc = attr_once.run([&] { return cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); })) return rc;
-    attn_prefill_kernel<128><<<grid, 128, SMEM, stream>>>(qp, kp, vp, op, cu_q, ctx_lens, block_tables, max_blocks, n_q,
+    launch_pdl(attn_prefill_kernel<128>, dim3(grid), dim3(128), SMEM, stream, qp, kp, vp, op, cu_q, ctx_lens, block_tables, max_blocks, n_q,
                                                           n_kv, page_size, scale_log2, q_stride, out_stride, num_pages,
                                                           status);
   } else {
     constexpr int SMEM = 4 * 16 * 64 * 2 + 4 * 64 * 64 * 2;
     static DeviceOnce attr_once;
     if (const int rc = attr_once.run([&] { return cudaFuncSetAttribute(attn_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); })) return rc;
-    attn_prefill_kernel<64><<<grid, 128, SMEM, stream>>>(qp, kp, vp, op, cu_q, ctx_lens, block_tables, max_blocks, n_q,
+    launch_pdl(attn_prefill_kernel<64>, dim3(grid), dim3(128), SMEM, stream, qp, kp, vp, op, cu_q, ctx_lens, block_tables, max_blocks, n_q,
                                                          n_kv, page_size, scale_log2, q_stride, out_stride, num_pages,
                                                          status);
   }
@@ -617,11 +655,15 @@ extern "C" int64_t b2_attn_decode_workspace(int batch, int n_q, int head_dim, in
   return static_cast<int64_t>(batch) * n_q * num_splits * (head_dim + 2) * 4;
 }
 
+// Split decode on the TMA path merges its partials in the split that finishes last, counted per (sequence, kv head) in
+// `counters` (u32, zero before the first launch; every launch leaves them at zero). Bytes needed for `batch` sequences:
+extern "C" int64_t b2_attn_decode_counter_bytes(int batch, int n_kv) { return static_cast<int64_t>(batch) * n_kv * 4; }
+
 extern "C" int b2_attn_decode_bf16(const void* q, const void* k_cache, const void* v_cache, void* out,
                                    const int32_t* ctx_lens, const int32_t* block_tables, float* workspace, int batch,
                                    int max_blocks, int n_q, int n_kv, int head_dim, int page_size, int num_splits,
                                    float scale, int64_t q_stride, int64_t out_stride, int64_t num_pages,
-                                   Status* status, cudaStream_t stream) {
+                                   uint32_t* counters, Status* status, cudaStream_t stream) {
   if (batch <= 0) return 0;
   if (n_kv <= 0 || n_q % n_kv != 0 || n_q / n_kv > 16 || (head_dim != 128 && head_dim != 64) || q_stride % 8 != 0 ||
       num_splits < 1 || (num_splits > 1 && workspace == nullptr))
@@ -645,20 +687,20 @@ extern "C" int b2_attn_decode_bf16(const void* q, const void* k_cache, const voi
       constexpr int SMEM = STAGES * 2 * 32 * 128 * 2 + 16 * 128 * 2 + 64 + 1024;
       static DeviceOnce attr_once;
     if (const int rc = attr_once.run([&] { return cudaFuncSetAttribute(attn_decode_tma_kernel<128, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); })) return rc;
-      attn_decode_tma_kernel<128, STAGES><<<grid, 32, SMEM, stream>>>(tk, tv, qp, op, ctx_lens, block_tables, workspace, max_blocks,
+      launch_pdl(attn_decode_tma_kernel<128, STAGES>, dim3(grid), dim3(32), SMEM, stream, tk, tv, qp, op, ctx_lens, block_tables, workspace, max_blocks,
                                                                     n_q, n_kv, page_size, num_splits, scale_log2, q_stride,
-                                                                    out_stride, num_pages, status);
-      if (num_splits > 1)
-        attn_decode_reduce_kernel<128><<<(total + 3) / 4, 128, 0, stream>>>(workspace, op, n_q, num_splits, out_stride, total);
+                                                                    out_stride, num_pages, counters, status);
+      if (num_splits > 1 && counters == nullptr)
+        launch_pdl(attn_decode_reduce_kernel<128>, dim3((total + 3) / 4), dim3(128), 0, stream, workspace, op, n_q, num_splits, out_stride, total);
     } else {
       constexpr int SMEM = STAGES * 2 * 32 * 64 * 2 + 16 * 64 * 2 + 64 + 1024;
       static DeviceOnce attr_once;
     if (const int rc = attr_once.run([&] { return cudaFuncSetAttribute(attn_decode_tma_kernel<64, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); })) return rc;
-      attn_decode_tma_kernel<64, STAGES><<<grid, 32, SMEM, stream>>>(tk, tv, qp, op, ctx_lens, block_tables, workspace, max_blocks,
+      launch_pdl(attn_decode_tma_kernel<64, STAGES>, dim3(grid), dim3(32), SMEM, stream, tk, tv, qp, op, ctx_lens, block_tables, workspace, max_blocks,
                                                                    n_q, n_kv, page_size, num_splits, scale_log2, q_stride,
-                                                                   out_stride, num_pages, status);
-      if (num_splits > 1)
-        attn_decode_reduce_kernel<64><<<(total + 3) / 4, 128, 0, stream>>>(workspace, op, n_q, num_splits, out_stride, total);
+                                                                    out_stride, num_pages, counters, status);
+      if (num_splits > 1 && counters == nullptr)
+        launch_pdl(attn_decode_reduce_kernel<64>, dim3((total + 3) / 4), dim3(128), 0, stream, workspace, op, n_q, num_splits, out_stride, total);
     }
     return last_launch_rc();
   }
@@ -666,20 +708,20 @@ extern "C" int b2_attn_decode_bf16(const void* q, const void* k_cache, const voi
     constexpr int SMEM = 4 * (16 * 128 * 2 + 4 * 32 * 128 * 2);
     static DeviceOnce attr_once;
     if (const int rc = attr_once.run([&] { return cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); })) return rc;
-    attn_decode_kernel<128><<<grid, 128, SMEM, stream>>>(qp, kp, vp, op, ctx_lens, block_tables, workspace, max_blocks,
+    launch_pdl(attn_decode_kernel<128>, dim3(grid), dim3(128), SMEM, stream, qp, kp, vp, op, ctx_lens, block_tables, workspace, max_blocks,
                                                          n_q, n_kv, page_size, num_splits, scale_log2, q_stride,
                                                          out_stride, num_pages, status);
     if (num_splits > 1)
-      attn_decode_reduce_kernel<128><<<(total + 3) / 4, 128, 0, stream>>>(workspace, op, n_q, num_splits, out_stride, total);
+      launch_pdl(attn_decode_reduce_kernel<128>, dim3((total + 3) / 4), dim3(128), 0, stream, workspace, op, n_q, num_splits, out_stride, total);
   } else {
     constexpr int SMEM = 4 * (16 * 64 * 2 + 4 * 32 * 64 * 2);
     static DeviceOnce attr_once;
     if (const int rc = attr_once.run([&] { return cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); })) return rc;
-    attn_decode_kernel<64><<<grid, 128, SMEM, stream>>>(qp, kp, vp, op, ctx_lens, block_tables, workspace, max_blocks,
+    launch_pdl(attn_decode_kernel<64>, dim3(grid), dim3(128), SMEM, stream, qp, kp, vp, op, ctx_lens, block_tables, workspace, max_blocks,
                                                         n_q, n_kv, page_size, num_splits, scale_log2, q_stride,
                                                         out_stride, num_pages, status);
     if (num_splits > 1)
-      attn_decode_reduce_kernel<64><<<(total + 3) / 4, 128, 0, stream>>>(workspace, op, n_q, num_splits, out_stride, total);
+      launch_pdl(attn_decode_reduce_kernel<64>, dim3((total + 3) / 4), dim3(128), 0, stream, workspace, op, n_q, num_splits, out_stride, total);
   }
   return last_launch_rc();
 }

@@ -84,6 +84,7 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
 __global__ void __launch_bounds__(kThreadsAttn, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_v, AttnTcParams prm, Status* status) {
+  ptx::grid_dep_sync();
   int seq = blockIdx.z, qt = blockIdx.x;
   const int head = blockIdx.y;
   if (prm.work != nullptr) {
@@ -431,6 +432,6 @@ extern "C" int b2_attn_prefill_tc_bf16(const void* q, const void* k_cache, const
     return rc;
   dim3 grid((max_q_len + kTile - 1) / kTile, n_q, batch);
   if (work != nullptr) grid = dim3(work_items, n_q, 1);
-  attn_prefill_tc_kernel<<<grid, kThreadsAttn, kSmemAttn, stream>>>(tq, tk, tv, prm, status);
+  launch_pdl(attn_prefill_tc_kernel, dim3(grid), dim3(kThreadsAttn), kSmemAttn, stream, tq, tk, tv, prm, status);
   return last_launch_rc();
 }

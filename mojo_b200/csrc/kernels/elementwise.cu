@@ -5,6 +5,7 @@
 #include <cstdint>
 #include <cuda_bf16.h>
 #include "b2/api.h"
+#include "b2/launch.h"
 #include "b2/ptx.cuh"
 #include "b2/vec.cuh"
 
@@ -18,6 +19,7 @@ template <int VPT, bool QUANT>
 __global__ void rmsnorm_kernel(const uint4* __restrict__ x, uint4* __restrict__ residual,
                                const uint4* __restrict__ weight, uint4* __restrict__ out,
                                uint8_t* __restrict__ q_out, float* __restrict__ q_scale, int hidden, float eps) {
+  ptx::grid_dep_sync();
   __shared__ float scratch[33];
   const int row = blockIdx.x;
   const int nvec = hidden >> 3;
@@ -87,6 +89,7 @@ __global__ void rmsnorm_kernel(const uint4* __restrict__ x, uint4* __restrict__ 
 
 __global__ void quant_e4m3_1x128_kernel(const uint4* __restrict__ x, uint8_t* __restrict__ q_out,
                                         float* __restrict__ scale_out, int rows, int cols) {
+  ptx::grid_dep_sync();
   // One half-warp (16 lanes x 8 elements) per 128-column group.
   const int groups_per_row = cols >> 7;
   const int64_t gid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
@@ -128,6 +131,7 @@ __global__ void rope_kvwrite_kernel(__nv_bfloat16* __restrict__ q, __nv_bfloat16
                                     int n_kv, int head_dim, int rot_dim, int interleaved, int64_t q_stride,
                                     int64_t k_stride, int64_t v_stride, int page_size, int64_t num_slots, int max_pos,
                                     Status* status) {
+  ptx::grid_dep_sync();
   const int t = blockIdx.x;
   int pos = positions[t];
   if (!B2_ASSERT(status, pos >= 0 && pos < max_pos, kSiteKvIndex, pos, max_pos)) pos = 0;
@@ -217,6 +221,7 @@ __global__ void rope_kvwrite_kernel(__nv_bfloat16* __restrict__ q, __nv_bfloat16
 // interleaved = false: row = [gate (ffn) | up (ffn)]. interleaved = true: alternating blocks of 16 gate and 16 up
 // columns (the output of a plain GEMM against a weight stacked for the SwiGLU GEMM epilogue).
 __global__ void swiglu_kernel(const uint4* __restrict__ gate_up, uint4* __restrict__ out, int rows, int ffn_vecs, bool interleaved) {
+  ptx::grid_dep_sync();
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t total = static_cast<int64_t>(rows) * ffn_vecs;
   if (idx >= total) return;
@@ -232,8 +237,21 @@ __global__ void swiglu_kernel(const uint4* __restrict__ gate_up, uint4* __restri
   out[idx] = f32_to_bf16x8(o);
 }
 
+// tok[rows[i]] = prev[src[i]] for i < n: the input token of a decode row is the token the previous step sampled for that
+// sequence, still on the device when the next step is staged (the host reads it one step later).
+__global__ void patch_tokens_kernel(int64_t* __restrict__ tok, const int32_t* __restrict__ rows, const int32_t* __restrict__ src,
+                                    const int64_t* __restrict__ prev, int n, int64_t tok_rows, int64_t prev_rows, Status* status) {
+  ptx::grid_dep_sync();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t r = rows[i], s2 = src[i];
+  if (!B2_ASSERT(status, r >= 0 && r < tok_rows && s2 >= 0 && s2 < prev_rows, kSiteSampling, r, s2)) return;
+  tok[r] = prev[s2];
+}
+
 __global__ void embedding_kernel(const int64_t* __restrict__ ids, const uint4* __restrict__ table,
                                  uint4* __restrict__ out, int hidden_vecs, int64_t vocab_start, int64_t vocab_rows) {
+  ptx::grid_dep_sync();
   const int t = blockIdx.x;
   const int64_t id = ids[t] - vocab_start;
   const bool inside = id >= 0 && id < vocab_rows;
@@ -246,6 +264,7 @@ __global__ void embedding_kernel(const int64_t* __restrict__ ids, const uint4* _
 
 __global__ void gather_rows_kernel(const uint4* __restrict__ src, const int64_t* __restrict__ index,
                                    uint4* __restrict__ out, int col_vecs, int64_t rows_src, Status* status) {
+  ptx::grid_dep_sync();
   const int r = blockIdx.x;
   const int64_t s = index[r];
   if (!B2_ASSERT(status, s >= 0 && s < rows_src, kSiteKvIndex, s, rows_src)) return;
@@ -255,6 +274,7 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ src, const int64_t*
 
 __global__ void scatter_rows_kernel(const uint4* __restrict__ src, const int64_t* __restrict__ slots, uint4* __restrict__ dst,
                                     int col_vecs, int64_t rows_dst, Status* status) {
+  ptx::grid_dep_sync();
   const int r = blockIdx.x;
   const int64_t d = slots[r];
   if (d < 0) return;  // padding row
@@ -265,6 +285,7 @@ __global__ void scatter_rows_kernel(const uint4* __restrict__ src, const int64_t
 __global__ void copy_pages_kernel(uint4* __restrict__ cache, const int64_t* __restrict__ src_pages,
                                   const int64_t* __restrict__ dst_pages, int64_t page_vecs, int64_t num_pages,
                                   Status* status) {
+  ptx::grid_dep_sync();
   const int64_t s = src_pages[blockIdx.y], d = dst_pages[blockIdx.y];
   if (!B2_ASSERT(status, s >= 0 && s < num_pages && d >= 0 && d < num_pages, kSiteKvIndex, s, d)) return;
   for (int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < page_vecs;
@@ -286,10 +307,10 @@ int launch_rmsnorm(const void* x, void* residual, const void* weight, void* out,
   auto op = static_cast<uint4*>(out);
   auto qp = static_cast<uint8_t*>(q_out);
   switch (vpt) {
-    case 1: rmsnorm_kernel<1, QUANT><<<rows, threads, 0, stream>>>(xp, rp, wp, op, qp, q_scale, hidden, eps); break;
-    case 2: rmsnorm_kernel<2, QUANT><<<rows, threads, 0, stream>>>(xp, rp, wp, op, qp, q_scale, hidden, eps); break;
-    case 4: rmsnorm_kernel<4, QUANT><<<rows, threads, 0, stream>>>(xp, rp, wp, op, qp, q_scale, hidden, eps); break;
-    case 8: rmsnorm_kernel<8, QUANT><<<rows, threads, 0, stream>>>(xp, rp, wp, op, qp, q_scale, hidden, eps); break;
+    case 1: launch_pdl(rmsnorm_kernel<1, QUANT>, dim3(rows), dim3(threads), 0, stream, xp, rp, wp, op, qp, q_scale, hidden, eps); break;
+    case 2: launch_pdl(rmsnorm_kernel<2, QUANT>, dim3(rows), dim3(threads), 0, stream, xp, rp, wp, op, qp, q_scale, hidden, eps); break;
+    case 4: launch_pdl(rmsnorm_kernel<4, QUANT>, dim3(rows), dim3(threads), 0, stream, xp, rp, wp, op, qp, q_scale, hidden, eps); break;
+    case 8: launch_pdl(rmsnorm_kernel<8, QUANT>, dim3(rows), dim3(threads), 0, stream, xp, rp, wp, op, qp, q_scale, hidden, eps); break;
     default: return -kBadArgument;
   }
   return 0;
@@ -318,7 +339,7 @@ extern "C" int b2_quant_e4m3_1x128(const void* x, void* q_out, float* scale_out,
   const int64_t groups = static_cast<int64_t>(rows) * (cols / 128);
   const int threads = 256;
   const int64_t blocks = (groups * 16 + threads - 1) / threads;
-  quant_e4m3_1x128_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+  launch_pdl(quant_e4m3_1x128_kernel, dim3(static_cast<unsigned>(blocks)), dim3(threads), 0, stream, 
       static_cast<const uint4*>(x), static_cast<uint8_t*>(q_out), scale_out, rows, cols);
   return 0;
 }
@@ -332,7 +353,7 @@ extern "C" int b2_rope_kvwrite_bf16(void* q, void* k, const void* v, const float
   if (head_dim % 8 != 0 || rot_dim % 16 != 0 || rot_dim > head_dim || q_stride % 8 != 0 || k_stride % 8 != 0 ||
       v_stride % 8 != 0)
     return -kBadArgument;
-  rope_kvwrite_kernel<<<tokens, 128, 0, stream>>>(
+  launch_pdl(rope_kvwrite_kernel, dim3(tokens), dim3(128), 0, stream, 
       static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), cos_sin,
       positions, slots, static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), n_q, n_kv,
       head_dim, rot_dim, interleaved, q_stride, k_stride, v_stride, page_size, num_slots, max_pos, status);
@@ -344,7 +365,7 @@ extern "C" int b2_swiglu_bf16(const void* gate_up, void* out, int rows, int ffn,
   if (ffn % 8 != 0 || (interleaved && ffn % 16 != 0)) return -kBadArgument;
   const int64_t total = static_cast<int64_t>(rows) * (ffn / 8);
   const int threads = 256;
-  swiglu_kernel<<<static_cast<unsigned>((total + threads - 1) / threads), threads, 0, stream>>>(
+  launch_pdl(swiglu_kernel, dim3(static_cast<unsigned>((total + threads - 1) / threads)), dim3(threads), 0, stream, 
       static_cast<const uint4*>(gate_up), static_cast<uint4*>(out), rows, ffn / 8, interleaved != 0);
   return 0;
 }
@@ -354,16 +375,24 @@ extern "C" int b2_embedding_bf16(const int64_t* ids, const void* table, void* ou
   if (tokens <= 0) return 0;
   if (hidden % 8 != 0) return -kBadArgument;
   const int threads = hidden / 8 >= 256 ? 256 : 128;
-  embedding_kernel<<<tokens, threads, 0, stream>>>(ids, static_cast<const uint4*>(table), static_cast<uint4*>(out),
+  launch_pdl(embedding_kernel, dim3(tokens), dim3(threads), 0, stream, ids, static_cast<const uint4*>(table), static_cast<uint4*>(out),
                                                    hidden / 8, vocab_start, vocab_rows);
   return 0;
+}
+
+extern "C" int b2_patch_tokens(int64_t* tok, const int32_t* rows, const int32_t* src, const int64_t* prev, int n, int64_t tok_rows,
+                               int64_t prev_rows, Status* status, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (tok == nullptr || rows == nullptr || src == nullptr || prev == nullptr) return -kBadArgument;
+  launch_pdl(patch_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tok, rows, src, prev, n, tok_rows, prev_rows, status);
+  return last_launch_rc();
 }
 
 extern "C" int b2_gather_rows_bf16(const void* src, const int64_t* index, void* out, int rows_out, int cols,
                                    int64_t rows_src, Status* status, cudaStream_t stream) {
   if (rows_out <= 0) return 0;
   if (cols % 8 != 0) return -kBadArgument;
-  gather_rows_kernel<<<rows_out, 128, 0, stream>>>(static_cast<const uint4*>(src), index, static_cast<uint4*>(out),
+  launch_pdl(gather_rows_kernel, dim3(rows_out), dim3(128), 0, stream, static_cast<const uint4*>(src), index, static_cast<uint4*>(out),
                                                    cols / 8, rows_src, status);
   return 0;
 }
@@ -376,7 +405,7 @@ extern "C" int b2_copy_pages(void* cache, const int64_t* src_pages, const int64_
   const int threads = 256;
   int bx = static_cast<int>((vecs + threads - 1) / threads);
   if (bx > 64) bx = 64;
-  copy_pages_kernel<<<dim3(bx, n), threads, 0, stream>>>(static_cast<uint4*>(cache), src_pages, dst_pages, vecs,
+  launch_pdl(copy_pages_kernel, dim3(dim3(bx, n)), dim3(threads), 0, stream, static_cast<uint4*>(cache), src_pages, dst_pages, vecs,
                                                          num_pages, status);
   return 0;
 }
@@ -385,7 +414,7 @@ extern "C" int b2_scatter_rows_bf16(const void* src, const int64_t* slots, void*
                                     Status* status, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (cols % 8 != 0) return -kBadArgument;
-  scatter_rows_kernel<<<rows, 128, 0, stream>>>(static_cast<const uint4*>(src), slots, static_cast<uint4*>(dst), cols / 8,
+  launch_pdl(scatter_rows_kernel, dim3(rows), dim3(128), 0, stream, static_cast<const uint4*>(src), slots, static_cast<uint4*>(dst), cols / 8,
                                                 rows_dst, status);
   return 0;
 }

@@ -347,7 +347,7 @@ int launch(const void* x, const void* w, int M, int N, int K, int64_t ldx, int64
   const uint64_t pol_w = ptx::kEvictFirst, pol_x = ptx::kEvictLast;
   const uint64_t pol_p = SWAP ? pol_w : (M <= 1024 ? pol_x : ptx::kEvictNormal);
   const uint64_t pol_q = SWAP ? pol_x : (M <= 1024 ? pol_w : ptx::kEvictNormal);
-  kern<<<grid, gemm::kThreads, L::kTotalBytes, stream>>>(tp, tq, sched, ep, pol_p, pol_q, status);
+  launch_pdl(kern, dim3(grid), dim3(gemm::kThreads), L::kTotalBytes, stream, tp, tq, sched, ep, pol_p, pol_q, status);
   return last_launch_rc();
 }
 

@@ -109,6 +109,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   ptx::cluster_sync();   // the peer's barriers are initialised before anything is signalled across the pair
   ptx::tc_fence_after();
   const uint32_t tmem_base = *holder;
+  ptx::grid_dep_sync();   // the set-up above overlapped the previous kernel's tail; operands and outputs are global memory
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -278,7 +279,7 @@ int launch_pair(const void* x, const void* w, void* y, int M, int N, int K, int6
     return rc;
   const int total = p.m_tiles * p.n_tiles;
   const int pairs = total < kNumSMs / 2 ? total : kNumSMs / 2;
-  gemm_bf16_pair_kernel<BN><<<2 * pairs, kPairThreads, Cfg::kSmem, stream>>>(tx, tw, p, status);
+  launch_pdl(gemm_bf16_pair_kernel<BN>, dim3(2 * pairs), dim3(kPairThreads), Cfg::kSmem, stream, tx, tw, p, status);
   return last_launch_rc();
 }
 

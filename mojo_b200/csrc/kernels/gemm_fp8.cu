@@ -67,6 +67,7 @@ template <int BN, int STAGES, int SLABS, bool SWAP, int MODE, bool WG2>
 __global__ void __launch_bounds__(WG2 ? kThreads + 128 : kThreads, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q, Fp8Params prm,
                 const __grid_constant__ tp::RsSched rs_sched, const __grid_constant__ Fp8Fused fz, Status* status) {
+  ptx::grid_dep_sync();
   constexpr bool RS = MODE == kModeRs;
   constexpr bool AG = MODE == kModeAg;
   static_assert(!(RS && WG2), "the fused reduce-scatter epilogue is written for four epilogue warps");
@@ -454,7 +455,7 @@ int launch_fp8(const void* xq, const float* xs, const void* wq, const float* ws,
   const int total = prm.p_blocks * prm.q_blocks * prm.splits;
   static const tp::RsSched no_sched{};
   static const Fp8Fused no_fused{};
-  kern<<<total < kNumSMs ? total : kNumSMs, WG2 ? kThreads + 128 : kThreads, SMEM, stream>>>(tp, tq, prm, no_sched, no_fused, status);
+  launch_pdl(kern, dim3(total < kNumSMs ? total : kNumSMs), dim3(WG2 ? kThreads + 128 : kThreads), SMEM, stream, tp, tq, prm, no_sched, no_fused, status);
   return last_launch_rc();
 }
 
@@ -505,7 +506,7 @@ int launch_fp8_rs(const void* xq, const float* xs, const void* wq, const float* 
   fz.rs = rs;
   fz.ectl = ectl;
   fz.n_gemm = n_gemm;
-  kern<<<kNumSMs, kThreads, SMEM, stream>>>(tmp, tmq, prm, sched, fz, status);
+  launch_pdl(kern, dim3(kNumSMs), dim3(kThreads), SMEM, stream, tmp, tmq, prm, sched, fz, status);
   return last_launch_rc();
 }
 
@@ -559,7 +560,7 @@ int launch_fp8_ag(const void* xq_all, const float* xs_all, const void* wq, const
       }))
     return rc;
   static const tp::RsSched no_sched{};
-  kern<<<n_gemm + ag.n_comm, WG2 ? kThreads + 128 : kThreads, SMEM, stream>>>(tmp, tmq, prm, no_sched, fz, status);
+  launch_pdl(kern, dim3(n_gemm + ag.n_comm), dim3(WG2 ? kThreads + 128 : kThreads), SMEM, stream, tmp, tmq, prm, no_sched, fz, status);
   return last_launch_rc();
 }
 

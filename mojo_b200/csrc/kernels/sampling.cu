@@ -99,6 +99,7 @@ __device__ ArgMax block_argmax(const void* row, int vocab, ArgMax* scratch) {
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads) argmax_kernel(const void* logits, int64_t* ids, float* max_out, int vocab,
                                                            int64_t row_stride) {
+  ptx::grid_dep_sync();
   __shared__ ArgMax scratch[33];
   const int row = blockIdx.x;
   const void* base = static_cast<const char*>(logits) + static_cast<int64_t>(row) * row_stride * (BF16 ? 2 : 4);
@@ -154,6 +155,7 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const void* logits, in
                                                            const int32_t* top_k, const float* top_p,
                                                            const float* uniforms, uint64_t seed, uint64_t step,
                                                            int vocab, int64_t row_stride) {
+  ptx::grid_dep_sync();
   __shared__ ArgMax scratch[33];
   __shared__ float fscratch[33];
   __shared__ float hist[256];
@@ -238,8 +240,8 @@ extern "C" int b2_argmax(const void* logits, int is_bf16, int64_t* ids, float* m
                          int64_t row_stride, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return -kBadArgument;
-  if (is_bf16) argmax_kernel<true><<<rows, kThreads, 0, stream>>>(logits, ids, max_out, vocab, row_stride);
-  else argmax_kernel<false><<<rows, kThreads, 0, stream>>>(logits, ids, max_out, vocab, row_stride);
+  if (is_bf16) launch_pdl(argmax_kernel<true>, dim3(rows), dim3(kThreads), 0, stream, logits, ids, max_out, vocab, row_stride);
+  else launch_pdl(argmax_kernel<false>, dim3(rows), dim3(kThreads), 0, stream, logits, ids, max_out, vocab, row_stride);
   return last_launch_rc();
 }
 
@@ -249,10 +251,10 @@ extern "C" int b2_sample(const void* logits, int is_bf16, int64_t* ids, const fl
   if (rows <= 0) return 0;
   if (vocab <= 0) return -kBadArgument;
   if (is_bf16)
-    sample_kernel<true><<<rows, kThreads, 0, stream>>>(logits, ids, temperature, top_k, top_p, uniforms, seed, step,
+    launch_pdl(sample_kernel<true>, dim3(rows), dim3(kThreads), 0, stream, logits, ids, temperature, top_k, top_p, uniforms, seed, step,
                                                        vocab, row_stride);
   else
-    sample_kernel<false><<<rows, kThreads, 0, stream>>>(logits, ids, temperature, top_k, top_p, uniforms, seed, step,
+    launch_pdl(sample_kernel<false>, dim3(rows), dim3(kThreads), 0, stream, logits, ids, temperature, top_k, top_p, uniforms, seed, step,
                                                         vocab, row_stride);
   return last_launch_rc();
 }

@@ -86,6 +86,7 @@ __device__ __forceinline__ uint4 sum_peers(const CollParams& p, int64_t byte_off
 template <int ALGO>
 __global__ void __launch_bounds__(kCollThreads) all_reduce_kernel(CollParams p, EpochCtl ectl, uint8_t* mc_base, uint4* out, int64_t n_vec,
                                                                   Status* status) {
+  ptx::grid_dep_sync();
   const uint32_t epoch = tp::epoch_begin(ectl);
   const bool ok = arrive_and_wait(p, p.off_flags_a, epoch, blockIdx.x == 0, status);
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -121,6 +122,7 @@ template <int VPT>
 __global__ void __launch_bounds__(kCollThreads) all_reduce_rmsnorm_kernel(CollParams p, EpochCtl ectl, uint4* __restrict__ residual,
                                                                           const uint4* __restrict__ weight, uint4* __restrict__ out, int rows,
                                                                           int hidden, float eps, Status* status) {
+  ptx::grid_dep_sync();
   __shared__ float scratch[33];
   const uint32_t epoch = tp::epoch_begin(ectl);
   const bool ok = arrive_and_wait(p, p.off_flags_a, epoch, blockIdx.x == 0, status);
@@ -181,6 +183,7 @@ template <int VPT>
 __global__ void __launch_bounds__(kCollThreads) all_reduce_rmsnorm_nvls_kernel(CollParams p, EpochCtl ectl, uint8_t* mc_base,
                                                                                const uint4* __restrict__ residual, const uint4* __restrict__ weight,
                                                                                int rows, int hidden, float eps, int64_t off_res_out, Status* status) {
+  ptx::grid_dep_sync();
   __shared__ float scratch[33];
   const uint32_t epoch = tp::epoch_begin(ectl);
   const bool ok = arrive_and_wait(p, p.off_flags_a, epoch, blockIdx.x == 0, status);
@@ -235,6 +238,7 @@ __global__ void __launch_bounds__(kCollThreads) all_reduce_rmsnorm_nvls_kernel(C
 
 __global__ void __launch_bounds__(kCollThreads) reduce_scatter_kernel(CollParams p, EpochCtl ectl, uint4* out, int64_t n_vec_per_rank,
                                                                       Status* status) {
+  ptx::grid_dep_sync();
   const uint32_t epoch = tp::epoch_begin(ectl);
   const bool ok = arrive_and_wait(p, p.off_flags_a, epoch, blockIdx.x == 0, status);
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -245,6 +249,7 @@ __global__ void __launch_bounds__(kCollThreads) reduce_scatter_kernel(CollParams
 }
 
 __global__ void __launch_bounds__(kCollThreads) all_gather_kernel(CollParams p, EpochCtl ectl, const uint4* in, int64_t n_vec, Status* status) {
+  ptx::grid_dep_sync();
   const uint32_t epoch = tp::epoch_begin(ectl);
   const bool ok = arrive_and_wait(p, p.off_flags_a, epoch, blockIdx.x == 0, status);
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -267,6 +272,7 @@ __global__ void __launch_bounds__(kCollThreads) all_gather_kernel(CollParams p, 
 // of the fused kernels is measured: with the library's own peer loads and stores, not with a driver copy.
 __global__ void __launch_bounds__(kCollThreads) p2p_probe_kernel(CollParams p, EpochCtl ectl, int n_peers, uint32_t senders, int pull,
                                                                  int64_t n_vec, int64_t block_vec, Status* status) {
+  ptx::grid_dep_sync();
   const uint32_t epoch = tp::epoch_begin(ectl);
   const bool ok = arrive_and_wait(p, p.off_flags_a, epoch, blockIdx.x == 0, status);
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -303,6 +309,7 @@ struct A2ACounts {
 
 __global__ void __launch_bounds__(kCollThreads) all_to_all_kernel(CollParams p, EpochCtl ectl, const uint4* in, A2ACounts counts, int max_rows,
                                                                   int64_t row_vec, int parity, Status* status) {
+  ptx::grid_dep_sync();
   const uint32_t epoch = tp::epoch_begin(ectl);
   const bool ok = arrive_and_wait(p, p.off_flags_a, epoch, blockIdx.x == 0, status);
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -332,6 +339,7 @@ __device__ __forceinline__ uint32_t orderable(float f) {
 
 __global__ void __launch_bounds__(kCollThreads) vocab_argmax_kernel(CollParams p, EpochCtl ectl, const __nv_bfloat16* logits, int64_t ld,
                                                                     const int64_t* local_idx, int64_t* tokens, int S, int v_local, int v_stride, Status* status) {
+  ptx::grid_dep_sync();
   const uint32_t epoch = tp::epoch_begin(ectl);
   const bool ok = arrive_and_wait(p, p.off_flags_a, epoch, true, status);
   if (ok) {
@@ -403,9 +411,9 @@ extern "C" int b2_coll_all_reduce_bf16(const B2TpRegion* reg, const B2CollLayout
   if ((algo == 0 && out == nullptr) || (algo == 2 && mc_base == nullptr)) return -kBadArgument;
   const int64_t n_vec = n / 8;
   const int grid = grid_for(algo == 0 ? n_vec : (n_vec + p.tp - 1) / p.tp);
-  if (algo == 0) all_reduce_kernel<0><<<grid, kCollThreads, 0, stream>>>(p, ectl, nullptr, static_cast<uint4*>(out), n_vec, status);
-  else if (algo == 1) all_reduce_kernel<1><<<grid, kCollThreads, 0, stream>>>(p, ectl, nullptr, nullptr, n_vec, status);
-  else all_reduce_kernel<2><<<grid, kCollThreads, 0, stream>>>(p, ectl, static_cast<uint8_t*>(mc_base), nullptr, n_vec, status);
+  if (algo == 0) launch_pdl(all_reduce_kernel<0>, dim3(grid), dim3(kCollThreads), 0, stream, p, ectl, nullptr, static_cast<uint4*>(out), n_vec, status);
+  else if (algo == 1) launch_pdl(all_reduce_kernel<1>, dim3(grid), dim3(kCollThreads), 0, stream, p, ectl, nullptr, nullptr, n_vec, status);
+  else launch_pdl(all_reduce_kernel<2>, dim3(grid), dim3(kCollThreads), 0, stream, p, ectl, static_cast<uint8_t*>(mc_base), nullptr, n_vec, status);
   return launched();
 }
 
@@ -424,10 +432,10 @@ extern "C" int b2_coll_all_reduce_rmsnorm_bf16(const B2TpRegion* reg, const B2Co
   uint4* res = static_cast<uint4*>(residual);
   const uint4* w = static_cast<const uint4*>(weight);
   uint4* o = static_cast<uint4*>(out);
-  if (vpt <= 1) all_reduce_rmsnorm_kernel<1><<<grid, kCollThreads, 0, stream>>>(p, ectl, res, w, o, rows, hidden, eps, status);
-  else if (vpt <= 2) all_reduce_rmsnorm_kernel<2><<<grid, kCollThreads, 0, stream>>>(p, ectl, res, w, o, rows, hidden, eps, status);
-  else if (vpt <= 4) all_reduce_rmsnorm_kernel<4><<<grid, kCollThreads, 0, stream>>>(p, ectl, res, w, o, rows, hidden, eps, status);
-  else all_reduce_rmsnorm_kernel<8><<<grid, kCollThreads, 0, stream>>>(p, ectl, res, w, o, rows, hidden, eps, status);
+  if (vpt <= 1) launch_pdl(all_reduce_rmsnorm_kernel<1>, dim3(grid), dim3(kCollThreads), 0, stream, p, ectl, res, w, o, rows, hidden, eps, status);
+  else if (vpt <= 2) launch_pdl(all_reduce_rmsnorm_kernel<2>, dim3(grid), dim3(kCollThreads), 0, stream, p, ectl, res, w, o, rows, hidden, eps, status);
+  else if (vpt <= 4) launch_pdl(all_reduce_rmsnorm_kernel<4>, dim3(grid), dim3(kCollThreads), 0, stream, p, ectl, res, w, o, rows, hidden, eps, status);
+  else launch_pdl(all_reduce_rmsnorm_kernel<8>, dim3(grid), dim3(kCollThreads), 0, stream, p, ectl, res, w, o, rows, hidden, eps, status);
   return launched();
 }
 
@@ -449,7 +457,7 @@ extern "C" int b2_coll_all_reduce_rmsnorm_nvls_bf16(const B2TpRegion* reg, const
   const uint4* w = static_cast<const uint4*>(weight);
   uint8_t* mc = static_cast<uint8_t*>(mc_base);
   const int64_t off_res = p.off_out + bytes;
-#define B2_NVLS_NORM(V) all_reduce_rmsnorm_nvls_kernel<V><<<grid, kCollThreads, 0, stream>>>(p, ectl, mc, res, w, rows, hidden, eps, off_res, status)
+#define B2_NVLS_NORM(V) launch_pdl(all_reduce_rmsnorm_nvls_kernel<V>, dim3(grid), dim3(kCollThreads), 0, stream, p, ectl, mc, res, w, rows, hidden, eps, off_res, status)
   if (vpt <= 1) B2_NVLS_NORM(1);
   else if (vpt <= 2) B2_NVLS_NORM(2);
   else if (vpt <= 4) B2_NVLS_NORM(4);
@@ -465,7 +473,7 @@ extern "C" int b2_coll_reduce_scatter_bf16(const B2TpRegion* reg, const B2CollLa
   if (!fill(p, ectl, reg, lay, slot, timeout_ns) || n <= 0 || out == nullptr || n % (8 * reg->tp) != 0) return -kBadArgument;
   if (n * 2 > lay->buf_half_bytes) return -kTooLarge;
   const int64_t per = n / 8 / p.tp;
-  reduce_scatter_kernel<<<grid_for(per), kCollThreads, 0, stream>>>(p, ectl, static_cast<uint4*>(out), per, status);
+  launch_pdl(reduce_scatter_kernel, dim3(grid_for(per)), dim3(kCollThreads), 0, stream, p, ectl, static_cast<uint4*>(out), per, status);
   return launched();
 }
 
@@ -477,7 +485,7 @@ extern "C" int b2_coll_all_gather(const B2TpRegion* reg, const B2CollLayout* lay
       (reinterpret_cast<uintptr_t>(in) & 15) != 0)
     return -kBadArgument;
   if (bytes * p.tp > lay->out_half_bytes) return -kTooLarge;
-  all_gather_kernel<<<grid_for(bytes / 16), kCollThreads, 0, stream>>>(p, ectl, static_cast<const uint4*>(in), bytes / 16, status);
+  launch_pdl(all_gather_kernel, dim3(grid_for(bytes / 16)), dim3(kCollThreads), 0, stream, p, ectl, static_cast<const uint4*>(in), bytes / 16, status);
   return launched();
 }
 
@@ -496,7 +504,7 @@ extern "C" int b2_coll_all_to_all(const B2TpRegion* reg, const B2CollLayout* lay
     c.n[i] = send_counts[i];
     most = send_counts[i] > most ? send_counts[i] : most;
   }
-  all_to_all_kernel<<<grid_for(most * (row_bytes / 16)), kCollThreads, 0, stream>>>(p, ectl, static_cast<const uint4*>(in), c, max_rows,
+  launch_pdl(all_to_all_kernel, dim3(grid_for(most * (row_bytes / 16))), dim3(kCollThreads), 0, stream, p, ectl, static_cast<const uint4*>(in), c, max_rows,
                                                                                    row_bytes / 16, slot & 1, status);
   return launched();
 }
@@ -510,7 +518,7 @@ extern "C" int b2_coll_vocab_argmax(const B2TpRegion* reg, const B2CollLayout* l
   if (!fill(p, ectl, reg, lay, slot, timeout_ns) || logits == nullptr || local_idx == nullptr || tokens == nullptr || v_local <= 0 || v_stride < v_local)
     return -kBadArgument;
   if (static_cast<int64_t>(S) * p.tp * 8 > lay->out_half_bytes) return -kTooLarge;
-  vocab_argmax_kernel<<<1, kCollThreads, 0, stream>>>(p, ectl, static_cast<const __nv_bfloat16*>(logits), ld, local_idx, tokens, S, v_local,
+  launch_pdl(vocab_argmax_kernel, dim3(1), dim3(kCollThreads), 0, stream, p, ectl, static_cast<const __nv_bfloat16*>(logits), ld, local_idx, tokens, S, v_local,
                                                       v_stride, status);
   return launched();
 }
@@ -522,6 +530,6 @@ extern "C" int b2_coll_p2p_probe(const B2TpRegion* reg, const B2CollLayout* lay,
   if (!fill(p, ectl, reg, lay, slot, timeout_ns) || bytes <= 0 || bytes % 16 != 0 || n_peers < 1 || n_peers >= p.tp || ctas < 1 || ctas > 8 * kNumSMs)
     return -kBadArgument;
   if (bytes > lay->buf_half_bytes || bytes * p.tp > lay->out_half_bytes) return -kTooLarge;
-  p2p_probe_kernel<<<ctas, kCollThreads, 0, stream>>>(p, ectl, n_peers, senders, pull ? 1 : 0, bytes / 16, bytes / 16, status);
+  launch_pdl(p2p_probe_kernel, dim3(ctas), dim3(kCollThreads), 0, stream, p, ectl, n_peers, senders, pull ? 1 : 0, bytes / 16, bytes / 16, status);
   return launched();
 }

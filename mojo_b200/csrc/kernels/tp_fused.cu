@@ -56,6 +56,7 @@ template <int BN, int STAGES, bool SWAP, bool SIDE>
 __global__ void __launch_bounds__(SIDE ? kRsThreads : gemm::kThreads, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
                const __grid_constant__ RsSched sched, RsParams prm_in, EpochCtl ectl, int n_gemm, Status* status) {
+  ptx::grid_dep_sync();
   constexpr uint32_t idesc = ptx::make_idesc(1, 1, 128, BN);
   RsParams prm = prm_in;
   prm.epoch = epoch_begin(ectl);
@@ -131,14 +132,14 @@ int launch_rs(const void* x, const void* w, int M, int N, int K, int64_t ldx, in
     // Full persistent grid: every CTA that has tiles runs the GEMM with its reduction side warps; CTAs beyond the
     // tile count only reduce.
     const int n_gemm = total < kNumSMs ? total : kNumSMs;
-    gemm_rs_kernel<BN, STAGES, SWAP, true><<<kNumSMs, kRsThreads, SMEM, stream>>>(tp, tq, sched, prm, ectl, n_gemm, status);
+    launch_pdl(gemm_rs_kernel<BN, STAGES, SWAP, true>, dim3(kNumSMs), dim3(kRsThreads), SMEM, stream, tp, tq, sched, prm, ectl, n_gemm, status);
   } else {
     // Twelve CTAs only reduce, from the start: the reduction of finished units then overlaps the rest of the GEMM
     // (measured: with none, the all-reduce of a 4096-token tile set is 15 % slower although the GEMM has more SMs).
     const int n_red = prm.tp > 1 ? 12 : 0;
     int n_gemm = kNumSMs - n_red;
     if (total < n_gemm) n_gemm = total;
-    gemm_rs_kernel<BN, STAGES, SWAP, false><<<kNumSMs, gemm::kThreads, SMEM, stream>>>(tp, tq, sched, prm, ectl, n_gemm, status);
+    launch_pdl(gemm_rs_kernel<BN, STAGES, SWAP, false>, dim3(kNumSMs), dim3(gemm::kThreads), SMEM, stream, tp, tq, sched, prm, ectl, n_gemm, status);
   }
   return last_launch_rc();
 }
@@ -201,6 +202,7 @@ template <int BN, int STAGES, bool SWAP, bool SIDE>
 __global__ void __launch_bounds__(SIDE ? kAgThreads : gemm::kThreads, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q, AgSched sched,
                AgParams prm_in, PlainEpiParams ep, EpochCtl ectl, Status* status) {
+  ptx::grid_dep_sync();
   AgParams prm = prm_in;
   prm.epoch = epoch_begin(ectl);
   constexpr uint32_t idesc = ptx::make_idesc(1, 1, 128, BN);
@@ -227,6 +229,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant
 
 // Standalone push all-gather (no GEMM): used where the gathered rows feed something other than a GEMM.
 __global__ void __launch_bounds__(256) ag_push_kernel(AgParams prm_in, EpochCtl ectl, Status* status) {
+  ptx::grid_dep_sync();
   AgParams prm = prm_in;
   prm.epoch = epoch_begin(ectl);
   extern __shared__ uint8_t smem_dyn[];
@@ -282,17 +285,18 @@ int launch_ag(const void* xall_local, const void* w, void* y, int M, int N, int 
   const int total = sched.p_blocks * sched.q_blocks;
   if (side) {
     const int grid = total < kNumSMs ? total : kNumSMs;
-    ag_gemm_kernel<BN, STAGES, SWAP, true><<<grid, kAgThreads, L::kTotalBytes, stream>>>(tp, tq, sched, prm, ep, ectl, status);
+    launch_pdl(ag_gemm_kernel<BN, STAGES, SWAP, true>, dim3(grid), dim3(kAgThreads), L::kTotalBytes, stream, tp, tq, sched, prm, ep, ectl, status);
   } else {
     int n_gemm = kNumSMs - prm.n_comm;
     if (total < n_gemm) n_gemm = total;
-    ag_gemm_kernel<BN, STAGES, SWAP, false><<<n_gemm + prm.n_comm, gemm::kThreads, L::kTotalBytes, stream>>>(tp, tq, sched, prm, ep, ectl, status);
+    launch_pdl(ag_gemm_kernel<BN, STAGES, SWAP, false>, dim3(n_gemm + prm.n_comm), dim3(gemm::kThreads), L::kTotalBytes, stream, tp, tq, sched, prm, ep, ectl, status);
   }
   return last_launch_rc();
 }
 
 // Cross-GPU barrier: every rank raises its slot on every peer, then waits for all slots.
 __global__ void symm_barrier_kernel(B2TpRegion reg, int64_t off_flags, EpochCtl ectl, uint64_t timeout_ns, Status* status) {
+  ptx::grid_dep_sync();
   const int t = threadIdx.x;
   const uint32_t epoch = epoch_begin(ectl);
   if (t < reg.tp) {
@@ -305,6 +309,7 @@ __global__ void symm_barrier_kernel(B2TpRegion reg, int64_t off_flags, EpochCtl 
 
 // Test hook for the timeout path: wait on a flag that nothing raises, with a short deadline.
 __global__ void wait_flag_kernel(const uint32_t* flag, uint32_t want, uint64_t timeout_ns, Status* status) {
+  ptx::grid_dep_sync();
   if (threadIdx.x == 0 && !ptx::wait_flag_ge_sys(flag, want, timeout_ns)) status_record(status, kTimeout, kSiteTest, want, 0);
 }
 
@@ -349,6 +354,7 @@ extern "C" int b2_tp_gemm_rs_bf16(const void* x, const void* w, const B2TpRegion
   prm.out = static_cast<__nv_bfloat16*>(out);
   prm.timeout_ns = timeout_ns;
   prm.region_bytes = lay->total_bytes;
+  prm.mc_base = tp > 1 ? static_cast<uint8_t*>(reg->mc_base) : nullptr;   // non-null: reduce in the NVLink switch
   bool swap = M <= 128;
   int bn = swap ? pick_bn_swap(M) : 128;
   if (config != 0) {
@@ -467,7 +473,7 @@ extern "C" int b2_tp_all_gather(const B2TpRegion* reg, const B2TpLayout* lay, in
         return e;
       }))
     return rc;
-  ag_push_kernel<<<prm.n_comm, 256, kPushSmem, stream>>>(prm, ectl, status);
+  launch_pdl(ag_push_kernel, dim3(prm.n_comm), dim3(256), kPushSmem, stream, prm, ectl, status);
   return last_launch_rc();
 }
 
@@ -476,12 +482,12 @@ extern "C" int b2_symm_barrier(const B2TpRegion* reg, const B2TpLayout* lay, uin
   if (reg == nullptr || lay == nullptr || reg->tp < 1 || reg->tp > kMaxTp) return -kBadArgument;
   uint8_t* self = static_cast<uint8_t*>(reg->peer[reg->rank]);
   EpochCtl ectl{reinterpret_cast<uint32_t*>(self + lay->off_epoch_bar), reinterpret_cast<uint32_t*>(self + lay->off_epoch_bar + 4)};
-  symm_barrier_kernel<<<1, 32, 0, stream>>>(*reg, lay->off_barrier, ectl, timeout_ns, status);
+  launch_pdl(symm_barrier_kernel, dim3(1), dim3(32), 0, stream, *reg, lay->off_barrier, ectl, timeout_ns, status);
   return last_launch_rc();
 }
 
 extern "C" int b2_wait_flag(const uint32_t* flag, uint32_t want, uint64_t timeout_ns, b2::Status* status,
                             cudaStream_t stream) {
-  wait_flag_kernel<<<1, 32, 0, stream>>>(flag, want, timeout_ns, status);
+  launch_pdl(wait_flag_kernel, dim3(1), dim3(32), 0, stream, flag, want, timeout_ns, status);
   return last_launch_rc();
 }

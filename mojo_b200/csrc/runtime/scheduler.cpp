@@ -81,28 +81,32 @@ void Scheduler::emit(Request& r, int64_t n, Batch* b) {
   }
   r.computed = start + n;
   // The pages become prefix-cache entries only once the step that writes their KV has completed (commit_step).
-  pending_commits_.push_back({r.id, r.computed});
+  if (pending_commits_.empty()) pending_commits_.emplace_back();
+  pending_commits_.back().push_back({r.id, r.computed});
   b->max_q_len = std::max<int>(b->max_q_len, static_cast<int>(n));
 }
 
 void Scheduler::commit_step() {
-  for (const auto& pc : pending_commits_) {
+  if (pending_commits_.empty()) return;
+  for (const auto& pc : pending_commits_.front()) {
     auto it = reqs_.find(pc.first);
     if (it == reqs_.end()) continue;
     kv_->commit(pc.first, it->second.tokens.data(), std::min<int64_t>(pc.second, static_cast<int64_t>(it->second.tokens.size())));
   }
-  pending_commits_.clear();
+  pending_commits_.pop_front();
 }
 
 void Scheduler::drop_pending_commit(int64_t id) {
-  pending_commits_.erase(std::remove_if(pending_commits_.begin(), pending_commits_.end(),
-                                        [id](const std::pair<int64_t, int64_t>& pc) { return pc.first == id; }),
-                         pending_commits_.end());
+  for (auto& batch : pending_commits_)
+    batch.erase(std::remove_if(batch.begin(), batch.end(), [id](const std::pair<int64_t, int64_t>& pc) { return pc.first == id; }), batch.end());
 }
 
 Batch Scheduler::step() {
-  // Asking for the next batch says that the previous one ran to completion: its pages may now be shared.
-  commit_step();
+  // Asking for the next batch says that the previous one ran to completion: its pages may now be shared. A pipelined
+  // engine schedules ahead of the device, turns this off and confirms each batch itself when it has read its tokens.
+  if (auto_commit_)
+    while (!pending_commits_.empty()) commit_step();
+  pending_commits_.emplace_back();
   Batch b;
   int64_t budget = cfg_.max_num_batched_tokens;
   std::vector<Entry> entries;
@@ -165,6 +169,7 @@ Batch Scheduler::step() {
     const auto& t = kv_->block_table(b.seq_ids[s]);
     std::copy(t.begin(), t.end(), b.block_tables.begin() + s * b.max_blocks);
   }
+  if (b.seq_ids.empty()) pending_commits_.pop_back();   // nothing was scheduled: no batch to confirm later
   return b;
 }
 
@@ -175,6 +180,20 @@ bool Scheduler::append_token(int64_t id, int32_t token) {
   r.tokens.push_back(token);
   ++r.generated;
   return r.generated >= r.max_new_tokens || static_cast<int64_t>(r.tokens.size()) >= cfg_.max_model_len;
+}
+
+bool Scheduler::set_token(int64_t id, int64_t pos, int32_t token) {
+  auto it = reqs_.find(id);
+  if (it == reqs_.end()) return false;
+  Request& r = it->second;
+  if (pos < 0 || pos >= static_cast<int64_t>(r.tokens.size())) return false;
+  r.tokens[pos] = token;
+  return true;
+}
+
+int64_t Scheduler::num_tokens(int64_t id) const {
+  auto it = reqs_.find(id);
+  return it == reqs_.end() ? -1 : static_cast<int64_t>(it->second.tokens.size());
 }
 
 void Scheduler::finish(int64_t id) {

@@ -54,6 +54,10 @@ class EngineConfig:
     ep_size: int = 1
     lockstep: bool = False                # data-parallel attention + expert parallelism: a rank without work still joins every MoE layer
     autotune: bool = False                # measure GEMM configurations for this model's shapes at start-up
+    # Pipelined stepping: step k + 1 is scheduled, staged and launched while the device still runs step k, so the host's
+    # per-step work (scheduler, staging, output bookkeeping) is hidden behind the device. `step()` then returns the
+    # outputs of the step launched one call earlier. Off in lock-step (expert-parallel) engines.
+    async_scheduling: bool = False
 
 
 @dataclass
@@ -123,8 +127,10 @@ class LLMEngine:
         from .model_runner import ModelRunner
 
         self.runner = ModelRunner(self.model, self.kv_caches, cfg)
-        if cfg.autotune:
-            self.runner.autotune()
+        self._inflight = None     # pipelined stepping: the launched step whose tokens the host has not read yet
+        if cfg.async_scheduling and not cfg.lockstep:
+            self.scheduler.set_auto_commit(False)   # a batch is confirmed when its tokens have been read, not when the next is scheduled
+        self.tune_report = self.runner.autotune() if cfg.autotune else {}
         if cfg.use_cuda_graphs and cfg.capture_graphs_at_start:
             # after tuning: the captured launches carry the tuned configurations
             self.runner.capture_graphs(mixed=cfg.capture_mixed_graphs_at_start)
@@ -197,13 +203,14 @@ class LLMEngine:
     def abort_all(self) -> list[int]:
         """Abort every request that has not finished (after a failed step the batch's state is unknown: the KV written
         by the step may be partial). Returns their ids."""
+        self.discard_inflight()
         rids = [rid for rid, st in self.requests.items() if not st.finished]
         for rid in rids:
             self.abort_request(rid)
         return rids
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished()
+        return self.scheduler.has_unfinished() or self._inflight is not None
 
     # ------------------------------------------------------------------------------------------------
     def step(self) -> list[RequestOutput]:
@@ -211,6 +218,8 @@ class LLMEngine:
 
         Before anything is launched the host-side failure hooks run: an injected fault may raise, sleep or skip the
         launch, and the heartbeat check raises `WorkerLost` when a peer rank has left or gone silent."""
+        if self.cfg.async_scheduling and not self.cfg.lockstep:
+            return self._step_pipelined()
         skip = self.fault.before_step(self.step_count)
         if self.heartbeat is not None:
             self.heartbeat.check()
@@ -240,13 +249,24 @@ class LLMEngine:
         if self.heartbeat is not None:
             self.heartbeat.beat(self.step_count)
         self.step_count += 1
+        return self._deliver(sample_ids, tokens, states, self.runner.last_logprobs, None)
+
+    def _deliver(self, sample_ids, tokens, states, step_lp, pending) -> list[RequestOutput]:
+        """Book the sampled tokens of one step: append them to their sequences, time them, decide who has finished.
+        `pending` is None for a step that was waited for; for a pipelined step it holds, per sampled row, the position
+        the placeholder took in the sequence and whether the sequence reached its length limit at launch."""
         now = time.perf_counter()
         outs = []
         ttfts, itls = [], []
-        step_lp = self.runner.last_logprobs     # None unless a request of this batch asked for log-probabilities
         for row, (rid, tok, st) in enumerate(zip(sample_ids, tokens, states)):
             rid, tok = int(rid), int(tok)
-            hit_max = self.scheduler.append_token(rid, tok)
+            if pending is None:
+                hit_max = self.scheduler.append_token(rid, tok)
+            else:
+                if st.finished:
+                    continue      # stopped (EOS, stop token, abort) after this step had been launched: its token is dropped
+                pos, hit_max = pending[row]
+                self.scheduler.set_token(rid, pos, tok)
             st.output_ids.append(tok)
             new_lp = None
             if step_lp is not None and st.params.logprobs is not None:
@@ -269,7 +289,7 @@ class LLMEngine:
                 reason = "length"
             if reason is not None:
                 st.finished, st.finish_reason = True, reason
-                self.scheduler.finish(rid)
+                self.scheduler.finish(rid)      # (a pipelined step that ran into its length limit was finished at launch: no-op)
                 self.finished_requests += 1
             outs.append(RequestOutput(rid, [tok], st.output_ids, st.finished, reason, new_lp))
         self.generated_tokens += len(outs)
@@ -282,6 +302,76 @@ class LLMEngine:
             np.add.at(self._itl_hist, np.searchsorted(self.itl_bounds_ms, v, side="left"), 1)
             self._itl_sum_ms += float(v.sum())
         return outs
+
+    def _step_pipelined(self) -> list[RequestOutput]:
+        """One iteration with the host one step ahead of the device: schedule and launch the next step, then read and
+        book the tokens of the step launched by the previous call (which the device has been running meanwhile).
+
+        A sequence sampled by the step in flight gets a placeholder token at once, so the scheduler can plan its next
+        decode row; the row's input is filled on the device from the in-flight step's output. Whether a sequence reaches
+        its length limit is known at launch, so it leaves the batch without delay; a stop token shows only when the
+        tokens are read, one step later, and the token the sequence produced in between is dropped."""
+        skip = self.fault.before_step(self.step_count)
+        if self.heartbeat is not None:
+            self.heartbeat.check()
+        if skip:
+            self.skipped_launches += 1
+            self.step_count += 1
+            return self.flush()
+        prev = self._inflight
+        with trace.span("engine.schedule"):
+            batch = self.scheduler.step()
+        launched = None
+        if batch.num_seqs > 0:
+            sample_ids = batch.sample_seq_ids
+            states = [self.requests[int(r)] for r in sample_ids]
+            if self.watchdog is not None:
+                self.watchdog.begin_step()
+            with trace.span("engine.execute"):
+                handle = self.runner.launch(batch, states, self.step_count, prev=(prev[0], prev[1]) if prev is not None else None)
+            self.fault.after_execute(self.step_count)
+            pending = []
+            for rid in sample_ids:
+                rid = int(rid)
+                hit_max = self.scheduler.append_token(rid, -1)
+                pending.append((self.scheduler.num_tokens(rid) - 1, hit_max))
+                if hit_max:
+                    self.scheduler.finish(rid)      # leaves the batch now; its last token is booked when it is read
+            launched = (handle, sample_ids, states, self.runner.last_logprobs, pending)
+            self.step_count += 1
+        outs = self._collect(prev)
+        self._inflight = launched
+        if launched is not None and self.runner.last_logprobs is not None:
+            # a step that computed log-probabilities waited for the device anyway: deliver it in the same call
+            outs += self.flush()
+        return outs
+
+    def _collect(self, inflight) -> list[RequestOutput]:
+        if inflight is None:
+            return []
+        handle, sample_ids, states, step_lp, pending = inflight
+        tokens = self.runner.collect(handle)
+        self.scheduler.commit_step()      # that step has completed: its full pages may enter the prefix cache
+        if self.watchdog is not None:
+            self.watchdog.end_step(self.step_count)
+        if self.heartbeat is not None:
+            self.heartbeat.beat(self.step_count)
+        return self._deliver(sample_ids, tokens, states, step_lp, pending)
+
+    def discard_inflight(self) -> None:
+        """Pipelined stepping: wait for the step in flight and drop its tokens unbooked (before aborting or re-queueing
+        requests: their sequences still hold that step's placeholders)."""
+        inflight, self._inflight = self._inflight, None
+        if inflight is not None:
+            try:
+                self.runner.collect(inflight[0])
+            except Exception:  # noqa: BLE001 - the step is being thrown away
+                pass
+
+    def flush(self) -> list[RequestOutput]:
+        """Pipelined stepping: wait for the step in flight and return its outputs (no-op otherwise)."""
+        inflight, self._inflight = self._inflight, None
+        return self._collect(inflight)
 
     def forget(self, rid: int) -> None:
         """Drop the bookkeeping of a finished (or aborted) request. A long-running server calls this when a stream

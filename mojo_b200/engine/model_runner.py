@@ -89,6 +89,11 @@ class ModelRunner:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.ids_host = torch.empty(cfg.max_num_seqs, dtype=torch.int64, pin_memory=self.cuda)
+        # sampled ids come back through two pinned slots, so that a step can be launched before the previous one is read
+        self.ids_slots = [torch.empty(cfg.max_num_seqs, dtype=torch.int64, pin_memory=self.cuda) for _ in range(2)]
+        self.ids_events = [torch.cuda.Event() if self.cuda else None for _ in range(2)]
+        self.ids_turn = 0
+        self.steps_launched = 0          # steps handed to the device so far (a pipelined `step()` call may launch none)
         self.graphs: dict[int, "_DecodeGraph"] = {}
         self.use_graphs = bool(cfg.use_cuda_graphs and self.cuda)
         self.graph_launches = 0          # graph replays
@@ -224,8 +229,57 @@ class ModelRunner:
 
     # ------------------------------------------------------------------------------------------------
     def execute(self, batch, states, step: int) -> list[int]:
+        """Run one step and return its sampled tokens (launch, then wait for the result)."""
+        return self.collect(self.launch(batch, states, step))
+
+    def collect(self, h: "StepHandle") -> list[int]:
+        """The sampled token ids of a launched step: waits for its device->host copy."""
+        if h.tokens is not None:
+            return h.tokens
+        if h.S == 0:
+            return []
+        h.event.synchronize()
+        return self.ids_slots[h.slot][:h.S].tolist()
+
+    def _finish_launch(self, ids, S: int) -> "StepHandle":
+        """Queue the copy of the sampled ids into a pinned slot (two slots: a step is collected before the launch after
+        the next reuses its slot) and return the handle that `collect` waits on."""
+        self.d2h_bytes = S * 8
+        if not self.cuda:
+            return StepHandle(S, ids, tokens=ids.tolist() if S else [])
+        if S == 0:
+            return StepHandle(0, ids)
+        self.ids_turn ^= 1
+        slot = self.ids_turn
+        self.ids_slots[slot][:S].copy_(ids[:S], non_blocking=True)
+        self.ids_events[slot].record()
+        return StepHandle(S, ids, slot=slot, event=self.ids_events[slot])
+
+    def _patch_plan(self, batch, prev):
+        """Rows of this batch whose input token is still a placeholder (-1): the token the previous step sampled for that
+        sequence, not yet read back by the host. Returns (row indices, indices into the previous step's sampled ids)."""
+        tok = batch.token_ids
+        neg = np.nonzero(tok < 0)[0]
+        if neg.size == 0:
+            return None
+        if prev is None:
+            raise RuntimeError("a placeholder token without a step in flight to take it from")
+        _, prev_seq_ids = prev
+        where = {int(r): j for j, r in enumerate(prev_seq_ids)}
+        seq_of_row = np.searchsorted(batch.cu_q, neg, side="right") - 1
+        seq_ids = batch.seq_ids
+        src = np.fromiter((where[int(seq_ids[i])] for i in seq_of_row), dtype=np.int32, count=neg.size)
+        return neg.astype(np.int32), src
+
+    def launch(self, batch, states, step: int, prev=None) -> "StepHandle":
+        """Stage and launch one step without waiting for it. `prev` = (handle of the step launched before this one, the
+        sequence ids of its sampled rows) when the host has not read that step's tokens yet: decode rows whose input is
+        such a token carry -1 in the batch and are filled on the device from the previous step's output."""
         self.last_num_tokens = int(batch.num_tokens)
         self.last_logprobs = None
+        self.steps_launched += 1
+        plan = self._patch_plan(batch, prev)
+        prev_ids = prev[0].ids if (plan is not None) else None
         top_lp = max((s.params.logprobs for s in states if s.params.logprobs is not None), default=None)
         if (top_lp is None and self.use_graphs and batch.num_prefill == 0 and batch.num_decode > 0
                 and all(s.params.temperature <= 0.0 for s in states)):
@@ -234,7 +288,7 @@ class ModelRunner:
             if g is None and self.ep is None and bb not in self.failed_buckets:
                 g = self._capture(bb)          # first use of a bucket that was not captured at start-up
             if g is not None and g.usable():
-                return self._execute_decode_graph(batch)
+                return self._launch_decode_graph(batch, plan, prev_ids)
         if (top_lp is None and self.use_mixed_graphs and batch.num_prefill > 0
                 and all(s.params.temperature <= 0.0 for s in states)):
             key = self.mixed_key(int(batch.num_tokens), int(batch.num_decode), int(batch.num_prefill))
@@ -243,7 +297,7 @@ class ModelRunner:
                 if g is None and key not in self.failed_buckets:
                     g = self._capture_mixed(key)      # first use of a shape that was not captured at start-up
                 if g is not None:
-                    return self._execute_mixed_graph(g, batch)
+                    return self._launch_mixed_graph(g, batch, plan, prev_ids)
         st = self.staging
         st.begin()
         T, B = int(batch.num_tokens), int(batch.num_seqs)
@@ -268,9 +322,13 @@ class ModelRunner:
             seg_temp = st.put(np.array([s.params.temperature for s in states], dtype=np.float32), np.float32)
             seg_topk = st.put(np.array([s.params.top_k for s in states], dtype=np.int32), np.int32)
             seg_topp = st.put(np.array([s.params.top_p for s in states], dtype=np.float32), np.float32)
+        if plan is not None:
+            seg_prow, seg_psrc = st.put(plan[0], np.int32), st.put(plan[1], np.int32)
         self.h2d_bytes = st.flush()
 
         token_ids = st.view(seg_tok, torch.int64)
+        if plan is not None:
+            self._patch(token_ids, st.view(seg_prow, torch.int32), st.view(seg_psrc, torch.int32), prev_ids, len(plan[0]))
         slots = st.view(seg_slot, torch.int64)
         positions = st.view(seg_pos, torch.int32)
         ctx_np = batch.ctx_lens
@@ -290,8 +348,7 @@ class ModelRunner:
             self.model.forward(token_ids, positions, slots, meta, self.kv_caches, rows)
             if self.step_events is not None:
                 self.step_events[1].record()
-            self.d2h_bytes = 0
-            return []
+            return self._finish_launch(None, 0)
         # log-probabilities need the logits themselves: no arg-max inside the forward pass for such a step
         fused_greedy = greedy and top_lp is None and getattr(self.model, "greedy_in_forward", False)
         if fused_greedy:
@@ -318,14 +375,16 @@ class ModelRunner:
                 self.last_logprobs = [(chosen[r], []) for r in range(S)]
         if self.step_events is not None:
             self.step_events[1].record()
-        if self.cuda:
-            self.ids_host[:S].copy_(ids, non_blocking=True)
-            torch.cuda.current_stream(self.device).synchronize()
-            out = self.ids_host[:S].tolist()
+        return self._finish_launch(ids, S)
+
+    def _patch(self, token_ids, rows, src, prev_ids, n: int) -> None:
+        if token_ids.is_cuda:
+            from .. import _ext
+
+            _ext.require().patch_tokens(token_ids, rows, src, prev_ids, n, ops._state.get(self.device).status)
+            ops._count()
         else:
-            out = ids.tolist()
-        self.d2h_bytes = S * 8
-        return out
+            token_ids[rows[:n].long()] = prev_ids[src[:n].long()].to(token_ids.dtype)
 
     # ------------------------------------------------------------------------------------------------
     # decode-only steps: CUDA graph per batch-size bucket
@@ -336,11 +395,13 @@ class ModelRunner:
                 return x
         return self.buckets[-1]
 
-    def _execute_decode_graph(self, batch) -> list[int]:
+    def _launch_decode_graph(self, batch, plan=None, prev_ids=None) -> "StepHandle":
         B = int(batch.num_seqs)
         bb = self._bucket(B)
         g = self.graphs[bb]
-        self.h2d_bytes = g.stage(batch, B)
+        self.h2d_bytes = g.stage(batch, B, plan)
+        if plan is not None:
+            self._patch(g.tok, g.fix_rows, g.fix_src, prev_ids, len(plan[0]))
         if self.step_events is not None:
             self.step_events[0].record()
         g.graph.replay()
@@ -350,14 +411,16 @@ class ModelRunner:
         self.graph_kernel_launches += g.kernel_launches
         if self.ep is not None:
             self.ep._calls += g.ep_calls     # the replay ran that many MoE layers: keep the buffer-bank parity in step
-        self.ids_host[:B].copy_(g.ids[:B], non_blocking=True)
-        torch.cuda.current_stream(self.device).synchronize()
-        self.d2h_bytes = B * 8
-        return self.ids_host[:B].tolist()
+        return self._finish_launch(g.ids, B)
 
-    def _execute_mixed_graph(self, g: "_MixedGraph", batch) -> list[int]:
+    def _execute_decode_graph(self, batch) -> list[int]:
+        return self.collect(self._launch_decode_graph(batch))
+
+    def _launch_mixed_graph(self, g: "_MixedGraph", batch, plan=None, prev_ids=None) -> "StepHandle":
         S = int(len(batch.sample_rows))
-        self.h2d_bytes = g.stage(batch)
+        self.h2d_bytes = g.stage(batch, plan)
+        if plan is not None:
+            self._patch(g.tok, g.fix_rows, g.fix_src, prev_ids, len(plan[0]))
         if self.step_events is not None:
             self.step_events[0].record()
         g.graph.replay()
@@ -366,13 +429,17 @@ class ModelRunner:
         self.graph_launches += 1
         self.mixed_launches += 1
         self.graph_kernel_launches += g.kernel_launches
-        if S == 0:
-            self.d2h_bytes = 0      # mid-prompt chunks only: nothing to read back, the host runs ahead
-            return []
-        self.ids_host[:S].copy_(g.ids[:S], non_blocking=True)
-        torch.cuda.current_stream(self.device).synchronize()
-        self.d2h_bytes = S * 8
-        return self.ids_host[:S].tolist()
+        return self._finish_launch(g.ids, S)     # S == 0: mid-prompt chunks only, nothing to read back
+
+
+class StepHandle:
+    """A launched step: `ids` is the device tensor of its sampled token ids (first `S` entries), of which a copy is on
+    its way into pinned slot `slot` (`event` marks its arrival); `tokens` holds them already when nothing was queued."""
+
+    __slots__ = ("S", "ids", "slot", "event", "tokens")
+
+    def __init__(self, S, ids, slot=0, event=None, tokens=None):
+        self.S, self.ids, self.slot, self.event, self.tokens = S, ids, slot, event, tokens
 
 
 class _DecodeGraph:
@@ -387,7 +454,8 @@ class _DecodeGraph:
         self.o_tok, self.o_slot = 0, 8 * bb
         self.o_pos, self.o_ctx = 16 * bb, 20 * bb
         self.o_bt = _align(24 * bb)
-        nbytes = self.o_bt + 4 * bb * mb
+        self.o_fix = _align(self.o_bt + 4 * bb * mb)      # rows / sources of tokens still on the device (pipelined stepping)
+        nbytes = self.o_fix + 8 * bb
         self.host = torch.zeros(nbytes, dtype=torch.uint8, pin_memory=True)
         self.np = self.host.numpy()
         self.dev = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
@@ -398,6 +466,10 @@ class _DecodeGraph:
         self.ctx = d[self.o_ctx:self.o_ctx + 4 * bb].view(torch.int32)
         self.bt = d[self.o_bt:self.o_bt + 4 * bb * mb].view(torch.int32).view(bb, mb)
         self.cu = torch.arange(bb + 1, dtype=torch.int32, device=dev)
+        self.fix_rows = d[self.o_fix:self.o_fix + 4 * bb].view(torch.int32)
+        self.fix_src = d[self.o_fix + 4 * bb:self.o_fix + 8 * bb].view(torch.int32)
+        self.h_fix = self.np[self.o_fix:self.o_fix + 8 * bb].view(np.int32)
+        self.copied = torch.cuda.Event()
         self.h_tok = self.np[self.o_tok:self.o_tok + 8 * bb].view(np.int64)
         self.h_slot = self.np[self.o_slot:self.o_slot + 8 * bb].view(np.int64)
         self.h_pos = self.np[self.o_pos:self.o_pos + 4 * bb].view(np.int32)
@@ -447,8 +519,13 @@ class _DecodeGraph:
         ep = self.runner.ep
         return ep is None or (self.ep_calls % 2 == 0 and (ep._calls & 1) == self.ep_parity)
 
-    def stage(self, batch, B: int) -> int:
+    def stage(self, batch, B: int, plan=None) -> int:
         bb = self.bb
+        self.copied.synchronize()       # the previous copy out of this block has been consumed
+        if plan is not None:
+            n = len(plan[0])
+            self.h_fix[:n] = plan[0]
+            self.h_fix[bb:bb + n] = plan[1]
         self.h_tok[:B] = batch.token_ids
         self.h_slot[:B] = batch.slots
         self.h_pos[:B] = batch.positions
@@ -461,6 +538,7 @@ class _DecodeGraph:
         bt = batch.block_tables
         self.h_bt[:B, :bt.shape[1]] = bt
         self.dev.copy_(self.host, non_blocking=True)
+        self.copied.record()
         return self.host.numel()
 
 
@@ -486,6 +564,7 @@ class _MixedGraph:
         seg("d_ctx", 4 * max(db, 1)); seg("d_bt", 4 * max(db, 1) * mb)
         seg("p_cu", 4 * (pb + 1)); seg("p_ctx", 4 * pb); seg("p_bt", 4 * pb * mb)
         seg("work", 8 * self.max_items); seg("n_work", 4); seg("rows", 8 * self.sb)
+        seg("fix_rows", 4 * self.sb); seg("fix_src", 4 * self.sb)   # tokens still on the device (pipelined stepping)
         self.nbytes = off
         self.host = torch.zeros(off, dtype=torch.uint8, pin_memory=True)
         self.dev = torch.zeros(off, dtype=torch.uint8, device=dev)
@@ -505,11 +584,13 @@ class _MixedGraph:
         self.h = {"tok": hv("tok", np.int64), "slot": hv("slot", np.int64), "pos": hv("pos", np.int32),
                   "d_ctx": hv("d_ctx", np.int32), "d_bt": hv("d_bt", np.int32, (max(db, 1), mb)),
                   "p_cu": hv("p_cu", np.int32), "p_ctx": hv("p_ctx", np.int32), "p_bt": hv("p_bt", np.int32, (pb, mb)),
-                  "work": hv("work", np.int32, (self.max_items, 2)), "n_work": hv("n_work", np.int32), "rows": hv("rows", np.int64)}
+                  "work": hv("work", np.int32, (self.max_items, 2)), "n_work": hv("n_work", np.int32), "rows": hv("rows", np.int64),
+                  "fix_rows": hv("fix_rows", np.int32), "fix_src": hv("fix_src", np.int32)}
         self.h["slot"][:] = -1
         self.dev.copy_(self.host)
         self.tok, self.slot, self.pos = dv("tok", torch.int64), dv("slot", torch.int64), dv("pos", torch.int32)
         self.rows = dv("rows", torch.int64)
+        self.fix_rows, self.fix_src = dv("fix_rows", torch.int32), dv("fix_src", torch.int32)
         n_kv = runner.kv_caches[0][0].shape[1]
         static = ops.StaticAttn(db, dv("d_ctx", torch.int32), dv("d_bt", torch.int32, (max(db, 1), mb)),
                                 ops._decode_splits(db, n_kv, runner.cfg.max_model_len) if db else 1,
@@ -543,10 +624,16 @@ class _MixedGraph:
         self.kernel_launches = ops.launch_count - before
         ops.launch_count = before
 
-    def stage(self, batch) -> int:
+    def stage(self, batch, plan=None) -> int:
         """Fill the pinned block from the scheduler's batch and start its copy. Returns the bytes copied."""
         self.copied.synchronize()       # the previous copy out of this block has been consumed
         h = self.h
+        if plan is not None:
+            n = len(plan[0])
+            if n > self.sb:
+                raise RuntimeError(f"mixed-step graph {self.tb, self.db, self.pb}: {n} device-side tokens exceed {self.sb}")
+            h["fix_rows"][:n] = plan[0]
+            h["fix_src"][:n] = plan[1]
         T, B, nd = int(batch.num_tokens), int(batch.num_seqs), int(batch.num_decode)
         P = B - nd
         h["tok"][:T] = batch.token_ids

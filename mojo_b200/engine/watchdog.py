@@ -127,6 +127,8 @@ def recover(engine) -> list[int]:
     """Re-queue every unfinished request of `engine` for recomputation: its new prompt is the old prompt plus the
     tokens already produced, its token budget shrinks by the same amount, and its KV pages are released. Returns
     the re-queued request ids (same ids, so callers that stream by id keep working)."""
+    if hasattr(engine, "discard_inflight"):
+        engine.discard_inflight()      # a pipelined engine may have a step in flight whose tokens were never booked
     redo = []
     for rid, st in list(engine.requests.items()):
         if st.finished:

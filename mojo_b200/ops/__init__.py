@@ -332,6 +332,12 @@ def _decode_splits(batch: int, n_kv: int, max_ctx: int) -> int:
     return max(1, min(want, max_ctx // 128, 32))
 
 
+def _decode_launches(splits: int, page_size: int) -> int:
+    """Kernels one decode-attention call launches: the split that finishes last merges the partials itself on the TMA
+    path (page sizes that are multiples of 32); the cp.async path merges with a second kernel."""
+    return 1 if splits == 1 or page_size % 32 == 0 else 2
+
+
 # Prefill attention on tcgen05 for head_dim 128 and 128-token pages (False: the mma.sync kernel for every shape).
 prefill_tensor_core = True
 
@@ -357,8 +363,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         # captured step: fixed grids, everything that varies is read from device memory
         if sa.d_rows > 0:
             C.attn_decode(q[:sa.d_rows], k_cache, v_cache, out[:sa.d_rows], sa.d_ctx, sa.d_bt, st.attn_ws, head_dim, sa.d_splits,
-                          scale, st.status)
-            _count(2 if sa.d_splits > 1 else 1)
+                          scale, st.status, st.attn_counters)
+            _count(_decode_launches(sa.d_splits, k_cache.shape[2]))
         if sa.max_items > 0:
             C.attn_prefill_tc(q, k_cache, v_cache, out, sa.p_cu, sa.p_ctx, sa.p_bt, sa.max_q_len, scale, 0, st.status,
                               sa.work, sa.n_work, sa.max_items)
@@ -368,8 +374,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     if nd > 0:
         splits = _decode_splits(nd, k_cache.shape[1], meta.max_ctx)
         C.attn_decode(q[:nd], k_cache, v_cache, out[:nd], meta.ctx_lens[:nd], meta.block_tables[:nd], st.attn_ws, head_dim,
-                      splits, scale, st.status)
-        _count(2 if splits > 1 else 1)
+                      splits, scale, st.status, st.attn_counters)
+        _count(_decode_launches(splits, k_cache.shape[2]))
     if ns > nd:
         # cu_q offsets are absolute token rows, so q/out are passed whole
         if prefill_on_tensor_core(head_dim, k_cache.shape[2]):

@@ -33,6 +33,8 @@ class _DeviceState:
         self.status = torch.zeros(8, dtype=torch.int32, device=device)
         self.gemm_ws = torch.zeros(GEMM_WORKSPACE_BYTES // 4, dtype=torch.int32, device=device)
         self.attn_ws = torch.empty(ATTN_WORKSPACE_BYTES // 4, dtype=torch.float32, device=device)
+        # per (sequence, kv head) arrival counters of the split decode attention (self-resetting; zero between launches)
+        self.attn_counters = torch.zeros(1 << 18, dtype=torch.int32, device=device)
 
 
 _states: dict[int, _DeviceState] = {}
@@ -61,4 +63,5 @@ def check_status(device: torch.device | None = None, reset: bool = True) -> None
     if reset:
         st.status.zero_()
         st.gemm_ws[: 65536].zero_()  # split-K counters may be left mid-count by an aborted kernel
+        st.attn_counters.zero_()
     raise KernelError(code, int(words[1]), int(words[2]), int(words[3]), a, b)

@@ -55,34 +55,47 @@ def _rope_kvwrite(q, k, v, cos_sin, positions, slots, k_cache, v_cache, head_dim
 
 
 def _paged_attention(q, k_cache, v_cache, meta, scale, head_dim, out=None):
+    """Decode rows and prefill chunks as two batched scaled_dot_product_attention calls over K/V gathered through the
+    block tables and padded to the longest context / chunk of the step (`meta.max_ctx`, `meta.max_q_len`, both known on
+    the host): no per-sequence loop and no device->host synchronisation."""
     T = q.shape[0]
     n_kv, page = k_cache.shape[1], k_cache.shape[2]
     qh = q.reshape(T, -1, head_dim)
-    o = torch.empty(T, qh.shape[1], head_dim, dtype=q.dtype, device=q.device)
-    nd = meta.num_decode
+    n_q = qh.shape[1]
+    # one spare row takes the writes of padding positions
+    o = torch.zeros(T + 1, n_q, head_dim, dtype=q.dtype, device=q.device)
+    nd, ns = meta.num_decode, meta.num_seqs
+    n_pages = max(1, min((max(meta.max_ctx, 1) + page - 1) // page, meta.block_tables.shape[1]))
+    kpos = torch.arange(n_pages * page, device=q.device)
+
+    def gather(bt):
+        k = k_cache[bt.long()].permute(0, 2, 1, 3, 4).reshape(bt.shape[0], n_kv, -1, head_dim)
+        v = v_cache[bt.long()].permute(0, 2, 1, 3, 4).reshape(bt.shape[0], n_kv, -1, head_dim)
+        return k, v
+
     if nd > 0:
-        bt = meta.block_tables[:nd].long()
-        k = k_cache[bt].permute(0, 2, 1, 3, 4).reshape(nd, n_kv, -1, head_dim)
-        v = v_cache[bt].permute(0, 2, 1, 3, 4).reshape(nd, n_kv, -1, head_dim)
-        mask = torch.arange(k.shape[2], device=q.device)[None, :] < meta.ctx_lens[:nd, None]
+        k, v = gather(meta.block_tables[:nd, :n_pages])
+        mask = kpos[None, :] < meta.ctx_lens[:nd, None]
         o[:nd] = F.scaled_dot_product_attention(qh[:nd].unsqueeze(2), k, v, attn_mask=mask[:, None, None, :], scale=scale,
                                                 enable_gqa=True).squeeze(2)
-    cu, ctx = meta.cu_q.tolist(), meta.ctx_lens.tolist()
-    for b in range(nd, meta.num_seqs):
-        s, e, c = cu[b], cu[b + 1], ctx[b]
-        n_pages = (c + page - 1) // page
-        bt = meta.block_tables[b, :n_pages].long()
-        k = k_cache[bt].permute(1, 0, 2, 3).reshape(n_kv, -1, head_dim)[:, :c]
-        v = v_cache[bt].permute(1, 0, 2, 3).reshape(n_kv, -1, head_dim)[:, :c]
-        ql = e - s
-        mask = torch.arange(c, device=q.device)[None, :] <= torch.arange(c - ql, c, device=q.device)[:, None]
-        o[s:e] = F.scaled_dot_product_attention(qh[s:e].transpose(0, 1).unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0),
-                                                attn_mask=mask, scale=scale, enable_gqa=True)[0].transpose(0, 1)
-    return o.reshape(T, -1)
+    if ns > nd:
+        P, Lq = ns - nd, max(1, meta.max_q_len)
+        cu = meta.cu_q[nd:].long()
+        q_len, ctx = cu[1:] - cu[:-1], meta.ctx_lens[nd:].long()
+        ar = torch.arange(Lq, device=q.device)
+        valid = ar[None, :] < q_len[:, None]                                   # [P, Lq]
+        rows = torch.where(valid, cu[:-1, None] + ar[None, :], torch.full_like(valid, T, dtype=torch.long))
+        qp = qh[rows.clamp(max=T - 1)].permute(0, 2, 1, 3)                      # [P, heads, Lq, D]
+        k, v = gather(meta.block_tables[nd:, :n_pages])
+        pos_q = (ctx - q_len)[:, None] + ar[None, :]                            # absolute position of every query row
+        mask = kpos[None, None, :] <= pos_q[:, :, None]                         # causal; rows past the chunk see a harmless prefix
+        res = F.scaled_dot_product_attention(qp, k, v, attn_mask=mask[:, None], scale=scale, enable_gqa=True)
+        o.index_put_((rows.reshape(-1),), res.permute(0, 2, 1, 3).reshape(P * Lq, n_q, head_dim))
+    return o[:T].reshape(T, -1)
 
 
 def enable() -> None:
-    """Swap the op table. CUDA-graph capture stays off for this mode (the attention fallback syncs)."""
+    """Swap the op table. CUDA-graph capture stays off for this mode (plain eager PyTorch is the point of the arm)."""
     global _enabled
     if _enabled:
         return

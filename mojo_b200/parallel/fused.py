@@ -71,6 +71,8 @@ class FusedTPComm:
         self.layout = lay
         self.region = SymmRegion(off, info)
         self.peers = self.region.ptrs
+        # with a multicast mapping the fused GEMM -> reduce-scatter / all-reduce kernel reduces inside the NVLink switch
+        self.mc_ptr = int(self.region.mc_ptr) if self.nvls else 0
         self.timeout_ns = int(timeout_s * 1e9)
         self._rs_calls = 0
         self._ag_calls = 0
@@ -141,7 +143,7 @@ class FusedTPComm:
             return coll.all_reduce_staged((M, N))
         slot = self._rs_calls & 1
         self._rs_calls += 1
-        self.C.tp_gemm_rs(x, w, self.rank, self.peers, self.layout, None, residual, 1, slot, self.timeout_ns, config, self.status)
+        self.C.tp_gemm_rs(x, w, self.rank, self.peers, self.layout, None, residual, 1, slot, self.timeout_ns, config, self.status, self.mc_ptr)
         ops._count()
         return self.region.view(self.layout.off_yall + slot * self.layout.yall_half_bytes, (M, N), torch.bfloat16)
 
@@ -212,7 +214,14 @@ class FusedTPComm:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
                 times[form] = float(t)
             report[M] = times
-            table.append((M, min(times, key=times.get)))
+            best = min(times, key=times.get)
+            # the single-kernel forms leave one launch fewer in the captured step than what this eager timing shows:
+            # another form must win clearly to displace them
+            for single in ("nvls_norm", "oneshot_norm"):
+                if single in times and times[single] <= 1.08 * times[best]:
+                    best = single
+                    break
+            table.append((M, best))
         self._norm_table[(N, K)] = table
         ops.check_status(dev)
         return report
@@ -252,7 +261,7 @@ class FusedTPComm:
         out = torch.empty(M // self.world_size, N, dtype=x.dtype, device=x.device)
         slot = self._rs_calls & 1
         self._rs_calls += 1
-        self.C.tp_gemm_rs(x, w, self.rank, self.peers, self.layout, out, residual, 0, slot, self.timeout_ns, config, self.status)
+        self.C.tp_gemm_rs(x, w, self.rank, self.peers, self.layout, out, residual, 0, slot, self.timeout_ns, config, self.status, self.mc_ptr)
         ops._count()
         return out
 

@@ -264,16 +264,17 @@ def test_decode_graph_dispatch_and_fallback_when_a_capture_fails(monkeypatch):
         def usable(self):
             return True
 
-    def fake_replay(batch):
+    def fake_replay(batch, plan=None, prev_ids=None):
         replayed.append(int(batch.num_seqs))
         runner.use_graphs = False                      # compute the step's tokens through the eager path
         try:
-            return runner.execute(batch, [eng.requests[int(r)] for r in batch.sample_seq_ids], 0)
+            toks = runner.execute(batch, [eng.requests[int(r)] for r in batch.sample_seq_ids], 0)
         finally:
             runner.use_graphs = True
+        return mr.StepHandle(len(toks), None, tokens=toks)
 
     monkeypatch.setattr(mr, "_DecodeGraph", FakeGraph)
-    monkeypatch.setattr(runner, "_execute_decode_graph", fake_replay)
+    monkeypatch.setattr(runner, "_launch_decode_graph", fake_replay)
     runner.use_graphs = True
     with warnings.catch_warnings(record=True) as w:
         warnings.simplefilter("always")
@@ -315,3 +316,100 @@ def test_mixed_step_buckets_cover_every_schedulable_batch():
         tb, db, pb = k
         assert k in keys and tb >= T and db >= nd and pb >= P and db <= tb and pb <= tb
     assert r.mixed_key(300, 2, 33) is None and r.mixed_key(300, 300, 0) is None     # too many chunks / no chunk: not a mixed step
+
+
+def test_torch_baseline_attention_matches_the_oracle():
+    """The comparison arm's attention (two padded scaled_dot_product_attention calls) against the fp32 oracle on a batch
+    of decode rows and prefill chunks with cached prefixes."""
+    from mojo_b200 import ops
+    from mojo_b200.ops import reference, torch_baseline
+
+    g = torch.Generator().manual_seed(5)
+    n_q, n_kv, D, page = 4, 2, 32, 16
+    q_lens, ctx = [1, 1, 7, 20, 3], [9, 33, 7, 36, 19]          # two decode rows; chunks with 0, 16 and 16 cached tokens
+    T, B = sum(q_lens), len(q_lens)
+    pages_per = [(c + page - 1) // page for c in ctx]
+    num_pages = sum(pages_per) + 1
+    kc, vc = torch.randn(num_pages, n_kv, page, D, generator=g), torch.randn(num_pages, n_kv, page, D, generator=g)
+    bt = torch.zeros(B, max(pages_per), dtype=torch.int32)
+    nxt = 1
+    for b, n in enumerate(pages_per):
+        bt[b, :n] = torch.arange(nxt, nxt + n)
+        nxt += n
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    q = torch.randn(T, n_q * D, generator=g)
+    meta = ops.AttnMeta(cu, torch.tensor(ctx, dtype=torch.int32), bt, 2, max(q_lens), max(ctx))
+    want = reference.paged_attention(q.reshape(T, n_q, D), kc, vc, cu, meta.ctx_lens, bt, 0.2).reshape(T, -1)
+    got = torch_baseline._paged_attention(q, kc, vc, meta, 0.2, D)
+    torch.testing.assert_close(got, want, atol=2e-5, rtol=1e-4)
+
+
+def _pipelined_engine(**kw):
+    base = dict(model=tiny_llama(), device="cpu", dtype=torch.float32, page_size=16, num_pages=64, max_num_seqs=8,
+                max_num_batched_tokens=64, max_model_len=256, seed=0, async_scheduling=True)
+    base.update(kw)
+    return LLMEngine(EngineConfig(**base))
+
+
+def test_pipelined_stepping_gives_the_same_tokens_one_call_later():
+    """The host schedules one step ahead: placeholders stand in for tokens not read yet, decode rows take their input
+    from the in-flight step's output, length limits take effect at launch. Same tokens as the step-by-step engine."""
+    g = torch.Generator().manual_seed(31)
+    prompts = [torch.randint(0, 32000, (n,), generator=g).tolist() for n in (5, 70, 33, 16, 100, 3)]
+    params = [SamplingParams(max_tokens=m) for m in (12, 1, 7, 30, 2, 9)]
+    want = make_engine(budget=64).generate(prompts, params)
+    eng = _pipelined_engine()
+    got = eng.generate(prompts, params)
+    assert got == want
+    assert eng._inflight is None and not eng.has_unfinished() and eng.kv.check_invariants() == ""
+    assert eng.kv.stats().free_pages == eng.kv.stats().num_pages          # every page came back
+    # outputs trail the launches by one call
+    eng = _pipelined_engine()
+    eng.add_request(prompts[0], SamplingParams(max_tokens=3))
+    assert eng.step() == []                                # prefill launched, nothing read yet
+    first = eng.step()
+    assert len(first) == 1 and len(first[0].output_ids) == 1
+
+
+def test_pipelined_stepping_drops_the_token_after_a_stop_token_and_recovers_from_preemption():
+    g = torch.Generator().manual_seed(32)
+    prompts = [torch.randint(0, 32000, (40,), generator=g).tolist() for _ in range(4)]
+    ref = make_engine().generate(prompts, SamplingParams(max_tokens=40))
+    # a stop token that appears in the reference output ends that request there, also when the next step was already in flight
+    stop = ref[1][5]
+    params = SamplingParams(max_tokens=40, stop_token_ids=(stop,))
+    want = make_engine().generate(prompts, params)
+    assert any(len(w) < 40 for w in want)
+    got = _pipelined_engine(max_num_batched_tokens=256, max_model_len=512).generate(prompts, params)
+    assert got == want
+    # twelve pages cannot hold four sequences of 80 tokens: someone is preempted with a placeholder pending
+    eng = _pipelined_engine(num_pages=12, max_num_batched_tokens=256, max_model_len=512)
+    assert eng.generate(prompts, SamplingParams(max_tokens=40)) == ref
+    assert eng.scheduler.total_preemptions() > 0 and eng.kv.check_invariants() == ""
+
+
+def test_pipelined_stepping_with_prefix_cache_and_recovery():
+    from mojo_b200.engine.watchdog import recover
+    from mojo_b200.utils import fault
+
+    g = torch.Generator().manual_seed(33)
+    shared = torch.randint(0, 32000, (48,), generator=g).tolist()
+    prompts = [shared + [11, 12, 13], shared + [21, 22], shared[:20]]
+    sp = SamplingParams(max_tokens=8)
+    want = make_engine().generate(prompts, sp)
+    eng = _pipelined_engine(enable_prefix_cache=True)
+    assert eng.generate(prompts[:1], sp) == want[:1]
+    assert eng.generate(prompts[1:], sp) == want[1:]
+    assert eng.kv.stats().prefix_hits >= 3 and eng.kv.check_invariants() == ""
+    # a fault after a launch: the step in flight is discarded, the requests are re-queued, the tokens are unchanged
+    eng = _pipelined_engine()
+    eng.fault = fault.FaultInjector("raise_after:rank=0:step=3", 0)
+    rids = [eng.add_request(p, sp) for p in prompts]
+    raised = 0
+    while eng.has_unfinished():
+        try:
+            eng.step()
+        except fault.InjectedFault:
+            raised += 1
+            assert recover(eng)
+    assert raised == 1 and [eng.requests[r].output_ids for r in rids] == want

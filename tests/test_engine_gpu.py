@@ -65,9 +65,10 @@ def _cfg128():
                        vocab_size=4096, max_position_embeddings=2048, tie_word_embeddings=True)
 
 
-def _engine128(device, dtype, graphs, budget, page=128, mixed=True):
+def _engine128(device, dtype, graphs, budget, page=128, mixed=True, pipelined=False):
     ecfg = EngineConfig(model=_cfg128(), device=device, dtype=dtype, page_size=page, num_pages=64 if page == 128 else 512, max_num_seqs=8,
-                        max_num_batched_tokens=budget, max_model_len=1024, seed=0, use_cuda_graphs=graphs, mixed_step_graphs=mixed)
+                        max_num_batched_tokens=budget, max_model_len=1024, seed=0, use_cuda_graphs=graphs, mixed_step_graphs=mixed,
+                        async_scheduling=pipelined)
     model = build_model(_cfg128(), device, dtype).init_random(0, std=0.08)
     return LLMEngine(ecfg, model=model)
 
@@ -105,6 +106,24 @@ def test_mixed_step_graphs_give_the_eager_tokens():
     assert [o[0] for o in got] == [o[0] for o in got_eager]
     # a second batch through the same (already captured) graphs: replay is deterministic
     assert eng.generate(prompts, sp) == got
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_pipelined_stepping_matches_step_by_step_on_the_device(graphs):
+    """The host one step ahead of the device: decode rows take their input token from the in-flight step's output through
+    the patch kernel, sampled ids come back through two pinned slots. Same launches, same inputs: identical tokens."""
+    g = torch.Generator().manual_seed(23)
+    prompts = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in (300, 40, 700, 129, 5, 260)]
+    params = [SamplingParams(max_tokens=m) for m in (20, 1, 9, 33, 2, 17)]
+    want = _engine128("cuda", torch.bfloat16, graphs, budget=256).generate(prompts, params)
+    eng = _engine128("cuda", torch.bfloat16, graphs, budget=256, pipelined=True)
+    got = eng.generate(prompts, params)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert got == want
+    assert eng._inflight is None and eng.kv.check_invariants() == ""
+    if graphs:
+        assert eng.runner.mixed_launches > 0 and eng.runner.graph_launches > eng.runner.mixed_launches
 
 
 @pytest.mark.parametrize("graphs", [False, True])

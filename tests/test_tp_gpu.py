@@ -24,10 +24,20 @@ def test_fused_tp_kernels_two_gpus():
     assert "TP_FUSED_OK 2" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_tp_kernels_in_switch_reduction_two_gpus():
+    """The fused GEMM -> reduce-scatter / all-reduce kernel with its reduction in the NVLink switch (partials stay local,
+    the owner reads them with multimem.ld_reduce). Every rank runs to the end: no wait is made to run out here."""
+    p = _run("mp_tp_fused.py", 2, 29620, extra_env={"B2_TEST_NVLS": "1"})
+    assert "TP_FUSED_OK 2" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_fused_tp_kernels_all_gpus():
     n = 8 if torch.cuda.device_count() >= 8 else 4
     p = _run("mp_tp_fused.py", n, 29612)
+    assert f"TP_FUSED_OK {n}" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+    p = _run("mp_tp_fused.py", n, 29621, extra_env={"B2_TEST_NVLS": "1"})
     assert f"TP_FUSED_OK {n}" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
 
 
