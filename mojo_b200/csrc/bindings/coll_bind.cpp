@@ -5,6 +5,7 @@
 #include "b2/api.h"
 #include "b2/launch.h"
 #include "b2/coll.h"
+#include "b2/symm_heap.h"
 namespace py = pybind11;
 
 namespace {
@@ -36,6 +37,54 @@ B2TpRegion make_region(int rank, const std::vector<int64_t>& ptrs) {
 }  // namespace
 
 void bind_coll(py::module_& m) {
+  // VMM-based symmetric heap segment (csrc/runtime/symm_heap.cpp). Errors surface as RuntimeError with the driver's code.
+  py::class_<b2::symm::HeapSegment>(m, "SymmHeapSegment")
+      .def(py::init<>())
+      .def("create",
+           [](b2::symm::HeapSegment& h, int device, int rank, int world, size_t bytes, bool multicast) {
+             const std::string e = h.create(device, rank, world, bytes, multicast);
+             if (!e.empty()) throw std::runtime_error(e);
+           })
+      .def("export_fd",
+           [](b2::symm::HeapSegment& h) {
+             std::string e;
+             const int fd = h.export_fd(&e);
+             if (fd < 0) throw std::runtime_error(e);
+             return fd;
+           })
+      .def("map_peer",
+           [](b2::symm::HeapSegment& h, int peer, int fd) {
+             const std::string e = h.map_peer(peer, fd);
+             if (!e.empty()) throw std::runtime_error(e);
+           })
+      .def("multicast_supported", &b2::symm::HeapSegment::multicast_supported)
+      .def("mc_create",
+           [](b2::symm::HeapSegment& h) {
+             std::string e;
+             const int fd = h.mc_create(&e);
+             if (fd < 0) throw std::runtime_error(e);
+             return fd;
+           })
+      .def("mc_import",
+           [](b2::symm::HeapSegment& h, int fd) {
+             const std::string e = h.mc_import(fd);
+             if (!e.empty()) throw std::runtime_error(e);
+           })
+      .def("mc_add_device",
+           [](b2::symm::HeapSegment& h) {
+             const std::string e = h.mc_add_device();
+             if (!e.empty()) throw std::runtime_error(e);
+           })
+      .def("mc_bind_and_map",
+           [](b2::symm::HeapSegment& h) {
+             const std::string e = h.mc_bind_and_map();
+             if (!e.empty()) throw std::runtime_error(e);
+           })
+      .def("bytes", &b2::symm::HeapSegment::bytes)
+      .def("ptr", &b2::symm::HeapSegment::ptr)
+      .def("mc_ptr", &b2::symm::HeapSegment::mc_ptr)
+      .def("close", &b2::symm::HeapSegment::close);
+
   py::class_<B2CollLayout>(m, "CollLayout")
       .def(py::init([]() { return B2CollLayout{}; }))
       .def_readwrite("off_buf", &B2CollLayout::off_buf)

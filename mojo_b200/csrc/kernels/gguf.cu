@@ -17,6 +17,27 @@
 namespace b2 {
 namespace {
 
+// One thread per 64 weights, wide loads (tensor 16-byte aligned).
+__global__ void dequant64_kernel(const uint8_t* __restrict__ wq, int ggml_type, __nv_bfloat16* __restrict__ out, int64_t n_pairs) {
+  const int64_t pidx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (pidx >= n_pairs) return;
+  const int64_t blk = pidx >> 2;
+  const int g0 = static_cast<int>(pidx & 3) * 2;
+  float v[64];
+  if (ggml_type == gguf::kTypeQ4K) gguf::q4k_dequant64(wq + blk * gguf::kQ4KBytes, g0, v);
+  else gguf::q6k_dequant64(wq + blk * gguf::kQ6KBytes, g0, v);
+  uint4* dst = reinterpret_cast<uint4*>(out + pidx * 64);
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint4 pk;
+    pk.x = ptx::pack_bf16x2(v[c * 8 + 0], v[c * 8 + 1]);
+    pk.y = ptx::pack_bf16x2(v[c * 8 + 2], v[c * 8 + 3]);
+    pk.z = ptx::pack_bf16x2(v[c * 8 + 4], v[c * 8 + 5]);
+    pk.w = ptx::pack_bf16x2(v[c * 8 + 6], v[c * 8 + 7]);
+    dst[c] = pk;
+  }
+}
+
 __global__ void dequant_kernel(const uint8_t* __restrict__ wq, int ggml_type, __nv_bfloat16* __restrict__ out, int64_t n_groups) {
   // one thread per 32 weights
   const int64_t gidx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -43,6 +64,7 @@ struct GgufFill {
   static constexpr bool kActive = true;
   const uint8_t* wq;
   int ggml_type, N, blocks_per_row;
+  int wide;   // the packed tensor is 16-byte aligned: Q4_K blocks are read 16 bytes at a time, Q6_K blocks 2 bytes at a time
   __device__ __forceinline__ void operator()(const gemm::WorkUnit& u, int kb, uint8_t* stage, int fw, int lane) const {
     const int r = fw * 32 + lane;
     const int n = u.p_coord + r;
@@ -51,8 +73,14 @@ struct GgufFill {
       const int sb = kb >> 2, g0 = (kb & 3) * 2;
       const uint8_t* blk = wq + (static_cast<int64_t>(n) * blocks_per_row + sb) * (ggml_type == gguf::kTypeQ4K ? gguf::kQ4KBytes : gguf::kQ6KBytes);
       if (ggml_type == gguf::kTypeQ4K) {
-        gguf::q4k_dequant32(blk, g0, v);
-        gguf::q4k_dequant32(blk, g0 + 1, v + 32);
+        if (wide) {
+          gguf::q4k_dequant64(blk, g0, v);
+        } else {
+          gguf::q4k_dequant32(blk, g0, v);
+          gguf::q4k_dequant32(blk, g0 + 1, v + 32);
+        }
+      } else if (wide) {
+        gguf::q6k_dequant64(blk, g0, v);
       } else {
         gguf::q6k_dequant32(blk, g0, v);
         gguf::q6k_dequant32(blk, g0 + 1, v + 32);
@@ -125,7 +153,7 @@ int launch_gguf(const void* x, const void* wq, int ggml_type, void* y, int M, in
   sched.num_kb = K / 64;
   sched.kb_per_split = sched.num_kb;
   sched.bn = BN;
-  GgufFill fill{static_cast<const uint8_t*>(wq), ggml_type, N, K / gguf::kQK};
+  GgufFill fill{static_cast<const uint8_t*>(wq), ggml_type, N, K / gguf::kQK, (reinterpret_cast<uintptr_t>(wq) & 15) == 0 ? 1 : 0};
   GgufEpiParams ep{static_cast<__nv_bfloat16*>(y), N, M, N};
   auto kern = gemm_gguf_kernel<BN, STAGES>;
   static DeviceOnce attr_once;
@@ -147,6 +175,12 @@ using namespace b2;
 extern "C" int b2_dequant_gguf(const void* wq, int ggml_type, void* out_bf16, int64_t n_elems, cudaStream_t stream) {
   if (n_elems <= 0) return 0;
   if (n_elems % gguf::kQK != 0 || gguf::block_bytes(ggml_type) == 0) return -kBadArgument;
+  if ((reinterpret_cast<uintptr_t>(wq) & 15) == 0 && (reinterpret_cast<uintptr_t>(out_bf16) & 15) == 0) {
+    const int64_t pairs = n_elems / 64;
+    dequant64_kernel<<<static_cast<unsigned>((pairs + 127) / 128), 128, 0, stream>>>(static_cast<const uint8_t*>(wq), ggml_type,
+                                                                                    static_cast<__nv_bfloat16*>(out_bf16), pairs);
+    return last_launch_rc();
+  }
   const int64_t groups = n_elems / 32;
   dequant_kernel<<<static_cast<unsigned>((groups + 127) / 128), 128, 0, stream>>>(static_cast<const uint8_t*>(wq), ggml_type,
                                                                                   static_cast<__nv_bfloat16*>(out_bf16), groups);

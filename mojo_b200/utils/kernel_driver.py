@@ -4,7 +4,8 @@ Small, self-terminating workloads (inputs larger than the 126 MB L2, a few GB at
 profiler capture of one kernel; with `--time` the case is timed with CUDA events instead and one JSON line is printed.
 Cases: gemm_large, gemm_pair (the same product on CTA pairs), gemm_prefill, gemm_decode, gemm_swiglu, gemm_fp8,
 gemm_fp8_decode, gemm_fp8_decode_nosplit (a narrow tensor-parallel shard at 256 tokens, with and without split-K),
-attn_decode, attn_prefill, mla_decode, mla_prefill, rmsnorm, sampling.
+attn_decode, attn_prefill, mla_decode, mla_prefill, rmsnorm, sampling (arg-max), sample_topk_topp, gemm_gguf_q4k,
+gemm_gguf_q6k, rope_kvwrite, all_reduce_norm_single.
 """
 from __future__ import annotations
 
@@ -169,11 +170,67 @@ def _case(name: str):
     if name == "sampling":
         lg = rnd(256, 128256)
         return (lambda: ops.argmax(lg)), 0.0, lg.numel() * 2
+    if name == "sample_topk_topp":
+        # temperature / top-k / top-p sampling of 256 rows over the Llama-3 vocabulary (radix select + Philox)
+        lg = rnd(256, 128256, scale=3.0)
+        temp = torch.full((256,), 0.8, device=DEV)
+        top_k = torch.full((256,), 50, dtype=torch.int32, device=DEV)
+        top_p = torch.full((256,), 0.9, device=DEV)
+        step = [0]
+
+        def run():
+            step[0] += 1
+            return ops.sample(lg, temp, top_k, top_p, 1234, step[0])
+
+        return run, 0.0, lg.numel() * 2
+    if name in ("gemm_gguf_q4k", "gemm_gguf_q6k"):
+        # decode-sized product against GGUF super-blocks (dequantisation fused into the tcgen05 GEMM): 16 tokens against a
+        # Llama-3.1-8B gate/up-sized matrix; the packed weights (Q4_K 4.5 bits, Q6_K 6.56 bits per weight) rotate through
+        # more copies than fit the L2
+        ggml = ops.GGML_Q4_K if name.endswith("q4k") else ops.GGML_Q6_K
+        M, N, K = 16, 28672, 4096
+        per = 144 if ggml == ops.GGML_Q4_K else 210
+        copies = [ref.random_gguf_blocks(N * K // 256, ggml, seed=i).to(DEV) for i in range(3)]
+        x = rnd(M, K)
+        turn = [0]
+
+        def run():
+            turn[0] += 1
+            return ops.linear_gguf(x, copies[turn[0] % len(copies)], ggml, N)
+
+        return run, 2.0 * M * N * K, N * K // 256 * per + (M * K + M * N) * 2
+    if name == "all_reduce_norm_single":
+        # all-reduce + residual add + RMSNorm on a world of one (the only "peer" is this GPU's own region): the one-shot
+        # kernel's memory behaviour without link traffic. The in-switch form needs a multicast mapping, which a single
+        # rank does not have; its multi-GPU timings are in the tuning tables of the serving benchmark.
+        from ..parallel.coll import SymmCollectives
+        from ..parallel.dist import DistInfo
+
+        rows, h = 32768, 4096
+        coll = SymmCollectives(DistInfo(0, 1, 0, torch.device(DEV), None, None), max_bytes=rows * h * 2, timeout_s=2.0)
+        part, res, w = rnd(rows, h), rnd(rows, h), torch.ones(h, device=DEV, dtype=torch.bfloat16)
+
+        def run():
+            coll.staging_view((rows, h)).copy_(part)
+            return coll.all_reduce_rmsnorm_staged((rows, h), w, 1e-5, res, form="one_shot")
+
+        return run, 0.0, rows * h * 2 * 4
+    if name == "rope_kvwrite":
+        T, n_q, n_kv, D, page = 16384, 32, 8, 128, 128
+        qkv = rnd(T, (n_q + 2 * n_kv) * D)
+        pages = T // page
+        kc, vc = torch.zeros(pages, n_kv, page, D, device=DEV, dtype=torch.bfloat16), torch.zeros(pages, n_kv, page, D, device=DEV, dtype=torch.bfloat16)
+        cos_sin = ref.rope_table(T, D, 500000.0, None).to(DEV)
+        pos = torch.arange(T, dtype=torch.int32, device=DEV)
+        slots = torch.arange(T, dtype=torch.int64, device=DEV)
+        q, k, v = qkv[:, :n_q * D], qkv[:, n_q * D:(n_q + n_kv) * D], qkv[:, (n_q + n_kv) * D:]
+        return (lambda: ops.rope_kvwrite(q, k, v, cos_sin, pos, slots, kc, vc, D)), 0.0, (2 * T * (n_q + n_kv) * D + 3 * T * n_kv * D) * 2
     raise SystemExit(f"unknown case {name!r}")
 
 
 CASES = ("gemm_large", "gemm_pair", "gemm_prefill", "gemm_decode", "gemm_swiglu", "gemm_fp8", "gemm_fp8_decode", "gemm_fp8_decode_nosplit",
-         "attn_decode", "attn_prefill", "mla_decode", "mla_prefill", "rmsnorm", "sampling")
+         "attn_decode", "attn_prefill", "mla_decode", "mla_prefill", "rmsnorm", "sampling", "sample_topk_topp", "gemm_gguf_q4k", "gemm_gguf_q6k",
+         "rope_kvwrite", "all_reduce_norm_single")
 # single-rank forms of the fused tensor-parallel and expert-parallel kernels (profiling only): tp_gemm_rs_single,
 # tp_ag_gemm_single, moe_ep_single
 

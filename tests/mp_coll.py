@@ -144,7 +144,7 @@ def main():
     assert coll.region.check_guard() == 0, f"rank {rank}: {coll.region.check_guard()} byte(s) of the guard band after the symmetric region were overwritten"
     dist.barrier()
     if rank == 0:
-        print(f"COLL_OK {tp} nvls={int(bool(coll.mc_ptr))}", flush=True)
+        print(f"COLL_OK {tp} nvls={int(bool(coll.mc_ptr))} heap={coll.region.backend}", flush=True)
     from mojo_b200.parallel.dist import shutdown
 
     shutdown()
