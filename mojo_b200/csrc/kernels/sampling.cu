@@ -110,32 +110,72 @@ __global__ void __launch_bounds__(kThreads) argmax_kernel(const void* logits, in
   }
 }
 
+// Visit every logit of a row with its index: 16-byte loads (8 bf16 / 4 f32 per load, consecutive threads on
+// consecutive vectors) when the row is 16-byte aligned, scalar loads otherwise and for the tail.
+template <bool BF16, class F>
+__device__ __forceinline__ void for_each_logit(const void* row, int vocab, F&& f) {
+  constexpr int V = BF16 ? 8 : 4;
+  const bool aligned = (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
+  const int nvec = aligned ? vocab / V : 0;
+  const uint4* rv = static_cast<const uint4*>(row);
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const uint4 q = rv[v];
+    if (BF16) {
+      float x[8];
+      bf16x8_to_f32(q, x);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f(x[j], v * 8 + j);
+    } else {
+      f(__uint_as_float(q.x), v * 4 + 0);
+      f(__uint_as_float(q.y), v * 4 + 1);
+      f(__uint_as_float(q.z), v * 4 + 2);
+      f(__uint_as_float(q.w), v * 4 + 3);
+    }
+  }
+  for (int i = nvec * V + threadIdx.x; i < vocab; i += blockDim.x) f(load_logit<BF16>(row, i), i);
+}
+
+constexpr int kWarps = kThreads / 32;
+
 // MSB-first radix walk. MASS = false: find the key of the `want`-th largest element (counts).
 // MASS = true: find the key at which the mass of strictly larger keys first reaches `want`.
 // Only keys >= floor_key participate. Returns the selected key.
+// Every warp accumulates into its own 256-bin histogram (logits crowd into a few exponent buckets: one shared
+// histogram serialises all 1024 threads on the same two or three words), and the warps' histograms are added up
+// afterwards. bf16 logits have 16 significant key bits, so their walk is two digits long instead of four.
 template <bool BF16, bool MASS>
 __device__ uint32_t radix_select(const void* row, int vocab, float want, uint32_t floor_key, float mx, float inv_t,
-                                 float* hist /* [256] */, float* bcast) {
+                                 float* hist /* [kWarps + 1][256] */, float* bcast) {
   uint32_t prefix = 0, mask = 0;
-  for (int pass = 3; pass >= 0; --pass) {
-    for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[b] = 0.0f;
+  const int warp = threadIdx.x >> 5;
+  float* mine = hist + warp * 256;
+  float* total = hist + kWarps * 256;
+  constexpr int kLastPass = BF16 ? 2 : 0;
+  for (int pass = 3; pass >= kLastPass; --pass) {
+    for (int b = threadIdx.x; b < (kWarps + 1) * 256; b += blockDim.x) hist[b] = 0.0f;
     __syncthreads();
     const int shift = pass * 8;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-      const float x = load_logit<BF16>(row, i);
+    for_each_logit<BF16>(row, vocab, [&](float x, int) {
       const uint32_t key = float_key(x);
       if (key >= floor_key && (key & mask) == prefix) {
         const float w = MASS ? ptx::ex2((x - mx) * inv_t) : 1.0f;
-        atomicAdd(&hist[(key >> shift) & 0xffu], w);
+        atomicAdd(&mine[(key >> shift) & 0xffu], w);
       }
+    });
+    __syncthreads();
+    if (threadIdx.x < 256) {
+      float acc = 0.0f;
+#pragma unroll 4
+      for (int w2 = 0; w2 < kWarps; ++w2) acc += hist[w2 * 256 + threadIdx.x];
+      total[threadIdx.x] = acc;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
       float acc = 0.0f;
       int b = 255;
       for (; b > 0; --b) {
-        if (acc + hist[b] >= want) break;
-        acc += hist[b];
+        if (acc + total[b] >= want) break;
+        acc += total[b];
       }
       bcast[0] = acc;
       bcast[1] = __int_as_float(b);
@@ -158,7 +198,7 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const void* logits, in
   ptx::grid_dep_sync();
   __shared__ ArgMax scratch[33];
   __shared__ float fscratch[33];
-  __shared__ float hist[256];
+  __shared__ float hist[(kWarps + 1) * 256];
   __shared__ float bcast[2];
   __shared__ float sums[kThreads];
   const int row = blockIdx.x;
@@ -179,10 +219,9 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const void* logits, in
     floor_key = radix_select<BF16, false>(base, vocab, static_cast<float>(k), 0u, mx, inv_t, hist, bcast);
   if (pp < 1.0f) {
     float z = 0.0f;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-      const float x = load_logit<BF16>(base, i);
+    for_each_logit<BF16>(base, vocab, [&](float x, int) {
       if (float_key(x) >= floor_key) z += ptx::ex2((x - mx) * inv_t);
-    }
+    });
     z = block_sum(z, fscratch);
     const uint32_t pkey = radix_select<BF16, true>(base, vocab, pp * z, floor_key, mx, inv_t, hist, bcast);
     floor_key = max(floor_key, pkey);
