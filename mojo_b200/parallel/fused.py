@@ -187,7 +187,7 @@ class FusedTPComm:
             return "oneshot_norm"
         return "split" if self._norm_form_ok("split", M, N) else "fused"
 
-    def tune_all_reduce_norm(self, N: int, K: int, token_counts, norm_weight: torch.Tensor | None = None, iters: int = 5) -> dict:
+    def tune_all_reduce_norm(self, N: int, K: int, token_counts, norm_weight: torch.Tensor | None = None, iters: int = 4) -> dict:
         """Time every valid form of `linear_all_reduce_norm` at each token count (all ranks call this together; the slowest
         rank decides) and remember the fastest. Returns {M: {form: microseconds}}."""
         dev = self.info.device
@@ -204,15 +204,18 @@ class FusedTPComm:
                 self.linear_all_reduce_norm(x, w, nw, 1e-5, res, form=form)
                 torch.cuda.synchronize(dev)
                 dist.barrier(group=self.group)
-                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                s.record()
-                for _ in range(iters):
-                    self.linear_all_reduce_norm(x, w, nw, 1e-5, res, form=form)
-                e.record()
-                e.synchronize()
-                t = torch.tensor([s.elapsed_time(e) * 1e3 / iters], device=dev)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
-                times[form] = float(t)
+                best = float("inf")
+                for _ in range(2):      # two rounds, the better one counts: a single hiccup must not decide the form
+                    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    s.record()
+                    for _ in range(iters):
+                        self.linear_all_reduce_norm(x, w, nw, 1e-5, res, form=form)
+                    e.record()
+                    e.synchronize()
+                    t = torch.tensor([s.elapsed_time(e) * 1e3 / iters], device=dev)
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+                    best = min(best, float(t))
+                times[form] = best
             report[M] = times
             best = min(times, key=times.get)
             # the single-kernel forms leave one launch fewer in the captured step than what this eager timing shows:

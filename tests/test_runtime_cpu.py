@@ -267,3 +267,17 @@ def test_assertion_modes_config_matrix(mode, ran_cheap, cheap, ran_costly, costl
     assert got["ran_passing"] == "1" and got["passing"] == "OK"
     if cheap == "ASSERT":      # the first record is kept: site kSiteTest with the offending index and its limit
         assert (got["site"], got["a"], got["b"]) == ("15", "41", "8")
+
+
+def test_symmetric_heap_rendezvous_passes_descriptors_between_ranks():
+    """The side channel of the VMM symmetric heap (descriptors over AF_UNIX sockets with SCM_RIGHTS, all ranks agreeing on
+    every step) with three CPU ranks and ordinary files standing in for the device allocations."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
+           "--master-port", "29655", os.path.join(root, "tests", "mp_fd_exchange_cpu.py")]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=180, cwd=root)
+    assert "FD_EXCHANGE_OK 3" in p.stdout, p.stdout[-2000:] + p.stderr[-2000:]
