@@ -44,6 +44,8 @@ METRIC_NAMES = {"llama-3.1-8b": "Llama-3.1-8B bf16", "llama-3.3-70b-fp8": "Llama
 # configurations that are one fixed batch present at t = 0: (requests, prompt tokens, output tokens)
 FIXED = {"llama-3.3-70b-fp8": (256, 1024, 256), "deepseek-v2-lite": (512, 512, 256), "tiny-deepseek": (64, 64, 16)}
 SECONDARY_DEADLINE_S = 420.0     # the two extra configurations together; past it the headline line goes out without them
+SECONDARY_GRACE_S = 90.0         # after the deadline the runs stop between steps; only if that does not happen either, every rank leaves
+ABANDON = threading.Event()
 
 
 def parse_args():
@@ -254,6 +256,17 @@ class Run:
         ops.check_status(info.device)
         return ramp
 
+    def abandoned(self) -> bool:
+        """True on every rank once rank 0's deadline for the secondary configurations has passed (rank 0 decides, the
+        others hear it over the host group, so that all ranks stop after the same step)."""
+        import torch
+
+        if self.info.world_size == 1:
+            return ABANDON.is_set()
+        flag = torch.tensor([1 if ABANDON.is_set() else 0], dtype=torch.int64)
+        torch.distributed.broadcast(flag, src=0, group=self.info.host_group)
+        return bool(flag[0])
+
     def sync(self) -> None:
         import torch
 
@@ -287,6 +300,11 @@ class Run:
             if outs is None:
                 continue
             k += 1
+            if steps is None and k % 32 == 0 and self.abandoned():
+                # every rank leaves at the same step, with nothing of the next one launched
+                engine.discard_inflight()
+                self.sync()
+                raise TimeoutError(f"abandoned after {k} steps: the time allowed for the secondary configurations ran out")
             tokens += len(outs)
             h2d += engine.runner.h2d_bytes
             d2h += engine.runner.d2h_bytes
@@ -456,13 +474,15 @@ def main() -> None:
         def give_up():
             # a secondary configuration that hangs must not cost the headline: every rank leaves, rank 0 prints what it has
             if info.rank == 0:
-                line["secondary"].setdefault("error", f"not finished within {SECONDARY_DEADLINE_S:.0f} s")
+                line["secondary"].setdefault("error", f"not finished within {SECONDARY_DEADLINE_S + SECONDARY_GRACE_S:.0f} s")
                 print(json.dumps(line), flush=True)
             os._exit(0)
 
-        timer = threading.Timer(SECONDARY_DEADLINE_S, give_up)
-        timer.daemon = True
-        timer.start()
+        soft = threading.Timer(SECONDARY_DEADLINE_S, ABANDON.set)       # stop between steps, on all ranks together
+        timer = threading.Timer(SECONDARY_DEADLINE_S + SECONDARY_GRACE_S, give_up)
+        for t in (soft, timer):
+            t.daemon = True
+            t.start()
         for name in ("llama-3.3-70b-fp8", "deepseek-v2-lite"):
             t0 = time.perf_counter()
             try:
@@ -477,6 +497,7 @@ def main() -> None:
                 torch.distributed.all_reduce(ok, op=torch.distributed.ReduceOp.MIN, group=info.host_group)
             if int(ok[0]) == 0:
                 break
+        soft.cancel()
         timer.cancel()
     if info.rank == 0:
         print(json.dumps(line), flush=True)
