@@ -257,10 +257,46 @@ def _logprobs_from(body: dict, chat: bool) -> int | None:
     return k
 
 
+def _refuse_unsupported(body: dict) -> None:
+    """OpenAI request fields this server does not implement are refused when they ask for something (HTTP 400), never
+    dropped: a client that sends `n: 4` and gets one choice back has been answered wrongly."""
+    for key in ("n", "best_of"):
+        if body.get(key) not in (None, 1):
+            raise ValueError(f"{key} other than 1 is not supported")
+    for key in ("presence_penalty", "frequency_penalty", "repetition_penalty"):
+        v = body.get(key)
+        if v is not None and float(v) != (1.0 if key == "repetition_penalty" else 0.0):
+            raise ValueError(f"{key} is not supported")
+    if body.get("logit_bias"):
+        raise ValueError("logit_bias is not supported")
+    if body.get("echo"):
+        raise ValueError("echo is not supported")
+    if body.get("suffix"):
+        raise ValueError("suffix is not supported")
+    if body.get("tools") or body.get("functions") or body.get("response_format") not in (None, {"type": "text"}):
+        raise ValueError("tools, functions and structured response formats are not supported")
+
+
 def _sampling_from(body: dict, default_max: int = 16, chat: bool = False) -> SamplingParams:
+    _refuse_unsupported(body)
     stop_ids = tuple(body.get("stop_token_ids") or ())
-    return SamplingParams(logprobs=_logprobs_from(body, chat), temperature=float(body.get("temperature", 0.0) or 0.0), top_k=int(body.get("top_k", 0) or 0),
-                          top_p=float(body.get("top_p", 1.0) or 1.0), max_tokens=int(body.get("max_tokens") or default_max),
+    def given(key, default):      # absent or null means the default; 0 is a value, not "unset"
+        v = body.get(key)
+        return default if v is None else v
+
+    temperature = float(given("temperature", 0.0))
+    top_p = float(given("top_p", 1.0))
+    top_k = int(given("top_k", 0))
+    max_tokens = int(given("max_completion_tokens", given("max_tokens", default_max)))
+    if not (0.0 <= temperature <= 100.0) or temperature != temperature:
+        raise ValueError("temperature must be between 0 and 100")
+    if not (0.0 < top_p <= 1.0):
+        raise ValueError("top_p must be in (0, 1]")
+    if top_k < 0:
+        raise ValueError("top_k must be 0 (off) or positive")
+    if max_tokens < 1:
+        raise ValueError("max_tokens must be at least 1")
+    return SamplingParams(logprobs=_logprobs_from(body, chat), temperature=temperature, top_k=top_k, top_p=top_p, max_tokens=max_tokens,
                           stop_token_ids=stop_ids, ignore_eos=bool(body.get("ignore_eos", False)), seed=body.get("seed"))
 
 

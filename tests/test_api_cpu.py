@@ -258,3 +258,32 @@ def test_openai_server_logprobs():
         assert got == pytest.approx([lp for lp, _ in ref.logprobs], abs=1e-5)
         assert c.post("/v1/completions", json={"prompt": prompt, "logprobs": 99}).status_code == 400
     app.state.engine.shutdown()
+
+
+def test_openai_server_refuses_what_it_does_not_implement():
+    """Fields that would change the answer but are not implemented get HTTP 400 (never silently dropped); values that mean
+    "default" pass; sampling parameters are range-checked before anything is queued."""
+    from fastapi.testclient import TestClient
+
+    from mojo_b200.serve import build_app
+
+    app = build_app(tiny_llm(), "tiny-llama")
+    base = {"prompt": [5, 900, 77], "max_tokens": 2}
+    with TestClient(app) as c:
+        for extra in ({"n": 2}, {"best_of": 3}, {"presence_penalty": 0.5}, {"frequency_penalty": -1}, {"repetition_penalty": 1.2},
+                      {"logit_bias": {"50": 10}}, {"echo": True}, {"suffix": "x"}, {"temperature": -0.5}, {"top_p": 0.0}, {"top_p": 1.5},
+                      {"top_k": -1}, {"max_tokens": -3}, {"temperature": "hot"}):
+            r = c.post("/v1/completions", json={**base, **extra})
+            assert r.status_code == 400, (extra, r.status_code)
+        chat = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 2}
+        assert c.post("/v1/chat/completions", json={**chat, "tools": [{"type": "function"}]}).status_code == 400
+        assert c.post("/v1/chat/completions", json={**chat, "response_format": {"type": "json_object"}}).status_code == 400
+        assert c.post("/v1/chat/completions", json={**chat, "n": 2}).status_code == 400
+        # the spellings of "default" are accepted
+        ok = c.post("/v1/completions", json={**base, "n": 1, "best_of": 1, "presence_penalty": 0, "frequency_penalty": 0.0, "logit_bias": {},
+                                             "echo": False, "temperature": 0, "top_p": 1})
+        assert ok.status_code == 200 and len(ok.json()["choices"][0]["token_ids"]) == 2
+        ok = c.post("/v1/chat/completions", json={**{k: v for k, v in chat.items() if k != "max_tokens"}, "max_completion_tokens": 3,
+                                                  "response_format": {"type": "text"}})
+        assert ok.status_code == 200 and ok.json()["usage"]["completion_tokens"] == 3
+    app.state.engine.shutdown()
