@@ -30,6 +30,19 @@ class SamplingParams:
     seed: int | None = None
     logprobs: int | None = None       # None: off; k >= 0: log-probability of each sampled token plus the k most likely ones
 
+    def __post_init__(self):
+        # one place for every entry point (Python API, server, CLI): a value the sampling kernel would misread is refused here
+        if not (0.0 <= float(self.temperature) <= 100.0):      # also false for NaN
+            raise ValueError("temperature must be between 0 and 100")
+        if not (0.0 < float(self.top_p) <= 1.0):
+            raise ValueError("top_p must be in (0, 1]")
+        if int(self.top_k) < 0:
+            raise ValueError("top_k must be 0 (off) or positive")
+        if int(self.max_tokens) < 1:
+            raise ValueError("max_tokens must be at least 1")
+        if self.logprobs is not None and not (0 <= int(self.logprobs) <= 20):
+            raise ValueError("logprobs must be between 0 and 20")
+
 
 @dataclass
 class EngineConfig:

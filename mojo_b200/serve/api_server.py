@@ -288,14 +288,7 @@ def _sampling_from(body: dict, default_max: int = 16, chat: bool = False) -> Sam
     top_p = float(given("top_p", 1.0))
     top_k = int(given("top_k", 0))
     max_tokens = int(given("max_completion_tokens", given("max_tokens", default_max)))
-    if not (0.0 <= temperature <= 100.0) or temperature != temperature:
-        raise ValueError("temperature must be between 0 and 100")
-    if not (0.0 < top_p <= 1.0):
-        raise ValueError("top_p must be in (0, 1]")
-    if top_k < 0:
-        raise ValueError("top_k must be 0 (off) or positive")
-    if max_tokens < 1:
-        raise ValueError("max_tokens must be at least 1")
+    # ranges are checked by SamplingParams itself (ValueError -> 400 at the endpoint)
     return SamplingParams(logprobs=_logprobs_from(body, chat), temperature=temperature, top_k=top_k, top_p=top_p, max_tokens=max_tokens,
                           stop_token_ids=stop_ids, ignore_eos=bool(body.get("ignore_eos", False)), seed=body.get("seed"))
 

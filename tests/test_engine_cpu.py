@@ -413,3 +413,11 @@ def test_pipelined_stepping_with_prefix_cache_and_recovery():
             raised += 1
             assert recover(eng)
     assert raised == 1 and [eng.requests[r].output_ids for r in rids] == want
+
+
+@pytest.mark.parametrize("bad", [dict(temperature=-1.0), dict(temperature=float("nan")), dict(top_p=0.0), dict(top_p=1.01), dict(top_k=-2),
+                                 dict(max_tokens=0), dict(logprobs=21)])
+def test_sampling_params_refuse_values_the_kernels_would_misread(bad):
+    with pytest.raises(ValueError):
+        SamplingParams(**bad)
+    SamplingParams(temperature=0.0, top_p=1.0, top_k=0, max_tokens=1, logprobs=0)      # the edges themselves are fine
